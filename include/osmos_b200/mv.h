@@ -1,0 +1,54 @@
+/* The decode step's dequant-fused matrix-vector products over F32 activations.
+ *
+ * Drop-in for the reference's include/osmos/gpu/mv.h:7-20 (mv_run, mv_group, mv_group_tok, mv_strided): same names,
+ * argument meaning, limits and refusals. W is any GGUF block type of qtype.h (QTYPE_PATH_MV / _MV_TOK), row-major
+ * `rows` x `cols` as the file stores it; x and y are F32 in device-readable memory.
+ *
+ * A row's sum is a function of the row alone: its 8-value chunks are dealt to 32 lanes (chunk c to lane c % 32),
+ * each lane adds its chunks in order with one fmaf a value, and the 32 lane sums are combined by the xor tree
+ * 16, 8, 4, 2, 1 - the reference's order (kernels/mv.h:14-70), so a token's output has the same bits alone or in a
+ * batch, on any stream, at any launch shape.
+ *
+ * Every entry returns true when the work was queued on `stream` (a cudaStream_t, NULL = default stream; not
+ * waited for) and false when it was refused - then nothing was queued.
+ */
+#ifndef OSMOS_B200_MV_H
+#define OSMOS_B200_MV_H
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MV_MAX_TOKENS 8    /* tokens a call of mv_run / an entry of mv_group_tok takes (reference: mv.h:7) */
+#define MV_MAX_GROUP 65535 /* matrices a grouped call takes (reference: mv.h:8) */
+
+/* y[t * rows + r] = sum_c W[r, c] x[t * cols + c], t < n_tok <= MV_MAX_TOKENS (reference: mv.h:10, mv.hip:264-268).
+   false for an unknown type, cols not whole blocks, n_tok 0 or past MV_MAX_TOKENS. */
+bool mv_run(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t n_tok, float *y,
+            void *stream);
+/* n matrices of one type and shape (w: device table of n pointers), one vector each:
+   y[m * rows + r] = sum_c W_m[r, c] x[(m / x_div) * x_mat + c] (reference: mv.h:12, mv.hip:234-262).
+   false as mv_run, and for n 0 or past MV_MAX_GROUP, x_div 0, x_mat not a multiple of 8. */
+bool mv_group(uint32_t type, const void *const *w, uint32_t n, uint32_t rows, uint32_t cols, const float *x,
+              uint32_t x_mat, uint32_t x_div, float *y, void *stream);
+/* n matrices, matrix m on its cnt[m] (0 = entry skipped; at most max_cnt <= MV_MAX_TOKENS) rows of x starting at
+   row xrow[m] (rows xs floats apart) into the same rows of y (ys apart); w, cnt, xrow are device arrays
+   (reference: mv.h:14, mv.hip:168-231). false as mv_run, and for n 0 or past MV_MAX_GROUP, max_cnt 0 or past
+   MV_MAX_TOKENS, xs shorter than a row or not a multiple of 8. */
+bool mv_group_tok(uint32_t type, const void *const *w, const int32_t *cnt, const int32_t *xrow, uint32_t n,
+                  uint32_t max_cnt, uint32_t rows, uint32_t cols, const float *x, uint32_t xs, float *y, uint32_t ys,
+                  void *stream);
+/* mv_run with token t's x at x + t * x_stride and y at y + t * y_stride, any n_tok >= 1 (reference: mv.h:17,
+   mv.hip:270-299). false as mv_run (but for the token limit), and for a stride not a multiple of 8 or, with more
+   than one token, shorter than its row. */
+bool mv_strided(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t x_stride,
+                uint32_t n_tok, float *y, uint32_t y_stride, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

@@ -1,0 +1,123 @@
+"""ctypes view of libosmos_b200.so: every entry point of include/osmos_b200/*.h with its C signature.
+
+Pointers are passed as integers (torch `tensor.data_ptr()`, or 0 for NULL); streams as `torch.cuda.Stream.cuda_stream`
+or 0 for the default stream. The functions return the C ABI's bool: True = queued, False = refused.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libosmos_b200.so")
+
+P, U32, U64, I32, F32, B = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_float, C.c_bool
+
+
+class Q4xX16(C.Structure):
+    _fields_ = [("x16", P), ("overflow", P), ("cols", U32), ("row0", U32)]
+
+
+class Q4xExpertTiles(C.Structure):
+    _fields_ = [("base", P * 3), ("bytes", U64 * 3), ("tab", P * 3), ("ptr", P * 3), ("cnt", P), ("gidx", P),
+                ("hidx", P), ("xg", P), ("yg", P), ("xd", P), ("yd", P), ("where", P), ("off", P)]
+
+
+class Q4xExpertBounds(C.Structure):
+    _fields_ = [("first", U32 * 4), ("count", U32 * 4), ("entries", U32), ("slots", U32)]
+
+
+class LaneExperts(C.Structure):
+    _fields_ = [("base", P * 3), ("bytes", U64 * 3), ("tab", P * 3)]
+
+
+class LaneTables(C.Structure):
+    _fields_ = [("w", P * 3), ("cnt", P), ("xrow", P), ("tok", P), ("pair", P), ("row_of", P), ("order", P),
+                ("off", P), ("counts", P), ("max_entries", U32)]
+
+
+class LaneLayer(C.Structure):
+    _fields_ = [("type_gu", U32), ("type_down", U32), ("dim", U32), ("ff", U32), ("n_exp", U32), ("k", U32),
+                ("lim", F32), ("experts", LaneExperts)]
+
+
+class LaneScratch(C.Structure):
+    _fields_ = [("max_tok", U32), ("xq", P), ("xqd", P), ("hh", P), ("hq", P), ("hqd", P), ("ye", P),
+                ("tab", LaneTables)]
+
+
+class QTypeInfo(C.Structure):
+    _fields_ = [("id", U32), ("values", U32), ("bytes", U32), ("paths", U32), ("name", C.c_char_p)]
+
+
+SIGNATURES = {
+    # quant.h / qtype.h
+    "qtype_info": (C.POINTER(QTypeInfo), [U32]),
+    "qtype_tensor_bytes": (U64, [U32, U64, U64]),
+    "quant_known": (B, [U32]),
+    "quant_dequant": (B, [U32, P, U64, P, P]),
+    "quant_dequant_f16": (B, [U32, P, U64, P, P]),
+    # mv.h
+    "mv_run": (B, [U32, P, U32, U32, P, U32, P, P]),
+    "mv_group": (B, [U32, P, U32, U32, U32, P, U32, U32, P, P]),
+    "mv_group_tok": (B, [U32, P, P, P, U32, U32, U32, U32, P, U32, P, U32, P]),
+    "mv_strided": (B, [U32, P, U32, U32, P, U32, U32, P, U32, P]),
+    # q8.h
+    "q8_round": (B, [P, U32, U32, U32, P, P, P]),
+    "q8_0_round": (B, [P, U32, U32, U32, P, P, P]),
+    "q8_group_tok": (B, [U32, P, P, P, P, U32, U32, U32, U32, P, P, P, U32, P]),
+    "q8_gate_up": (B, [U32, P, P, P, P, P, P, U32, U32, U32, U32, P, P, P, F32, P, U32, P]),
+    "q8_run": (B, [U32, P, U32, U32, P, P, U32, P, U32, P]),
+    # mmq.h
+    "mmq_known": (B, [U32]),
+    "mmq_x8_rows": (B, [P, U32, P, U32, U32, P, P, P, P]),
+    "mmq_group": (B, [U32, P, P, U32, U32, U32, U32, P, P, P, P, P, P, U32, P]),
+    # moe.h
+    "q4x_route": (B, [P, U32, U32, U32, P, P, P, P]),
+    "q4x_expert_bounds": (None, [U32, U32, C.POINTER(Q4xExpertBounds)]),
+    "q4x_expert_tiles": (B, [P, U32, U32, U32, U32, U32, C.POINTER(Q4xExpertTiles), P]),
+    "q4x_swiglu": (B, [P, P, U64, P, C.POINTER(Q4xX16), P]),
+    "q4x_moe_sum": (B, [P, P, P, U32, U32, U32, P, P, P, P]),
+    # ops.h
+    "ops_router": (B, [P, P, U32, U32, F32, U32, P, P, P]),
+    "ops_router_scored": (B, [P, P, U32, U32, F32, C.c_int, U32, P, P, P]),
+    "ops_swiglu": (B, [P, P, U32, F32, P, U32, P, P]),
+    "ops_swiglu_lane": (B, [P, P, U32, F32, P, U32, P, P]),
+    "ops_gather_rows": (B, [P, P, P, U32, U32, P]),
+    "ops_gather_sum": (B, [P, P, P, U32, U32, U32, P]),
+    "ops_gather_sum_add": (B, [P, P, P, U32, U32, U32, P, P]),
+    "ops_copy_rows": (B, [P, P, P, U32, U32, P]),
+    "ops_wait": (B, [P, U32, P]),
+    "ops_wait_set_limit_ms": (None, [U32]),
+    "ops_wait_limit_ms": (U32, []),
+    "ops_wait_status": (U32, []),
+    "ops_fp4_round": (B, [P, U64, U32, B, P, U32, P]),
+    "ops_fp8_round": (B, [P, U64, P, U32, P]),
+    # lane.h
+    "lane_max_entries": (U32, [U32, U32]),
+    "lane_tables": (B, [P, U32, U32, U32, U32, U32, C.POINTER(LaneExperts), C.POINTER(LaneTables), P]),
+    "lane_scratch_bytes": (U64, [C.POINTER(LaneLayer), U32]),
+    "lane_scratch_bind": (B, [C.POINTER(LaneLayer), U32, P, U64, C.POINTER(LaneScratch)]),
+    "lane_ffn": (B, [C.POINTER(LaneLayer), C.POINTER(LaneScratch), P, P, P, U32, P, P, P]),
+}
+
+
+class Lib:
+    def __init__(self, path=LIB_PATH):
+        if not os.path.exists(path):
+            raise RuntimeError(
+                "libosmos_b200.so is not built (%s): run `python -m libosmos_b200.build`; there is no fallback" % path)
+        self.path = path
+        self.dll = C.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(self.dll, name)  # AttributeError = the library does not export what the headers declare
+            fn.restype, fn.argtypes = res, args
+            setattr(self, name, fn)
+
+
+_LIB = None
+
+
+def load():
+    global _LIB
+    if _LIB is None:
+        _LIB = Lib()
+    return _LIB

@@ -1,0 +1,213 @@
+// The int8 lane (include/osmos_b200/q8.h): activation rounding and the grouped expert matvecs over int8 inputs,
+// with the gate + up + activation fusion. One kernel template serves q8_group_tok, q8_gate_up and q8_run.
+//
+// Thread mapping of this generic kernel: a lane of the contract is a thread; a warp holds 32 / L rows. It takes any
+// shape the entry points accept. The order of every floating-point operation is fixed by the contract, so any other
+// kernel for the same entry points must (and is tested to) give the same bits.
+#include "decode.cuh"
+#include "dispatch.cuh"
+#include "osmos_b200/mv.h"
+#include "osmos_b200/q8.h"
+
+namespace osmos {
+namespace {
+
+constexpr int kWarps = 8, kThreads = kWarps * kWarp;
+constexpr uint32_t kLongCols = 4096;  // rows this long or longer split over 32 lanes, shorter over 16
+
+struct LaneArgs {
+  const uint8_t* w_dense;       // q8_run: the matrix (tables NULL)
+  const uint8_t* const* wg;     // the entries' matrices (gate, or the only one)
+  const uint8_t* const* wu;     // FUSED: the entries' up matrices
+  const int32_t *cnt, *xrow, *xin, *win;
+  const int8_t* q;
+  const float* d;
+  const float* scale;
+  float lim;
+  float* out;
+  uint32_t rows, cols, out_stride, n_tok;
+};
+
+template <uint32_t T, int NT, bool FUSED, bool DENSE>
+__global__ void __launch_bounds__(kThreads) lane_kernel(const LaneArgs a) {
+  __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
+  const Grids g = stage_grids<T>(tables);
+  const int lane = threadIdx.x % kWarp;
+  const int L = a.cols >= kLongCols ? 32 : 16, ll = lane % L;
+  const uint32_t row = (blockIdx.x * kWarps + threadIdx.x / kWarp) * (uint32_t) (kWarp / L) + (uint32_t) (lane / L);
+  const uint32_t nblk = a.cols / 32;
+
+  const uint8_t *wg, *wu = nullptr;
+  uint32_t r0, live;
+  if constexpr (DENSE) {
+    r0 = blockIdx.y * NT;
+    live = a.n_tok - r0 < (uint32_t) NT ? a.n_tok - r0 : (uint32_t) NT;
+    wg = a.w_dense;
+  } else {
+    const uint32_t m = blockIdx.y;
+    const int32_t c = a.cnt[m];
+    if (c <= 0) return;
+    r0 = (uint32_t) a.xrow[m], live = (uint32_t) c < (uint32_t) NT ? (uint32_t) c : (uint32_t) NT;
+    wg = a.wg[m];
+    if constexpr (FUSED) wu = a.wu[m];
+  }
+  const uint64_t off = (uint64_t) (row < a.rows ? row : 0) * (uint64_t) (a.cols / Fmt<T>::values) * Fmt<T>::bytes;
+  wg += off;
+  if constexpr (FUSED) wu += off;
+
+  // the input row of each token slot (a slot past the live ones is skipped: nothing of it is read)
+  uint64_t xr[NT];
+#pragma unroll
+  for (int t = 0; t < NT; t++) {
+    const uint32_t r = r0 + ((uint32_t) t < live ? (uint32_t) t : live - 1);
+    xr[t] = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
+  }
+  float ag[NT], au[NT];
+#pragma unroll
+  for (int t = 0; t < NT; t++) ag[t] = au[t] = 0.0f;
+
+  constexpr int kSubs = Fmt<T>::subs;
+  for (uint32_t s = ll; s < nblk; s += L) {
+    LaneCodes cg, cu;
+    const uint64_t at = (uint64_t) (s / kSubs) * Fmt<T>::bytes;
+    lane_codes<T>(wg + at, (int) (s % kSubs), cg, g);
+    if constexpr (FUSED) lane_codes<T>(wu + at, (int) (s % kSubs), cu, g);
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+      if ((uint32_t) t < live) {
+        const int4* xp = (const int4*) (a.q + xr[t] * a.cols + (uint64_t) s * 32);
+        const int4 lo = __ldg(xp), hi = __ldg(xp + 1);
+        const int x[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const float dx = __ldg(a.d + xr[t] * nblk + s);
+        ag[t] = __fmaf_rn(dx, lane_block_sum<T>(cg, x), ag[t]);
+        if constexpr (FUSED) au[t] = __fmaf_rn(dx, lane_block_sum<T>(cu, x), au[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < NT; t++) {
+    float vg = ag[t], vu = au[t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      if (o < L) {
+        vg = __fadd_rn(vg, __shfl_xor_sync(0xFFFFFFFFu, vg, o, kWarp));
+        if constexpr (FUSED) vu = __fadd_rn(vu, __shfl_xor_sync(0xFFFFFFFFu, vu, o, kWarp));
+      }
+    if (ll == 0 && row < a.rows && (uint32_t) t < live) {
+      const uint64_t r = r0 + (uint32_t) t;
+      if constexpr (FUSED)
+        a.out[r * a.out_stride + row] = lane_swiglu(vg, vu, a.lim, a.scale[a.win ? a.win[r] : r]);
+      else
+        a.out[r * a.out_stride + row] = vg;
+    }
+  }
+}
+
+template <uint32_t T, int NT, bool FUSED, bool DENSE>
+bool launch(const LaneArgs& a, uint32_t grid_y, cudaStream_t s) {
+  const uint32_t per_block = kWarps * (kWarp / (a.cols >= kLongCols ? 32 : 16));
+  lane_kernel<T, NT, FUSED, DENSE><<<dim3(blocks_for(a.rows, per_block), grid_y), kThreads, 0, s>>>(a);
+  return launched();
+}
+
+template <uint32_t T, bool FUSED, bool DENSE>
+bool by_tokens(const LaneArgs& a, uint32_t n, uint32_t grid_y, cudaStream_t s) {
+  if (n <= 1) return launch<T, 1, FUSED, DENSE>(a, grid_y, s);
+  if (n <= 2) return launch<T, 2, FUSED, DENSE>(a, grid_y, s);
+  if (n <= 4) return launch<T, 4, FUSED, DENSE>(a, grid_y, s);
+  return launch<T, 8, FUSED, DENSE>(a, grid_y, s);
+}
+
+// a warp a block of 32 values: the block's largest magnitude by the warp's tree, each lane its code
+template <bool GGML>
+__global__ void __launch_bounds__(kThreads) round_kernel(const float* __restrict__ x, uint32_t rows, uint32_t cols,
+                                                         uint32_t xs, int8_t* __restrict__ q, float* __restrict__ d) {
+  const uint32_t nblk = cols / 32;
+  const uint64_t blk = (uint64_t) blockIdx.x * kWarps + threadIdx.x / kWarp;
+  const int lane = threadIdx.x % kWarp;
+  if (blk >= (uint64_t) rows * nblk) return;  // the whole warp
+  const uint32_t r = (uint32_t) (blk / nblk), s = (uint32_t) (blk % nblk);
+  const float v = x[(uint64_t) r * xs + (uint64_t) s * 32 + lane];
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o, kWarp));
+  int code;
+  float scale;
+  if constexpr (GGML) {
+    const float dd = __fdiv_rn(amax, 127.0f), id = dd != 0.0f ? __fdiv_rn(1.0f, dd) : 0.0f;
+    code = (int) roundf(mul_rn(v, id));
+    scale = __half2float(__float2half_rn(dd));
+  } else {
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    code = (int) rintf(mul_rn(v, inv));
+    scale = __fdiv_rn(amax, 127.0f);
+  }
+  q[(uint64_t) r * cols + (uint64_t) s * 32 + lane] = (int8_t) code;
+  if (lane == 0) d[(uint64_t) r * nblk + s] = scale;
+}
+
+template <bool GGML>
+bool round_rows(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d, cudaStream_t s) {
+  if (!x || !q || !d || !rows || !cols || cols % 32 || xs < cols) return false;
+  const uint64_t blocks = (uint64_t) rows * (cols / 32);
+  round_kernel<GGML><<<blocks_for(blocks, kWarps), kThreads, 0, s>>>(x, rows, cols, xs, q, d);
+  return launched();
+}
+
+}  // namespace
+}  // namespace osmos
+
+using namespace osmos;
+
+extern "C" bool q8_round(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d, void* stream) {
+  return round_rows<false>(x, rows, cols, xs, q, d, stream_of(stream));
+}
+
+extern "C" bool q8_0_round(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d,
+                           void* stream) {
+  return round_rows<true>(x, rows, cols, xs, q, d, stream_of(stream));
+}
+
+extern "C" bool q8_group_tok(uint32_t type, const void* const* w, const int32_t* cnt, const int32_t* xrow,
+                             const int32_t* xin, uint32_t n, uint32_t max_cnt, uint32_t rows, uint32_t cols,
+                             const int8_t* q, const float* d, float* y, uint32_t ys, void* stream) {
+  if (!w || !cnt || !xrow || !q || !d || !y || !n || n > MV_MAX_GROUP || !rows || !max_cnt ||
+      max_cnt > MV_MAX_TOKENS || !cols || cols % 256)
+    return false;
+  LaneArgs a{};
+  a.wg = (const uint8_t* const*) w, a.cnt = cnt, a.xrow = xrow, a.xin = xin, a.q = q, a.d = d, a.out = y;
+  a.rows = rows, a.cols = cols, a.out_stride = ys;
+#define CASE(T) return by_tokens<T, false, false>(a, max_cnt, n, stream_of(stream));
+  OSMOS_SWITCH_LANE(type, CASE, return false)
+#undef CASE
+}
+
+extern "C" bool q8_gate_up(uint32_t type, const void* const* wg, const void* const* wu, const int32_t* cnt,
+                           const int32_t* xrow, const int32_t* xin, const int32_t* win, uint32_t n, uint32_t max_cnt,
+                           uint32_t rows, uint32_t cols, const int8_t* q, const float* d, const float* scale, float lim,
+                           float* h, uint32_t hs, void* stream) {
+  if (!wg || !wu || !cnt || !xrow || !q || !d || !h || !n || n > MV_MAX_GROUP || !rows || !max_cnt ||
+      max_cnt > MV_MAX_TOKENS || !cols || cols % 256 || !scale || hs < rows)
+    return false;
+  LaneArgs a{};
+  a.wg = (const uint8_t* const*) wg, a.wu = (const uint8_t* const*) wu, a.cnt = cnt, a.xrow = xrow, a.xin = xin;
+  a.win = win, a.q = q, a.d = d, a.scale = scale, a.lim = lim, a.out = h, a.rows = rows, a.cols = cols, a.out_stride = hs;
+#define CASE(T) return by_tokens<T, true, false>(a, max_cnt, n, stream_of(stream));
+  OSMOS_SWITCH_LANE(type, CASE, return false)
+#undef CASE
+}
+
+extern "C" bool q8_run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const int8_t* q, const float* d,
+                       uint32_t n_tok, float* y, uint32_t ys, void* stream) {
+  const OsmosQTypeInfo* t = qtype_row(type);
+  if (!t || !w || !q || !d || !y || !rows || !n_tok || !cols || cols % t->values || cols % 32 || (n_tok > 1 && ys < rows))
+    return false;
+  LaneArgs a{};
+  a.w_dense = (const uint8_t*) w, a.q = q, a.d = d, a.out = y, a.rows = rows, a.cols = cols, a.out_stride = ys;
+  a.n_tok = n_tok;
+#define CASE(T)                                                                                        \
+  return n_tok > 8 ? launch<T, 8, false, true>(a, (n_tok + 7) / 8, stream_of(stream))                  \
+                   : by_tokens<T, false, true>(a, n_tok, 1, stream_of(stream));
+  OSMOS_SWITCH_LANE_EXT(type, CASE, return false)
+#undef CASE
+}

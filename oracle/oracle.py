@@ -1,0 +1,263 @@
+"""ctypes bindings for the CPU checkers - TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+`Oracle` wraps this repository's scalar C restatement (oracle/osmos_oracle.c). `Reference` wraps the reference's
+own CPU lane compiled unmodified into oracle/_ref/libosmos_ref.so, when that file is present (it is built only
+where the reference tree is mounted; the file itself travels with the working tree).
+
+Only tests/, the smoke check and bench.py's CPU-baseline / reference legs may import this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "_build", "libosmos_oracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libosmos_ref.so")
+
+TYPES = {"Q4_0": 2, "Q8_0": 8, "Q2_K": 10, "Q4_K": 12, "IQ2_XXS": 16, "IQ2_XS": 17, "IQ3_XXS": 18, "IQ1_S": 19,
+         "IQ2_S": 22, "IQ1_M": 29, "MXFP4": 39, "NVFP4": 40}
+BLOCK = {2: (32, 18), 8: (32, 34), 10: (256, 84), 12: (256, 144), 16: (256, 66), 17: (256, 74), 18: (256, 98),
+         19: (256, 50), 22: (256, 82), 29: (256, 56), 39: (32, 17), 40: (64, 36)}
+LANE_TYPES = ("IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ1_S", "IQ2_S", "IQ1_M", "Q2_K")
+
+
+def build(ref_tree="/root/reference"):
+    """Compile the restatement, and the reference's CPU lane when its tree is present."""
+    grids = os.path.join(HERE, "..", "libosmos_b200", "csrc", "_gen", "osmos_grids.h")
+    if not os.path.exists(grids):
+        os.makedirs(os.path.dirname(grids), exist_ok=True)
+        subprocess.check_call(["python", os.path.join(HERE, "..", "libosmos_b200", "csrc", "gen_grids.py"), grids])
+    subprocess.check_call(["make", "-s", "-C", HERE])
+    if os.path.isdir(os.path.join(ref_tree, "src", "cpu")):
+        subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + ref_tree])
+
+
+def _p(a, t=None):
+    if a is None:
+        return None
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def tensor_bytes(type_id, rows, cols):
+    v, b = BLOCK[type_id]
+    assert cols % v == 0
+    return rows * (cols // v) * b
+
+
+class Oracle:
+    def __init__(self, path=ORACLE_SO):
+        if not os.path.exists(path):
+            build()
+        self.lib = C.CDLL(path)
+        L = self.lib
+        L.orc_dequant.restype = C.c_int
+        L.orc_mv_rows.restype = C.c_int
+        L.orc_q8_round.restype = C.c_int
+        L.orc_q8_0_round.restype = C.c_int
+        L.orc_q8_rows.restype = C.c_int
+        L.orc_q8_block_dots.restype = C.c_int
+        L.orc_lane_expert.restype = C.c_int
+        L.orc_mmq_x8_rows.restype = C.c_int
+        L.orc_mmq_rows.restype = C.c_int
+        L.orc_fp4_round.restype = C.c_int
+        L.orc_fp8_round.restype = C.c_int
+        L.orc_lane_exp.restype = C.c_float
+        L.orc_lane_exp.argtypes = [C.c_float]
+        L.orc_mmq_x8_at.restype = C.c_uint64
+        L.orc_mmq_dx_at.restype = C.c_uint64
+
+    def dequant(self, type_id, raw, values):
+        raw = np.ascontiguousarray(raw, dtype=np.uint8)
+        out = np.empty(values, dtype=np.float32)
+        ok = self.lib.orc_dequant(C.c_uint32(type_id), _p(raw), C.c_uint64(values), _p(out))
+        return out if ok else None
+
+    def mv_rows(self, type_id, w, rows, cols, x):
+        """x: [n_tok, cols] f32 -> y [n_tok, rows]"""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        n = x.shape[0]
+        y = np.empty((n, rows), dtype=np.float32)
+        ok = self.lib.orc_mv_rows(C.c_uint32(type_id), _p(w), C.c_uint32(cols), C.c_uint32(0), C.c_uint32(rows), _p(x),
+                                  C.c_uint32(x.shape[1]), C.c_uint32(n), _p(y), C.c_uint32(rows))
+        return y if ok else None
+
+    def q8_round(self, x, ggml_q8_0=False):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        q = np.empty((rows, cols), dtype=np.int8)
+        d = np.empty((rows, cols // 32), dtype=np.float32)
+        fn = self.lib.orc_q8_0_round if ggml_q8_0 else self.lib.orc_q8_round
+        ok = fn(_p(x), C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(cols), _p(q), _p(d))
+        return (q, d) if ok else None
+
+    def q8_rows(self, type_id, w, rows, cols, q, d):
+        q = np.ascontiguousarray(q, dtype=np.int8)
+        d = np.ascontiguousarray(d, dtype=np.float32)
+        n = q.shape[0]
+        y = np.empty((n, rows), dtype=np.float32)
+        ok = self.lib.orc_q8_rows(C.c_uint32(type_id), _p(w), C.c_uint32(cols), C.c_uint32(0), C.c_uint32(rows),
+                                  _p(q), _p(d), C.c_uint32(n), _p(y), C.c_uint32(rows))
+        return y if ok else None
+
+    def q8_block_dots(self, type_id, w_row, cols, q_row):
+        out = np.empty(2 * (cols // 32), dtype=np.int32)
+        q_row = np.ascontiguousarray(q_row, dtype=np.int8)
+        ok = self.lib.orc_q8_block_dots(C.c_uint32(type_id), _p(w_row), C.c_uint32(cols), _p(q_row), _p(out))
+        return out if ok else None
+
+    def swiglu_lane(self, g, u, lim, scale):
+        g = np.ascontiguousarray(g, dtype=np.float32)
+        u = np.ascontiguousarray(u, dtype=np.float32)
+        scale = np.ascontiguousarray(scale, dtype=np.float32)
+        h = np.empty_like(g)
+        self.lib.orc_swiglu_lane(_p(g), _p(u), C.c_uint32(g.shape[1]), C.c_float(lim), _p(scale),
+                                 C.c_uint32(g.shape[0]), _p(h))
+        return h
+
+    def lane_exp(self, x):
+        return np.array([self.lib.orc_lane_exp(float(v)) for v in np.asarray(x, dtype=np.float32)], dtype=np.float32)
+
+    def lane_expert(self, type_gu, type_down, gate, up, down, dim, ff, lim, x, scale):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        scale = np.ascontiguousarray(scale, dtype=np.float32)
+        cnt = x.shape[0]
+        y = np.empty((cnt, dim), dtype=np.float32)
+        ok = self.lib.orc_lane_expert(C.c_uint32(type_gu), C.c_uint32(type_down), _p(gate), _p(up), _p(down),
+                                      C.c_uint32(dim), C.c_uint32(ff), C.c_float(lim), _p(x), _p(scale),
+                                      C.c_uint32(cnt), _p(y))
+        return y if ok else None
+
+    def gather_sum(self, src, idx, m, add=None):
+        src = np.ascontiguousarray(src, dtype=np.float32)
+        idx = np.ascontiguousarray(idx, dtype=np.int32)
+        n, dim = idx.size // m, src.shape[1]
+        y = np.empty((n, dim), dtype=np.float32)
+        if add is not None:
+            add = np.ascontiguousarray(add, dtype=np.float32)
+        self.lib.orc_gather_sum(_p(y), _p(src), _p(idx), C.c_uint32(m), C.c_uint32(n), C.c_uint32(dim), _p(add))
+        return y
+
+    def mmq_x8_rows(self, x, idx, cols):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        idx = np.ascontiguousarray(idx, dtype=np.int32)
+        slots = idx.size
+        tiles = (slots + 15) // 16
+        x8 = np.zeros(tiles * 16 * cols, dtype=np.int8)
+        dx = np.zeros(tiles * 16 * (cols // 32), dtype=np.float32)
+        sx = np.zeros_like(dx)
+        ok = self.lib.orc_mmq_x8_rows(_p(x), C.c_uint32(x.shape[1]), _p(idx), C.c_uint32(slots), C.c_uint32(cols),
+                                      _p(x8), _p(dx), _p(sx))
+        return (x8, dx, sx) if ok else None
+
+    def mmq_rows(self, w, rows, cols, x8, dx, sx, soff, cnt, want_ints=False):
+        y = np.empty((cnt, rows), dtype=np.float32)
+        ints = np.empty((rows, cnt, cols // 32), dtype=np.int32) if want_ints else None
+        ok = self.lib.orc_mmq_rows(_p(w), C.c_uint32(0), C.c_uint32(rows), C.c_uint32(cols), _p(x8), _p(dx), _p(sx),
+                                   C.c_uint32(soff), C.c_uint32(cnt), _p(y), C.c_uint32(rows), _p(ints))
+        if not ok:
+            return None
+        return (y, ints) if want_ints else y
+
+    def fp4_round(self, x, block=32, e4m3_scale=False, dim=None):
+        x = np.array(x, dtype=np.float32, copy=True).reshape(-1)
+        packed = None
+        if dim:
+            packed = np.zeros((x.size // dim) * (dim // 2 + dim // block), dtype=np.uint8)
+        ok = self.lib.orc_fp4_round(_p(x), C.c_uint64(x.size), C.c_uint32(block), C.c_int(int(e4m3_scale)),
+                                    _p(packed), C.c_uint32(dim or 0))
+        return (x, packed) if ok else None
+
+    def fp8_round(self, x, dim=None):
+        x = np.array(x, dtype=np.float32, copy=True).reshape(-1)
+        packed = None
+        if dim:
+            packed = np.zeros((x.size // dim) * (dim + dim // 32), dtype=np.uint8)
+        ok = self.lib.orc_fp8_round(_p(x), C.c_uint64(x.size), _p(packed), C.c_uint32(dim or 0))
+        return (x, packed) if ok else None
+
+
+class CpuLaneExpert(C.Structure):
+    _fields_ = [("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p), ("row0", C.c_uint32),
+                ("cnt", C.c_uint32)]
+
+
+class CpuLaneJob(C.Structure):
+    _fields_ = [("type_gu", C.c_uint32), ("type_down", C.c_uint32), ("dim", C.c_uint32), ("ff", C.c_uint32),
+                ("lim", C.c_float), ("x", C.c_void_p), ("scale", C.c_void_p), ("n_rows", C.c_uint32),
+                ("e", C.POINTER(CpuLaneExpert)), ("n_e", C.c_uint32), ("y", C.c_void_p), ("seq", C.c_void_p),
+                ("value", C.c_uint32)]
+
+
+class Reference:
+    """The reference's own CPU lane (include/osmos/cpu/{q8,expert,lane}.h), unmodified."""
+
+    def __init__(self, path=REF_SO):
+        self.lib = C.CDLL(path)
+        L = self.lib
+        for f in ("cpu_q8_ready", "cpu_q8_round", "cpu_q8_rows", "cpu_mv_known", "cpu_mv_rows", "cpu_lane_submit",
+                  "cpu_lane_wait"):
+            getattr(L, f).restype = C.c_bool
+        L.cpu_lane_create.restype = C.c_void_p
+        L.cpu_lane_create.argtypes = [C.c_int, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]
+        L.cpu_lane_destroy.argtypes = [C.c_void_p]
+        L.cpu_lane_submit.argtypes = [C.c_void_p, C.POINTER(CpuLaneJob)]
+        L.cpu_lane_wait.argtypes = [C.c_void_p]
+
+    @staticmethod
+    def available(path=REF_SO):
+        if not os.path.exists(path):
+            return False
+        try:
+            return bool(Reference(path).lib.cpu_q8_ready())
+        except OSError:
+            return False
+
+    def q8_round(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        q = np.empty((rows, cols), dtype=np.int8)
+        d = np.empty((rows, cols // 32), dtype=np.float32)
+        ok = self.lib.cpu_q8_round(_p(x), C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(cols), _p(q), _p(d))
+        return (q, d) if ok else None
+
+    def q8_rows(self, type_id, w, rows, cols, q, d):
+        q = np.ascontiguousarray(q, dtype=np.int8)
+        d = np.ascontiguousarray(d, dtype=np.float32)
+        n = q.shape[0]
+        y = np.empty((n, rows), dtype=np.float32)
+        ok = self.lib.cpu_q8_rows(C.c_uint32(type_id), _p(w), C.c_uint32(cols), C.c_uint32(0), C.c_uint32(rows),
+                                  _p(q), _p(d), C.c_uint32(n), _p(y), C.c_uint32(rows))
+        return y if ok else None
+
+    def mv_rows(self, type_id, w, rows, cols, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        n = x.shape[0]
+        y = np.empty((n, rows), dtype=np.float32)
+        ok = self.lib.cpu_mv_rows(C.c_uint32(type_id), _p(w), C.c_uint32(cols), C.c_uint32(0), C.c_uint32(rows),
+                                  _p(x), C.c_uint32(x.shape[1]), C.c_uint32(n), _p(y), C.c_uint32(rows))
+        return y if ok else None
+
+    def lane_ffn(self, threads, type_gu, type_down, dim, ff, lim, x, scale, experts, pool=None):
+        """experts: list of (gate, up, down, row0, cnt) numpy byte arrays; x [n_rows, dim]; returns y [n_rows, dim].
+        pool: an existing cpu_lane_create handle to reuse (else one is made and destroyed)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        scale = np.ascontiguousarray(scale, dtype=np.float32)
+        n_rows = x.shape[0]
+        y = np.zeros((n_rows, dim), dtype=np.float32)
+        arr = (CpuLaneExpert * len(experts))()
+        for i, (g, u, dn, row0, cnt) in enumerate(experts):
+            arr[i] = CpuLaneExpert(g.ctypes.data, u.ctypes.data, dn.ctypes.data, row0, cnt)
+        seq = np.zeros(1, dtype=np.uint32)
+        own = pool is None
+        if own:
+            pool = self.lib.cpu_lane_create(threads, None, max(n_rows, 1), dim, ff)
+            if not pool:
+                return None
+        job = CpuLaneJob(type_gu, type_down, dim, ff, lim, x.ctypes.data, scale.ctypes.data, n_rows, arr,
+                         len(experts), y.ctypes.data, seq.ctypes.data, 1)
+        ok = self.lib.cpu_lane_submit(pool, C.byref(job)) and self.lib.cpu_lane_wait(pool)
+        if own:
+            self.lib.cpu_lane_destroy(pool)
+        return y if ok and seq[0] == 1 else None

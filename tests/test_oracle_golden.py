@@ -1,0 +1,112 @@
+"""The CPU oracle against the committed golden vectors (no GPU): gguf-py's values for every block decoder, and the
+reference's own CPU lane outputs for the int8 lane, the F32 matvec and the expert FFN."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle.oracle import BLOCK, LANE_TYPES, TYPES, Reference
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("name", sorted(TYPES))
+def test_decoder_matches_gguf_py(oracle, name):
+    g = np.load(os.path.join(GOLD, "dequant.npz"))
+    raw, want = g[name + "_raw"], g[name + "_values"]
+    got = oracle.dequant(TYPES[name], raw, raw.shape[0] * BLOCK[TYPES[name]][0])
+    assert got is not None
+    assert np.array_equal(_bits(got), _bits(want))
+
+
+@pytest.mark.parametrize("name", LANE_TYPES)
+def test_lane_matches_reference_cpu(oracle, name):
+    g = np.load(os.path.join(GOLD, "lane_%s.npz" % name))
+    tid = TYPES[name]
+    for cols in (512, 768, 4096):
+        w, x = g["w_%d" % cols], g["x_%d" % cols]
+        q, d = oracle.q8_round(x)
+        assert np.array_equal(q, g["q_%d" % cols]) and np.array_equal(_bits(d), _bits(g["d_%d" % cols]))
+        y = oracle.q8_rows(tid, w, 10, cols, q, d)
+        assert np.array_equal(_bits(y), _bits(g["y_%d" % cols])), "int8 lane sums differ from the reference's"
+        ymv = oracle.mv_rows(tid, w, 10, cols, x)
+        assert np.array_equal(_bits(ymv), _bits(g["ymv_%d" % cols])), "F32 matvec sums differ from the reference's"
+
+
+def test_round_special_blocks(oracle):
+    # the reference's own assertions (tests/test_cpu_q8.c:191-197): zeros give d 0 / q 0, a lone -2.5 gives -127
+    x = np.zeros((1, 64), dtype=np.float32)
+    x[0, 37] = -2.5
+    q, d = oracle.q8_round(x)
+    assert d[0, 0] == 0.0 and not q[0, :32].any() and q[0, 37] == -127 and d[0, 1] == np.float32(2.5) / np.float32(127)
+
+
+@pytest.mark.parametrize("name", ["IQ3_XXS", "IQ1_M"])
+def test_expert_ffn_matches_reference_cpu(oracle, name):
+    g = np.load(os.path.join(GOLD, "ffn.npz"))
+    dim, ff, lim = int(g["dim"]), int(g["ff"]), float(g["lim"])
+    tid = TYPES[name]
+    x, scale, want = g[name + "_x"], g[name + "_scale"], g[name + "_y"]
+    row0 = 0
+    for e, c in enumerate(g[name + "_counts"]):
+        y = oracle.lane_expert(tid, tid, g["%s_gate%d" % (name, e)], g["%s_up%d" % (name, e)],
+                               g["%s_down%d" % (name, e)], dim, ff, lim, x[row0:row0 + c], scale[row0:row0 + c])
+        assert np.array_equal(_bits(y), _bits(want[row0:row0 + c]))
+        row0 += c
+
+
+def test_lane_exp_is_close_to_exp(oracle):
+    x = np.linspace(-20, 20, 4001).astype(np.float32)
+    got = oracle.lane_exp(x).astype(np.float64)
+    assert np.max(np.abs(got / np.exp(x.astype(np.float64)) - 1)) < 5e-7
+
+
+@pytest.mark.skipif(not Reference.available(), reason="the reference's CPU lane is not built here or lacks AVX-512 VNNI")
+@pytest.mark.parametrize("name", LANE_TYPES)
+def test_oracle_matches_reference_live(oracle, name):
+    """fresh random inputs every type, straight against the reference's compiled CPU code"""
+    from libosmos_b200 import synth
+    ref = Reference()
+    tid = TYPES[name]
+    for cols in (256, 1024, 5120):
+        rng = synth.rng_for(7, tid, cols)
+        w = synth.random_tensor(tid, 6, cols, rng)
+        x = rng.standard_normal((9, cols)).astype(np.float32)
+        q, d = oracle.q8_round(x)
+        q2, d2 = ref.q8_round(x)
+        assert np.array_equal(q, q2) and np.array_equal(_bits(d), _bits(d2))
+        assert np.array_equal(_bits(oracle.q8_rows(tid, w, 6, cols, q, d)), _bits(ref.q8_rows(tid, w, 6, cols, q, d)))
+        assert np.array_equal(_bits(oracle.mv_rows(tid, w, 6, cols, x)), _bits(ref.mv_rows(tid, w, 6, cols, x)))
+
+
+def test_mmq_oracle_integer_dots_and_bound(oracle):
+    """the Q4_K x int8 restatement: its group dots are the plain integer dots, and its F32 result stays within the
+    reference test's error bound of a double sum over the same quantized operands (tests/gpu/test_mmq_gpu.hip:207-233)"""
+    from libosmos_b200 import synth
+    rows, cols, n = 16, 512, 5
+    rng = synth.rng_for(8)
+    w = synth.random_tensor(12, rows, cols, rng)
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    idx = np.arange(n, dtype=np.int32)
+    x8, dx, sx = oracle.mmq_x8_rows(x, idx, cols)
+    y, ints = oracle.mmq_rows(w, rows, cols, x8, dx, sx, 0, n, want_ints=True)
+    wv = oracle.dequant(12, w, rows * cols).reshape(rows, cols).astype(np.float64)
+    groups = cols // 32
+    blk = w.reshape(rows, cols // 256, 144)
+    for t in range(n):
+        xq = np.array([[x8[oracle.lib.orc_mmq_x8_at(t, c, cols)] for c in range(cols)]], dtype=np.int64)[0]
+        dxt = np.array([dx[oracle.lib.orc_mmq_dx_at(t, g, groups)] for g in range(groups)], dtype=np.float64)
+        xdq = xq.reshape(groups, 32) * dxt[:, None]
+        want = wv @ xdq.reshape(-1)
+        mag = np.abs(wv) @ np.abs(xdq.reshape(-1))
+        assert np.all(np.abs(y[t] - want) <= 64 * 2.0 ** -24 * mag + 1e-30)
+        # integer dots: nibbles against x8
+        for r in (0, 7, 15):
+            for g in (0, 5, groups - 1):
+                b, gi = g // 8, g % 8
+                nib = (blk[r, b, 16 + (gi // 2) * 32:16 + (gi // 2) * 32 + 32] >> (4 * (gi % 2))) & 0x0F
+                assert ints[r, t, g] == int(nib.astype(np.int64) @ xq[g * 32:(g + 1) * 32])
