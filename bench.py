@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight matrix path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (config.workload): the Qwen-style MoE FFN layer in IQ3_XXS - 512 experts, 64 tokens routed top-10, hidden
+2048, expert width 512 - run as the int8 lane: softmax router, activations rounded to int8 per 32, fused gate + up +
+activation over the picked experts, the activations rounded again, down, each token's rows summed in ascending
+expert id. A step is one pass of the layer over one 64-token batch; successive steps use successive cold copies of
+the layer's weights (a model's next layer), 616 MB each, so no step finds its weights in L2.
+
+Prints ONE JSON line: tokens/s through the layer (value: inputs resident in HBM; e2e: host buffers in, host
+buffer out through the C ABI), the dominant kernel's weight-GB/s against the measured HBM peak (roofline), and the
+reference's own CPU lane on this host's cores beside it (cpu_baseline). `--impl reference` times only that CPU
+path.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC, UNIT = "moe_layer_tokens_per_s", "tokens/s"
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi's SM clock and throttle reasons sampled while the timed region runs"""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, world, int(os.environ.get("LOCAL_RANK", str(rank)))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# the reference arm: the reference's CPU lane (oracle/_ref, its sources compiled unmodified) or, where that library
+# is missing or this CPU lacks its AVX-512 VNNI kernels, this repository's scalar restatement of it
+# ---------------------------------------------------------------------------------------------------------------------
+def cpu_step_inputs(cfg, step):
+    from libosmos_b200 import workloads
+    x, logits = workloads.moe_inputs_host(cfg, step)
+    ids, wts = workloads.softmax_topk(logits, cfg["k"])
+    # rows by (expert, pick): the lane's layout (a row an expert's copy of its token's input)
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    xr = np.ascontiguousarray(x[order // cfg["k"]])
+    sc = np.ascontiguousarray(wts.reshape(-1)[order])
+    experts, r = [], 0
+    for e in np.unique(flat):
+        c = int((flat == e).sum())
+        experts.append((int(e), r, c))
+        r += c
+    return xr, sc, experts, order
+
+
+class CpuArm:
+    def __init__(self, cfg, host_tensors, threads=None):
+        from libosmos_b200 import synth, workloads
+        from oracle.oracle import Oracle, Reference
+        self.cfg, self.host = cfg, host_tensors
+        self.tid = synth.TYPE_ID[cfg["type"]]
+        self.per = workloads.moe_expert_bytes(cfg)
+        self.cores = os.cpu_count() or 1
+        self.kind = "reference" if Reference.available() else "port"
+        if self.kind == "reference":
+            self.ref = Reference()
+            self.threads = min(64, threads or self.cores)
+            self.pool = self.ref.lib.cpu_lane_create(self.threads, None, cfg["n_tok"] * cfg["k"], cfg["dim"], cfg["ff"])
+            if not self.pool:
+                self.kind = "port"
+        if self.kind == "port":
+            self.oracle, self.threads = Oracle(), 1
+
+    def parts(self, e):
+        return [self.host[m][e * self.per[m]:(e + 1) * self.per[m]] for m in range(3)]
+
+    def run(self, xr, sc, experts, limit_rows=None):
+        """one step's expert FFN rows on the CPU; returns (seconds, rows done, y)"""
+        cfg = self.cfg
+        if self.kind == "reference":
+            ex = [tuple(self.parts(e)) + (r0, c) for e, r0, c in experts]
+            t0 = time.perf_counter()
+            y = self.ref.lane_ffn(self.threads, self.tid, self.tid, cfg["dim"], cfg["ff"], cfg["lim"], xr, sc, ex, pool=self.pool)
+            dt = time.perf_counter() - t0
+            assert y is not None, "the reference's cpu_lane refused the job"
+            return dt, xr.shape[0], y
+        done, t0 = 0, time.perf_counter()
+        y = np.zeros((xr.shape[0], cfg["dim"]), np.float32)
+        for e, r0, c in experts:
+            p = self.parts(e)
+            y[r0:r0 + c] = self.oracle.lane_expert(self.tid, self.tid, p[0], p[1], p[2], cfg["dim"], cfg["ff"], cfg["lim"],
+                                                   xr[r0:r0 + c], sc[r0:r0 + c])
+            done += c
+            if limit_rows and done >= limit_rows:
+                break
+        return time.perf_counter() - t0, done, y
+
+
+def run_reference(args):
+    from libosmos_b200 import workloads
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    cfg = workloads.MOE_IQ3
+    arm = CpuArm(cfg, workloads.moe_layer_host(cfg))
+    limit = None if arm.kind == "reference" else 24  # the scalar port: a bounded sample of a step's rows
+    times, rows = [], 0
+    for s in range(args.warmup + args.steps):
+        xr, sc, experts, _ = cpu_step_inputs(cfg, s)
+        dt, done, _ = arm.run(xr, sc, experts, limit)
+        if s >= args.warmup:
+            times.append(dt), (rows := rows + done)
+    tok_s = rows / cfg["k"] / sum(times)
+    sample = ("full steps of %d tokens (%d expert rows each)" % (cfg["n_tok"], cfg["n_tok"] * cfg["k"])
+              if limit is None else "the first %d expert rows of each step, scaled to tokens" % limit)
+    line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
+            "config": {"workload": cfg["name"], "tokens": cfg["n_tok"], "experts": cfg["n_exp"], "top_k": cfg["k"],
+                       "hidden": cfg["dim"], "expert_ff": cfg["ff"], "format": cfg["type"]},
+            "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": arm.threads, "kind": arm.kind, "sample": sample},
+            "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+
+    import libosmos_b200
+    from libosmos_b200 import runner, workloads
+    rank, world, local = dist_env()
+    assert world == args.gpus or world == 1, "launch N ranks for --gpus N"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from libosmos_b200 import ep
+        return ep.run_bench(args, rank, world, dev, METRIC, UNIT, ClockSampler, measured_peaks)
+
+    lib = libosmos_b200.load()
+    cfg = workloads.MOE_IQ3
+    n_tok, dim = cfg["n_tok"], cfg["dim"]
+    host = workloads.moe_layer_host(cfg)
+    copies = 4
+    layer = runner.MoeLane(lib, cfg, dev, copies=copies, host_tensors=host)
+    n_inputs = 8
+    hx, hl = zip(*[workloads.moe_inputs_host(cfg, s) for s in range(n_inputs)])
+    dx = [torch.from_numpy(a).to(dev) for a in hx]
+    dl = [torch.from_numpy(a).to(dev) for a in hl]
+    px = [torch.from_numpy(a).pin_memory() for a in hx]
+    pl = [torch.from_numpy(a).pin_memory() for a in hl]
+    out = torch.empty((n_tok, dim), dtype=torch.float32, device=dev)
+    pout = torch.empty((n_tok, dim), dtype=torch.float32).pin_memory()
+    sx, sl = torch.empty_like(dx[0]), torch.empty_like(dl[0])
+    stream = torch.cuda.current_stream().cuda_stream
+
+    # parity first: step 0 against the CPU oracle on a few tokens (the GPU tests hold the rest)
+    from oracle.oracle import Oracle
+    layer.step(dx[0], dl[0], out, n_tok, 0, stream)
+    torch.cuda.synchronize()
+    ids = layer.ids.cpu().numpy().reshape(n_tok, cfg["k"])
+    wts = layer.wts.cpu().numpy().reshape(n_tok, cfg["k"])
+    want = runner.moe_oracle(Oracle(), cfg, host, hx[0][:2], ids[:2], wts[:2])
+    got = out.cpu().numpy()[:2]
+    if not np.array_equal(got.view(np.uint32), want.view(np.uint32)):
+        raise SystemExit("bench: the GPU layer's output differs from the CPU oracle's bits - not timing a wrong result")
+    distinct = [len(np.unique(workloads.softmax_topk(l, cfg["k"])[0])) for l in hl]
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(steps):
+            fn(s)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3
+
+    def resident(s):
+        layer.step(dx[s % n_inputs], dl[s % n_inputs], out, n_tok, s % copies, stream)
+
+    def end_to_end(s):
+        sx.copy_(px[s % n_inputs], non_blocking=True)
+        sl.copy_(pl[s % n_inputs], non_blocking=True)
+        layer.step(sx, sl, out, n_tok, s % copies, stream)
+        pout.copy_(out, non_blocking=True)
+
+    for s in range(args.warmup):
+        resident(s), end_to_end(s)
+    with ClockSampler(local) as clocks:
+        t_res = timed(resident, args.steps)
+        t_e2e = timed(end_to_end, args.steps)
+        # the dominant kernel alone: events around q8_gate_up inside the same step
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        torch.cuda.synchronize()
+        for s, (a, b) in enumerate(evs):
+            layer.step_timed_gate_up(dx[s % n_inputs], dl[s % n_inputs], out, n_tok, s % copies, a, b, stream)
+        torch.cuda.synchronize()
+    k_ms = [a.elapsed_time(b) for a, b in evs]
+    per = workloads.moe_expert_bytes(cfg)
+    alg = [distinct[s % n_inputs] * (per[0] + per[1]) for s in range(args.steps)]
+    achieved = float(np.sum(alg) / (np.sum(k_ms) * 1e-3) / 1e9)
+    peak, peak_kind = measured_peaks()
+
+    # the CPU baseline beside it: the reference's CPU lane on this host, one to three steps
+    cpu = None
+    try:
+        arm = CpuArm(cfg, host)
+        limit = None if arm.kind == "reference" else 24
+        tt, rows = 0.0, 0
+        for s in range(3 if arm.kind == "reference" else 1):
+            xr, sc, experts, _ = cpu_step_inputs(cfg, s)
+            dt, done, _ = arm.run(xr, sc, experts, limit)
+            if s or arm.kind != "reference":
+                tt, rows = tt + dt, rows + done
+        cpu = {"value": rows / cfg["k"] / tt, "unit": UNIT, "cores": arm.threads, "kind": arm.kind,
+               "sample": "2 full 64-token steps after 1 warm-up" if limit is None else "24 expert rows of one step, scaled"}
+    except Exception as e:  # the baseline is reported, never required
+        cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "unavailable", "sample": str(e)[:120]}
+
+    line = {"metric": METRIC, "value": n_tok * args.steps / t_res, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
+            "config": {"workload": cfg["name"], "tokens": n_tok, "experts": cfg["n_exp"], "top_k": cfg["k"], "hidden": dim,
+                       "expert_ff": cfg["ff"], "format": cfg["type"], "parallelism": "1 gpu",
+                       "cold_cache": "%d copies of the layer's 616 MB of weights cycled; each step touches ~%d MB > 126 MB L2"
+                                     % (copies, int(np.mean(distinct)) * sum(per) // 1000000)},
+            "e2e": {"value": n_tok * args.steps / t_e2e, "unit": UNIT,
+                    "h2d_bytes_per_step": int(px[0].numel() * 4 + pl[0].numel() * 4), "d2h_bytes_per_step": int(pout.numel() * 4)},
+            "gpu_launches": layer.kernels_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "q8_gate_up (lane_kernel, IQ3_XXS, fused gate+up+activation)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                         "traffic": None, "algorithmic_bytes_per_launch": float(np.mean(alg)),
+                         "us_per_launch": float(np.mean(k_ms) * 1e3)},
+            "cpu_baseline": cpu, "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,157 @@
+"""GPU parity, through the C ABI: the int8 lane (q8_round, q8_group_tok, q8_gate_up, q8_run) against the reference's
+CPU lane (golden vectors) and the oracle. Bit-exact: bytes, scales, integer dots, F32 sums, activations."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import pointer_table, ptr, same_bits, sync, to_dev
+from libosmos_b200 import synth
+from oracle.oracle import LANE_TYPES, TYPES
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _round(lib, dev, x, fn="q8_round", xs=None):
+    rows, cols = x.shape[0], x.shape[1] if xs is None else xs[0]
+    stride = x.shape[1]
+    q = torch.zeros((rows, cols), dtype=torch.int8, device=dev)
+    d = torch.zeros((rows, cols // 32), dtype=torch.float32, device=dev)
+    assert getattr(lib, fn)(ptr(to_dev(x, dev)), rows, cols, stride, ptr(q), ptr(d), None)
+    sync()
+    return q, d
+
+
+@pytest.mark.parametrize("name", LANE_TYPES)
+def test_lane_matches_reference_cpu_golden(lib, dev, name):
+    g = np.load(os.path.join(GOLD, "lane_%s.npz" % name))
+    tid = TYPES[name]
+    for cols in (512, 768, 4096):
+        w, x = g["w_%d" % cols], g["x_%d" % cols]
+        q, d = _round(lib, dev, x)
+        assert np.array_equal(q.cpu().numpy(), g["q_%d" % cols]) and same_bits(d.cpu().numpy(), g["d_%d" % cols])
+        n = x.shape[0]
+        y = torch.empty((n, 10), dtype=torch.float32, device=dev)
+        assert lib.q8_run(tid, ptr(to_dev(w, dev)), 10, cols, ptr(q), ptr(d), n, ptr(y), 10, None)
+        sync()
+        assert same_bits(y.cpu().numpy(), g["y_%d" % cols])
+
+
+def test_round_strided_and_special_blocks(lib, dev, oracle):
+    rng = synth.rng_for(21)
+    x = (rng.standard_normal((11, 96 + 32)) * 3).astype(np.float32)
+    x[0, :32] = 0.0
+    x[1, 32:64] = 0.0
+    x[1, 37] = -2.5
+    q, d = _round(lib, dev, x, xs=(96,))
+    wq, wd = oracle.q8_round(np.ascontiguousarray(x[:, :96]))
+    assert np.array_equal(q.cpu().numpy(), wq) and same_bits(d.cpu().numpy(), wd)
+    assert d[0, 0].item() == 0.0 and q[1, 37].item() == -127
+    q0, d0 = _round(lib, dev, x, fn="q8_0_round", xs=(96,))
+    wq0, wd0 = oracle.q8_round(np.ascontiguousarray(x[:, :96]), ggml_q8_0=True)
+    assert np.array_equal(q0.cpu().numpy(), wq0) and same_bits(d0.cpu().numpy(), wd0)
+
+
+def _tables(dev, mats, cnt, xrow):
+    pool = to_dev(np.concatenate(mats), dev)
+    table = pointer_table(pool, [m * mats[0].size for m in range(len(mats))], dev)
+    return pool, table, to_dev(np.asarray(cnt, dtype=np.int32), dev), to_dev(np.asarray(xrow, dtype=np.int32), dev)
+
+
+@pytest.mark.parametrize("name", LANE_TYPES)
+@pytest.mark.parametrize("cols", [512, 4096])
+def test_group_tok_and_gate_up(lib, dev, oracle, name, cols):
+    tid = TYPES[name]
+    rows, n_mat = 21, 4
+    rng = synth.rng_for(22, tid, cols)
+    gate = [synth.random_tensor(tid, rows, cols, rng) for _ in range(n_mat)]
+    up = [synth.random_tensor(tid, rows, cols, rng) for _ in range(n_mat)]
+    cnt, xrow = [2, 8, 1, 5], [0, 2, 10, 11]
+    total, n_tok = 16, 6
+    x = rng.standard_normal((n_tok, cols)).astype(np.float32)
+    xin = rng.integers(0, n_tok, size=total + 8).astype(np.int32)      # each row's token
+    win = rng.permutation(total + 8).astype(np.int32)                  # each row's weight slot
+    scale = rng.uniform(0.05, 0.5, size=total + 8).astype(np.float32)
+    lim = 1.5
+    wq, wd = oracle.q8_round(x)
+    q, d = to_dev(wq, dev), to_dev(wd, dev)
+    pg, tg, cd, xd_ = _tables(dev, gate, cnt, xrow)
+    pu, tu, _, _ = _tables(dev, up, cnt, xrow)
+    ys = rows + 3
+    yg = torch.full((total + 8, ys), -9.0, dtype=torch.float32, device=dev)
+    yu = torch.full((total + 8, ys), -9.0, dtype=torch.float32, device=dev)
+    xin_d = to_dev(xin, dev)
+    assert lib.q8_group_tok(tid, ptr(tg), ptr(cd), ptr(xd_), ptr(xin_d), n_mat, 8, rows, cols, ptr(q), ptr(d), ptr(yg), ys, None)
+    assert lib.q8_group_tok(tid, ptr(tu), ptr(cd), ptr(xd_), ptr(xin_d), n_mat, 8, rows, cols, ptr(q), ptr(d), ptr(yu), ys, None)
+    sync()
+    want_g, want_u = np.full((total + 8, ys), -9.0, np.float32), np.full((total + 8, ys), -9.0, np.float32)
+    for m in range(n_mat):
+        for t in range(cnt[m]):
+            r = xrow[m] + t
+            tok = xin[r]
+            want_g[r, :rows] = oracle.q8_rows(tid, gate[m], rows, cols, wq[tok:tok + 1], wd[tok:tok + 1])[0]
+            want_u[r, :rows] = oracle.q8_rows(tid, up[m], rows, cols, wq[tok:tok + 1], wd[tok:tok + 1])[0]
+    assert same_bits(yg.cpu().numpy(), want_g) and same_bits(yu.cpu().numpy(), want_u)
+    # the fusion = the two sums then the lane's activation, bit for bit; weights by `win`
+    h = torch.full((total + 8, ys), -9.0, dtype=torch.float32, device=dev)
+    assert lib.q8_gate_up(tid, ptr(tg), ptr(tu), ptr(cd), ptr(xd_), ptr(xin_d), ptr(to_dev(win, dev)), n_mat, 8, rows,
+                          cols, ptr(q), ptr(d), ptr(to_dev(scale, dev)), lim, ptr(h), ys, None)
+    sync()
+    want_h = np.full((total + 8, ys), -9.0, np.float32)
+    for m in range(n_mat):
+        for t in range(cnt[m]):
+            r = xrow[m] + t
+            want_h[r, :rows] = oracle.swiglu_lane(want_g[r:r + 1, :rows], want_u[r:r + 1, :rows], lim, scale[win[r]:win[r] + 1])[0]
+    assert same_bits(h.cpu().numpy(), want_h)
+    # and through ops_swiglu_lane on the GPU's own sums
+    gg = yg[:total, :rows].contiguous()
+    uu = yu[:total, :rows].contiguous()
+    live = np.zeros(total, dtype=bool)
+    for m in range(n_mat):
+        live[xrow[m]:xrow[m] + cnt[m]] = True
+    sc_rows = to_dev(scale[win[:total]], dev)
+    hh = torch.empty_like(gg)
+    assert lib.ops_swiglu_lane(ptr(gg), ptr(uu), rows, lim, ptr(sc_rows), total, ptr(hh), None)
+    sync()
+    assert same_bits(hh.cpu().numpy()[live], h.cpu().numpy()[:total, :rows][live])
+    # a token's bits do not depend on max_cnt or on its neighbours: entry 2 (one row) alone at max_cnt 1
+    y1 = torch.full((total + 8, ys), -9.0, dtype=torch.float32, device=dev)
+    assert lib.q8_group_tok(tid, ptr(tg[2:]), ptr(cd[2:]), ptr(xd_[2:]), ptr(xin_d), 1, 1, rows, cols, ptr(q), ptr(d), ptr(y1), ys, None)
+    sync()
+    assert same_bits(y1.cpu().numpy()[10, :rows], want_g[10, :rows])
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q8_0"])
+@pytest.mark.parametrize("cols", [2048, 4096])
+def test_q8_run_plain_blocks(lib, dev, oracle, name, cols):
+    """the extension of the lane order to one-scale blocks: bit-equal to the oracle's restatement, whose integer dots
+    are checked against plain integer arithmetic and whose result is within rounding of a double sum"""
+    tid = TYPES[name]
+    rows, ntok = 50, 11
+    rng = synth.rng_for(23, tid, cols)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    x = rng.standard_normal((ntok, cols)).astype(np.float32)
+    for ggml in (False, True):
+        wq, wd = oracle.q8_round(x, ggml_q8_0=ggml)
+        want = oracle.q8_rows(tid, w, rows, cols, wq, wd)
+        y = torch.empty((ntok, rows), dtype=torch.float32, device=dev)
+        assert lib.q8_run(tid, ptr(to_dev(w, dev)), rows, cols, ptr(to_dev(wq, dev)), ptr(to_dev(wd, dev)), ntok, ptr(y), rows, None)
+        sync()
+        assert same_bits(y.cpu().numpy(), want)
+        # against exact arithmetic over the same quantized operands
+        wv = oracle.dequant(tid, w, rows * cols).reshape(rows, cols).astype(np.float64)
+        xv = (wq.astype(np.float64).reshape(ntok, cols // 32, 32) * wd.astype(np.float64)[:, :, None]).reshape(ntok, cols)
+        exact = xv @ wv.T
+        mag = np.abs(xv) @ np.abs(wv.T)
+        assert np.all(np.abs(want - exact) <= (cols / 32 / (32 if cols >= 4096 else 16) + 8) * 2.0 ** -24 * mag)
+    # integer block dots of a row: the oracle's against numpy's
+    dots = oracle.q8_block_dots(tid, w[:w.size // rows], cols, wq[0])
+    blk = w[:w.size // rows].reshape(cols // 32, -1)
+    if name == "Q4_0":
+        codes = np.concatenate([(blk[:, 2:] & 0x0F).astype(np.int64) - 8, (blk[:, 2:] >> 4).astype(np.int64) - 8], axis=1)
+    else:
+        codes = blk[:, 2:].view(np.int8).astype(np.int64)
+    xi = wq[0].astype(np.int64).reshape(cols // 32, 32)
+    assert np.array_equal(dots.reshape(-1, 2).sum(1), (codes * xi).sum(1))

@@ -1,0 +1,136 @@
+"""GPU parity, through the C ABI: block decoders and the F32-activation matvec family against the CPU oracle and
+the committed golden vectors. Bit-exact everywhere."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import pointer_table, ptr, same_bits, sync, to_dev
+from libosmos_b200 import synth
+from oracle.oracle import BLOCK, LANE_TYPES, TYPES
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+ALL = sorted(TYPES)
+
+
+@pytest.mark.parametrize("name", ALL)
+def test_dequant_golden(lib, dev, name):
+    g = np.load(os.path.join(GOLD, "dequant.npz"))
+    raw, want = g[name + "_raw"], g[name + "_values"]
+    src, dst = to_dev(raw, dev), torch.empty(want.size, dtype=torch.float32, device=dev)
+    assert lib.quant_dequant(TYPES[name], ptr(src), want.size, ptr(dst), None)
+    sync()
+    assert same_bits(dst.cpu().numpy(), want)
+    h = torch.empty(want.size, dtype=torch.float16, device=dev)
+    assert lib.quant_dequant_f16(TYPES[name], ptr(src), want.size, ptr(h), None)
+    sync()
+    with np.errstate(over="ignore"):
+        want16 = want.astype(np.float16)
+    assert np.array_equal(h.cpu().numpy().view(np.uint16), want16.view(np.uint16))
+
+
+@pytest.mark.parametrize("name", ALL)
+def test_dequant_large_vs_oracle(lib, dev, oracle, name):
+    tid = TYPES[name]
+    values = BLOCK[tid][0] * 3000 + (0 if BLOCK[tid][0] == 256 else BLOCK[tid][0] * 5)
+    raw = synth.random_blocks(tid, values // BLOCK[tid][0], synth.rng_for(11, tid))
+    want = oracle.dequant(tid, raw, values)
+    dst = torch.full((values + 8,), -7.0, dtype=torch.float32, device=dev)
+    assert lib.quant_dequant(tid, ptr(to_dev(raw, dev)), values, ptr(dst), None)
+    sync()
+    got = dst.cpu().numpy()
+    assert same_bits(got[:values], want) and (got[values:] == -7.0).all()
+    assert not lib.quant_dequant(tid, ptr(dst), values + 1, ptr(dst), None)
+
+
+def _mv_case(tid, rows, cols, ntok, key):
+    rng = synth.rng_for(12, tid, rows, cols, key)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    x = rng.standard_normal((ntok, cols)).astype(np.float32)
+    return w, x
+
+
+@pytest.mark.parametrize("name", ALL)
+def test_mv_run_bits_and_batch_invariance(lib, dev, oracle, name):
+    tid = TYPES[name]
+    rows, cols = 37, 1024 if BLOCK[tid][0] == 256 else 1056  # rows not a multiple of the block's rows; ragged chunks
+    w, x = _mv_case(tid, rows, cols, 8, 0)
+    want = oracle.mv_rows(tid, w, rows, cols, x)
+    wd, xd = to_dev(w, dev), to_dev(x, dev)
+    y = torch.full((8, rows), np.nan, dtype=torch.float32, device=dev)
+    assert lib.mv_run(tid, ptr(wd), rows, cols, ptr(xd), 8, ptr(y), None)
+    sync()
+    assert same_bits(y.cpu().numpy(), want)
+    for n in (1, 2, 3, 5, 7):  # every count the same bits for each token (schedule invariance)
+        y2 = torch.full((n, rows), np.nan, dtype=torch.float32, device=dev)
+        assert lib.mv_run(tid, ptr(wd), rows, cols, ptr(xd), n, ptr(y2), None)
+        sync()
+        assert same_bits(y2.cpu().numpy(), want[:n])
+    y1 = torch.empty((1, rows), dtype=torch.float32, device=dev)
+    for t in (0, 4, 7):  # each token alone
+        assert lib.mv_run(tid, ptr(wd), rows, cols, ptr(xd[t]), 1, ptr(y1), None)
+        sync()
+        assert same_bits(y1.cpu().numpy()[0], want[t])
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "IQ3_XXS", "Q4_K", "MXFP4"])
+def test_mv_strided_many_tokens(lib, dev, oracle, name):
+    tid = TYPES[name]
+    rows, cols, ntok, xs, ys = 19, 512, 77, 520, 24
+    rng = synth.rng_for(13, tid)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    x = rng.standard_normal((ntok, xs)).astype(np.float32)
+    want = oracle.mv_rows(tid, w, rows, cols, np.ascontiguousarray(x[:, :cols]))
+    y = torch.full((ntok, ys), -3.0, dtype=torch.float32, device=dev)
+    assert lib.mv_strided(tid, ptr(to_dev(w, dev)), rows, cols, ptr(to_dev(x, dev)), xs, ntok, ptr(y), ys, None)
+    sync()
+    got = y.cpu().numpy()
+    assert same_bits(got[:, :rows], want) and (got[:, rows:] == -3.0).all()
+
+
+@pytest.mark.parametrize("name", LANE_TYPES)
+def test_mv_matches_reference_cpu_golden(lib, dev, name):
+    g = np.load(os.path.join(GOLD, "lane_%s.npz" % name))
+    for cols in (512, 768, 4096):
+        w, x, want = g["w_%d" % cols], g["x_%d" % cols], g["ymv_%d" % cols]
+        y = torch.empty(want.shape, dtype=torch.float32, device=dev)
+        assert lib.mv_run(TYPES[name], ptr(to_dev(w, dev)), 10, cols, ptr(to_dev(x, dev)), x.shape[0], ptr(y), None)
+        sync()
+        assert same_bits(y.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("name", ["IQ3_XXS", "IQ1_M", "Q8_0", "MXFP4"])
+def test_mv_group_and_group_tok(lib, dev, oracle, name):
+    tid = TYPES[name]
+    rows, cols, n_mat = 24, 512, 5
+    rng = synth.rng_for(14, tid)
+    mats = [synth.random_tensor(tid, rows, cols, rng) for _ in range(n_mat)]
+    pool = to_dev(np.concatenate(mats), dev)
+    nbytes = mats[0].size
+    table = pointer_table(pool, [m * nbytes for m in range(n_mat)], dev)
+    # mv_group: matrix m on vector m / 2
+    x = rng.standard_normal((3, cols)).astype(np.float32)
+    y = torch.empty((n_mat, rows), dtype=torch.float32, device=dev)
+    assert lib.mv_group(tid, ptr(table), n_mat, rows, cols, ptr(to_dev(x, dev)), cols, 2, ptr(y), None)
+    sync()
+    got = y.cpu().numpy()
+    for m in range(n_mat):
+        assert same_bits(got[m], oracle.mv_rows(tid, mats[m], rows, cols, x[m // 2:m // 2 + 1])[0])
+    # mv_group_tok: entries of 1..8 rows, one skipped (count 0), rows xs apart, outputs untouched elsewhere
+    cnt = np.array([3, 0, 8, 1, 5], dtype=np.int32)
+    xrow = np.array([0, 3, 3, 11, 12], dtype=np.int32)
+    total, xs, ys = 17, cols + 8, rows + 4
+    xx = rng.standard_normal((total + 8, xs)).astype(np.float32)
+    yy = torch.full((total + 8, ys), -5.0, dtype=torch.float32, device=dev)
+    assert lib.mv_group_tok(tid, ptr(table), ptr(to_dev(cnt, dev)), ptr(to_dev(xrow, dev)), n_mat, 8, rows, cols,
+                            ptr(to_dev(xx, dev)), xs, ptr(yy), ys, None)
+    sync()
+    got = yy.cpu().numpy()
+    want = np.full_like(got, -5.0)
+    for m in range(n_mat):
+        for t in range(cnt[m]):
+            r = xrow[m] + t
+            want[r, :rows] = oracle.mv_rows(tid, mats[m], rows, cols, np.ascontiguousarray(xx[r:r + 1, :cols]))[0]
+    assert same_bits(got, want)
