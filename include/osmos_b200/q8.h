@@ -59,6 +59,17 @@ bool q8_run(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const in
    written here as that f16's F32 value so q8_run reads it like q8_round's. Same layout and refusals as q8_round. */
 bool q8_0_round(const float *x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t *q, float *d, void *stream);
 
+/* The lane entry points run one of two kernels that give the same bits: a staged one (weight tiles brought into
+   shared memory by bulk copies, for whole 256-value blocks, rows in eights and 16-byte aligned matrices and
+   activations) and a generic one for every other shape. q8_set_staged(0) forces the generic kernel (the tests compare
+   the two); the default is 1. */
+void q8_set_staged(int on);
+/* The staged kernel never waits without a bound and never faults on a misaligned matrix: it records the event and
+   leaves. Reads and clears the current device's record (synchronizes the device): bit 0 a bulk copy did not land
+   within the bound, bit 1 a matrix address was not 16-byte aligned; after either, the launch's outputs are not
+   valid. */
+uint32_t q8_status(void);
+
 #ifdef __cplusplus
 }
 #endif

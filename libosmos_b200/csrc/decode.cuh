@@ -196,71 +196,126 @@ struct LaneCodes {
 __device__ __forceinline__ uint32_t byte_mask4(uint32_t bits) {
   return (((bits & 0xFu) * 0x00204081u) & 0x01010101u) * 0xFFu;
 }
-// 8 unsigned grid bytes negated where their sign bit is set, as two words of int8: (v ^ m) + (m & 1) a byte - no byte
-// of an IQ2 / IQ3 grid is 0, so no carry crosses a byte
-__device__ __forceinline__ void apply_signs(uint64_t grid, uint32_t signs, int& lo, int& hi) {
-  const uint32_t m0 = byte_mask4(signs), m1 = byte_mask4(signs >> 4);
+template <uint32_t T> constexpr bool kLaneIq1 = (T == QTYPE_IQ1_S || T == QTYPE_IQ1_M);
+template <uint32_t T> constexpr bool kLanePlain = (T == QTYPE_Q4_0 || T == QTYPE_Q8_0);
+
+// How a block's bytes are read: through a pointer (global or shared memory, 2-byte aligned at best) ...
+struct PtrReader {
+  const uint8_t* b;
+  __device__ __forceinline__ uint32_t u8(int o) const { return b[o]; }
+  __device__ __forceinline__ uint32_t u16(int o) const { return ld16(b + o); }
+  __device__ __forceinline__ uint32_t u32(int o) const { return ld32(b + o); }
+  __device__ __forceinline__ uint64_t u64(int o) const { return ld64(b + o); }
+};
+// ... or out of registers: the block's bytes were loaded as NW aligned 32-bit words, the block starting A bytes
+// (0 or 2) into the first one. Every offset a decoder asks for is a compile-time constant once its loops are
+// unrolled, so each read is one shift / byte-permute of a named register.
+template <int NW, int A>
+struct WordWindow {
+  uint32_t w[NW];
+  __device__ __forceinline__ uint32_t u8(int o) const { const int p = o + A; return __byte_perm(w[p >> 2], 0, 0x4440 + (p & 3)); }
+  __device__ __forceinline__ uint32_t u16(int o) const { const int p = o + A; return __byte_perm(w[p >> 2], 0, (p & 2) ? 0x4432 : 0x4410); }
+  __device__ __forceinline__ uint32_t u32(int o) const {
+    const int p = o + A;
+    return (p & 2) ? __funnelshift_r(w[p >> 2], w[(p >> 2) + 1], 16) : w[p >> 2];
+  }
+  __device__ __forceinline__ uint64_t u64(int o) const { return (uint64_t) u32(o) | (uint64_t) u32(o + 4) << 32; }
+};
+
+// How the codebooks are looked up: plain tables (one copy) ...
+struct PlainLuts {
+  Grids g;
+  __device__ __forceinline__ uint64_t grid64(uint32_t i) const { return g.g64[i]; }
+  __device__ __forceinline__ uint32_t grid32(uint32_t i) const { return g.g32[i]; }
+  __device__ __forceinline__ void sign_masks(uint32_t s7, uint32_t& m0, uint32_t& m1) const {
+    const uint32_t s = g.sign[s7];
+    m0 = byte_mask4(s), m1 = byte_mask4(s >> 4);
+  }
+  __device__ __forceinline__ uint4 sign_masks4(uint32_t s7) const {
+    uint32_t m0, m1;
+    sign_masks(s7, m0, m1);
+    return make_uint4(m0, m1, m0 & 0x01010101u, m1 & 0x01010101u);
+  }
+};
+
+// 8 unsigned grid bytes negated where the mask bytes are 0xFF, as two words of int8: (v ^ m) + (m & 1) a byte - no
+// byte of an IQ2 / IQ3 grid is 0, so no carry crosses a byte
+__device__ __forceinline__ void apply_masks(uint64_t grid, uint32_t m0, uint32_t m1, int& lo, int& hi) {
   lo = (int) (((uint32_t) grid ^ m0) + (m0 & 0x01010101u));
   hi = (int) (((uint32_t) (grid >> 32) ^ m1) + (m1 & 0x01010101u));
 }
 
-template <uint32_t T> constexpr bool kLaneIq1 = (T == QTYPE_IQ1_S || T == QTYPE_IQ1_M);
-template <uint32_t T> constexpr bool kLanePlain = (T == QTYPE_Q4_0 || T == QTYPE_Q8_0);
+// the same with the masks' "+ 1" words (m & 0x01010101) already at hand
+__device__ __forceinline__ void apply_masks_carry(uint32_t g0, uint32_t g1, uint4 m, int& lo, int& hi) {
+  lo = (int) ((g0 ^ m.x) + m.z), hi = (int) ((g1 ^ m.y) + m.w);
+}
 
-// sub-block j (32 values) of the block at b
-template <uint32_t T> __device__ __forceinline__ void lane_codes(const uint8_t* b, int j, LaneCodes& c, const Grids& g) {
+// IQ1_M's f16 scale out of its four scale words
+template <class R> __device__ __forceinline__ float iq1m_scale_rd(const R& rd) {
+  const uint32_t s0 = rd.u16(48), s1 = rd.u16(50), s2 = rd.u16(52), s3 = rd.u16(54);
+  return half_value((s0 >> 12) | ((s1 >> 8) & 0x00F0) | ((s2 >> 4) & 0x0F00) | (s3 & 0xF000));
+}
+
+// sub-block j (32 values) of the block read through rd, its codebooks through lut
+template <uint32_t T, class R, class L>
+__device__ __forceinline__ void lane_codes_rd(const R& rd, int j, LaneCodes& c, const L& lut) {
   if constexpr (T == QTYPE_IQ2_XXS) {
-    const uint8_t* q = b + 2 + 8 * j;
-    const uint32_t aux = ld32(q + 4);
+    const uint32_t aux = rd.u32(2 + 8 * j + 4);
 #pragma unroll
-    for (int k = 0; k < 4; k++) apply_signs(g.g64[q[k]], g.sign[(aux >> (7 * k)) & 0x7F], c.w[2 * k], c.w[2 * k + 1]);
+    for (int k = 0; k < 4; k++) {
+      const uint64_t grid = lut.grid64(rd.u8(2 + 8 * j + k));
+      apply_masks_carry((uint32_t) grid, (uint32_t) (grid >> 32), lut.sign_masks4((aux >> (7 * k)) & 0x7F), c.w[2 * k], c.w[2 * k + 1]);
+    }
     c.s21[0] = c.s21[1] = 2 * (int) (aux >> 28) + 1;
-    c.d = half_value(ld16(b));
+    c.d = half_value(rd.u16(0));
   } else if constexpr (T == QTYPE_IQ2_XS) {
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const uint32_t q = ld16(b + 2 + 2 * (4 * j + k));
-      apply_signs(g.g64[q & 511], g.sign[q >> 9], c.w[2 * k], c.w[2 * k + 1]);
+      const uint32_t q = rd.u16(2 + 2 * (4 * j + k));
+      const uint64_t grid = lut.grid64(q & 511);
+      apply_masks_carry((uint32_t) grid, (uint32_t) (grid >> 32), lut.sign_masks4(q >> 9), c.w[2 * k], c.w[2 * k + 1]);
     }
-    const uint32_t s = b[66 + j];
+    const uint32_t s = rd.u8(66 + j);
     c.s21[0] = 2 * (int) (s & 0x0F) + 1, c.s21[1] = 2 * (int) (s >> 4) + 1;
-    c.d = half_value(ld16(b));
+    c.d = half_value(rd.u16(0));
   } else if constexpr (T == QTYPE_IQ2_S) {
+    const uint32_t qh = rd.u8(66 + j);
 #pragma unroll
     for (int k = 0; k < 4; k++) {
       const int kk = 4 * j + k;
-      apply_signs(g.g64[b[2 + kk] | ((b[66 + j] >> (2 * k)) & 0x03) << 8], b[34 + kk], c.w[2 * k], c.w[2 * k + 1]);
+      const uint32_t sg = rd.u8(34 + kk);
+      apply_masks(lut.grid64(rd.u8(2 + kk) | ((qh >> (2 * k)) & 0x03) << 8), byte_mask4(sg), byte_mask4(sg >> 4),
+                  c.w[2 * k], c.w[2 * k + 1]);
     }
-    const uint32_t s = b[74 + j];
+    const uint32_t s = rd.u8(74 + j);
     c.s21[0] = 2 * (int) (s & 0x0F) + 1, c.s21[1] = 2 * (int) (s >> 4) + 1;
-    c.d = half_value(ld16(b));
+    c.d = half_value(rd.u16(0));
   } else if constexpr (T == QTYPE_IQ3_XXS) {
-    const uint8_t* q = b + 2 + 8 * j;
-    const uint32_t aux = ld32(b + 66 + 4 * j);
+    const uint32_t aux = rd.u32(66 + 4 * j);
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const uint64_t grid = (uint64_t) g.g32[q[2 * k]] | (uint64_t) g.g32[q[2 * k + 1]] << 32;
-      apply_signs(grid, g.sign[(aux >> (7 * k)) & 0x7F], c.w[2 * k], c.w[2 * k + 1]);
+      apply_masks_carry(lut.grid32(rd.u8(2 + 8 * j + 2 * k)), lut.grid32(rd.u8(2 + 8 * j + 2 * k + 1)),
+                        lut.sign_masks4((aux >> (7 * k)) & 0x7F), c.w[2 * k], c.w[2 * k + 1]);
     }
     c.s21[0] = c.s21[1] = 2 * (2 * (int) (aux >> 28) + 1);
-    c.d = half_value(ld16(b));
+    c.d = half_value(rd.u16(0));
   } else if constexpr (T == QTYPE_IQ1_S) {
-    const uint32_t h = ld16(b + 34 + 2 * j);
+    const uint32_t h = rd.u16(34 + 2 * j);
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const uint64_t grid = g.g64[b[2 + 4 * j + k] | ((h >> (3 * k)) & 0x07) << 8];
+      const uint64_t grid = lut.grid64(rd.u8(2 + 4 * j + k) | ((h >> (3 * k)) & 0x07) << 8);
       c.w[2 * k] = (int) (uint32_t) grid, c.w[2 * k + 1] = (int) (uint32_t) (grid >> 32);
       c.delta[k] = h & 0x8000 ? -1 : 1;
     }
     c.s21[0] = c.s21[1] = 2 * (int) ((h >> 12) & 0x07) + 1;
-    c.d = half_value(ld16(b));
+    c.d = half_value(rd.u16(0));
   } else if constexpr (T == QTYPE_IQ1_M) {
-    const uint64_t sc = ld64(b + 48);
+    const uint64_t sc = rd.u64(48);
 #pragma unroll
     for (int k = 0; k < 4; k++) {
       const int kk = 4 * j + k;
-      const uint32_t h = (b[32 + kk / 2] >> (4 * (kk % 2))) & 0x0F;
-      const uint64_t grid = g.g64[b[kk] | (h & 0x07) << 8];
+      const uint32_t h = (rd.u8(32 + kk / 2) >> (4 * (kk % 2))) & 0x0F;
+      const uint64_t grid = lut.grid64(rd.u8(kk) | (h & 0x07) << 8);
       c.w[2 * k] = (int) (uint32_t) grid, c.w[2 * k + 1] = (int) (uint32_t) (grid >> 32);
       c.delta[k] = h & 0x08 ? -1 : 1;
     }
@@ -269,30 +324,37 @@ template <uint32_t T> __device__ __forceinline__ void lane_codes(const uint8_t* 
       const int kk = 4 * j + 2 * h;
       c.s21[h] = 2 * (int) ((sc >> (16 * (kk / 8) + 3 * ((kk / 2) % 4))) & 0x07) + 1;
     }
-    c.d = iq1m_scale(b);
+    c.d = iq1m_scale_rd(rd);
   } else if constexpr (T == QTYPE_Q2_K) {
-    const uint8_t* qs = b + 16 + 32 * (j / 4);
-    const int shift = 2 * (j % 4);
+    const int base = 16 + 32 * (j / 4), shift = 2 * (j % 4);
 #pragma unroll
-    for (int t = 0; t < 8; t++) c.w[t] = (int) ((ld32(qs + 4 * t) >> shift) & 0x03030303u);
+    for (int t = 0; t < 8; t++) c.w[t] = (int) ((rd.u32(base + 4 * t) >> shift) & 0x03030303u);
 #pragma unroll
-    for (int h = 0; h < 2; h++) c.s21[h] = 8 * (b[2 * j + h] & 0x0F), c.m8[h] = 8 * (b[2 * j + h] >> 4);
-    c.d = half_value(ld16(b + 80)), c.dmin = half_value(ld16(b + 82));
+    for (int h = 0; h < 2; h++) {
+      const uint32_t sm = rd.u8(2 * j + h);
+      c.s21[h] = 8 * (int) (sm & 0x0F), c.m8[h] = 8 * (int) (sm >> 4);
+    }
+    c.d = half_value(rd.u16(80)), c.dmin = half_value(rd.u16(82));
   } else if constexpr (T == QTYPE_Q4_0) {
     // value i < 16 is byte i's low nibble, 16 + i its high nibble, each less 8: as signed bytes without a borrow
-    // between them ((n | 0x80) - 8) ^ 0x80
+    // between them ((n | 0x80) - 8) ^ 0x80. (j: the 18-byte block's index in the bytes rd holds)
 #pragma unroll
     for (int t = 0; t < 4; t++) {
-      const uint32_t raw = ld32(b + 2 + 4 * t);
+      const uint32_t raw = rd.u32(18 * j + 2 + 4 * t);
       c.w[t] = (int) ((((raw & 0x0F0F0F0Fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u);
       c.w[4 + t] = (int) (((((raw >> 4) & 0x0F0F0F0Fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u);
     }
-    c.d = half_value(ld16(b));
+    c.d = half_value(rd.u16(18 * j));
   } else if constexpr (T == QTYPE_Q8_0) {
 #pragma unroll
-    for (int t = 0; t < 8; t++) c.w[t] = (int) ld32(b + 2 + 4 * t);
-    c.d = half_value(ld16(b));
+    for (int t = 0; t < 8; t++) c.w[t] = (int) rd.u32(34 * j + 2 + 4 * t);
+    c.d = half_value(rd.u16(34 * j));
   }
+}
+
+// sub-block j (32 values) of the block at b (for the 32-value types j is 0: b is the block itself)
+template <uint32_t T> __device__ __forceinline__ void lane_codes(const uint8_t* b, int j, LaneCodes& c, const Grids& g) {
+  lane_codes_rd<T>(PtrReader{b}, j, c, PlainLuts{g});
 }
 
 __device__ __forceinline__ float lane_part(float d, int s21, int isum) {

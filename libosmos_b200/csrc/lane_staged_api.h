@@ -1,0 +1,30 @@
+// what q8.cu asks of the staged lane kernel (lane_staged.cu)
+#pragma once
+#include <cstdint>
+
+namespace osmos {
+namespace staged {
+
+struct Request {
+  bool fused, dense;
+  const void* w_dense;       // dense: the matrix
+  const void* const* wg;     // grouped: the entries' matrices (gate, or the only one)
+  const void* const* wu;     // fused: the entries' up matrices
+  const int32_t *cnt, *xrow, *xin, *win;
+  const int8_t* q;
+  const float* d;
+  const float* scale;
+  float lim;
+  float* out;
+  uint32_t rows, cols, out_stride, n_entries, max_cnt, n_tok;
+};
+
+// 1: queued on the stream; 0: not a shape this kernel takes (nothing queued: use the generic kernel); -1: the launch
+// was refused
+int try_launch(uint32_t type, const Request& r, void* stream);
+// the current device's status word, read and cleared (synchronizes): bit 0 a copy never landed, bit 1 a matrix
+// pointer was not 16-byte aligned
+uint32_t read_status();
+
+}  // namespace staged
+}  // namespace osmos

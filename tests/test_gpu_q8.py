@@ -155,3 +155,99 @@ def test_q8_run_plain_blocks(lib, dev, oracle, name, cols):
         codes = blk[:, 2:].view(np.int8).astype(np.int64)
     xi = wq[0].astype(np.int64).reshape(cols // 32, 32)
     assert np.array_equal(dots.reshape(-1, 2).sum(1), (codes * xi).sum(1))
+
+
+ALL_LANE = list(LANE_TYPES)
+
+
+@pytest.mark.parametrize("name", ALL_LANE)
+@pytest.mark.parametrize("cols,rows", [(512, 136), (2048, 64), (4096, 24)])
+def test_staged_kernel_matches_generic_and_oracle(lib, dev, oracle, name, cols, rows):
+    """shapes the staged (bulk-copy) kernel takes: its bits are the generic kernel's and the oracle's, for every count
+    1..8, with token and weight indirection, a skipped entry, and rows that leave the last tile partial"""
+    tid = TYPES[name]
+    n_mat = 6
+    rng = synth.rng_for(24, tid, cols)
+    gate = [synth.random_tensor(tid, rows, cols, rng) for _ in range(n_mat)]
+    up = [synth.random_tensor(tid, rows, cols, rng) for _ in range(n_mat)]
+    cnt, xrow = [1, 8, 0, 3, 2, 5], [0, 1, 9, 9, 12, 14]
+    total, n_tok = 19, 7
+    x = rng.standard_normal((n_tok, cols)).astype(np.float32)
+    xin = rng.integers(0, n_tok, size=total).astype(np.int32)
+    win = rng.permutation(total).astype(np.int32)
+    scale = rng.uniform(0.05, 0.5, size=total).astype(np.float32)
+    wq, wd = oracle.q8_round(x)
+    q, d = to_dev(wq, dev), to_dev(wd, dev)
+    pg, tg, cd, xd_ = _tables(dev, gate, cnt, xrow)
+    pu, tu, _, _ = _tables(dev, up, cnt, xrow)
+    xin_d, win_d, sc_d = to_dev(xin, dev), to_dev(win, dev), to_dev(scale, dev)
+    ys, lim = rows + 5, 2.0
+    results = []
+    for staged in (1, 0):
+        lib.q8_set_staged(staged)
+        yg = torch.full((total, ys), -9.0, dtype=torch.float32, device=dev)
+        h = torch.full((total, ys), -9.0, dtype=torch.float32, device=dev)
+        assert lib.q8_group_tok(tid, ptr(tg), ptr(cd), ptr(xd_), ptr(xin_d), n_mat, 8, rows, cols, ptr(q), ptr(d), ptr(yg), ys, None)
+        assert lib.q8_gate_up(tid, ptr(tg), ptr(tu), ptr(cd), ptr(xd_), ptr(xin_d), ptr(win_d), n_mat, 8, rows, cols,
+                              ptr(q), ptr(d), ptr(sc_d), lim, ptr(h), ys, None)
+        sync()
+        results.append((yg.cpu().numpy(), h.cpu().numpy()))
+    lib.q8_set_staged(1)
+    assert lib.q8_status() == 0
+    want_g, want_h = np.full((total, ys), -9.0, np.float32), np.full((total, ys), -9.0, np.float32)
+    for m in range(n_mat):
+        for t in range(cnt[m]):
+            r = xrow[m] + t
+            tok = xin[r]
+            g_ = oracle.q8_rows(tid, gate[m], rows, cols, wq[tok:tok + 1], wd[tok:tok + 1])
+            u_ = oracle.q8_rows(tid, up[m], rows, cols, wq[tok:tok + 1], wd[tok:tok + 1])
+            want_g[r, :rows] = g_[0]
+            want_h[r, :rows] = oracle.swiglu_lane(g_, u_, lim, scale[win[r]:win[r] + 1])[0]
+    assert same_bits(results[1][0], want_g) and same_bits(results[1][1], want_h), "generic kernel"
+    assert same_bits(results[0][0], want_g) and same_bits(results[0][1], want_h), "staged kernel"
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q8_0", "IQ3_XXS", "IQ1_M"])
+@pytest.mark.parametrize("cols,rows,ntok", [(2048, 96, 1), (4096, 40, 5), (256, 8, 8)])
+def test_staged_dense_matches_generic_and_oracle(lib, dev, oracle, name, cols, rows, ntok):
+    tid = TYPES[name]
+    rng = synth.rng_for(25, tid, cols)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    x = rng.standard_normal((ntok, cols)).astype(np.float32)
+    wq, wd = oracle.q8_round(x)
+    want = oracle.q8_rows(tid, w, rows, cols, wq, wd)
+    wdv, q, d = to_dev(w, dev), to_dev(wq, dev), to_dev(wd, dev)
+    for staged in (1, 0):
+        lib.q8_set_staged(staged)
+        y = torch.full((ntok, rows + 2), -4.0, dtype=torch.float32, device=dev)
+        assert lib.q8_run(tid, ptr(wdv), rows, cols, ptr(q), ptr(d), ntok, ptr(y), rows + 2, None)
+        sync()
+        got = y.cpu().numpy()
+        assert same_bits(got[:, :rows], want) and (got[:, rows:] == -4.0).all(), "staged" if staged else "generic"
+    lib.q8_set_staged(1)
+    assert lib.q8_status() == 0
+
+
+def test_staged_refuses_misaligned_matrix_without_faulting(lib, dev, oracle):
+    """a matrix table entry that is not 16-byte aligned: the staged kernel records it and leaves (no fault, the
+    context stays usable); the generic kernel takes the same call"""
+    tid, rows, cols = TYPES["IQ3_XXS"], 64, 2048
+    rng = synth.rng_for(26)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    pool = torch.zeros(w.size + 64, dtype=torch.uint8, device=dev)
+    pool[2:2 + w.size] = to_dev(w, dev)
+    table = torch.tensor([pool.data_ptr() + 2], dtype=torch.int64, device=dev)
+    x = rng.standard_normal((1, cols)).astype(np.float32)
+    wq, wd = oracle.q8_round(x)
+    q, d = to_dev(wq, dev), to_dev(wd, dev)
+    one, zero = to_dev(np.array([1], np.int32), dev), to_dev(np.array([0], np.int32), dev)
+    y = torch.zeros((1, rows), dtype=torch.float32, device=dev)
+    lib.q8_set_staged(1)
+    assert lib.q8_group_tok(tid, ptr(table), ptr(one), ptr(zero), None, 1, 1, rows, cols, ptr(q), ptr(d), ptr(y), rows, None)
+    sync()
+    assert lib.q8_status() & 2
+    lib.q8_set_staged(0)
+    assert lib.q8_group_tok(tid, ptr(table), ptr(one), ptr(zero), None, 1, 1, rows, cols, ptr(q), ptr(d), ptr(y), rows, None)
+    sync()
+    lib.q8_set_staged(1)
+    assert same_bits(y.cpu().numpy(), oracle.q8_rows(tid, w, rows, cols, wq, wd))
