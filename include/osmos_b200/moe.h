@@ -63,6 +63,20 @@ void q4x_expert_bounds(uint32_t n, uint32_t n_exp, Q4xExpertBounds *b);
    (reference: q4x_ops.h:155-156, kernels/q4x_moe.hip:70-165,221-233). */
 bool q4x_expert_tiles(const int32_t *ids, uint32_t n, uint32_t k, uint32_t n_exp, uint32_t dim, uint32_t ff,
                       const Q4xExpertTiles *t, void *stream);
+/* q4x_expert_tiles for callers that cannot allocate device memory. No counterpart in the reference.
+   Who needs it: an engine step that runs inside a fixed memory budget handed out at start-up (the step path of an
+   inference server must never call cudaMalloc: it synchronizes the whole device and can fail under load), or host
+   code embedded in a runtime that owns the allocator and gives a plug-in none. Such a caller still passes every
+   input and output table; only the tables' scratch (t->off, which is ignored here and may be NULL) lives in a
+   fixed 12 KB array inside this library - room for the entry point's own limit of 1024 experts; more is refused
+   (false, nothing queued). The array exists once per device that loads the library and is kept until the process
+   exits. Nothing is allocated or freed by any call. The first call on a device looks up the array's device address
+   (cudaGetSymbolAddress, with that device current) and keeps it: make that first call during set-up, before any
+   stream capture. Every call on a device shares the one array and each call overwrites all of it that it reads,
+   so calls one after another on a stream are fine, but two calls whose kernels overlap on the GPU (different
+   streams without an event between them) race on it. Same results, same refusals otherwise, as q4x_expert_tiles. */
+bool q4x_expert_tiles_static(const int32_t *ids, uint32_t n, uint32_t k, uint32_t n_exp, uint32_t dim, uint32_t ff,
+                             const Q4xExpertTiles *t, void *stream);
 /* y = silu(g) * u (libm expf), also to side when not NULL (reference: q4x_ops.h:157, q4x_moe.hip:167-170,253-259) */
 bool q4x_swiglu(const float *g, const float *u, uint64_t n, float *y, const Q4xX16 *side, void *stream);
 /* out[t][d] = sum_j y[where[t k + j]][d] * w[t k + j] in pick order from 0, + shared[t][d] * sigmoid(shared_logit[t])

@@ -76,6 +76,7 @@ SIGNATURES = {
     "q4x_route": (B, [P, U32, U32, U32, P, P, P, P]),
     "q4x_expert_bounds": (None, [U32, U32, C.POINTER(Q4xExpertBounds)]),
     "q4x_expert_tiles": (B, [P, U32, U32, U32, U32, U32, C.POINTER(Q4xExpertTiles), P]),
+    "q4x_expert_tiles_static": (B, [P, U32, U32, U32, U32, U32, C.POINTER(Q4xExpertTiles), P]),
     "q4x_swiglu": (B, [P, P, U64, P, C.POINTER(Q4xX16), P]),
     "q4x_moe_sum": (B, [P, P, P, U32, U32, U32, P, P, P, P]),
     # ops.h

@@ -361,6 +361,31 @@ extern "C" bool q4x_expert_tiles(const int32_t* ids, uint32_t n, uint32_t k, uin
   return launched();
 }
 
+// ---- q4x_expert_tiles without caller scratch ----------------------------------------------------------------------
+// The tables' scratch (an expert's first place, first slot and count) in a fixed device array of this library, for
+// callers that must not allocate: see include/osmos_b200/moe.h. One array a device that loads the library, held until
+// the process exits; every call on a device shares it.
+constexpr uint32_t kStaticTilesExperts = 1024;  // the most experts the fixed scratch holds (12 KB)
+static __device__ __align__(256) int32_t g_tiles_scratch[3 * kStaticTilesExperts];
+constexpr int kStaticTilesDevices = 64;
+static int32_t* g_tiles_scratch_at[kStaticTilesDevices];  // the array's device address, per device, once looked up
+
+extern "C" bool q4x_expert_tiles_static(const int32_t* ids, uint32_t n, uint32_t k, uint32_t n_exp, uint32_t dim,
+                                        uint32_t ff, const Q4xExpertTiles* t, void* stream) {
+  if (!t || !n_exp || n_exp > kStaticTilesExperts) return false;  // past the fixed scratch: refused, nothing queued
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kStaticTilesDevices) return false;
+  if (!g_tiles_scratch_at[device]) {
+    // host code cannot use the array's name as an address: ask the runtime where it lives on the current device
+    void* at = nullptr;
+    if (cudaGetSymbolAddress(&at, g_tiles_scratch) != cudaSuccess || !at) return false;
+    g_tiles_scratch_at[device] = (int32_t*) at;
+  }
+  Q4xExpertTiles with_scratch = *t;
+  with_scratch.off = g_tiles_scratch_at[device];
+  return q4x_expert_tiles(ids, n, k, n_exp, dim, ff, &with_scratch, stream);
+}
+
 extern "C" bool q4x_swiglu(const float* g, const float* u, uint64_t n, float* y, const Q4xX16* side, void* stream) {
   if (!g || !u || !y || !n) return false;
   const Q4xX16 s = side ? *side : Q4xX16{nullptr, nullptr, 1, 0};
