@@ -11,7 +11,6 @@ namespace staged {
 namespace {
 
 constexpr uint32_t kSmemLimit = 226u * 1024u;  // dynamic; the block also has a few static words (227 KB in all a block)
-constexpr uint32_t kTileTarget = 26u * 1024u;  // a tile's bytes of one matrix, about
 
 __device__ uint32_t g_status;
 
@@ -41,14 +40,19 @@ int launch(const Request& r, cudaStream_t s) {
   if (!dev) return 0;
   constexpr int M = FUSED ? 2 : 1;
   const uint32_t row_bytes = r.cols / 256 * Super<T>::bytes;
-  uint32_t tr = kTileTarget / row_bytes & ~7u;
+  // a tile's rows: as many as one pass of the compute warps covers (phase A: a thread a superblock of one matrix), in
+  // eights; the light one-scale blocks take half a pass, so that more stages are in flight
+  const uint32_t nsb = r.cols / 256, pass = (FUSED ? kComputeThreads / 2 : kComputeThreads) / (kLanePlain<T> ? 2 : 1);
+  uint32_t tr = (pass / nsb) & ~7u;
   if (tr > r.rows) tr = r.rows;
   if (tr < 8) tr = 8;
   if (DENSE)  // a small matrix: enough tiles that every block has a few to pipeline
     while (tr > 8 && (uint64_t) ((r.rows + tr - 1) / tr) * ((r.n_tok + kNT - 1) / kNT) < 4ull * dev->sms) tr -= 8;
-  while (tr > 8 && make_plan<T>(r.cols, tr, M).total > kSmemLimit) tr -= 8;
-  const Plan p = make_plan<T>(r.cols, tr, M);
-  if (p.total > kSmemLimit) return 0;
+  while (tr > 8 && make_plan<T>(r.cols, tr, M, 2).total > kSmemLimit) tr -= 8;
+  if (make_plan<T>(r.cols, tr, M, 2).total > kSmemLimit) return 0;
+  uint32_t stages = 2;  // as deep a ring as shared memory holds
+  while (stages < (uint32_t) kMaxStages && make_plan<T>(r.cols, tr, M, stages + 1).total <= kSmemLimit) stages++;
+  const Plan p = make_plan<T>(r.cols, tr, M, stages);
   static bool sized = false;  // (one flag a template instance)
   auto kernel = lane_staged_kernel<T, FUSED, DENSE>;
   if (!sized) {
@@ -60,6 +64,7 @@ int launch(const Request& r, cudaStream_t s) {
   a.cnt = r.cnt, a.xrow = r.xrow, a.xin = r.xin, a.win = r.win, a.q = r.q, a.d = r.d, a.scale = r.scale, a.lim = r.lim;
   a.out = r.out, a.rows = r.rows, a.cols = r.cols, a.out_stride = r.out_stride, a.n_entries = r.n_entries;
   a.max_cnt = DENSE ? r.n_tok : r.max_cnt, a.n_tok = r.n_tok, a.tile_rows = tr, a.tiles = (r.rows + tr - 1) / tr;
+  a.stages = stages;
   a.status = dev->status;
   uint32_t grid = (uint32_t) dev->sms;
   if (DENSE) {

@@ -2,16 +2,18 @@
 // engine through a two-stage mbarrier ring, every block of a tile decoded out of registers, codebooks replicated
 // per lane so their lookups never collide in a bank.
 //
-// Work item = (entry, row tile, pair of tokens). A block walks its items in a fixed stride; warp 0 issues the next
-// item's copies (the tile of gate rows, of up rows when fused, each live token's int8 row as 256-byte pieces, its
-// scales) before the block starts on the current one, so one stage is always in flight while one is consumed.
+// Work item = (entry, row tile, pair of tokens). A block walks its items in a fixed stride; a seventeenth warp issues
+// the items' copies (the tile of gate rows, of up rows when fused, each live token's int8 row as 256-byte pieces, its
+// scales) as many stages ahead as shared memory holds, and leaves each item's small facts (live tokens, output rows,
+// routed weights) beside its stage, so the sixteen compute warps never wait on a global load.
 //
 // Per item, two phases:
 //   A  a thread takes whole 256-value superblocks of the tile's flat byte stream (thread g: superblock g, two
 //      neighbours in a warp two superblocks apart, so every window load is bank-conflict free and its 2-byte
-//      alignment is the warp's, a template constant). It reads the superblock as aligned 32-bit words into
-//      registers, decodes its eight 32-value sub-blocks and writes each sub-block's value before x's scale (two
-//      exact integer half dots, then the contract's products) to shared memory.
+//      alignment is the warp's, a template constant; of a fused pair a warp takes the gate's or the up's). It reads
+//      the superblock as aligned 32-bit words into registers, decodes its eight 32-value sub-blocks and writes each
+//      sub-block's value before x's scale (two exact integer half dots, then the contract's products) to shared
+//      memory.
 //   B  a thread is a lane of the contract: it runs the fmaf chain acc = fmaf(d_x, block, acc) over its blocks
 //      l, l + L, ... in order, the L lanes of a row are combined by the xor tree, lane 0 stores the sum or the
 //      activation of the gate and up sums.
@@ -31,7 +33,7 @@ namespace staged {
 constexpr int kComputeWarps = 16, kComputeThreads = kComputeWarps * kWarp;
 constexpr int kThreads = kComputeThreads + kWarp, kWarps = kThreads / kWarp;  // + the warp that issues the copies
 constexpr int kNT = 2;             // tokens an item carries
-constexpr int kStages = 2;
+constexpr int kMaxStages = 6;
 constexpr int kXPiece = 256 + 16;  // a token's 256 int8 of one superblock, padded so neighbours fall in other banks
 constexpr uint32_t kListMax = 1024;  // entries whose live (entry, token pair) list a block builds at a time
 constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;  // no copy of a tile takes anywhere near 0.2 s
@@ -178,20 +180,31 @@ struct Args {
   float* out;
   uint32_t rows, cols, out_stride, n_entries, max_cnt, n_tok;
   uint32_t tile_rows, tiles;  // rows a tile, tiles a matrix
+  uint32_t stages;            // the ring's depth
   uint32_t* status;
 };
 
+// an item's facts, written by the copy warp beside the item's stage before its copies are issued
+struct Meta {
+  uint32_t live;        // tokens of this item (1 .. kNT)
+  uint32_t out_row;     // its first token's output row
+  uint32_t row0, trows; // the tile's first row and its rows
+  float scale[kNT];     // fused: each token's routed weight
+};
+
 struct Plan {  // byte offsets into dynamic shared memory; the same function on the host and the device
-  uint32_t lut, bars, list, stage0, stage_bytes, w_bytes, x_off, x_tok, dx_off, bs, bs_bytes, plane, total;
+  uint32_t lut, bars, meta, list, stage0, stage_bytes, w_bytes, x_off, x_tok, dx_off, bs, bs_bytes, plane, total;
 };
 
 template <uint32_t T>
-__host__ __device__ inline Plan make_plan(uint32_t cols, uint32_t tile_rows, int mats) {
+__host__ __device__ inline Plan make_plan(uint32_t cols, uint32_t tile_rows, int mats, uint32_t stages) {
   Plan p;
   const uint32_t nsb = cols / 256, nblk = cols / 32, row_bytes = nsb * Super<T>::bytes;
   uint32_t at = 0;
   p.lut = at, at += (Rep<T>::bytes + 127u) & ~127u;
-  p.bars = at, at += 64;  // full[2], empty[2]
+  p.bars = at, at += 2 * kMaxStages * 8;  // full[], empty[]
+  at = (at + 31u) & ~31u;
+  p.meta = at, at += kMaxStages * 32;
   p.list = at, at += kListMax * 4 * 2;  // (entry, token pair) as 16 bits, at most 4 pairs an entry
   at = (at + 127u) & ~127u;
   p.w_bytes = (tile_rows * row_bytes + 15u) & ~15u;
@@ -199,16 +212,16 @@ __host__ __device__ inline Plan make_plan(uint32_t cols, uint32_t tile_rows, int
   p.x_tok = nsb * kXPiece;
   p.dx_off = p.x_off + kNT * p.x_tok;
   p.stage_bytes = (p.dx_off + kNT * nblk * 4 + 127u) & ~127u;
-  p.stage0 = at, at += kStages * p.stage_bytes;
   p.plane = tile_rows * nblk / 32 * 36;  // floats of one (matrix, token) plane: 4 floats of padding every 32
   p.bs_bytes = mats * kNT * p.plane * 4;
   p.bs = at, at += p.bs_bytes;
+  p.stage0 = at, at += stages * p.stage_bytes;
   p.total = at;
   return p;
 }
 
 // where sub-block value f (a float index into one (matrix, token) plane of the tile) is kept: 4 floats of padding after
-// every 32, so that phase A's 16-byte writes (threads 16 floats apart) and phase B's reads (a lane a float) both
+// every 32, so that phase A's 32-byte writes (threads 16 floats apart) and phase B's reads (a lane a float) both
 // spread over the banks
 __device__ __forceinline__ uint32_t bs_at(uint32_t f) { return f + (f >> 5) * 4; }
 
@@ -217,20 +230,23 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int M = FUSED ? 2 : 1;
   constexpr int SB = Super<T>::bytes;
-  const Plan p = make_plan<T>(a.cols, a.tile_rows, M);
+  static_assert(sizeof(Meta) <= 32, "a stage's facts fit their slot");
+  const uint32_t S = a.stages;
+  const Plan p = make_plan<T>(a.cols, a.tile_rows, M, S);
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
   const bool producer = warp == (uint32_t) kComputeWarps;
   const uint32_t nsb = a.cols / 256, nblk = a.cols / 32, row_bytes = nsb * SB;
   const int L = a.cols >= 4096 ? 32 : 16;
   uint64_t* full = (uint64_t*) (smem + p.bars);
-  uint64_t* empty = full + kStages;
+  uint64_t* empty = full + kMaxStages;
+  Meta* metas = (Meta*) (smem + p.meta);
   uint16_t* list = (uint16_t*) (smem + p.list);
   const uint32_t bs_addr = smem_addr(smem + p.bs);
   __shared__ int s_live_pairs, s_fail;
   __shared__ int s_scan[kWarps];
 
   if (tid == 0) {
-    for (int st = 0; st < kStages; st++) bar_init(&full[st], 1), bar_init(&empty[st], kComputeWarps);
+    for (uint32_t st = 0; st < S; st++) bar_init(&full[st], 1), bar_init(&empty[st], kComputeWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_fail = 0;
   }
@@ -243,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
     const int32_t c = a.cnt[m];
     return c <= 0 ? 0u : ((uint32_t) c < a.max_cnt ? (uint32_t) c : a.max_cnt);
   };
-  // an item's sources -> its stage; every lane of the producer warp. false: a matrix was not 16-byte aligned
+  // an item's facts and sources -> its stage; every lane of the copy warp. false: a matrix was not 16-byte aligned
   auto issue = [&](uint32_t m, uint32_t grp, uint32_t tile, uint32_t stage) -> bool {
     uint8_t* st = smem + p.stage0 + stage * p.stage_bytes;
     const uint32_t row0 = tile * a.tile_rows;
@@ -255,14 +271,21 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
     const uint8_t* wu_ = wg;
     if constexpr (FUSED) wu_ = a.wu[m] + (uint64_t) row0 * row_bytes;
     if ((((uintptr_t) wg | (uintptr_t) wu_) & 15u) != 0) return false;  // a bulk copy needs 16-byte aligned sources
-    if (lane == 0) bar_expect(&full[stage], M * wbytes + live * (a.cols + nblk * 4));
+    const uint32_t r0 = (DENSE ? 0u : (uint32_t) a.xrow[m]) + t0;
+    if constexpr (FUSED) {
+      if (lane < live) metas[stage].scale[lane] = a.scale[a.win ? a.win[r0 + lane] : r0 + lane];  // token t's routed weight
+      __syncwarp();
+    }
+    if (lane == 0) {
+      metas[stage].live = live, metas[stage].out_row = r0, metas[stage].row0 = row0, metas[stage].trows = trows;
+      bar_expect(&full[stage], M * wbytes + live * (a.cols + nblk * 4));
+    }
     __syncwarp();
     if (lane == 0) bulk_load(st, wg, wbytes, &full[stage]);
     if constexpr (FUSED)
       if (lane == 1) bulk_load(st + p.w_bytes, wu_, wbytes, &full[stage]);
-    const uint32_t r0 = DENSE ? 0u : (uint32_t) a.xrow[m];
     for (uint32_t t = 0; t < live; t++) {
-      const uint32_t r = r0 + t0 + t;
+      const uint32_t r = r0 + t;
       const uint64_t xr = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
       for (uint32_t i = lane; i < nsb; i += kWarp)
         bulk_load(st + p.x_off + t * p.x_tok + i * kXPiece, a.q + xr * a.cols + i * 256, 256, &full[stage]);
@@ -271,38 +294,35 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
     return true;
   };
 
-  // ---- phase A for one superblock alignment (A: its start's byte offset in its first word) and one half (H: its
-  // sub-blocks 4H .. 4H + 3). The window's words the half never reads are never loaded (their loads are dead code).
-  auto phase_a = [&](auto align_tag, auto half_tag, uint32_t st, uint32_t tile_sb, uint32_t live, uint32_t g_first) {
-    constexpr int A = decltype(align_tag)::value, H = decltype(half_tag)::value;
-    for (uint32_t g = g_first; g < tile_sb; g += kComputeThreads / 2) {
+  // ---- phase A for one superblock alignment (A: its start's byte offset in its first word) and one count of live
+  // tokens (NTL): superblock g of matrix `mat`, all eight sub-blocks
+  auto phase_a = [&](auto align_tag, auto live_tag, uint32_t st, uint32_t tile_sb, uint32_t mat, uint32_t g_first,
+                     uint32_t g_step) {
+    constexpr int A = decltype(align_tag)::value, NTL = decltype(live_tag)::value;
+    for (uint32_t g = g_first; g < tile_sb; g += g_step) {
       const uint32_t r = g / nsb, i = g - r * nsb;
-      const uint32_t xa = st + p.x_off + i * kXPiece + H * 128;
-      const uint32_t fo = bs_at(r * nblk + i * 8 + 4 * H);
-#pragma unroll 1
-      for (int mat = 0; mat < M; mat++) {
-        WordWindow<Super<T>::words, A> win;
-        const uint32_t src = st + mat * p.w_bytes + g * SB - A;
+      const uint32_t xa = st + p.x_off + i * kXPiece;
+      const uint32_t out = bs_addr + 4 * (mat * kNT * p.plane + bs_at(r * nblk + i * 8));
+      WordWindow<Super<T>::words, A> win;
+      const uint32_t src = st + mat * p.w_bytes + g * SB - A;
 #pragma unroll
-        for (int k = 0; k < Super<T>::words; k++) win.w[k] = lds32(src + 4 * k);
-        float v[kNT][4];
+      for (int k = 0; k < Super<T>::words; k++) win.w[k] = lds32(src + 4 * k);
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        float v[NTL][4];
 #pragma unroll
         for (int jj = 0; jj < 4; jj++) {
           LaneCodes c;
-          lane_codes_rd<T>(win, 4 * H + jj, c, luts);
+          lane_codes_rd<T>(win, 4 * h + jj, c, luts);
 #pragma unroll
-          for (int t = 0; t < kNT; t++) {
-            if ((uint32_t) t < live) {
-              const int4 lo = lds128(xa + t * p.x_tok + jj * 32), hi = lds128(xa + t * p.x_tok + jj * 32 + 16);
-              const int x[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-              v[t][jj] = lane_block_sum<T>(c, x);
-            }
+          for (int t = 0; t < NTL; t++) {
+            const int4 lo = lds128(xa + t * p.x_tok + (4 * h + jj) * 32), hi = lds128(xa + t * p.x_tok + (4 * h + jj) * 32 + 16);
+            const int x[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            v[t][jj] = lane_block_sum<T>(c, x);
           }
         }
 #pragma unroll
-        for (int t = 0; t < kNT; t++)
-          if ((uint32_t) t < live)
-            sts128(bs_addr + 4 * ((uint32_t) (mat * kNT + t) * p.plane + fo), v[t][0], v[t][1], v[t][2], v[t][3]);
+        for (int t = 0; t < NTL; t++) sts128(out + 4 * (t * p.plane + 4 * h), v[t][0], v[t][1], v[t][2], v[t][3]);
       }
     }
   };
@@ -349,11 +369,11 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
     };
 
     if (producer) {
-      // ---- the copy warp: stays one stage ahead of the compute warps ----
+      // ---- the copy warp: up to S stages ahead of the compute warps ----
       for (uint32_t q = blockIdx.x; q < items; q += gridDim.x, it++) {
-        const uint32_t stage = it & 1u;
+        const uint32_t stage = it % S, use = it / S;
         bool ok = true;
-        if (it >= (uint32_t) kStages) ok = bar_wait(&empty[stage], ((it >> 1) - 1u) & 1u);  // the stage's last readers done
+        if (use > 0) ok = bar_wait(&empty[stage], (use - 1u) & 1u);  // the stage's last readers are done with it
         uint32_t m, grp, tile;
         decode_item(q, m, grp, tile);
         const bool aligned = ok && issue(m, grp, tile, stage);
@@ -364,34 +384,39 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
       }
     } else {
       // ---- the compute warps ----
+      // which superblocks of a tile this warp takes: see the header
+      uint32_t mat = 0, g_first, g_step;
+      const uint32_t par = Super<T>::parity ? (warp & 1u) : 0u;
+      {
+        const uint32_t w2 = Super<T>::parity ? warp >> 1 : warp;                 // the warp's index among its phase's
+        const uint32_t span = Super<T>::parity ? 64u : 32u;                      // superblocks a warp pair / a warp covers
+        const uint32_t first = Super<T>::parity ? 2u * lane + par : lane;
+        const uint32_t nw = Super<T>::parity ? kComputeWarps / 2 : kComputeWarps;  // such warps
+        if constexpr (FUSED) {
+          mat = w2 & 1u;
+          g_first = first + span * (w2 >> 1), g_step = span * (nw / 2);
+        } else {
+          g_first = first + span * w2, g_step = span * nw;
+        }
+      }
       for (uint32_t q = blockIdx.x; q < items; q += gridDim.x, it++) {
-        const uint32_t stage = it & 1u;
-        uint32_t m, grp, tile;
-        decode_item(q, m, grp, tile);
-        if (!bar_wait(&full[stage], (it >> 1) & 1u)) s_fail = 1;  // a copy never landed
+        const uint32_t stage = it % S, use = it / S;
+        if (!bar_wait(&full[stage], use & 1u)) s_fail = 1;  // a copy never landed
         const uint32_t st = smem_addr(smem + p.stage0 + stage * p.stage_bytes);
-        const uint32_t row0 = tile * a.tile_rows;
-        const uint32_t trows = a.rows - row0 < a.tile_rows ? a.rows - row0 : a.tile_rows;
-        const uint32_t cnt = live_count(m);
-        const uint32_t t0 = grp * kNT, live = cnt - t0 < (uint32_t) kNT ? cnt - t0 : (uint32_t) kNT;
-        const uint32_t tile_sb = trows * nsb;
+        const Meta meta = metas[stage];
+        const uint32_t live = meta.live, tile_sb = meta.trows * nsb;
         if (!s_fail) {
-          // a warp's superblocks all start on the same 2-byte phase and it takes one half of each: warp w the phase
-          // w & 1 (for types whose superblocks are whole words: the second 32 of its 64), the half (w >> 1) & 1
-          const uint32_t par = Super<T>::parity ? (warp & 1u) : 0u, half = (warp >> 1) & 1u;
-          const uint32_t g_first = Super<T>::parity ? 2u * lane + par + 64u * (warp >> 2)
-                                                    : lane + 32u * (warp & 1u) + 64u * (warp >> 2);
           using I0 = std::integral_constant<int, 0>;
           using I1 = std::integral_constant<int, 1>;
           using I2 = std::integral_constant<int, 2>;
           if (par) {
             if constexpr (Super<T>::parity) {
-              if (half) phase_a(I2{}, I1{}, st, tile_sb, live, g_first);
-              else phase_a(I2{}, I0{}, st, tile_sb, live, g_first);
+              if (live == 2) phase_a(I2{}, I2{}, st, tile_sb, mat, g_first, g_step);
+              else phase_a(I2{}, I1{}, st, tile_sb, mat, g_first, g_step);
             }
           } else {
-            if (half) phase_a(I0{}, I1{}, st, tile_sb, live, g_first);
-            else phase_a(I0{}, I0{}, st, tile_sb, live, g_first);
+            if (live == 2) phase_a(I0{}, I2{}, st, tile_sb, mat, g_first, g_step);
+            else phase_a(I0{}, I1{}, st, tile_sb, mat, g_first, g_step);
           }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
@@ -401,8 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
         }
 
         // ---- phase B: the contract's lanes ----
-        const uint32_t r0 = DENSE ? 0u : (uint32_t) a.xrow[m];
-        const uint32_t lanes_total = trows * (uint32_t) L;
+        const uint32_t lanes_total = meta.trows * (uint32_t) L;
         for (uint32_t vl = tid; vl < lanes_total; vl += kComputeThreads) {
           const uint32_t r = vl / (uint32_t) L, ll = vl % (uint32_t) L;
 #pragma unroll
@@ -425,11 +449,9 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
                   if constexpr (FUSED) au = __fadd_rn(au, __shfl_xor_sync(0xFFFFFFFFu, au, o, kWarp));
                 }
               if (ll == 0) {
-                const uint64_t ro = (uint64_t) r0 + t0 + (uint32_t) t;
-                if constexpr (FUSED)
-                  a.out[ro * a.out_stride + row0 + r] = lane_swiglu(ag, au, a.lim, a.scale[a.win ? a.win[ro] : ro]);
-                else
-                  a.out[ro * a.out_stride + row0 + r] = ag;
+                const uint64_t ro = (uint64_t) meta.out_row + (uint32_t) t;
+                if constexpr (FUSED) a.out[ro * a.out_stride + meta.row0 + r] = lane_swiglu(ag, au, a.lim, meta.scale[t]);
+                else a.out[ro * a.out_stride + meta.row0 + r] = ag;
               }
             }
           }
