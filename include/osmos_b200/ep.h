@@ -1,0 +1,57 @@
+/* Expert-parallel pieces of the routed-expert layer: one process per GPU, experts in contiguous ranges per rank,
+ * tokens by home rank. No counterpart in the reference (it is single-GPU: no collective, no peer API anywhere in
+ * its tree); the arithmetic is q8.h's and the combine order is the single-GPU one, so the result has the same bits
+ * on any number of GPUs.
+ *
+ * A step on rank r (T = its home tokens, N ranks, k picks a token, E experts):
+ *   1. q4x_route and q8_round on its T tokens, written straight into its segment of the dispatch buffer
+ *      (ep_segment_bytes; ids, weights, int8 rows, scales);
+ *   2. all-gather of the segments (NCCL), ep_unpack -> every token's ids / weights / int8 row / scales, token-major;
+ *   3. lane_ffn_rows: the rows whose expert lies in [e0, e1) through gate / up / activation / down;
+ *   4. ep_scatter_rows: row of pick (t, j) -> send[home(t)][(t mod T) * k + j];
+ *   5. all-to-all of send (NCCL): recv[o] = what rank o computed for this rank's tokens;
+ *   6. ep_combine: each home token's k rows, taken from their owners' blocks, added in ascending expert id.
+ * Every bool entry returns true when the work was queued on `stream`, false when it was refused (nothing queued).
+ */
+#ifndef OSMOS_B200_EP_H
+#define OSMOS_B200_EP_H
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#include "osmos_b200/lane.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* a rank's dispatch segment for T tokens: [ids T*k i32][weights T*k f32][q T*dim i8][d T*(dim/32) f32], each part
+   16-byte aligned; these give the parts' byte offsets and the segment's size (a multiple of 16) */
+typedef struct EpSegment
+{
+  uint64_t ids, weights, q, d, bytes;
+} EpSegment;
+void ep_segment(uint32_t tokens, uint32_t k, uint32_t dim, EpSegment *s);
+
+/* the gathered segments (n_ranks of them, rank-major) -> token-major arrays over all n_ranks * tokens tokens */
+bool ep_unpack(const void *gathered, uint32_t n_ranks, uint32_t tokens, uint32_t k, uint32_t dim, int32_t *ids,
+               float *weights, int8_t *q, float *d, void *stream);
+/* rows -> the combine's send buffer: for every pick i (token t = i / k) with a row here (row_of[i] >= 0),
+   send[(t / tokens) * tokens * k + (t % tokens) * k + i % k][:] = ye[row_of[i]][:] */
+bool ep_scatter_rows(const float *ye, const int32_t *row_of, uint32_t n_picks, uint32_t k, uint32_t tokens,
+                     uint32_t dim, float *send, void *stream);
+/* out[t][:] = sum over this rank's token t's picks, in ascending expert id, of recv[owner][t * k + j][:], owner =
+   expert / experts_per_rank; ids are the home tokens' picks [tokens * k]; add (or NULL) added after the sum */
+bool ep_combine(const float *recv, const int32_t *ids, uint32_t tokens, uint32_t k, uint32_t experts_per_rank,
+                uint32_t dim, const float *add, float *out, void *stream);
+
+/* lane_ffn's middle for one rank: tokens already rounded (q, d, token-major), the rows of experts [e0, e1) into
+   s->ye (row r = the r-th of those picks sorted by (expert, pick)); s->tab.row_of says which row a pick got */
+bool lane_ffn_rows(const LaneLayer *l, const LaneScratch *s, const int8_t *q, const float *d, const int32_t *ids,
+                   const float *weights, uint32_t n_tok, uint32_t e0, uint32_t e1, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

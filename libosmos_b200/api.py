@@ -44,6 +44,10 @@ class LaneScratch(C.Structure):
                 ("tab", LaneTables)]
 
 
+class EpSegment(C.Structure):
+    _fields_ = [("ids", U64), ("weights", U64), ("q", U64), ("d", U64), ("bytes", U64)]
+
+
 class QTypeInfo(C.Structure):
     _fields_ = [("id", U32), ("values", U32), ("bytes", U32), ("paths", U32), ("name", C.c_char_p)]
 
@@ -100,6 +104,12 @@ SIGNATURES = {
     "lane_scratch_bytes": (U64, [C.POINTER(LaneLayer), U32]),
     "lane_scratch_bind": (B, [C.POINTER(LaneLayer), U32, P, U64, C.POINTER(LaneScratch)]),
     "lane_ffn": (B, [C.POINTER(LaneLayer), C.POINTER(LaneScratch), P, P, P, U32, P, P, P]),
+    # ep.h
+    "ep_segment": (None, [U32, U32, U32, C.POINTER(EpSegment)]),
+    "ep_unpack": (B, [P, U32, U32, U32, U32, P, P, P, P, P]),
+    "ep_scatter_rows": (B, [P, P, U32, U32, U32, U32, P, P]),
+    "ep_combine": (B, [P, P, U32, U32, U32, U32, P, P, P]),
+    "lane_ffn_rows": (B, [C.POINTER(LaneLayer), C.POINTER(LaneScratch), P, P, P, P, U32, U32, U32, P]),
 }
 
 

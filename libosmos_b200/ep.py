@@ -1,0 +1,163 @@
+"""Expert-parallel MoE layer across the GPUs of one box: one process per GPU, `torch.distributed` (NCCL) for the two
+exchanges, every computation a call into libosmos_b200.so (include/osmos_b200/ep.h describes the step).
+
+Sharding: rank r owns experts [r * E / N, (r + 1) * E / N) and is home to tokens [r * T, (r + 1) * T), T = tokens / N.
+Dispatch = all-gather of each rank's routed, int8-rounded home tokens (with top-k >= N nearly every rank needs every
+token, so the dispatch all-to-all degenerates to an all-gather of 2.4 KB a token); combine = all-to-all of the
+computed rows back to the tokens' homes, where each token's rows are added in ascending expert id - the single-GPU
+order, so the output bits do not depend on N.
+"""
+import json
+
+import numpy as np
+import torch
+
+from . import api, runner, synth, workloads
+
+
+def expert_range(rank, world, n_exp):
+    per = n_exp // world
+    return rank * per, (rank + 1) * per
+
+
+def home_tokens(rank, world, n_tok):
+    per = n_tok // world
+    return rank * per, (rank + 1) * per
+
+
+def send_slot(pick, k, tokens_per_rank):
+    """where pick i's row goes in the combine's send buffer (row index; blocks of tokens_per_rank * k rows a home)"""
+    t, j = pick // k, pick % k
+    return (t // tokens_per_rank) * tokens_per_rank * k + (t % tokens_per_rank) * k + j
+
+
+class EpMoeLane:
+    def __init__(self, lib, cfg, dev, rank, world, copies=1, host_tensors=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.lib, self.cfg, self.dev, self.rank, self.world = lib, cfg, dev, rank, world
+        assert cfg["n_exp"] % world == 0 and cfg["n_tok"] % world == 0
+        self.e0, self.e1 = expert_range(rank, world, cfg["n_exp"])
+        self.T = cfg["n_tok"] // world
+        self.k, self.dim, self.ff, self.n_exp, self.n_tok = cfg["k"], cfg["dim"], cfg["ff"], cfg["n_exp"], cfg["n_tok"]
+        self.local = runner.MoeLane(lib, cfg, dev, copies=copies, max_tok=cfg["n_tok"], host_tensors=host_tensors,
+                                    expert_range=(self.e0, self.e1))
+        self.seg = api.EpSegment()
+        lib.ep_segment(self.T, self.k, self.dim, self.seg)
+        self.segment = torch.zeros(self.seg.bytes, dtype=torch.uint8, device=dev)
+        self.gathered = torch.zeros(self.seg.bytes * world, dtype=torch.uint8, device=dev)
+        picks = self.n_tok * self.k
+        self.ids_all = torch.zeros(picks, dtype=torch.int32, device=dev)
+        self.wts_all = torch.zeros(picks, dtype=torch.float32, device=dev)
+        self.q_all = torch.zeros((self.n_tok, self.dim), dtype=torch.int8, device=dev)
+        self.d_all = torch.zeros((self.n_tok, self.dim // 32), dtype=torch.float32, device=dev)
+        self.rows = torch.zeros(self.T * self.k, dtype=torch.int32, device=dev)
+        self.send = torch.zeros((world, self.T * self.k, self.dim), dtype=torch.float32, device=dev)
+        self.recv = torch.zeros_like(self.send)
+        self.kernels_per_step = 10  # route, round, unpack, tables, order, gate_up, round, down, scatter, combine
+
+    def step(self, x_home, logits_home, out_home, copy=0, stream=0):
+        """x_home [T, dim], logits_home [T, n_exp], out_home [T, dim]: this rank's tokens; all on this GPU"""
+        lib, s, base = self.lib, self.seg, self.segment.data_ptr()
+        T, k = self.T, self.k
+        ok = lib.q4x_route(logits_home.data_ptr(), T, self.n_exp, k, base + s.ids, base + s.weights, self.rows.data_ptr(), stream)
+        ok = ok and lib.q8_round(x_home.data_ptr(), T, self.dim, self.dim, base + s.q, base + s.d, stream)
+        if not ok:
+            raise RuntimeError("libosmos_b200 refused a call (route / round)")
+        self.dist.all_gather_into_tensor(self.gathered, self.segment)
+        L = self.local
+        ok = lib.ep_unpack(self.gathered.data_ptr(), self.world, T, k, self.dim, self.ids_all.data_ptr(),
+                           self.wts_all.data_ptr(), self.q_all.data_ptr(), self.d_all.data_ptr(), stream)
+        ok = ok and lib.lane_ffn_rows(L.layers[copy % len(L.layers)], L.scratch, self.q_all.data_ptr(), self.d_all.data_ptr(),
+                                      self.ids_all.data_ptr(), self.wts_all.data_ptr(), self.n_tok, self.e0, self.e1, stream)
+        ok = ok and lib.ep_scatter_rows(L.scratch.ye, L.scratch.tab.row_of, self.n_tok * k, k, T, self.dim,
+                                        self.send.data_ptr(), stream)
+        if not ok:
+            raise RuntimeError("libosmos_b200 refused a call (unpack / experts / scatter)")
+        self.dist.all_to_all_single(self.recv, self.send)
+        if not lib.ep_combine(self.recv.data_ptr(), base + s.ids, T, k, self.n_exp // self.world, self.dim, None,
+                              out_home.data_ptr(), stream):
+            raise RuntimeError("libosmos_b200 refused a call (combine)")
+
+
+def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks):
+    import torch.distributed as dist
+
+    import libosmos_b200
+    lib = libosmos_b200.load()
+    cfg = workloads.MOE_IQ3
+    n_tok, dim, k = cfg["n_tok"], cfg["dim"], cfg["k"]
+    host = workloads.moe_layer_host(cfg)
+    copies = 4
+    layer = EpMoeLane(lib, cfg, dev, rank, world, copies=copies, host_tensors=host)
+    t0, t1 = home_tokens(rank, world, n_tok)
+    n_inputs = 8
+    hx, hl = zip(*[workloads.moe_inputs_host(cfg, s) for s in range(n_inputs)])
+    dx = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).to(dev) for a in hx]
+    dl = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).to(dev) for a in hl]
+    px = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).pin_memory() for a in hx]
+    pl = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).pin_memory() for a in hl]
+    out = torch.empty((t1 - t0, dim), dtype=torch.float32, device=dev)
+    pout = torch.empty((t1 - t0, dim), dtype=torch.float32).pin_memory()
+    sx, sl = torch.empty_like(dx[0]), torch.empty_like(dl[0])
+    stream = torch.cuda.current_stream().cuda_stream
+
+    # parity first: this rank's first home token against the CPU oracle (same bits as on one GPU)
+    from oracle.oracle import Oracle
+    layer.step(dx[0], dl[0], out, 0, stream)
+    torch.cuda.synchronize()
+    ids, wts = workloads.softmax_topk(hl[0][t0:t0 + 1], k)
+    got_ids = layer.segment[layer.seg.ids:layer.seg.ids + 4 * k].view(torch.int32).cpu().numpy()
+    want = runner.moe_oracle(Oracle(), cfg, host, hx[0][t0:t0 + 1], got_ids.reshape(1, k),
+                             layer.segment[layer.seg.weights:layer.seg.weights + 4 * k].view(torch.float32).cpu().numpy().reshape(1, k))
+    ok = np.array_equal(got_ids, ids.reshape(-1)) and np.array_equal(out.cpu().numpy()[:1].view(np.uint32), want.view(np.uint32))
+    flag = torch.tensor([0 if ok else 1], device=dev)
+    dist.all_reduce(flag)
+    if int(flag.item()):
+        raise SystemExit("bench: the expert-parallel layer's output differs from the CPU oracle's bits on some rank")
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(steps):
+            fn(s)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def resident(s):
+        layer.step(dx[s % n_inputs], dl[s % n_inputs], out, s % copies, stream)
+
+    def end_to_end(s):
+        sx.copy_(px[s % n_inputs], non_blocking=True)
+        sl.copy_(pl[s % n_inputs], non_blocking=True)
+        layer.step(sx, sl, out, s % copies, stream)
+        pout.copy_(out, non_blocking=True)
+
+    for s in range(args.warmup):
+        resident(s), end_to_end(s)
+    with ClockSampler(dev.index) as clocks:
+        t_res = timed(resident, args.steps)
+        t_e2e = timed(end_to_end, args.steps)
+    if rank == 0:
+        per = workloads.moe_expert_bytes(cfg)
+        line = {"metric": metric, "value": n_tok * args.steps / t_res, "unit": unit, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
+                "config": {"workload": cfg["name"], "tokens": n_tok, "experts": cfg["n_exp"], "top_k": k, "hidden": dim,
+                           "expert_ff": cfg["ff"], "format": cfg["type"],
+                           "parallelism": "ep%d: experts in contiguous ranges, tokens by home rank, all-gather dispatch, all-to-all combine" % world,
+                           "cold_cache": "%d copies of each rank's %d MB of expert weights cycled" % (copies, sum(per) * cfg["n_exp"] // world // 1000000)},
+                "e2e": {"value": n_tok * args.steps / t_e2e, "unit": unit,
+                        "h2d_bytes_per_step": int((px[0].numel() + pl[0].numel()) * 4 * world),
+                        "d2h_bytes_per_step": int(pout.numel() * 4 * world)},
+                "gpu_launches": layer.kernels_per_step * args.steps * world,
+                "roofline": None, "cpu_baseline": None, "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()

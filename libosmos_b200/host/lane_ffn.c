@@ -5,6 +5,7 @@
  */
 #include <stddef.h>
 
+#include "osmos_b200/ep.h"
 #include "osmos_b200/lane.h"
 #include "osmos_b200/ops.h"
 #include "osmos_b200/q8.h"
@@ -88,4 +89,21 @@ bool lane_ffn(const LaneLayer *l, const LaneScratch *s, const float *x, const in
   ok = ok && (add ? ops_gather_sum_add(out, s->ye, t->order, l->k, n_tok, D, add, stream)
                   : ops_gather_sum(out, s->ye, t->order, l->k, n_tok, D, stream));
   return ok;
+}
+
+/* the layer's experts [e0, e1) on tokens that are already int8 (another rank may have rounded them): tables for that
+   range, gate / up / activation, the activations to int8, down - rows into s->ye, none of the final sum */
+bool lane_ffn_rows(const LaneLayer *l, const LaneScratch *s, const int8_t *q, const float *d, const int32_t *ids,
+                   const float *weights, uint32_t n_tok, uint32_t e0, uint32_t e1, void *stream)
+{
+  if (!layer_ok(l) || !s || !q || !d || !ids || !weights || !n_tok || n_tok > s->max_tok || e0 >= e1 || e1 > l->n_exp)
+    return false;
+  const uint32_t picks = n_tok * l->k, D = l->dim, FF = l->ff;
+  const LaneTables *t = &s->tab;
+  return lane_tables(ids, picks, l->k, l->n_exp, e0, e1, &l->experts, t, stream) &&
+         q8_gate_up(l->type_gu, t->w[0], t->w[1], t->cnt, t->xrow, t->tok, t->pair, t->max_entries, LANE_MAX_TOKENS, FF,
+                    D, q, d, weights, l->lim, s->hh, FF, stream) &&
+         q8_round(s->hh, picks, FF, FF, s->hq, s->hqd, stream) &&
+         q8_group_tok(l->type_down, t->w[2], t->cnt, t->xrow, NULL, t->max_entries, LANE_MAX_TOKENS, D, FF, s->hq,
+                      s->hqd, s->ye, D, stream);
 }

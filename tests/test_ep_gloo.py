@@ -1,0 +1,94 @@
+"""The expert-parallel step's protocol on CPU: 2 `gloo` ranks run the same sharding, slot and ordering rules as
+libosmos_b200/ep.py (its index functions are the ones used here) with the CPU oracle standing in for the kernels, and
+the combined result must equal the single-rank layer bit for bit."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from libosmos_b200 import ep, runner, synth, workloads
+
+CFG = dict(workloads.MOE_IQ3, name="ep_test", n_exp=8, k=3, n_tok=6, dim=256, ff=256)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, result_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle.oracle import Oracle
+    orc = Oracle()
+    cfg = CFG
+    k, dim, ff, n_tok = cfg["k"], cfg["dim"], cfg["ff"], cfg["n_tok"]
+    host = workloads.moe_layer_host(cfg)
+    per = workloads.moe_expert_bytes(cfg)
+    x, logits = workloads.moe_inputs_host(cfg, 0)
+    t0, t1 = ep.home_tokens(rank, world, n_tok)
+    T = t1 - t0
+    e0, e1 = ep.expert_range(rank, world, cfg["n_exp"])
+    # 1. route and round the home tokens
+    ids_home, wts_home = workloads.softmax_topk(logits[t0:t1], k)
+    q_home, d_home = orc.q8_round(x[t0:t1])
+    # 2. dispatch: all-gather
+    def gather(a):
+        parts = [torch.zeros_like(torch.from_numpy(a)) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(a)))
+        return np.concatenate([p.numpy() for p in parts])
+    ids, wts, q, d = gather(ids_home), gather(wts_home), gather(q_home), gather(d_home)
+    # 3. the rows of the owned experts, sorted by (expert, pick)
+    flat = ids.reshape(-1)
+    order = [i for i in np.argsort(flat, kind="stable") if e0 <= flat[i] < e1]
+    tid = synth.TYPE_ID[cfg["type"]]
+    send = np.zeros((world * T * k, dim), np.float32)
+    for i in order:
+        e, t = int(flat[i]), i // k
+        parts = [host[m][e * per[m]:(e + 1) * per[m]] for m in range(3)]
+        g = orc.q8_rows(tid, parts[0], ff, dim, q[t:t + 1], d[t:t + 1])
+        u = orc.q8_rows(tid, parts[1], ff, dim, q[t:t + 1], d[t:t + 1])
+        h = orc.swiglu_lane(g, u, cfg["lim"], wts.reshape(-1)[i:i + 1])
+        hq, hd = orc.q8_round(h)
+        y = orc.q8_rows(tid, parts[2], dim, ff, hq, hd)
+        send[ep.send_slot(i, k, T)] = y[0]  # 4. scatter
+    # 5. combine exchange: block h of every rank's send buffer goes to rank h
+    blocks = [torch.zeros(world * T * k, dim) for _ in range(world)]
+    dist.all_gather(blocks, torch.from_numpy(send))
+    recv = np.stack([b.numpy().reshape(world, T * k, dim)[rank] for b in blocks])  # recv[o] = rank o's rows for my tokens
+    # 6. each home token's rows in ascending expert id
+    out = np.zeros((T, dim), np.float32)
+    for t in range(T):
+        acc = np.zeros(dim, np.float32)
+        for j in np.argsort(ids_home[t], kind="stable"):
+            owner = int(ids_home[t, j]) // (cfg["n_exp"] // world)
+            acc = (acc + recv[owner, t * k + j]).astype(np.float32)
+        out[t] = acc
+    outs = [torch.zeros(T, dim) for _ in range(world)]
+    dist.all_gather(outs, torch.from_numpy(out))
+    if rank == 0:
+        full = np.concatenate([o.numpy() for o in outs])
+        all_ids, all_wts = workloads.softmax_topk(logits, k)
+        want = runner.moe_oracle(orc, cfg, host, x, all_ids, all_wts)
+        np.save(result_path, np.array([np.array_equal(full.view(np.uint32), want.view(np.uint32))]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_equal_one_rank(tmp_path):
+    result = str(tmp_path / "ok.npy")
+    mp.spawn(_rank_main, args=(2, _free_port(), result), nprocs=2, join=True)
+    assert bool(np.load(result)[0])
+
+
+def test_sharding_rules():
+    assert ep.expert_range(3, 8, 512) == (192, 256) and ep.home_tokens(7, 8, 64) == (56, 64)
+    # every pick lands in a distinct slot, grouped by its token's home
+    k, T, world = 10, 8, 8
+    slots = [ep.send_slot(i, k, T) for i in range(world * T * k)]
+    assert sorted(slots) == list(range(world * T * k))
+    assert all(ep.send_slot(i, k, T) // (T * k) == (i // k) // T for i in range(world * T * k))
