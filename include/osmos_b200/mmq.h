@@ -56,6 +56,15 @@ bool mmq_group(uint32_t type, const void *const *w, const int32_t *cnt, uint32_t
                const uint32_t *yoff, uint32_t ys, void *stream);
 bool mmq_known(uint32_t type);
 
+/* ---- extensions: no counterpart in the reference -------------------------------------------------------------- */
+/* mmq_group runs one of two kernels that give the same bits: a tensor-core one (tcgen05 kind::i8, for rows in 128s
+   and 16-byte aligned activations) and a generic one for every other shape. mmq_set_tensor(0) forces the generic kernel
+   (the tests compare the two); the default is 1. */
+void mmq_set_tensor(int on);
+/* the tensor-core kernel's waits are bounded: reads and clears the current device's record (synchronizes the device);
+   bit 0: a wait ran out and the launch's outputs are not valid */
+uint32_t mmq_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -76,6 +76,8 @@ SIGNATURES = {
     "mmq_known": (B, [U32]),
     "mmq_x8_rows": (B, [P, U32, P, U32, U32, P, P, P, P]),
     "mmq_group": (B, [U32, P, P, U32, U32, U32, U32, P, P, P, P, P, P, U32, P]),
+    "mmq_set_tensor": (None, [C.c_int]),
+    "mmq_status": (U32, []),
     # moe.h
     "q4x_route": (B, [P, U32, U32, U32, P, P, P, P]),
     "q4x_expert_bounds": (None, [U32, U32, C.POINTER(Q4xExpertBounds)]),

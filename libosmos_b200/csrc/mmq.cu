@@ -4,6 +4,7 @@
 // weight block and the matching activation tile in shared memory and takes the group dots with dp4a. The order of
 // the F32 operations is the contract's, so it and any tensor-core kernel for the same entry point give the same bits.
 #include "common.cuh"
+#include "mmq_tc_api.h"
 #include "osmos_b200/mmq.h"
 
 namespace osmos {
@@ -100,10 +101,15 @@ __global__ void __launch_bounds__(kThreads) q4k_kernel(const uint8_t* const* __r
   }
 }
 
+bool g_use_tensor = true;
+
 }  // namespace
 }  // namespace osmos
 
 using namespace osmos;
+
+extern "C" void mmq_set_tensor(int on) { g_use_tensor = on != 0; }
+extern "C" uint32_t mmq_status(void) { return mmq_tc::read_status(); }
 
 extern "C" bool mmq_known(uint32_t type) { return type == QTYPE_Q4_K; }
 
@@ -121,6 +127,8 @@ extern "C" bool mmq_group(uint32_t type, const void* const* w, const int32_t* cn
   if (!mmq_known(type) || !w || !cnt || !x8 || !dx || !sx || !soff || !y || !yoff || !n_mat || !max_cnt || !rows ||
       rows % kTile || !cols || cols % kBlockValues || ys < rows)
     return false;
+  if (g_use_tensor)
+    if (const int st = mmq_tc::try_launch(w, cnt, n_mat, max_cnt, rows, cols, x8, dx, sx, soff, y, yoff, ys, stream)) return st > 0;
   const dim3 grid(rows / kTile, n_mat, (max_cnt + kTile - 1) / kTile);
   q4k_kernel<<<grid, kThreads, 0, stream_of(stream)>>>((const uint8_t* const*) w, cnt, cols, x8, dx, sx, soff, y, yoff, ys);
   return launched();

@@ -1,0 +1,428 @@
+// Q4_K x int8 on the 5th-generation tensor cores (include/osmos_b200/mmq.h): tcgen05.mma kind::i8 with the int32
+// group dots in tensor memory, drained group by group into the contract's F32 epilogue.
+//
+// A block computes 128 weight rows x 128 tokens of one matrix. Twenty warps, three roles:
+//   producers (3 warps)   per 256-value step: unpack the rows' Q4_K nibbles of that superblock into int8 operand
+//                         tiles (one 128 x 32 tile a 32-value group, K-major core matrices of 8 rows x 16 bytes),
+//                         copy the tokens' int8 codes into the same layout, and their dx / -sx beside them; then a
+//                         proxy fence and an arrive on the stage's "full" mbarrier. Three stages deep.
+//   issuer (1 warp)       per group one tcgen05.mma M128 N128 K32 that OVERWRITES one of four 128-column accumulators
+//                         in tensor memory, then tcgen05.commit onto that accumulator's "full" mbarrier; after a
+//                         step's eight groups a commit onto the stage's "empty" mbarrier (which also counts the sixteen
+//                         epilogue warps: they still read the stage's dx / -sx after the tensor core is done).
+//   epilogue (16 warps)   thread = one weight row (its TMEM lane) x 32 tokens: tcgen05.ld the group's int32 dots,
+//                         acc = fmaf((d sc) dx, (float) I, acc); acc = fmaf(dmin m, -sx, acc) in the contract's order.
+//                         The K loop runs partition by partition (256-value blocks p, p + 4, ...), and at the end of
+//                         partition p the thread's sums go to y (p = 0) or are added to it (p > 0): the reference's
+//                         "partitions added in order", with y as the running sum.
+// The integer dots are exact whatever computes them, and every F32 operation is the generic kernel's (mmq.cu), so
+// the two give the same bits. Why the epilogue and not the tensor pipe sets the pace: see DESIGN.md.
+//
+// Every mbarrier wait is bounded (%globaltimer); a wait that runs out raises the status word, every role falls
+// through to the common exit and tensor memory is released.
+#include "common.cuh"
+#include "mmq_tc_api.h"
+#include "osmos_b200/mmq.h"
+
+namespace osmos {
+namespace mmq_tc {
+namespace {
+
+constexpr int kM = 128, kN = 128;              // rows and tokens a block
+constexpr int kEpiWarps = 16, kProdWarps = 3;
+constexpr int kCols = kN / (kEpiWarps / 4);    // tokens an epilogue thread: 32
+constexpr int kIssuerWarp = kEpiWarps;         // warp 16
+constexpr int kFirstProdWarp = kEpiWarps + 1;  // warps 17 .. 19
+constexpr int kProdThreads = kProdWarps * kWarp;
+constexpr int kThreads = (kEpiWarps + 1 + kProdWarps) * kWarp;
+constexpr int kStages = 3, kAccs = 4;
+constexpr int kGroups = 8, kBlockBytes = 144, kBlockValues = 256;
+constexpr int kTileBytes = kM * MMQ_GROUP;     // one operand tile: 128 rows x 32 int8 = 4 KB
+constexpr int kStageBytes = 2 * kGroups * kTileBytes + 2 * kGroups * kN * 4;  // A, B, dx, -sx: 72 KB
+constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
+
+__device__ uint32_t g_status;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t a = smem_addr(bar);
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; spin++) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (spin == 0) t0 = global_ns();
+    else if (global_ns() - t0 > kWaitLimitNs) return false;
+  }
+}
+
+// shared-memory matrix descriptor of one operand tile: K-major, no swizzle, core matrices of 8 rows x 16 bytes;
+// the next 16 bytes of K are 128 bytes on (leading offset), the next 8 rows 256 bytes on (stride offset)
+__device__ __forceinline__ uint64_t tile_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) (lbo_bytes >> 4) << 16 | (uint64_t) (sbo_bytes >> 4) << 32 |
+         (uint64_t) 1 << 46;
+}
+// instruction descriptor: D int32, A unsigned 8-bit (the nibbles), B signed 8-bit, both K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t) (kN >> 3) << 17) | ((uint32_t) (kM >> 4) << 24);
+
+struct Args {
+  const uint8_t* const* wt;
+  const int32_t* cnt;
+  const int8_t* x8;
+  const float *dx, *sx;
+  const uint32_t *soff, *yoff;
+  float* y;
+  uint32_t cols, ys;
+  uint32_t* status;
+};
+
+struct Shared {
+  uint64_t full[kStages], empty[kStages], acc_full[kAccs], acc_empty[kAccs];
+  uint32_t tmem_base;
+  int fail;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ Shared sh;
+  const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
+  const uint32_t m = blockIdx.y, n_tok = (uint32_t) a.cnt[m], row0 = blockIdx.x * kM, c0 = blockIdx.z * kN;
+  if (c0 >= n_tok) return;  // the whole block, before anything is allocated
+  const uint32_t n_valid = n_tok - c0 < (uint32_t) kN ? n_tok - c0 : (uint32_t) kN;
+  const uint32_t n_valid16 = (n_valid + 15u) & ~15u;
+  const uint32_t nb = a.cols / kBlockValues, groups = a.cols / MMQ_GROUP;
+  const uint64_t row_bytes = (uint64_t) nb * kBlockBytes;
+  const uint8_t* w = a.wt[m] + (uint64_t) row0 * row_bytes;
+  const uint32_t s0 = a.soff[m] + c0;  // the block's first slot: a multiple of 16
+
+  if (tid == 0) {
+    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdWarps * kWarp), bar_init(&sh.empty[i], 1 + kEpiWarps);
+    for (int i = 0; i < kAccs; i++) bar_init(&sh.acc_full[i], 1), bar_init(&sh.acc_empty[i], kEpiWarps);
+    sh.fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == (uint32_t) kIssuerWarp) {  // all of tensor memory: four accumulators of 128 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sh.tmem_base)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sh.tmem_base;
+
+  // the K loop's order: partition p's blocks p, p + 4, ... for p = 0 .. 3; step `it` of it
+  auto block_of = [&](uint32_t it, uint32_t& p, bool& last_of_p) -> uint32_t {
+    uint32_t left = it;
+    for (p = 0; p < 4; p++) {
+      const uint32_t in_p = nb > p ? (nb - p + 3) / 4 : 0;
+      if (left < in_p) {
+        last_of_p = left + 1 == in_p;
+        return p + 4 * left;
+      }
+      left -= in_p;
+    }
+    last_of_p = true;
+    return 0;
+  };
+
+  if (warp >= (uint32_t) kFirstProdWarp) {
+    // ================= producers =================
+    const uint32_t pt = tid - kFirstProdWarp * kWarp;  // 0 .. kProdThreads - 1
+    for (uint32_t it = 0; it < nb; it++) {
+      const uint32_t stage = it % kStages, use = it / kStages;
+      if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
+        sh.fail = 1;
+        break;
+      }
+      uint32_t p;
+      bool last;
+      const uint32_t b = block_of(it, p, last);
+      uint8_t* st = smem + stage * kStageBytes;
+      uint8_t* sa = st;                              // A tiles, a group 4 KB
+      uint8_t* sb = st + kGroups * kTileBytes;       // B tiles
+      float* sdx = (float*) (st + 2 * kGroups * kTileBytes);
+      float* snsx = sdx + kGroups * kN;
+      // A: a task = (row, pair of groups): 32 bytes of nibbles -> the low nibbles' group and the high nibbles' group
+      for (uint32_t base = 0; base < 4u * kM; base += 2u * kProdThreads) {
+        uint4 r0[2], r1[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const uint32_t task = base + pt + kProdThreads * u, row = task >> 2, gp = task & 3u;
+          if (task < 4u * kM) {
+            const uint4* src = (const uint4*) (w + row * row_bytes + (uint64_t) b * kBlockBytes + 16 + gp * 32);
+            r0[u] = __ldg(src), r1[u] = __ldg(src + 1);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const uint32_t task = base + pt + kProdThreads * u, row = task >> 2, gp = task & 3u;
+          if (task < 4u * kM) {
+            const uint32_t at = (row >> 3) * 256 + (row & 7u) * 16;
+            uint8_t* lo = sa + (2 * gp) * kTileBytes + at;
+            uint8_t* hi = sa + (2 * gp + 1) * kTileBytes + at;
+            const uint32_t k = 0x0F0F0F0Fu;
+            *(uint4*) lo = make_uint4(r0[u].x & k, r0[u].y & k, r0[u].z & k, r0[u].w & k);
+            *(uint4*) (lo + 128) = make_uint4(r1[u].x & k, r1[u].y & k, r1[u].z & k, r1[u].w & k);
+            *(uint4*) hi = make_uint4((r0[u].x >> 4) & k, (r0[u].y >> 4) & k, (r0[u].z >> 4) & k, (r0[u].w >> 4) & k);
+            *(uint4*) (hi + 128) = make_uint4((r1[u].x >> 4) & k, (r1[u].y >> 4) & k, (r1[u].z >> 4) & k, (r1[u].w >> 4) & k);
+          }
+        }
+      }
+      // B: 16-byte pieces of the tokens' codes, in the order they lie in x8 (slot tile, group, slot, half); eight of a
+      // thread's loads go out before their stores
+      {
+        const uint32_t limit = (n_valid16 / 16) * kGroups * 32;
+        for (uint32_t base = 0; base < limit; base += 8u * kProdThreads) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; u++) {
+            const uint32_t i = base + pt + kProdThreads * u;
+            const uint32_t half = i & 1u, sl = (i >> 1) & 15u, g = (i >> 5) & 7u, tile = i >> 8;
+            if (i < limit)
+              v[u] = __ldg((const uint4*) (a.x8 + mmq_x8_at(s0 + tile * 16 + sl, (b * kGroups + g) * MMQ_GROUP + half * 16, a.cols)));
+          }
+#pragma unroll
+          for (int u = 0; u < 8; u++) {
+            const uint32_t i = base + pt + kProdThreads * u;
+            const uint32_t half = i & 1u, sl = (i >> 1) & 15u, g = (i >> 5) & 7u, n = (i >> 8) * 16 + sl;
+            if (i < limit) *(uint4*) (sb + g * kTileBytes + (n >> 3) * 256 + half * 128 + (n & 7u) * 16) = v[u];
+          }
+        }
+      }
+      // dx and -sx of the step's 8 groups x tokens
+      {
+        const uint32_t limit = n_valid16 * kGroups;
+        for (uint32_t base = 0; base < limit; base += 4u * kProdThreads) {
+          float vd[4], vs[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const uint32_t i = base + pt + kProdThreads * u;
+            const uint32_t sl = i & 15u, g = (i >> 4) & 7u, n = (i >> 7) * 16 + sl;
+            if (i < limit) {
+              const uint64_t at = mmq_dx_at(s0 + n, b * kGroups + g, groups);
+              vd[u] = __ldg(a.dx + at), vs[u] = __ldg(a.sx + at);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const uint32_t i = base + pt + kProdThreads * u;
+            const uint32_t sl = i & 15u, g = (i >> 4) & 7u, n = (i >> 7) * 16 + sl;
+            if (i < limit) sdx[g * kN + n] = vd[u], snsx[g * kN + n] = -vs[u];
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes before the tensor core's reads
+      bar_arrive(&sh.full[stage]);
+    }
+  } else if (warp == (uint32_t) kIssuerWarp) {
+    // ================= issuer =================
+    uint32_t acc_it = 0;
+    for (uint32_t it = 0; it < nb && !sh.fail; it++) {
+      const uint32_t stage = it % kStages, use = it / kStages;
+      if (!bar_wait(&sh.full[stage], use & 1u)) {
+        sh.fail = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t sa = smem_addr(smem + stage * kStageBytes), sb = sa + kGroups * kTileBytes;
+      for (uint32_t g = 0; g < (uint32_t) kGroups; g++, acc_it++) {
+        const uint32_t acc = acc_it % kAccs, ause = acc_it / kAccs;
+        if (ause > 0 && !bar_wait(&sh.acc_empty[acc], (ause - 1) & 1u)) {
+          sh.fail = 1;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (lane == 0) {
+          const uint64_t da = tile_desc(sa + g * kTileBytes, 128, 256), db = tile_desc(sb + g * kTileBytes, 128, 256);
+          asm volatile(
+              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(
+                  tmem + acc * kN),
+              "l"(da), "l"(db), "r"(kIdesc), "r"(0)
+              : "memory");
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           smem_addr(&sh.acc_full[acc]))
+                       : "memory");
+        }
+        __syncwarp();
+      }
+      if (sh.fail) break;
+      if (lane == 0)  // the stage's operands are free once these eight have run
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         smem_addr(&sh.empty[stage]))
+                     : "memory");
+      __syncwarp();
+    }
+  } else {
+    // ================= epilogue =================
+    const uint32_t row = 32u * (warp & 3u) + lane;  // this thread's weight row of the tile = its TMEM lane
+    const uint32_t col0 = (uint32_t) kCols * (warp >> 2);  // its 32 tokens
+    const uint32_t lane_base = tmem + ((32u * (warp & 3u)) << 16);
+    const uint8_t* wrow = w + row * row_bytes;
+    float* y = a.y + a.yoff[m] + (uint64_t) c0 * a.ys + row0 + row;
+    float acc[kCols];
+#pragma unroll
+    for (int i = 0; i < kCols; i++) acc[i] = 0.0f;
+    uint32_t acc_it = 0;
+    bool dead = false;
+    uint4 hd_next;
+    {
+      uint32_t p0;
+      bool l0;
+      hd_next = __ldg((const uint4*) (wrow + (uint64_t) block_of(0, p0, l0) * kBlockBytes));
+    }
+    for (uint32_t it = 0; it < nb && !dead; it++) {
+      const uint32_t stage = it % kStages;
+      uint32_t p;
+      bool last;
+      block_of(it, p, last);
+      // the row's scales of this block: d sc and dmin m for its 8 groups (the next block's header is already on its way)
+      const uint4 hd = hd_next;
+      if (it + 1 < nb) {
+        uint32_t p1;
+        bool l1;
+        hd_next = __ldg((const uint4*) (wrow + (uint64_t) block_of(it + 1, p1, l1) * kBlockBytes));
+      }
+      const float d = half_value(hd.x & 0xFFFFu), dmin = half_value(hd.x >> 16);
+      const uint32_t sw[3] = {hd.y, hd.z, hd.w};
+      auto sbyte = [&](int i) -> uint32_t { return (sw[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+      const float* sdx = (const float*) (smem + stage * kStageBytes + 2 * kGroups * kTileBytes);
+      const float* snsx = sdx + kGroups * kN;
+#pragma unroll
+      for (uint32_t g = 0; g < (uint32_t) kGroups; g++, acc_it++) {
+        uint32_t sc, mn;
+        if (g < 4) sc = sbyte(g) & 0x3F, mn = sbyte(g + 4) & 0x3F;
+        else sc = (sbyte(g + 4) & 0x0F) | ((sbyte(g - 4) >> 6) << 4), mn = (sbyte(g + 4) >> 4) | ((sbyte(g) >> 6) << 4);
+        const float dsc = mul_rn(d, (float) sc), dm = mul_rn(dmin, (float) mn);
+        const uint32_t ab = acc_it % kAccs, ause = acc_it / kAccs;
+        if (!bar_wait(&sh.acc_full[ab], ause & 1u)) {
+          sh.fail = 1, dead = true;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t r[32];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(lane_base + ab * kN + col0)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // the accumulator is read: hand it back before the arithmetic
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) bar_arrive(&sh.acc_empty[ab]);
+        const float4* dx4 = (const float4*) (sdx + g * kN + col0);
+        const float4* ns4 = (const float4*) (snsx + g * kN + col0);
+#pragma unroll
+        for (int q = 0; q < kCols / 4; q++) {
+          const float4 dv = dx4[q], nv = ns4[q];
+          const float dxs[4] = {dv.x, dv.y, dv.z, dv.w}, nss[4] = {nv.x, nv.y, nv.z, nv.w};
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            // (float) I without the conversion pipe: |I| <= 32 * 15 * 127 < 2^22, so 1.5 * 2^23 + I is exact
+            const float f = __fsub_rn(__int_as_float((int) r[4 * q + e] + 0x4B400000), 12582912.0f);
+            const float v = mul_rn(dsc, dxs[e]);
+            float s2 = acc[4 * q + e];
+            s2 = __fmaf_rn(v, f, s2);
+            s2 = __fmaf_rn(dm, nss[e], s2);
+            acc[4 * q + e] = s2;
+          }
+        }
+      }
+      if (dead) break;
+      __syncwarp();
+      if (lane == 0) bar_arrive(&sh.empty[stage]);  // done with the stage's dx / -sx
+      if (last) {  // partition p is complete: y = its sum (p = 0) or y + its sum
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+          const uint32_t t = col0 + i;
+          if (t < n_valid) {
+            float* at = y + (uint64_t) t * a.ys;
+            *at = p == 0 ? acc[i] : __fadd_rn(*at, acc[i]);
+          }
+          acc[i] = 0.0f;
+        }
+      }
+    }
+    if (!dead && nb < 4) {  // the partitions without a block still take part in the sum: + 0 (it turns a -0 into +0)
+#pragma unroll 1
+      for (int i = 0; i < kCols; i++) {
+        const uint32_t t = col0 + i;
+        if (t < n_valid) {
+          float* at = y + (uint64_t) t * a.ys;
+          *at = __fadd_rn(*at, 0.0f);
+        }
+      }
+    }
+  }
+  // ================= common exit =================
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == (uint32_t) kIssuerWarp) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+  }
+  if (tid == 0 && sh.fail) atomicOr(a.status, 1u);
+}
+
+uint32_t* status_word() {
+  static uint32_t* at[64];
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return nullptr;
+  if (!at[d]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status) != cudaSuccess) return nullptr;
+    at[d] = (uint32_t*) p;
+  }
+  return at[d];
+}
+
+}  // namespace
+
+int try_launch(const void* const* w, const int32_t* cnt, uint32_t n_mat, uint32_t max_cnt, uint32_t rows, uint32_t cols,
+               const int8_t* x8, const float* dx, const float* sx, const uint32_t* soff, float* y, const uint32_t* yoff,
+               uint32_t ys, void* stream) {
+  if (rows % kM || cols % kBlockValues || (((uintptr_t) x8 | (uintptr_t) dx | (uintptr_t) sx) & 15u)) return 0;
+  uint32_t* status = status_word();
+  if (!status) return 0;
+  static bool sized = false;
+  const int smem_bytes = kStages * kStageBytes;
+  if (!sized) {
+    if (cudaFuncSetAttribute(q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return 0;
+    sized = true;
+  }
+  Args a{(const uint8_t* const*) w, cnt, x8, dx, sx, soff, yoff, y, cols, ys, status};
+  const dim3 grid(rows / kM, n_mat, (max_cnt + kN - 1) / kN);
+  q4k_tc_kernel<<<grid, kThreads, smem_bytes, (cudaStream_t) stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+uint32_t read_status() {
+  uint32_t* at = status_word();
+  if (!at) return 0x80000000u;
+  uint32_t v = 0, zero = 0;
+  if (cudaMemcpy(&v, at, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return 0x80000000u;
+  cudaMemcpy(at, &zero, sizeof zero, cudaMemcpyHostToDevice);
+  return v;
+}
+
+}  // namespace mmq_tc
+}  // namespace osmos

@@ -31,3 +31,13 @@ def dev():
     assert torch.cuda.is_available(), "a gpu-marked test ran without a CUDA device"
     torch.cuda.init()
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _release_device_tensors():
+    yield
+    try:
+        import helpers
+        helpers.release()
+    except ImportError:
+        pass

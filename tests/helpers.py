@@ -3,9 +3,19 @@ import numpy as np
 import torch
 
 
+_KEEP = []  # every tensor to_dev made in the running test: a raw pointer handed to the C ABI must outlive the call
+
+
 def to_dev(a, dev):
-    """numpy array -> device tensor of the same bytes (int8 / uint8 / int32 / float32)."""
-    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    """numpy array -> device tensor of the same bytes (int8 / uint8 / int32 / float32). The tensor is kept alive until
+    the test ends (conftest clears the list), so `ptr(to_dev(...))` inside an argument list is safe."""
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    _KEEP.append(t)
+    return t
+
+
+def release():
+    _KEEP.clear()
 
 
 def ptr(t):

@@ -67,6 +67,44 @@ def test_mmq_group_bits(lib, dev, oracle, cnts):
     assert same_bits(got, want)
 
 
+@pytest.mark.parametrize("rows,cols,cnts", [(128, 256, [16]), (128, 512, [1, 37]), (256, 768, [130, 5, 64]),
+                                            (128, 2048, [300]), (384, 1024, [129])])
+def test_mmq_tensor_kernel_matches_generic_and_oracle(lib, dev, oracle, rows, cols, cnts):
+    """rows in 128s: mmq_group runs the tcgen05 kernel; its bits are the generic kernel's and the oracle's (K shorter
+    than four partitions, several token tiles, several matrices with their own slots and outputs, canary rows)"""
+    ys = rows + 8
+    rng = synth.rng_for(41, rows, cols, len(cnts))
+    mats = [synth.random_tensor(12, rows, cols, rng) for _ in cnts]
+    x = rng.standard_normal((max(cnts), cols)).astype(np.float32)
+    soff, idx = [], []
+    for c in cnts:
+        soff.append(len(idx))
+        idx += list(range(c)) + [-1] * ((16 - c % 16) % 16)
+    w8, wdx, wsx = oracle.mmq_x8_rows(x, np.array(idx, np.int32), cols)
+    yoff, total = [], 0
+    for c in cnts:
+        yoff.append(total * ys)
+        total += c
+    pool = to_dev(np.concatenate(mats), dev)
+    table = pointer_table(pool, [m * mats[0].size for m in range(len(mats))], dev)
+    args = (ptr(to_dev(np.array(cnts, np.int32), dev)), len(cnts), max(cnts), rows, cols, ptr(to_dev(w8, dev)),
+            ptr(to_dev(wdx, dev)), ptr(to_dev(wsx, dev)), ptr(to_dev(np.array(soff, np.uint32).view(np.int32), dev)))
+    yo = ptr(to_dev(np.array(yoff, np.uint32).view(np.int32), dev))
+    want = np.full((total + 4, ys), -11.0, np.float32)
+    r0 = 0
+    for m, c in enumerate(cnts):
+        want[r0:r0 + c, :rows] = oracle.mmq_rows(mats[m], rows, cols, w8, wdx, wsx, soff[m], c)
+        r0 += c
+    for tensor in (1, 0):
+        lib.mmq_set_tensor(tensor)
+        y = torch.full((total + 4, ys), -11.0, dtype=torch.float32, device=dev)
+        assert lib.mmq_group(12, ptr(table), *args, ptr(y), yo, ys, None)
+        sync()
+        assert same_bits(y.cpu().numpy(), want), "tensor-core kernel" if tensor else "generic kernel"
+    lib.mmq_set_tensor(1)
+    assert lib.mmq_status() == 0
+
+
 # ---- routing and tables -------------------------------------------------------------------------------------------
 def _softmax_topk(logits, k):
     l = logits.astype(np.float64)
