@@ -4,7 +4,7 @@
 // A block computes 128 weight rows x 128 tokens of one matrix. Twenty warps, three roles:
 //   producers (3 warps)   per 256-value step: unpack the rows' Q4_K nibbles of that superblock into int8 operand
 //                         tiles (one 128 x 32 tile a 32-value group, K-major core matrices of 8 rows x 16 bytes),
-//                         copy the tokens' int8 codes into the same layout, and their dx / -sx beside them; then a
+//                         copy the tokens' int8 codes into the same layout (cp.async), and their dx / sx beside them; then a
 //                         proxy fence and an arrive on the stage's "full" mbarrier. Three stages deep.
 //   issuer (1 warp)       per group one tcgen05.mma M128 N128 K32 that OVERWRITES one of four 128-column accumulators
 //                         in tensor memory, then tcgen05.commit onto that accumulator's "full" mbarrier; after a
@@ -38,7 +38,7 @@ constexpr int kThreads = (kEpiWarps + 1 + kProdWarps) * kWarp;
 constexpr int kStages = 3, kAccs = 4;
 constexpr int kGroups = 8, kBlockBytes = 144, kBlockValues = 256;
 constexpr int kTileBytes = kM * MMQ_GROUP;     // one operand tile: 128 rows x 32 int8 = 4 KB
-constexpr int kStageBytes = 2 * kGroups * kTileBytes + 2 * kGroups * kN * 4;  // A, B, dx, -sx: 72 KB
+constexpr int kStageBytes = 2 * kGroups * kTileBytes + 2 * kGroups * kN * 4;  // A, B, dx, sx: 72 KB
 constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
 
 __device__ uint32_t g_status;
@@ -69,6 +69,11 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
     if (spin == 0) t0 = global_ns();
     else if (global_ns() - t0 > kWaitLimitNs) return false;
   }
+}
+
+// 16 bytes global -> shared, asynchronously (both 16-byte aligned)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
 }
 
 // shared-memory matrix descriptor of one operand tile: K-major, no swizzle, core matrices of 8 rows x 16 bytes;
@@ -156,12 +161,30 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
       uint8_t* sa = st;                              // A tiles, a group 4 KB
       uint8_t* sb = st + kGroups * kTileBytes;       // B tiles
       float* sdx = (float*) (st + 2 * kGroups * kTileBytes);
-      float* snsx = sdx + kGroups * kN;
-      // A: a task = (row, pair of groups): 32 bytes of nibbles -> the low nibbles' group and the high nibbles' group
-      for (uint32_t base = 0; base < 4u * kM; base += 2u * kProdThreads) {
-        uint4 r0[2], r1[2];
+      float* ssx = sdx + kGroups * kN;
+      // B, dx, sx: asynchronous 16-byte copies straight to their places (no registers, all in flight at once): the
+      // tokens' codes in the order they lie in x8 (slot tile, group, slot, half), 16 floats of dx / sx a (tile, group)
+      {
+        const uint32_t limit = (n_valid16 / 16) * kGroups * 32;
+        for (uint32_t i = pt; i < limit; i += kProdThreads) {
+          const uint32_t half = i & 1u, sl = (i >> 1) & 15u, g = (i >> 5) & 7u, tile = i >> 8, n = tile * 16 + sl;
+          cp_async16(sb + g * kTileBytes + (n >> 3) * 256 + half * 128 + (n & 7u) * 16,
+                     a.x8 + mmq_x8_at(s0 + n, (b * kGroups + g) * MMQ_GROUP + half * 16, a.cols));
+        }
+        const uint32_t limit2 = (n_valid16 / 16) * kGroups * 4 * 2;  // (tile, group, quarter, dx | sx)
+        for (uint32_t i = pt; i < limit2; i += kProdThreads) {
+          const uint32_t which = i & 1u, qt = (i >> 1) & 3u, g = (i >> 3) & 7u, tile = i >> 6;
+          const uint64_t at = mmq_dx_at(s0 + tile * 16 + qt * 4, b * kGroups + g, groups);
+          cp_async16((which ? ssx : sdx) + g * kN + tile * 16 + qt * 4, (which ? a.sx : a.dx) + at);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
+      // A: a task = (row, pair of groups): 32 bytes of nibbles -> the low nibbles' group and the high nibbles' group;
+      // three tasks' loads go out before their stores
+      for (uint32_t base = 0; base < 4u * kM; base += 3u * kProdThreads) {
+        uint4 r0[3], r1[3];
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
+        for (int u = 0; u < 3; u++) {
           const uint32_t task = base + pt + kProdThreads * u, row = task >> 2, gp = task & 3u;
           if (task < 4u * kM) {
             const uint4* src = (const uint4*) (w + row * row_bytes + (uint64_t) b * kBlockBytes + 16 + gp * 32);
@@ -169,7 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
           }
         }
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
+        for (int u = 0; u < 3; u++) {
           const uint32_t task = base + pt + kProdThreads * u, row = task >> 2, gp = task & 3u;
           if (task < 4u * kM) {
             const uint32_t at = (row >> 3) * 256 + (row & 7u) * 16;
@@ -183,49 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
           }
         }
       }
-      // B: 16-byte pieces of the tokens' codes, in the order they lie in x8 (slot tile, group, slot, half); eight of a
-      // thread's loads go out before their stores
-      {
-        const uint32_t limit = (n_valid16 / 16) * kGroups * 32;
-        for (uint32_t base = 0; base < limit; base += 8u * kProdThreads) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; u++) {
-            const uint32_t i = base + pt + kProdThreads * u;
-            const uint32_t half = i & 1u, sl = (i >> 1) & 15u, g = (i >> 5) & 7u, tile = i >> 8;
-            if (i < limit)
-              v[u] = __ldg((const uint4*) (a.x8 + mmq_x8_at(s0 + tile * 16 + sl, (b * kGroups + g) * MMQ_GROUP + half * 16, a.cols)));
-          }
-#pragma unroll
-          for (int u = 0; u < 8; u++) {
-            const uint32_t i = base + pt + kProdThreads * u;
-            const uint32_t half = i & 1u, sl = (i >> 1) & 15u, g = (i >> 5) & 7u, n = (i >> 8) * 16 + sl;
-            if (i < limit) *(uint4*) (sb + g * kTileBytes + (n >> 3) * 256 + half * 128 + (n & 7u) * 16) = v[u];
-          }
-        }
-      }
-      // dx and -sx of the step's 8 groups x tokens
-      {
-        const uint32_t limit = n_valid16 * kGroups;
-        for (uint32_t base = 0; base < limit; base += 4u * kProdThreads) {
-          float vd[4], vs[4];
-#pragma unroll
-          for (int u = 0; u < 4; u++) {
-            const uint32_t i = base + pt + kProdThreads * u;
-            const uint32_t sl = i & 15u, g = (i >> 4) & 7u, n = (i >> 7) * 16 + sl;
-            if (i < limit) {
-              const uint64_t at = mmq_dx_at(s0 + n, b * kGroups + g, groups);
-              vd[u] = __ldg(a.dx + at), vs[u] = __ldg(a.sx + at);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; u++) {
-            const uint32_t i = base + pt + kProdThreads * u;
-            const uint32_t sl = i & 15u, g = (i >> 4) & 7u, n = (i >> 7) * 16 + sl;
-            if (i < limit) sdx[g * kN + n] = vd[u], snsx[g * kN + n] = -vs[u];
-          }
-        }
-      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes before the tensor core's reads
       bar_arrive(&sh.full[stage]);
     }
@@ -301,13 +282,13 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
       const uint32_t sw[3] = {hd.y, hd.z, hd.w};
       auto sbyte = [&](int i) -> uint32_t { return (sw[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
       const float* sdx = (const float*) (smem + stage * kStageBytes + 2 * kGroups * kTileBytes);
-      const float* snsx = sdx + kGroups * kN;
+      const float* ssx = sdx + kGroups * kN;
 #pragma unroll
       for (uint32_t g = 0; g < (uint32_t) kGroups; g++, acc_it++) {
         uint32_t sc, mn;
         if (g < 4) sc = sbyte(g) & 0x3F, mn = sbyte(g + 4) & 0x3F;
         else sc = (sbyte(g + 4) & 0x0F) | ((sbyte(g - 4) >> 6) << 4), mn = (sbyte(g + 4) >> 4) | ((sbyte(g) >> 6) << 4);
-        const float dsc = mul_rn(d, (float) sc), dm = mul_rn(dmin, (float) mn);
+        const float dsc = mul_rn(d, (float) sc), ndm = -mul_rn(dmin, (float) mn);  // (dmin m) (-sx) = (-(dmin m)) sx
         const uint32_t ab = acc_it % kAccs, ause = acc_it / kAccs;
         if (!bar_wait(&sh.acc_full[ab], ause & 1u)) {
           sh.fail = 1, dead = true;
@@ -330,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
         __syncwarp();
         if (lane == 0) bar_arrive(&sh.acc_empty[ab]);
         const float4* dx4 = (const float4*) (sdx + g * kN + col0);
-        const float4* ns4 = (const float4*) (snsx + g * kN + col0);
+        const float4* ns4 = (const float4*) (ssx + g * kN + col0);
 #pragma unroll
         for (int q = 0; q < kCols / 4; q++) {
           const float4 dv = dx4[q], nv = ns4[q];
@@ -342,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
             const float v = mul_rn(dsc, dxs[e]);
             float s2 = acc[4 * q + e];
             s2 = __fmaf_rn(v, f, s2);
-            s2 = __fmaf_rn(dm, nss[e], s2);
+            s2 = __fmaf_rn(ndm, nss[e], s2);
             acc[4 * q + e] = s2;
           }
         }
