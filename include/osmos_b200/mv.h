@@ -47,6 +47,14 @@ bool mv_group_tok(uint32_t type, const void *const *w, const int32_t *cnt, const
 bool mv_strided(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t x_stride,
                 uint32_t n_tok, float *y, uint32_t y_stride, void *stream);
 
+/* Not in the reference. mv_run / mv_strided have two kernels that give the same bits: one that stages whole rows
+   through shared memory with bulk copies (16-byte aligned w and x, rows whose bytes are a multiple of 16, x and a
+   ring of rows fitting shared memory) and a generic one for every other shape. mv_set_staged(0) forces the generic
+   kernel (the tests compare the two). mv_status() reads and clears the staged kernel's record on the current device
+   (it synchronizes): bit 0 = a bulk copy never landed within the kernel's wait limit, whose rows were not written. */
+void mv_set_staged(int on);
+uint32_t mv_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -70,6 +70,8 @@ SIGNATURES = {
     "q8_group_tok": (B, [U32, P, P, P, P, U32, U32, U32, U32, P, P, P, U32, P]),
     "q8_gate_up": (B, [U32, P, P, P, P, P, P, U32, U32, U32, U32, P, P, P, F32, P, U32, P]),
     "q8_run": (B, [U32, P, U32, U32, P, P, U32, P, U32, P]),
+    "mv_set_staged": (None, [C.c_int]),
+    "mv_status": (U32, []),
     "q8_set_staged": (None, [C.c_int]),
     "q8_status": (U32, []),
     # mmq.h

@@ -26,9 +26,12 @@
 #include <type_traits>
 
 #include "decode.cuh"
+#include "tma.cuh"
 
 namespace osmos {
 namespace staged {
+
+using namespace tma;
 
 constexpr int kComputeWarps = 16, kComputeThreads = kComputeWarps * kWarp;
 constexpr int kThreads = kComputeThreads + kWarp, kWarps = kThreads / kWarp;  // + the warp that issues the copies
@@ -36,7 +39,6 @@ constexpr int kNT = 2;             // tokens an item carries
 constexpr int kMaxStages = 6;
 constexpr int kXPiece = 256 + 16;  // a token's 256 int8 of one superblock, padded so neighbours fall in other banks
 constexpr uint32_t kListMax = 1024;  // entries whose live (entry, token pair) list a block builds at a time
-constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;  // no copy of a tile takes anywhere near 0.2 s
 
 // ---- the type's superblock: 256 values ---------------------------------------------------------------------------
 template <uint32_t T> struct Super {
@@ -54,32 +56,6 @@ template <uint32_t T> struct Rep {  // copies of the 64-bit grid / whether the 3
   static constexpr int mask = GridOf<T>::signs ? 8 : 0;  // copies of the (masks, +1 words) table, 16 bytes an entry
   static constexpr int bytes = GridOf<T>::words64 * g64 * 8 + GridOf<T>::words32 * g32 * 4 + 128 * mask * 16;
 };
-
-// shared-memory accesses by 32-bit shared-space address: the hot loops never form a generic pointer
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ int4 lds128(uint32_t a) {
-  int4 v;
-  asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float ldsf(uint32_t a) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void sts128(uint32_t a, float x, float y, float z, float w) {
-  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
-}
 
 // the tables' addresses with this thread's copy already chosen (lane l reads copy l, l mod 16, ...: its own banks)
 template <uint32_t T> struct RepLuts {
@@ -130,41 +106,6 @@ template <uint32_t T> __device__ inline RepLuts<T> build_luts(uint8_t* smem) {
     l.mask = smem_addr(d) + (lane & 7) * 16;
   }
   return l;
-}
-
-// ---- mbarrier and bulk copy ----------------------------------------------------------------------------------------
-__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void bar_expect(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// true when the phase of `parity` has completed; gives up kWaitLimitNs after its first look
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t a = smem_addr(bar);
-  uint64_t t0 = 0;
-  for (uint32_t spin = 0;; spin++) {
-    uint32_t done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(a), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if (spin == 0) t0 = global_ns();
-    else if (global_ns() - t0 > kWaitLimitNs) return false;
-  }
-}
-// global -> this block's shared memory, completion counted on `bar`; both addresses 16-byte aligned, bytes a multiple of 16
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
-               "l"(src), "r"(bytes), "r"(smem_addr(bar))
-               : "memory");
 }
 
 // ---- arguments and shared-memory plan ---------------------------------------------------------------------------------
@@ -247,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_staged_kernel(const Args a) 
 
   if (tid == 0) {
     for (uint32_t st = 0; st < S; st++) bar_init(&full[st], 1), bar_init(&empty[st], kComputeWarps);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    bar_init_fence();
     s_fail = 0;
   }
   const RepLuts<T> luts = build_luts<T>(smem + p.lut);

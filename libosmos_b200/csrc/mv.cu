@@ -4,6 +4,7 @@
 // loads, so x traffic from L1 is 1 / kRows of the naive count.
 #include "decode.cuh"
 #include "dispatch.cuh"
+#include "mv_staged_api.h"
 #include "osmos_b200/mv.h"
 
 namespace osmos {
@@ -116,11 +117,17 @@ bool by_tokens(const MvArgs& a, uint32_t n, uint32_t grid_y, cudaStream_t s) {
 
 template <uint32_t T> bool shape_ok(uint32_t cols) { return cols && cols % Fmt<T>::values == 0 && cols % kChunk == 0; }
 
+bool g_use_staged = true;  // mv_set_staged: the tests run both kernels and compare their bits
+
 template <uint32_t T>
 bool strided(const void* w, uint32_t rows, uint32_t cols, const float* x, uint32_t xs, uint32_t n_tok, float* y,
              uint32_t ys, cudaStream_t s) {
   if (!shape_ok<T>(cols) || !rows || !n_tok) return false;
   if ((n_tok > 1 && (xs < cols || ys < rows)) || xs % kChunk) return false;
+  if (g_use_staged && n_tok <= MV_MAX_TOKENS) {  // the staged kernel when it takes the shape: the same bits
+    const mvs::Request r{w, x, y, rows, cols, xs, ys, n_tok};
+    if (const int st = mvs::try_launch(T, r, s)) return st > 0;
+  }
   MvArgs a{};
   a.w = (const uint8_t*) w, a.x = x, a.y = y, a.rows = rows, a.cols = cols, a.xs = xs, a.ys = ys, a.n_tok = n_tok;
   if (n_tok > MV_MAX_TOKENS) return launch<T, 8, kDense>(a, (n_tok + 7) / 8, s);  // a prompt's: tiles of 8 tokens
@@ -159,6 +166,9 @@ extern "C" bool mv_strided(uint32_t type, const void* w, uint32_t rows, uint32_t
   OSMOS_SWITCH_QUANT(type, CASE, return false)
 #undef CASE
 }
+
+extern "C" void mv_set_staged(int on) { g_use_staged = on != 0; }
+extern "C" uint32_t mv_status(void) { return mvs::read_status(); }
 
 extern "C" bool mv_run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const float* x, uint32_t n_tok,
                        float* y, void* stream) {

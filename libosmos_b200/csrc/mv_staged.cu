@@ -1,0 +1,367 @@
+// The dense F32-activation matvec (mv_run / mv_strided, 1 .. 8 tokens) with the weights staged through shared memory
+// by bulk copies. Same sums as mv.cu's kernel: of a row, lane l runs one fmaf chain over chunks l, l + 32, ... (8
+// values a chunk, in value order), then the xor tree 16, 8, 4, 2, 1.
+//
+// A block takes a contiguous run of rows and keeps the tokens' x in shared memory. Its 16 warps do not meet again
+// after that: each warp owns a ring of slots (a slot: RW whole rows, one bulk copy, one mbarrier), issues its own
+// copies, and refills a slot as soon as it has summed it - so there is no block-wide barrier in the loop, and a
+// block holds 16 x (slots - 1) copies in flight. Plain 32-value blocks are decoded with one byte-permute and one fmaf a
+// value (see scaled4); the other types go through the same decode8 as the generic kernel.
+//
+// Two kernels. One token and rows of at most 2048 values (the decode step's usual shape): every lane keeps its 64
+// values of x in registers for the whole launch, so shared memory serves only the weights (mv_regx_kernel). Else x
+// lies in shared memory and is read a chunk at a time (mv_staged_kernel; one or two tokens - more go to the generic
+// kernel, which then reads x less often a row).
+#include "mv_staged_api.h"
+
+#include "decode.cuh"
+#include "dispatch.cuh"
+#include "tma.cuh"
+
+namespace osmos {
+namespace mvs {
+namespace {
+
+using namespace tma;
+
+constexpr int kWarps = 16, kThreads = kWarps * kWarp;
+constexpr int kMaxSlots = 4;
+// dynamic shared memory a block may ask for: 227 KB less the type's static tables and the barriers
+template <uint32_t T> constexpr uint32_t kSmemLimit = 226u * 1024u - (uint32_t) ((grid_smem_bytes<T>() + 1023) / 1024 * 1024);
+
+__device__ uint32_t g_status;
+
+struct Args {
+  const uint8_t* w;
+  const float* x;
+  float* y;
+  uint32_t rows, cols, xs, ys, n_tok;
+  uint32_t slots, slot_bytes, ring_off, units;
+  uint32_t* status;
+};
+
+// Small integers reach F32 without a conversion instruction: byte j of `bytes` (a value n < 256) placed in bits 8 .. 15
+// of 0x47000000 is the F32 32768 + n, one byte-permute.
+template <int J> __device__ __forceinline__ float biased(uint32_t bytes) {
+  return __uint_as_float(__byte_perm(bytes, 0x47000000u, 0x7404 | (J << 4)));
+}
+
+// d (n - bias) for the four bytes n of `bytes`, each one fmaf: d (32768 + n) - d (32768 + bias), where the second
+// product `c` is exact (d has 11 significant bits, 32768 + bias at most 13) and so is the difference - the same bits
+// as mul_rn(d, (float) (n - bias)), whose product is exact too.
+__device__ __forceinline__ void scaled4(uint32_t bytes, float d, float c, float* v) {
+  v[0] = __fmaf_rn(d, biased<0>(bytes), c), v[1] = __fmaf_rn(d, biased<1>(bytes), c);
+  v[2] = __fmaf_rn(d, biased<2>(bytes), c), v[3] = __fmaf_rn(d, biased<3>(bytes), c);
+}
+
+// ---- what of a row a lane reads, worked out once: the lane's chunk of each 256-value stretch is at a fixed place ----
+template <uint32_t T> struct LanePlan {  // any type: decode8 through a pointer
+  static constexpr uint32_t kStretch = Fmt<T>::bytes * (256 / Fmt<T>::values);
+  uint32_t lane;
+  __device__ __forceinline__ explicit LanePlan(uint32_t l) : lane(l) {}
+  __device__ __forceinline__ void values(uint32_t, const uint8_t* row_ptr, uint32_t it, float* v, const Grids& g) const {
+    const uint32_t c = lane + 32u * it;
+    decode8<T>(row_ptr + (c / Fmt<T>::chunks) * Fmt<T>::bytes, (int) (c % Fmt<T>::chunks), v, g);
+  }
+};
+template <> struct LanePlan<QTYPE_Q4_0> {
+  static constexpr uint32_t kStretch = 144;
+  uint32_t al, sh, doff, s4;
+  __device__ __forceinline__ explicit LanePlan(uint32_t l) {
+    const uint32_t b = l >> 2, k = l & 3u, a0 = b * 18u + 2u + 8u * (k & 1u);
+    al = a0 & ~3u, sh = (a0 & 2u) * 8u, doff = b * 18u, s4 = 4u * (k >> 1);
+  }
+  __device__ __forceinline__ void values(uint32_t row, const uint8_t*, uint32_t it, float* v, const Grids&) const {
+    const uint32_t base = row + it * kStretch;
+    const uint32_t r0 = lds32(base + al), r1 = lds32(base + al + 4), r2 = lds32(base + al + 8);
+    const float d = half_value(lds16(base + doff)), neg = mul_rn(d, -32776.0f);
+    scaled4((__funnelshift_r(r0, r1, sh) >> s4) & 0x0F0F0F0Fu, d, neg, v);
+    scaled4((__funnelshift_r(r1, r2, sh) >> s4) & 0x0F0F0F0Fu, d, neg, v + 4);
+  }
+};
+template <> struct LanePlan<QTYPE_Q8_0> {
+  static constexpr uint32_t kStretch = 272;
+  uint32_t al, sh, doff;
+  __device__ __forceinline__ explicit LanePlan(uint32_t l) {
+    const uint32_t b = l >> 2, k = l & 3u, a0 = b * 34u + 2u + 8u * k;
+    al = a0 & ~3u, sh = (a0 & 2u) * 8u, doff = b * 34u;
+  }
+  __device__ __forceinline__ void values(uint32_t row, const uint8_t*, uint32_t it, float* v, const Grids&) const {
+    const uint32_t base = row + it * kStretch;
+    const uint32_t r0 = lds32(base + al), r1 = lds32(base + al + 4), r2 = lds32(base + al + 8);
+    const float d = half_value(lds16(base + doff)), neg = mul_rn(d, -32896.0f);
+    scaled4(__funnelshift_r(r0, r1, sh) ^ 0x80808080u, d, neg, v);
+    scaled4(__funnelshift_r(r1, r2, sh) ^ 0x80808080u, d, neg, v + 4);
+  }
+};
+
+template <uint32_t T, int NT, int RW>
+__global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
+  __shared__ __align__(8) uint64_t full[kWarps][kMaxSlots];
+  const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
+  const uint32_t row_bytes = a.cols / Fmt<T>::values * Fmt<T>::bytes;
+  const uint32_t S = a.slots;
+  uint8_t* ring = smem + a.ring_off + warp * S * a.slot_bytes;
+
+  // this block's units (RW rows each), dealt to its warps round-robin
+  const uint32_t u_lo = (uint32_t) ((uint64_t) blockIdx.x * a.units / gridDim.x);
+  const uint32_t u_hi = (uint32_t) ((uint64_t) (blockIdx.x + 1) * a.units / gridDim.x);
+  auto issue = [&](uint32_t i) {  // one lane: the warp's i-th unit into slot i % S
+    const uint32_t u = u_lo + warp + i * kWarps;
+    if (u >= u_hi) return;
+    const uint32_t r0 = u * RW, nrows = a.rows - r0 < (uint32_t) RW ? a.rows - r0 : (uint32_t) RW;
+    const uint32_t slot = i % S, bytes = nrows * row_bytes;
+    bar_expect(&full[warp][slot], bytes);
+    bulk_load(ring + slot * a.slot_bytes, a.w + (uint64_t) r0 * row_bytes, bytes, &full[warp][slot]);
+  };
+  if (lane == 0) {
+    for (uint32_t s = 0; s < S; s++) bar_init(&full[warp][s], 1);
+    bar_init_fence();
+    for (uint32_t i = 0; i < S; i++) issue(i);
+  }
+
+  // the tokens' x (the live ones) and the codebooks, while the first copies fly
+  const uint32_t live = a.n_tok < (uint32_t) NT ? a.n_tok : (uint32_t) NT;
+  {
+    const uint32_t per = a.cols / 4;
+    for (uint32_t i = tid; i < live * per; i += kThreads) {
+      const uint32_t t = i / per, j = i - t * per;
+      ((float4*) smem)[i] = __ldg((const float4*) (a.x + (uint64_t) t * a.xs) + j);
+    }
+  }
+  const Grids g = stage_grids<T>(tables);
+  __syncthreads();
+
+  uint32_t xa[NT];  // a token slot past the live ones repeats the last live token: summed, never stored
+#pragma unroll
+  for (int t = 0; t < NT; t++) xa[t] = smem_addr(smem) + ((uint32_t) t < live ? (uint32_t) t : live - 1) * a.cols * 4u;
+  const uint32_t ni = a.cols / 256;
+  const LanePlan<T> plan(lane);
+
+  for (uint32_t i = 0;; i++) {
+    const uint32_t u = u_lo + warp + i * kWarps;
+    if (u >= u_hi) break;
+    const uint32_t slot = i % S;
+    if (!bar_wait(&full[warp][slot], (i / S) & 1u)) {  // a copy never landed: report it and leave
+      if (lane == 0) atomicOr(a.status, 1u);
+      break;
+    }
+    const uint8_t* sp = ring + slot * a.slot_bytes;
+    const uint32_t sa = smem_addr(sp);
+    float acc[RW][NT];
+#pragma unroll
+    for (int q = 0; q < RW; q++)
+#pragma unroll
+      for (int t = 0; t < NT; t++) acc[q][t] = 0.0f;
+    for (uint32_t it = 0; it < ni; it++) {
+      float v[RW][kChunk];
+#pragma unroll
+      for (int q = 0; q < RW; q++) plan.values(sa + q * row_bytes, sp + q * row_bytes, it, v[q], g);
+#pragma unroll
+      for (int t = 0; t < NT; t++) {
+        const uint32_t xc = xa[t] + (lane + 32u * it) * 32u;
+        const float4 lo = lds128f(xc), hi = lds128f(xc + 16u);
+#pragma unroll
+        for (int q = 0; q < RW; q++) {
+          float s = acc[q][t];
+          s = __fmaf_rn(v[q][0], lo.x, s), s = __fmaf_rn(v[q][1], lo.y, s);
+          s = __fmaf_rn(v[q][2], lo.z, s), s = __fmaf_rn(v[q][3], lo.w, s);
+          s = __fmaf_rn(v[q][4], hi.x, s), s = __fmaf_rn(v[q][5], hi.y, s);
+          s = __fmaf_rn(v[q][6], hi.z, s), s = __fmaf_rn(v[q][7], hi.w, s);
+          acc[q][t] = s;
+        }
+      }
+    }
+    // every lane is done reading the slot: refill it
+    __syncwarp();
+    if (lane == 0) {
+      fence_async_smem();
+      issue(i + S);
+    }
+    const uint32_t r0 = u * RW;
+#pragma unroll
+    for (int q = 0; q < RW; q++)
+#pragma unroll
+      for (int t = 0; t < NT; t++) {
+        const float s = xor_tree<kWarp>(acc[q][t]);
+        if (lane == 0 && r0 + q < a.rows && (uint32_t) t < live) a.y[(uint64_t) t * a.ys + r0 + q] = s;
+      }
+  }
+}
+
+constexpr int kRegIters = 8;  // 256-value stretches of a row whose x a lane can keep in registers (cols <= 2048)
+
+template <uint32_t T, int RW>
+__global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
+  __shared__ __align__(8) uint64_t full[kWarps][kMaxSlots];
+  const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
+  const uint32_t row_bytes = a.cols / Fmt<T>::values * Fmt<T>::bytes;
+  const uint32_t S = a.slots, ni = a.cols / 256;
+  uint8_t* ring = smem + warp * S * a.slot_bytes;
+
+  const uint32_t u_lo = (uint32_t) ((uint64_t) blockIdx.x * a.units / gridDim.x);
+  const uint32_t u_hi = (uint32_t) ((uint64_t) (blockIdx.x + 1) * a.units / gridDim.x);
+  auto issue = [&](uint32_t i) {  // one lane: the warp's i-th unit into slot i % S
+    const uint32_t u = u_lo + warp + i * kWarps;
+    if (u >= u_hi) return;
+    const uint32_t r0 = u * RW, nrows = a.rows - r0 < (uint32_t) RW ? a.rows - r0 : (uint32_t) RW;
+    const uint32_t slot = i % S, bytes = nrows * row_bytes;
+    bar_expect(&full[warp][slot], bytes);
+    bulk_load(ring + slot * a.slot_bytes, a.w + (uint64_t) r0 * row_bytes, bytes, &full[warp][slot]);
+  };
+  if (lane == 0) {
+    for (uint32_t s = 0; s < S; s++) bar_init(&full[warp][s], 1);
+    bar_init_fence();
+    for (uint32_t i = 0; i < S; i++) issue(i);
+  }
+  // the lane's x: chunk lane + 32 it of every stretch
+  float xr[kRegIters][kChunk];
+#pragma unroll
+  for (int it = 0; it < kRegIters; it++) {
+    float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+    if ((uint32_t) it < ni) {
+      const float4* xp = (const float4*) (a.x + (lane + 32u * it) * kChunk);
+      lo = __ldg(xp), hi = __ldg(xp + 1);
+    }
+    xr[it][0] = lo.x, xr[it][1] = lo.y, xr[it][2] = lo.z, xr[it][3] = lo.w;
+    xr[it][4] = hi.x, xr[it][5] = hi.y, xr[it][6] = hi.z, xr[it][7] = hi.w;
+  }
+  const Grids g = stage_grids<T>(tables);
+  __syncthreads();  // the barriers' initialisation, seen by every lane that will wait on them
+  const LanePlan<T> plan(lane);
+
+  for (uint32_t i = 0;; i++) {
+    const uint32_t u = u_lo + warp + i * kWarps;
+    if (u >= u_hi) break;
+    const uint32_t slot = i % S;
+    if (!bar_wait(&full[warp][slot], (i / S) & 1u)) {  // a copy never landed: report it and leave
+      if (lane == 0) atomicOr(a.status, 1u);
+      break;
+    }
+    const uint8_t* sp = ring + slot * a.slot_bytes;
+    const uint32_t sa = smem_addr(sp);
+    float acc[RW];
+#pragma unroll
+    for (int q = 0; q < RW; q++) acc[q] = 0.0f;
+#pragma unroll
+    for (int it = 0; it < kRegIters; it++) {
+      if ((uint32_t) it < ni) {
+#pragma unroll
+        for (int q = 0; q < RW; q++) {
+          float v[kChunk];
+          plan.values(sa + q * row_bytes, sp + q * row_bytes, (uint32_t) it, v, g);
+          float s = acc[q];
+#pragma unroll
+          for (int j = 0; j < kChunk; j++) s = __fmaf_rn(v[j], xr[it][j], s);
+          acc[q] = s;
+        }
+      }
+    }
+    __syncwarp();  // every lane is done reading the slot: refill it
+    if (lane == 0) {
+      fence_async_smem();
+      issue(i + S);
+    }
+    const uint32_t r0 = u * RW;
+#pragma unroll
+    for (int q = 0; q < RW; q++) {
+      const float s = xor_tree<kWarp>(acc[q]);
+      if (lane == 0 && r0 + q < a.rows) a.y[r0 + q] = s;
+    }
+  }
+}
+
+struct Device {
+  int sms = 0;
+  uint32_t* status = nullptr;
+};
+
+const Device* device_info() {
+  static Device devs[64];
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return nullptr;
+  if (!devs[d].status) {
+    void* at = nullptr;
+    int sms = 0;
+    if (cudaGetSymbolAddress(&at, g_status) != cudaSuccess || !at) return nullptr;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || sms <= 0) return nullptr;
+    devs[d].sms = sms, devs[d].status = (uint32_t*) at;
+  }
+  return &devs[d];
+}
+
+template <uint32_t T, int NT, int RW, bool REGX>
+int launch(const Request& r, const Device* dev, uint32_t slots, cudaStream_t s) {
+  const uint32_t row_bytes = r.cols / Fmt<T>::values * Fmt<T>::bytes;
+  Args a{};
+  a.w = (const uint8_t*) r.w, a.x = r.x, a.y = r.y, a.rows = r.rows, a.cols = r.cols, a.xs = r.xs, a.ys = r.ys;
+  a.n_tok = r.n_tok, a.slots = slots, a.slot_bytes = RW * row_bytes;
+  a.ring_off = REGX ? 0u : (r.n_tok * r.cols * 4u + 127u) & ~127u;
+  a.units = (r.rows + RW - 1) / RW;
+  a.status = dev->status;
+  const uint32_t total = a.ring_off + kWarps * slots * a.slot_bytes + 16u;  // + the window's read past a last block
+  static bool sized = false;  // (one flag a template instance)
+  void (*kernel)(const Args);
+  if constexpr (REGX) kernel = mv_regx_kernel<T, RW>;
+  else kernel = mv_staged_kernel<T, NT, RW>;
+  if (!sized) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit<T>) != cudaSuccess) return 0;
+    sized = true;
+  }
+  uint32_t grid = (uint32_t) dev->sms;
+  if (a.units < grid) grid = a.units;
+  kernel<<<grid, kThreads, total, s>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+template <uint32_t T>
+int by_shape(const Request& r, cudaStream_t s) {
+  const Device* dev = device_info();
+  if (!dev) return 0;
+  const uint32_t row_bytes = r.cols / Fmt<T>::values * Fmt<T>::bytes;
+  if (r.cols % 256 || row_bytes % 16u) return 0;  // whole 256-value stretches; a row's bytes are a bulk copy's
+  if (r.n_tok > 2) return 0;  // the generic kernel reads x less often a row then
+  const bool regx = r.n_tok == 1 && r.cols <= 256u * kRegIters;
+  const uint32_t budget = kSmemLimit<T> - 16u;
+  const uint32_t x_bytes = regx ? 0u : (r.n_tok * r.cols * 4u + 127u) & ~127u;
+  if (x_bytes >= budget) return 0;
+  auto slots_for = [&](uint32_t rw) -> uint32_t {  // as deep a ring as fits
+    const uint32_t n = (budget - x_bytes) / (kWarps * rw * row_bytes);
+    return n > (uint32_t) kMaxSlots ? (uint32_t) kMaxSlots : n;
+  };
+  // two rows a unit (the decode of one overlaps the other's chain; with x in shared memory they share its loads)
+  // when the matrix has rows to spare and the ring still has three slots
+  const bool pair = (uint64_t) r.rows >= 8ull * kWarps * dev->sms && slots_for(2) >= 3;
+  const uint32_t slots = slots_for(pair ? 2 : 1);
+  if (slots < 2) return 0;
+  if (regx) return pair ? launch<T, 1, 2, true>(r, dev, slots, s) : launch<T, 1, 1, true>(r, dev, slots, s);
+  if (r.n_tok <= 1) return pair ? launch<T, 1, 2, false>(r, dev, slots, s) : launch<T, 1, 1, false>(r, dev, slots, s);
+  return pair ? launch<T, 2, 2, false>(r, dev, slots, s) : launch<T, 2, 1, false>(r, dev, slots, s);
+}
+
+}  // namespace
+
+int try_launch(uint32_t type, const Request& r, void* stream) {
+  if (!r.rows || !r.n_tok || r.n_tok > 8 || r.cols % 8) return 0;
+  if (((uintptr_t) r.w | (uintptr_t) r.x) & 15u) return 0;
+  if (r.n_tok > 1 && r.xs % 4) return 0;
+#define CASE(T) return by_shape<T>(r, (cudaStream_t) stream);
+  OSMOS_SWITCH_QUANT(type, CASE, return 0)
+#undef CASE
+}
+
+uint32_t read_status() {
+  const Device* dev = device_info();
+  if (!dev) return 0x80000000u;
+  uint32_t v = 0, zero = 0;
+  if (cudaMemcpy(&v, dev->status, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return 0x80000000u;
+  cudaMemcpy(dev->status, &zero, sizeof zero, cudaMemcpyHostToDevice);
+  return v;
+}
+
+}  // namespace mvs
+}  // namespace osmos

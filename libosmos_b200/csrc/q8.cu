@@ -6,6 +6,7 @@
 // kernel for the same entry points must (and is tested to) give the same bits.
 #include "decode.cuh"
 #include "dispatch.cuh"
+#include "lane_plain_api.h"
 #include "lane_staged_api.h"
 #include "osmos_b200/mv.h"
 #include "osmos_b200/q8.h"
@@ -174,7 +175,7 @@ int staged_first(uint32_t type, const LaneArgs& a, bool fused, bool dense, uint3
 using namespace osmos;
 
 extern "C" void q8_set_staged(int on) { g_use_staged = on != 0; }
-extern "C" uint32_t q8_status(void) { return staged::read_status(); }
+extern "C" uint32_t q8_status(void) { return staged::read_status() | plain::read_status(); }
 
 extern "C" bool q8_round(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d, void* stream) {
   return round_rows<false>(x, rows, cols, xs, q, d, stream_of(stream));
@@ -226,6 +227,10 @@ extern "C" bool q8_run(uint32_t type, const void* w, uint32_t rows, uint32_t col
   LaneArgs a{};
   a.w_dense = (const uint8_t*) w, a.q = q, a.d = d, a.out = y, a.rows = rows, a.cols = cols, a.out_stride = ys;
   a.n_tok = n_tok;
+  if (g_use_staged) {  // the plain blocks' own kernel (Q4_0, Q8_0; one or two tokens)
+    const plain::Request r{w, q, d, y, rows, cols, ys, n_tok};
+    if (const int st = plain::try_launch(type, r, stream)) return st > 0;
+  }
   if (t->paths & (QTYPE_PATH_Q8 | QTYPE_PATH_Q8_EXT))
     if (const int st = staged_first(type, a, false, true, 1, n_tok, stream)) return st > 0;
 #define CASE(T)                                                                                        \

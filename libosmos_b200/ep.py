@@ -56,8 +56,9 @@ class EpMoeLane:
         self.recv = torch.zeros_like(self.send)
         self.kernels_per_step = 10  # route, round, unpack, tables, order, gate_up, round, down, scatter, combine
 
-    def step(self, x_home, logits_home, out_home, copy=0, stream=0):
-        """x_home [T, dim], logits_home [T, n_exp], out_home [T, dim]: this rank's tokens; all on this GPU"""
+    def step(self, x_home, logits_home, out_home, copy=0, stream=0, events=None):
+        """x_home [T, dim], logits_home [T, n_exp], out_home [T, dim]: this rank's tokens; all on this GPU.
+        events: a pair of CUDA events recorded around this rank's expert kernels (tables, gate + up, round, down)"""
         lib, s, base = self.lib, self.seg, self.segment.data_ptr()
         T, k = self.T, self.k
         ok = lib.q4x_route(logits_home.data_ptr(), T, self.n_exp, k, base + s.ids, base + s.weights, self.rows.data_ptr(), stream)
@@ -68,8 +69,12 @@ class EpMoeLane:
         L = self.local
         ok = lib.ep_unpack(self.gathered.data_ptr(), self.world, T, k, self.dim, self.ids_all.data_ptr(),
                            self.wts_all.data_ptr(), self.q_all.data_ptr(), self.d_all.data_ptr(), stream)
+        if events:
+            events[0].record()
         ok = ok and lib.lane_ffn_rows(L.layers[copy % len(L.layers)], L.scratch, self.q_all.data_ptr(), self.d_all.data_ptr(),
                                       self.ids_all.data_ptr(), self.wts_all.data_ptr(), self.n_tok, self.e0, self.e1, stream)
+        if events:
+            events[1].record()
         ok = ok and lib.ep_scatter_rows(L.scratch.ye, L.scratch.tab.row_of, self.n_tok * k, k, T, self.dim,
                                         self.send.data_ptr(), stream)
         if not ok:
@@ -144,8 +149,22 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
     with ClockSampler(dev.index) as clocks:
         t_res = timed(resident, args.steps)
         t_e2e = timed(end_to_end, args.steps)
+        # rank 0's expert kernels alone (tables, gate + up + activation, round, down), by events inside the step
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for s, pair in enumerate(evs):
+            layer.step(dx[s % n_inputs], dl[s % n_inputs], out, s % copies, stream, events=pair)
+        torch.cuda.synchronize()
+        dist.barrier()
     if rank == 0:
         per = workloads.moe_expert_bytes(cfg)
+        k_ms = [a.elapsed_time(b) for a, b in evs]
+        e0, e1 = expert_range(rank, world, cfg["n_exp"])
+        alg = []
+        for s in range(args.steps):
+            picked = np.unique(workloads.softmax_topk(hl[s % n_inputs], k)[0])
+            alg.append(int(((picked >= e0) & (picked < e1)).sum()) * sum(per))
+        achieved = float(np.sum(alg) / (np.sum(k_ms) * 1e-3) / 1e9)
+        peak, peak_kind = measured_peaks()
         line = {"metric": metric, "value": n_tok * args.steps / t_res, "unit": unit, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
@@ -157,7 +176,11 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
                         "h2d_bytes_per_step": int((px[0].numel() + pl[0].numel()) * 4 * world),
                         "d2h_bytes_per_step": int(pout.numel() * 4 * world)},
                 "gpu_launches": layer.kernels_per_step * args.steps * world,
-                "roofline": None, "cpu_baseline": None, "clocks": clocks.summary()}
+                "roofline": {"bound": "hbm", "kernel": "rank 0's expert kernels of a step (lane tables, q8_gate_up, q8_round, q8_group_tok)",
+                             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                             "traffic": None, "algorithmic_bytes_per_launch": float(np.mean(alg)),
+                             "us_per_launch": float(np.mean(k_ms) * 1e3)},
+                "cpu_baseline": None, "clocks": clocks.summary()}
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()

@@ -228,6 +228,34 @@ def test_staged_dense_matches_generic_and_oracle(lib, dev, oracle, name, cols, r
     assert lib.q8_status() == 0
 
 
+PLAIN_SHAPES = [(2048, 99, 1), (2048, 77, 2), (4096, 45, 1), (4096, 33, 2), (8192, 19, 1), (1024, 20, 2), (768, 21, 1),
+                (512, 37891 + 16 * 148 * 2, 1)]
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q8_0"])
+@pytest.mark.parametrize("cols,rows,ntok", PLAIN_SHAPES)
+def test_plain_dense_kernel_same_bits(lib, dev, oracle, name, cols, rows, ntok):
+    """q8_run's kernel for one-scale blocks and one or two tokens (x in registers, rows through a ring a warp)
+    against the generic kernel and the oracle; the last shape is tall enough for slots of several row groups"""
+    tid = TYPES[name]
+    rng = synth.rng_for(27, tid, cols, rows)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    x = rng.standard_normal((ntok, cols)).astype(np.float32)
+    wq, wd = oracle.q8_round(x)
+    want = oracle.q8_rows(tid, w, rows, cols, wq, wd)
+    wdv, q, d = to_dev(w, dev), to_dev(wq, dev), to_dev(wd, dev)
+    lib.q8_status()
+    for staged in (1, 0):
+        lib.q8_set_staged(staged)
+        y = torch.full((ntok, rows + 2), -4.0, dtype=torch.float32, device=dev)
+        assert lib.q8_run(tid, ptr(wdv), rows, cols, ptr(q), ptr(d), ntok, ptr(y), rows + 2, None)
+        sync()
+        got = y.cpu().numpy()
+        assert same_bits(got[:, :rows], want) and (got[:, rows:] == -4.0).all(), "staged" if staged else "generic"
+    lib.q8_set_staged(1)
+    assert lib.q8_status() == 0
+
+
 def test_staged_refuses_misaligned_matrix_without_faulting(lib, dev, oracle):
     """a matrix table entry that is not 16-byte aligned: the staged kernel records it and leaves (no fault, the
     context stays usable); the generic kernel takes the same call"""

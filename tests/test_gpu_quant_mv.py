@@ -75,6 +75,47 @@ def test_mv_run_bits_and_batch_invariance(lib, dev, oracle, name):
         assert same_bits(y1.cpu().numpy()[0], want[t])
 
 
+@pytest.mark.parametrize("name", ALL)
+def test_mv_staged_kernel_same_bits(lib, dev, oracle, name):
+    """the kernel that stages rows through shared memory against the generic one and the oracle"""
+    tid = TYPES[name]
+    rows, cols = 203, 2048
+    w, x = _mv_case(tid, rows, cols, 8, 1)
+    want = oracle.mv_rows(tid, w, rows, cols, x)
+    wd, xd = to_dev(w, dev), to_dev(x, dev)
+    lib.mv_status()
+    try:
+        for n in (1, 2, 3, 8):
+            got = []
+            for staged in (1, 0):
+                lib.mv_set_staged(staged)
+                y = torch.full((n, rows), np.nan, dtype=torch.float32, device=dev)
+                assert lib.mv_run(tid, ptr(wd), rows, cols, ptr(xd), n, ptr(y), None)
+                sync()
+                got.append(y.cpu().numpy())
+            assert same_bits(got[0], got[1]) and same_bits(got[0], want[:n])
+    finally:
+        lib.mv_set_staged(1)
+    assert lib.mv_status() == 0
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q8_0", "IQ3_XXS", "Q4_K"])
+def test_mv_staged_row_pairs(lib, dev, oracle, name):
+    """a matrix tall enough that a warp sums two rows at once; an odd row count leaves the last unit one row"""
+    tid = TYPES[name]
+    rows, cols = 8 * 16 * 160 + 3, 512
+    w, x = _mv_case(tid, rows, cols, 2, 2)
+    want = oracle.mv_rows(tid, w, rows, cols, x)
+    wd, xd = to_dev(w, dev), to_dev(x, dev)
+    lib.mv_status()
+    for n in (1, 2):
+        y = torch.full((n, rows), np.nan, dtype=torch.float32, device=dev)
+        assert lib.mv_run(tid, ptr(wd), rows, cols, ptr(xd), n, ptr(y), None)
+        sync()
+        assert same_bits(y.cpu().numpy(), want[:n])
+    assert lib.mv_status() == 0
+
+
 @pytest.mark.parametrize("name", ["Q4_0", "IQ3_XXS", "Q4_K", "MXFP4"])
 def test_mv_strided_many_tokens(lib, dev, oracle, name):
     tid = TYPES[name]
