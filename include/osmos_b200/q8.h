@@ -59,10 +59,12 @@ bool q8_run(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const in
    written here as that f16's F32 value so q8_run reads it like q8_round's. Same layout and refusals as q8_round. */
 bool q8_0_round(const float *x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t *q, float *d, void *stream);
 
-/* The lane entry points run one of two kernels that give the same bits: a staged one (weight tiles brought into
-   shared memory by bulk copies, for whole 256-value blocks, rows in eights and 16-byte aligned matrices and
-   activations) and a generic one for every other shape. q8_set_staged(0) forces the generic kernel (the tests compare
-   the two); the default is 1. */
+/* The lane entry points choose among kernels that give the same bits. For whole 256-value blocks and 16-byte aligned
+   matrices and activations the weights come into shared memory by bulk copies: a kernel whose warps each own a ring
+   of rows and keep their activations in registers (the grouped entry points, the common types and shapes; q8_run for
+   the plain blocks), else one that stages tiles for the whole block of threads. Every other shape runs a generic
+   kernel. q8_set_staged(0) forces the generic kernel, 2 leaves out the warp-ring kernel (the tests compare all
+   three); the default is 1. */
 void q8_set_staged(int on);
 /* The staged kernel never waits without a bound and never faults on a misaligned matrix: it records the event and
    leaves. Reads and clears the current device's record (synchronizes the device): bit 0 a bulk copy did not land

@@ -82,23 +82,23 @@ template <uint32_t T> struct RepLuts {
   }
 };
 
-template <uint32_t T> __device__ inline RepLuts<T> build_luts(uint8_t* smem) {
+template <uint32_t T> __device__ inline RepLuts<T> build_luts(uint8_t* smem, int threads = kThreads) {
   const uint32_t lane = threadIdx.x % kWarp;
   RepLuts<T> l{0, 0, 0};
   if constexpr (Rep<T>::g64 > 0) {
     uint64_t* d = (uint64_t*) smem;
     const uint64_t* s = global_grid64<T>();
-    for (int i = threadIdx.x; i < GridOf<T>::words64 * Rep<T>::g64; i += kThreads) d[i] = s[i / Rep<T>::g64];
+    for (int i = threadIdx.x; i < GridOf<T>::words64 * Rep<T>::g64; i += threads) d[i] = s[i / Rep<T>::g64];
     l.g64 = smem_addr(d) + (lane & (Rep<T>::g64 - 1)) * 8, smem += GridOf<T>::words64 * Rep<T>::g64 * 8;
   }
   if constexpr (Rep<T>::g32 > 0) {
     uint32_t* d = (uint32_t*) smem;
-    for (int i = threadIdx.x; i < GridOf<T>::words32 * 32; i += kThreads) d[i] = osmos_grid_iq3xxs[i / 32];
+    for (int i = threadIdx.x; i < GridOf<T>::words32 * 32; i += threads) d[i] = osmos_grid_iq3xxs[i / 32];
     l.g32 = smem_addr(d) + lane * 4, smem += GridOf<T>::words32 * 32 * 4;
   }
   if constexpr (Rep<T>::mask > 0) {
     uint4* d = (uint4*) smem;
-    for (int i = threadIdx.x; i < 128 * 8; i += kThreads) {
+    for (int i = threadIdx.x; i < 128 * 8; i += threads) {
       const uint32_t sg = osmos_ksigns[i / 8];
       const uint32_t m0 = byte_mask4(sg), m1 = byte_mask4(sg >> 4);
       d[i] = make_uint4(m0, m1, m0 & 0x01010101u, m1 & 0x01010101u);

@@ -7,6 +7,7 @@
 #include "decode.cuh"
 #include "dispatch.cuh"
 #include "lane_plain_api.h"
+#include "lane_ring_api.h"
 #include "lane_staged_api.h"
 #include "osmos_b200/mv.h"
 #include "osmos_b200/q8.h"
@@ -156,7 +157,17 @@ bool round_rows(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_
   return launched();
 }
 
-bool g_use_staged = true;  // q8_set_staged: the tests run both kernels and compare their bits
+int g_use_staged = 1;  // q8_set_staged: the tests run every kernel and compare their bits (0 generic only, 2 no ring)
+
+// the grouped entry points' warp-ring kernel when it takes the type and shape: 1 queued, 0 not taken, -1 refused
+int ring_first(uint32_t type, const LaneArgs& a, bool fused, uint32_t n_entries, uint32_t max_cnt, void* stream) {
+  if (g_use_staged != 1) return 0;
+  ring::Request r{};
+  r.fused = fused, r.wg = (const void* const*) a.wg, r.wu = (const void* const*) a.wu, r.cnt = a.cnt, r.xrow = a.xrow;
+  r.xin = a.xin, r.win = a.win, r.q = a.q, r.d = a.d, r.scale = a.scale, r.lim = a.lim, r.out = a.out, r.rows = a.rows;
+  r.cols = a.cols, r.out_stride = a.out_stride, r.n_entries = n_entries, r.max_cnt = max_cnt;
+  return ring::try_launch(type, r, stream);
+}
 
 // the staged kernel when it takes the shape: 1 queued, 0 not taken, -1 refused
 int staged_first(uint32_t type, const LaneArgs& a, bool fused, bool dense, uint32_t n_entries, uint32_t max_cnt, void* stream) {
@@ -174,8 +185,8 @@ int staged_first(uint32_t type, const LaneArgs& a, bool fused, bool dense, uint3
 
 using namespace osmos;
 
-extern "C" void q8_set_staged(int on) { g_use_staged = on != 0; }
-extern "C" uint32_t q8_status(void) { return staged::read_status() | plain::read_status(); }
+extern "C" void q8_set_staged(int on) { g_use_staged = on; }
+extern "C" uint32_t q8_status(void) { return staged::read_status() | plain::read_status() | ring::read_status(); }
 
 extern "C" bool q8_round(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d, void* stream) {
   return round_rows<false>(x, rows, cols, xs, q, d, stream_of(stream));
@@ -195,8 +206,10 @@ extern "C" bool q8_group_tok(uint32_t type, const void* const* w, const int32_t*
   LaneArgs a{};
   a.wg = (const uint8_t* const*) w, a.cnt = cnt, a.xrow = xrow, a.xin = xin, a.q = q, a.d = d, a.out = y;
   a.rows = rows, a.cols = cols, a.out_stride = ys;
-  if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8))
+  if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8)) {
+    if (const int st = ring_first(type, a, false, n, max_cnt, stream)) return st > 0;
     if (const int st = staged_first(type, a, false, false, n, max_cnt, stream)) return st > 0;
+  }
 #define CASE(T) return by_tokens<T, false, false>(a, max_cnt, n, stream_of(stream));
   OSMOS_SWITCH_LANE(type, CASE, return false)
 #undef CASE
@@ -212,8 +225,10 @@ extern "C" bool q8_gate_up(uint32_t type, const void* const* wg, const void* con
   LaneArgs a{};
   a.wg = (const uint8_t* const*) wg, a.wu = (const uint8_t* const*) wu, a.cnt = cnt, a.xrow = xrow, a.xin = xin;
   a.win = win, a.q = q, a.d = d, a.scale = scale, a.lim = lim, a.out = h, a.rows = rows, a.cols = cols, a.out_stride = hs;
-  if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8))
+  if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8)) {
+    if (const int st = ring_first(type, a, true, n, max_cnt, stream)) return st > 0;
     if (const int st = staged_first(type, a, true, false, n, max_cnt, stream)) return st > 0;
+  }
 #define CASE(T) return by_tokens<T, true, false>(a, max_cnt, n, stream_of(stream));
   OSMOS_SWITCH_LANE(type, CASE, return false)
 #undef CASE

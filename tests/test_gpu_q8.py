@@ -183,7 +183,7 @@ def test_staged_kernel_matches_generic_and_oracle(lib, dev, oracle, name, cols, 
     xin_d, win_d, sc_d = to_dev(xin, dev), to_dev(win, dev), to_dev(scale, dev)
     ys, lim = rows + 5, 2.0
     results = []
-    for staged in (1, 0):
+    for staged in (2, 0, 1):  # the tile-staging kernel, the generic one, the warp-ring one (where it takes the type)
         lib.q8_set_staged(staged)
         yg = torch.full((total, ys), -9.0, dtype=torch.float32, device=dev)
         h = torch.full((total, ys), -9.0, dtype=torch.float32, device=dev)
@@ -205,6 +205,7 @@ def test_staged_kernel_matches_generic_and_oracle(lib, dev, oracle, name, cols, 
             want_h[r, :rows] = oracle.swiglu_lane(g_, u_, lim, scale[win[r]:win[r] + 1])[0]
     assert same_bits(results[1][0], want_g) and same_bits(results[1][1], want_h), "generic kernel"
     assert same_bits(results[0][0], want_g) and same_bits(results[0][1], want_h), "staged kernel"
+    assert same_bits(results[2][0], want_g) and same_bits(results[2][1], want_h), "warp-ring kernel"
 
 
 @pytest.mark.parametrize("name", ["Q4_0", "Q8_0", "IQ3_XXS", "IQ1_M"])
