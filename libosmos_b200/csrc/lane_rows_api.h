@@ -1,0 +1,24 @@
+// what q8.cu asks of the thread-a-row lane kernel (lane_rows.cu): q8_group_tok on 512-column matrices
+#pragma once
+#include <cstdint>
+
+namespace osmos {
+namespace rows {
+
+struct Request {
+  const void* const* w;
+  const int32_t *cnt, *xrow, *xin;
+  const int8_t* q;
+  const float* d;
+  float* out;
+  uint32_t rows, cols, out_stride, n_entries, max_cnt;
+};
+
+// 1: queued on the stream; 0: not a type / shape this kernel takes (nothing queued); -1: the launch was refused
+int try_launch(uint32_t type, const Request& r, void* stream);
+// the current device's status word, read and cleared (synchronizes): bit 0 a copy never landed, bit 1 a matrix
+// pointer was not 16-byte aligned
+uint32_t read_status();
+
+}  // namespace rows
+}  // namespace osmos

@@ -8,6 +8,7 @@
 #include "dispatch.cuh"
 #include "lane_plain_api.h"
 #include "lane_ring_api.h"
+#include "lane_rows_api.h"
 #include "lane_staged_api.h"
 #include "osmos_b200/mv.h"
 #include "osmos_b200/q8.h"
@@ -186,7 +187,7 @@ int staged_first(uint32_t type, const LaneArgs& a, bool fused, bool dense, uint3
 using namespace osmos;
 
 extern "C" void q8_set_staged(int on) { g_use_staged = on; }
-extern "C" uint32_t q8_status(void) { return staged::read_status() | plain::read_status() | ring::read_status(); }
+extern "C" uint32_t q8_status(void) { return staged::read_status() | plain::read_status() | ring::read_status() | rows::read_status(); }
 
 extern "C" bool q8_round(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d, void* stream) {
   return round_rows<false>(x, rows, cols, xs, q, d, stream_of(stream));
@@ -207,6 +208,10 @@ extern "C" bool q8_group_tok(uint32_t type, const void* const* w, const int32_t*
   a.wg = (const uint8_t* const*) w, a.cnt = cnt, a.xrow = xrow, a.xin = xin, a.q = q, a.d = d, a.out = y;
   a.rows = rows, a.cols = cols, a.out_stride = ys;
   if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8)) {
+    if (g_use_staged == 1) {  // 512-column matrices: a thread a row
+      const rows::Request r{w, cnt, xrow, xin, q, d, y, rows, cols, ys, n, max_cnt};
+      if (const int st = rows::try_launch(type, r, stream)) return st > 0;
+    }
     if (const int st = ring_first(type, a, false, n, max_cnt, stream)) return st > 0;
     if (const int st = staged_first(type, a, false, false, n, max_cnt, stream)) return st > 0;
   }
