@@ -47,6 +47,22 @@ bool mv_group_tok(uint32_t type, const void *const *w, const int32_t *cnt, const
 bool mv_strided(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t x_stride,
                 uint32_t n_tok, float *y, uint32_t y_stride, void *stream);
 
+/* NVFP4 (QTYPE_NVFP4: 64-value blocks of four UE4M3 scales and 32 bytes of E2M1) over n = 1 .. 4 tokens, the tensor's
+   own scale on each sum: y[t * ys + r] = scale * sum_c W[r, c] x[t * xs + c] (reference: mv.h:19-22,
+   kernels/mv_fp4.hip:25-107, 301-320). Its own order of sums, not mv_run's: a row's blocks go to 32 lanes (lane l takes
+   blocks l, l + 32, ...), a block adds its four 16-value sub-blocks in turn - part = fmaf(v[j], x[j], fmaf(v[j + 8],
+   x[j + 8], part)) for j = 0 .. 7, then acc = fmaf(d, part, acc) - and the lanes meet in the xor tree. false for n
+   outside 1 .. 4, cols not whole blocks, xs not a multiple of 4, x not 16-byte or w not 4-byte aligned. */
+bool mv_fp4(const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t xs, uint32_t n, float *y,
+            uint32_t ys, float scale, void *stream);
+/* NVFP4 matrices each over its own 1 .. 4 tokens (mv_group_tok's tables; an entry of count 0 - or past 4 - is
+   skipped), no tensor scale (reference: mv.h:23-27, kernels/mv_fp4.hip:213-298, 322-341). A row's blocks go to 8
+   lanes (up to 24 blocks a row), 16 (up to 48) or 32, lane l taking blocks l, l + lanes, ...; the block's sums and the
+   tree as mv_fp4's. A token's bits are the same at every count. false for n 0 or past 65535, cols not whole blocks,
+   xs not a multiple of 4, x not 16-byte aligned. */
+bool mv_fp4_tok(const void *const *w, const int32_t *cnt, const int32_t *xrow, uint32_t n, uint32_t rows,
+                uint32_t cols, const float *x, uint32_t xs, float *y, uint32_t ys, void *stream);
+
 /* Not in the reference. mv_run / mv_strided have two kernels that give the same bits: one that stages whole rows
    through shared memory with bulk copies (16-byte aligned w and x, rows whose bytes are a multiple of 16, x and a
    ring of rows fitting shared memory) and a generic one for every other shape. mv_set_staged(0) forces the generic

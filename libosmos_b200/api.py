@@ -64,6 +64,12 @@ SIGNATURES = {
     "mv_group": (B, [U32, P, U32, U32, U32, P, U32, U32, P, P]),
     "mv_group_tok": (B, [U32, P, P, P, U32, U32, U32, U32, P, U32, P, U32, P]),
     "mv_strided": (B, [U32, P, U32, U32, P, U32, U32, P, U32, P]),
+    "mv_fp4": (B, [P, U32, U32, P, U32, U32, P, U32, C.c_float, P]),
+    "mv_fp4_tok": (B, [P, P, P, U32, U32, U32, P, U32, P, U32, P]),
+    # mm.h
+    "mm_x16": (B, [P, U32, U32, U32, P, P, P]),
+    "mm_x16_rows": (B, [P, U32, P, U32, U32, P, P, P]),
+    "mm_x16_heads": (B, [P, U32, U32, U32, U32, U32, P, P, P]),
     # q8.h
     "q8_round": (B, [P, U32, U32, U32, P, P, P]),
     "q8_0_round": (B, [P, U32, U32, U32, P, P, P]),

@@ -169,6 +169,26 @@ class Oracle:
                                     _p(packed), C.c_uint32(dim or 0))
         return (x, packed) if ok else None
 
+    def x16_rows(self, x, slots, cols, idx=None):
+        """(tiled f16 bits, overflow flag) of mm_x16 (idx None) / mm_x16_rows"""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        xs = x.shape[1]
+        padded = (slots + 15) // 16 * 16
+        out = np.zeros(padded * cols, dtype=np.uint16)
+        ip = None if idx is None else np.ascontiguousarray(idx, dtype=np.int32)
+        over = self.lib.orc_x16_rows(_p(x), C.c_uint32(xs), _p(ip), C.c_uint32(slots), C.c_uint32(cols), _p(out))
+        return out, int(over)
+
+    def mv_fp4_rows(self, w, rows, cols, x, lanes=32, scale=None):
+        """mv_fp4 (lanes 32, scale) / mv_fp4_tok (lanes by the row's length, no scale) of one matrix over x's rows"""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.uint8)
+        y = np.zeros((x.shape[0], rows), dtype=np.float32)
+        self.lib.orc_mv_fp4_rows(_p(w), C.c_uint32(rows), C.c_uint32(cols), _p(x), C.c_uint32(x.shape[1]),
+                                 C.c_uint32(x.shape[0]), C.c_uint32(lanes), C.c_float(scale if scale is not None else 1.0),
+                                 C.c_int(int(scale is not None)), _p(y), C.c_uint32(rows))
+        return y
+
     def fp8_round(self, x, dim=None):
         x = np.array(x, dtype=np.float32, copy=True).reshape(-1)
         packed = None

@@ -892,3 +892,70 @@ ORC_API int orc_fp8_round(float *x, uint64_t n, uint8_t *packed, uint32_t dim)
   }
   return 1;
 }
+
+/* ------------------------------------------------------------------------------------------------------------
+ * mm_x16 / mm_x16_rows (kernels/mm.h:41-51, kernels/mm.hip:77-159): F32 rows to f16 (nearest even) in the tiled
+ * layout token t, column c -> (t / 16) 16 xts + (c / 16) 256 + (t % 16) 16 + c % 16; slot s is row idx[s] of x (idx
+ * NULL: row s; -1 or a slot past `slots`: zeros), slots rounded up to whole tiles of 16. Returns 1 when a value was
+ * past f16's range (or NaN): the overflow flag.
+ * ---------------------------------------------------------------------------------------------------------- */
+ORC_API int orc_x16_rows(const float *x, uint32_t xs, const int32_t *idx, uint32_t slots, uint32_t cols, uint16_t *x16)
+{
+  int over = 0;
+  const uint32_t padded = (slots + 15) / 16 * 16;
+  for (uint32_t t = 0; t < padded; t++)
+  {
+    const int64_t r = t < slots ? (idx ? idx[t] : (int64_t)t) : -1;
+    for (uint32_t c = 0; c < cols; c++)
+    {
+      const float v = r >= 0 ? x[(uint64_t)r * xs + c] : 0.0f;
+      if (!(fabsf(v) <= 65504.0f))
+        over = 1;
+      x16[(uint64_t)(t / 16) * 16 * cols + (uint64_t)(c / 16) * 256 + (t % 16) * 16 + c % 16] = half_bits(v);
+    }
+  }
+  return over;
+}
+
+/* ------------------------------------------------------------------------------------------------------------
+ * mv_fp4 / mv_fp4_tok (kernels/mv_fp4.hip:25-107, 213-273): NVFP4 rows over F32 activations in that file's own order.
+ * A row's 64-value blocks go to `lanes` lanes (32 for mv_fp4; 8, 16 or 32 by the row's length for mv_fp4_tok), lane l
+ * taking blocks l, l + lanes, ...; of a block, each 16-value sub-block s: part = 0, then for j = 0 .. 7
+ * part = fmaf(v[j], x[j], fmaf(v[j + 8], x[j + 8], part)), acc = fmaf(d_s, part, acc) with d_s the UE4M3 scale halved
+ * and v the E2M1 values doubled; the lanes by the xor tree; the sum times `scale`.
+ * ---------------------------------------------------------------------------------------------------------- */
+ORC_API void orc_mv_fp4_rows(const uint8_t *w, uint32_t rows, uint32_t cols, const float *x, uint32_t xs, uint32_t n,
+                             uint32_t lanes, float scale, int use_scale, float *y, uint32_t ys)
+{
+  const uint32_t nb = cols / 64;
+  for (uint32_t t = 0; t < n; t++)
+    for (uint32_t r = 0; r < rows; r++)
+    {
+      float acc[32];
+      for (uint32_t l = 0; l < lanes; l++)
+      {
+        acc[l] = 0.0f;
+        for (uint32_t b = l; b < nb; b += lanes)
+        {
+          const uint8_t *blk = w + ((uint64_t)r * nb + b) * 36;
+          const float *xb = x + (uint64_t)t * xs + (uint64_t)b * 64;
+          for (int s = 0; s < 4; s++)
+          {
+            const float d = ue4m3_value(blk[s]) * 0.5f;
+            float part = 0.0f;
+            for (int j = 0; j < 8; j++)
+            {
+              const uint8_t q = blk[4 + 8 * s + j];
+              const float a = (float)osmos_e2m1_doubled[q & 0x0F], c = (float)osmos_e2m1_doubled[q >> 4];
+              part = fmaf(a, xb[16 * s + j], fmaf(c, xb[16 * s + j + 8], part));
+            }
+            acc[l] = fmaf(d, part, acc[l]);
+          }
+        }
+      }
+      for (uint32_t o = lanes / 2; o > 0; o >>= 1)
+        for (uint32_t l = 0; l < o; l++)
+          acc[l] = acc[l] + acc[l + o];
+      y[(uint64_t)t * ys + r] = use_scale ? acc[0] * scale : acc[0];
+    }
+}

@@ -70,6 +70,14 @@ def test_refusals_decided_on_the_host(lib):
     assert not lib.mv_group_tok(18, x, x, x, 4, 9, 16, 256, x, 256, x, 16, None)
     assert not lib.mv_group_tok(18, x, x, x, 4, 0, 16, 256, x, 256, x, 16, None)
     assert not lib.mv_group_tok(18, x, x, x, 4, 2, 16, 256, x, 128, x, 16, None)
+    # x16 and NVFP4's matvec (reference: kernels/mm.hip:469, 611; kernels/mv_fp4.hip:303, 326)
+    assert not lib.mm_x16(8, 64, 0, 64, 8, 8, None) and not lib.mm_x16(8, 64, 2049, 64, 8, 8, None)
+    assert not lib.mm_x16(8, 64, 2, 72, 8, 8, None) and not lib.mm_x16(8, 32, 2, 64, 8, 8, None)
+    assert not lib.mm_x16_rows(16, 66, 8, 4, 64, 8, 8, None) and not lib.mm_x16_rows(8, 64, 8, 4, 64, 8, 8, None)
+    assert not lib.mm_x16_heads(16, 64, 4, 3, 32, 16, 16, 8, None)  # the last head reaches past a row
+    assert not lib.mv_fp4(16, 8, 64, 16, 64, 0, 16, 8, 1.0, None) and not lib.mv_fp4(16, 8, 96, 16, 96, 1, 16, 8, 1.0, None)
+    assert not lib.mv_fp4_tok(16, 16, 16, 0, 8, 64, 16, 64, 16, 8, None)
+    assert not lib.mv_fp4_tok(16, 16, 16, 1, 8, 64, 16, 66, 16, 8, None)
     # q8 (reference: include/osmos/gpu/q8.h:26-44; tests/test_cpu_q8.c:226-229)
     assert not lib.q8_round(x, 1, 48, 48, x, x, None)
     assert not lib.q8_round(x, 1, 64, 32, x, x, None)

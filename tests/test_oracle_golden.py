@@ -110,3 +110,40 @@ def test_mmq_oracle_integer_dots_and_bound(oracle):
                 b, gi = g // 8, g % 8
                 nib = (blk[r, b, 16 + (gi // 2) * 32:16 + (gi // 2) * 32 + 32] >> (4 * (gi % 2))) & 0x0F
                 assert ints[r, t, g] == int(nib.astype(np.int64) @ xq[g * 32:(g + 1) * 32])
+
+
+def test_x16_layout_and_rounding_against_numpy(oracle):
+    """the tiled f16 layout (kernels/mm.h:47-49 in the reference) and nearest-even rounding, against numpy's float16"""
+    rng = np.random.default_rng(5)
+    n, cols = 21, 48
+    x = (rng.standard_normal((n, cols + 4)) * 100).astype(np.float32)
+    idx = rng.integers(-1, n, size=n).astype(np.int32)
+    for use_idx in (None, idx):
+        got, over = oracle.x16_rows(x, n, cols, use_idx)
+        assert over == 0 and got.size == 32 * cols
+        for t in range(32):
+            r = -1 if t >= n else (t if use_idx is None else int(use_idx[t]))
+            row = x[r, :cols].astype(np.float16).view(np.uint16) if r >= 0 else np.zeros(cols, np.uint16)
+            for c in range(cols):
+                assert got[(t // 16) * 16 * cols + (c // 16) * 256 + (t % 16) * 16 + c % 16] == row[c]
+    x[3, 5] = 65520.0  # rounds past the largest f16
+    assert oracle.x16_rows(x, n, cols)[1] == 1
+
+
+def test_mv_fp4_order_against_float64(oracle):
+    """NVFP4's own matvec order (kernels/mv_fp4.hip in the reference): every product exact, so the result is within
+    cols roundings of the float64 sum (the reference's bound, tests/gpu/test_mv_fp4_tok_gpu.hip:110)"""
+    from libosmos_b200 import synth
+    tid = TYPES["NVFP4"]
+    for cols, lanes in ((1536, 8), (3072, 16), (6144, 32)):
+        rows = 12
+        w = synth.random_tensor(tid, rows, cols, synth.rng_for(41, cols))
+        x = np.random.default_rng(cols).standard_normal((3, cols)).astype(np.float32)
+        y = oracle.mv_fp4_rows(w, rows, cols, x, lanes)
+        wv = oracle.dequant(tid, w, rows * cols).reshape(rows, cols).astype(np.float64)
+        exact, mag = x.astype(np.float64) @ wv.T, np.abs(x.astype(np.float64)) @ np.abs(wv.T)
+        assert np.all(np.abs(y - exact) <= cols * 6e-8 * (mag + 1e-30))
+        # a token's sums do not depend on the tokens beside it
+        assert np.array_equal(oracle.mv_fp4_rows(w, rows, cols, x[1:2], lanes).view(np.uint32), y[1:2].view(np.uint32))
+        scaled = oracle.mv_fp4_rows(w, rows, cols, x, lanes, 0.25)
+        assert np.array_equal(scaled, y * np.float32(0.25))
