@@ -291,12 +291,70 @@ def run_ours(args):
             "e2e": {"value": n_tok * args.steps / t_e2e, "unit": UNIT,
                     "h2d_bytes_per_step": int(px[0].numel() * 4 + pl[0].numel() * 4), "d2h_bytes_per_step": int(pout.numel() * 4)},
             "gpu_launches": layer.kernels_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "q8_gate_up (lane_kernel, IQ3_XXS, fused gate+up+activation)",
+            "roofline": {"bound": "hbm", "kernel": "q8_gate_up (lane_ring_kernel, IQ3_XXS, fused gate + up + activation)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                          "traffic": None, "algorithmic_bytes_per_launch": float(np.mean(alg)),
                          "us_per_launch": float(np.mean(k_ms) * 1e3)},
             "cpu_baseline": cpu, "clocks": clocks.summary()}
+    try:
+        line["matvec"] = matvec_leg(lib, dev, peak)
+    except Exception as e:  # a second figure beside the headline: reported, never required
+        line["matvec"] = {"unavailable": str(e)[:160]}
     print(json.dumps(line), flush=True)
+
+
+def matvec_leg(lib, dev, peak):
+    """BASELINE's first metric beside the headline: the decode matvec's weight-GB/s. Config 1's matrix (Q4_0
+    6144 x 2048, 7 MB: a launch is latency-bound) and the same rows eight times over, each through the int8 lane
+    form (q8_run: x rounded once by q8_round) and the F32 form in the reference's order (mv_run). 64 launches on
+    successive cold copies (more than 1 GiB cycled) captured in one CUDA graph, replayed; device time a launch."""
+    import torch
+
+    from libosmos_b200 import synth
+    tid = synth.TYPE_ID["Q4_0"]
+    out = {"format": "Q4_0", "tokens": 1, "timing": "64 launches on successive copies (> 1 GiB cycled) in a CUDA graph, replayed 5 times",
+           "cases": []}
+    for rows, cols in ((6144, 2048), (49152, 2048)):
+        w = synth.random_tensor(tid, rows, cols, synth.rng_for(1, tid, rows))
+        nb = int(w.size)
+        copies = max(2, int(1.1 * 2 ** 30 // nb) + 1)
+        pool = torch.from_numpy(w).to(dev).repeat(copies)
+        x = torch.randn(1, cols, device=dev)
+        q = torch.zeros(1, cols, dtype=torch.int8, device=dev)
+        d = torch.zeros(1, cols // 32, device=dev)
+        y = torch.empty(1, rows, device=dev)
+        assert lib.q8_round(x.data_ptr(), 1, cols, cols, q.data_ptr(), d.data_ptr(), None)
+        calls = {
+            "q8_run": lambda i, st: lib.q8_run(tid, pool.data_ptr() + (i % copies) * nb, rows, cols, q.data_ptr(),
+                                               d.data_ptr(), 1, y.data_ptr(), rows, st),
+            "mv_run": lambda i, st: lib.mv_run(tid, pool.data_ptr() + (i % copies) * nb, rows, cols, x.data_ptr(), 1,
+                                               y.data_ptr(), st),
+        }
+        case = {"rows": rows, "cols": cols, "weight_bytes": nb}
+        for name, fn in calls.items():
+            for i in range(3):
+                assert fn(i, None)
+            torch.cuda.synchronize()
+            n, reps = 64, 5
+            g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            with torch.cuda.graph(g, stream=st):
+                for i in range(n):
+                    assert fn(i, st.cuda_stream)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (n * reps)
+            case[name] = {"us_per_launch": us, "weight_gbs": nb / us / 1e3, "frac_of_hbm_peak": nb / us / 1e3 / peak}
+        out["cases"].append(case)
+        del pool
+    if lib.q8_status() or lib.mv_status():
+        raise SystemExit("bench: a staged matvec kernel reported a copy that never landed")
+    return out
 
 
 def main():
