@@ -11,6 +11,12 @@
  *   4. ep_scatter_rows: row of pick (t, j) -> send[home(t)][(t mod T) * k + j];
  *   5. all-to-all of send (NCCL): recv[o] = what rank o computed for this rank's tokens;
  *   6. ep_combine: each home token's k rows, taken from their owners' blocks, added in ascending expert id.
+ * The two exchanges have a second form that does not go through a collective library: every rank maps its peers'
+ * buffers (CUDA IPC) and the producing kernels store straight into the consumer's memory over NVLink - ep_push for
+ * step 2 (the segment to every rank), ep_scatter_rows_peer for steps 4 and 5 (a row to its token's home) - each
+ * followed by a release of a per-sender flag in the consumer's memory, which the consumer's ep_wait polls locally
+ * (bounded). Buffers are used in two alternating halves by step parity; a rank cannot run more than one step ahead of
+ * a peer because it waits on that peer's flag every step, so a half is never overwritten while it is still read.
  * Every bool entry returns true when the work was queued on `stream`, false when it was refused (nothing queued).
  */
 #ifndef OSMOS_B200_EP_H
@@ -44,6 +50,31 @@ bool ep_scatter_rows(const float *ye, const int32_t *row_of, uint32_t n_picks, u
    expert / experts_per_rank; ids are the home tokens' picks [tokens * k]; add (or NULL) added after the sum */
 bool ep_combine(const float *recv, const int32_t *ids, uint32_t tokens, uint32_t k, uint32_t experts_per_rank,
                 uint32_t dim, const float *add, float *out, void *stream);
+
+/* ---- the peer transport ---------------------------------------------------------------------------------------- */
+#define EP_MAX_RANKS 16
+#define EP_HANDLE_BYTES 64 /* a CUDA IPC memory handle */
+/* set-up, not the step: a zeroed device buffer other processes of this machine can map, and its handle; a peer's
+   buffer mapped from its handle (peer access enabled with it); their release. false when the CUDA call failed. */
+bool ep_peer_alloc(uint64_t bytes, void **ptr, uint8_t handle[EP_HANDLE_BYTES]);
+bool ep_peer_open(const uint8_t handle[EP_HANDLE_BYTES], void **ptr);
+bool ep_peer_close(void *ptr);
+bool ep_peer_free(void *ptr);
+/* `bytes` (a multiple of 16) of src, local, to dst[r] for every r < n_ranks (dst, flag: device arrays of addresses,
+   dst[r] and flag[r] inside rank r's memory - this rank's own included); when all of it is written and fenced,
+   *flag[r] = step for every r. counter: a zeroed local device word the kernel uses and leaves zero. */
+bool ep_push(const void *src, uint64_t bytes, void *const *dst, uint32_t *const *flag, uint32_t n_ranks, uint32_t step,
+             uint32_t *counter, void *stream);
+/* returns (on the stream) once flags[r] has reached `step` for every r < n_ranks - flags local, written by the
+   peers' ep_push / ep_scatter_rows_peer - or after the wait limit (2 s), which ep_wait_status() then reports (bit 0;
+   read and cleared, it synchronizes) */
+bool ep_wait(const uint32_t *flags, uint32_t n_ranks, uint32_t step, void *stream);
+uint32_t ep_wait_status(void);
+/* ep_scatter_rows without the send buffer: the row of pick (t, j) goes to recv[t / tokens] + ((t % tokens) * k + j) *
+   dim floats, recv[r] = where this rank's block lies in rank r's memory; then the flags as ep_push */
+bool ep_scatter_rows_peer(const float *ye, const int32_t *row_of, uint32_t n_picks, uint32_t k, uint32_t tokens,
+                          uint32_t dim, float *const *recv, uint32_t *const *flag, uint32_t n_ranks, uint32_t step,
+                          uint32_t *counter, void *stream);
 
 /* lane_ffn's middle for one rank: tokens already rounded (q, d, token-major), the rows of experts [e0, e1) into
    s->ye (row r = the r-th of those picks sorted by (expert, pick)); s->tab.row_of says which row a pick got */

@@ -119,6 +119,14 @@ SIGNATURES = {
     "ep_unpack": (B, [P, U32, U32, U32, U32, P, P, P, P, P]),
     "ep_scatter_rows": (B, [P, P, U32, U32, U32, U32, P, P]),
     "ep_combine": (B, [P, P, U32, U32, U32, U32, P, P, P]),
+    "ep_peer_alloc": (B, [C.c_uint64, P, P]),
+    "ep_peer_open": (B, [P, P]),
+    "ep_peer_close": (B, [P]),
+    "ep_peer_free": (B, [P]),
+    "ep_push": (B, [P, C.c_uint64, P, P, U32, U32, P, P]),
+    "ep_wait": (B, [P, U32, U32, P]),
+    "ep_wait_status": (U32, []),
+    "ep_scatter_rows_peer": (B, [P, P, U32, U32, U32, U32, P, P, U32, U32, P, P]),
     "lane_ffn_rows": (B, [C.POINTER(LaneLayer), C.POINTER(LaneScratch), P, P, P, P, U32, U32, U32, P]),
 }
 

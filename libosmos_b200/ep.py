@@ -6,7 +6,12 @@ Dispatch = all-gather of each rank's routed, int8-rounded home tokens (with top-
 token, so the dispatch all-to-all degenerates to an all-gather of 2.4 KB a token); combine = all-to-all of the
 computed rows back to the tokens' homes, where each token's rows are added in ascending expert id - the single-GPU
 order, so the output bits do not depend on N.
+
+Two transports for the exchanges: "peer" (the default) - the library's own kernels store into the peers' mapped
+buffers over NVLink and release per-sender flags (ep_push, ep_scatter_rows_peer, ep_wait); "nccl" - all-gather and
+all-to-all through torch.distributed. Same bits either way.
 """
+import ctypes as C
 import json
 
 import numpy as np
@@ -31,8 +36,55 @@ def send_slot(pick, k, tokens_per_rank):
     return (t // tokens_per_rank) * tokens_per_rank * k + (t % tokens_per_rank) * k + j
 
 
+class PeerBuffers:
+    """Every rank's exchange buffer, mapped into this process: [dispatch flags][combine flags][2 halves of gathered
+    segments][2 halves of received rows]; and the device tables of addresses the pushing kernels take."""
+
+    def __init__(self, lib, dist, dev, rank, world, seg_bytes, block_bytes):
+        self.lib, self.rank, self.world = lib, rank, world
+        up = lambda v: (v + 255) // 256 * 256
+        self.off_flag = [0, 256]
+        self.off_seg = [512 + p * up(world * seg_bytes) for p in range(2)]
+        base_recv = 512 + 2 * up(world * seg_bytes)
+        self.off_recv = [base_recv + p * up(world * block_bytes) for p in range(2)]
+        total = base_recv + 2 * up(world * block_bytes)
+        mine, handle = C.c_void_p(), (C.c_uint8 * 64)()
+        if not lib.ep_peer_alloc(total, C.byref(mine), handle):
+            raise RuntimeError("ep_peer_alloc failed")
+        self.mine = mine.value
+        all_handles = torch.empty(world * 64, dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(all_handles, torch.tensor(list(handle), dtype=torch.uint8, device=dev))
+        all_handles = all_handles.cpu().numpy().reshape(world, 64)
+        self.base = []
+        for r in range(world):
+            if r == rank:
+                self.base.append(self.mine)
+                continue
+            p = C.c_void_p()
+            h = (C.c_uint8 * 64)(*[int(b) for b in all_handles[r]])
+            if not lib.ep_peer_open(h, C.byref(p)):
+                raise RuntimeError("ep_peer_open failed for rank %d" % r)
+            self.base.append(p.value)
+        tbl = lambda f: torch.tensor([f(r) for r in range(world)], dtype=torch.int64, device=dev)
+        # where this rank's piece goes in rank r's buffer, and the flag this rank owns there
+        self.dst_seg = [tbl(lambda r, p=p: self.base[r] + self.off_seg[p] + rank * seg_bytes) for p in range(2)]
+        self.dst_recv = [tbl(lambda r, p=p: self.base[r] + self.off_recv[p] + rank * block_bytes) for p in range(2)]
+        self.flag = [tbl(lambda r, i=i: self.base[r] + self.off_flag[i] + rank * 4) for i in range(2)]
+        self.counters = torch.zeros(2, dtype=torch.int32, device=dev)
+        dist.barrier()  # every rank has mapped every buffer before anyone stores into one
+
+    def close(self, dist):
+        torch.cuda.synchronize()
+        dist.barrier()
+        for r, b in enumerate(self.base):
+            if r != self.rank:
+                self.lib.ep_peer_close(b)
+        dist.barrier()
+        self.lib.ep_peer_free(self.mine)
+
+
 class EpMoeLane:
-    def __init__(self, lib, cfg, dev, rank, world, copies=1, host_tensors=None):
+    def __init__(self, lib, cfg, dev, rank, world, copies=1, host_tensors=None, transport="peer"):
         import torch.distributed as dist
         self.dist = dist
         self.lib, self.cfg, self.dev, self.rank, self.world = lib, cfg, dev, rank, world
@@ -54,7 +106,19 @@ class EpMoeLane:
         self.rows = torch.zeros(self.T * self.k, dtype=torch.int32, device=dev)
         self.send = torch.zeros((world, self.T * self.k, self.dim), dtype=torch.float32, device=dev)
         self.recv = torch.zeros_like(self.send)
-        self.kernels_per_step = 10  # route, round, unpack, tables, order, gate_up, round, down, scatter, combine
+        self.transport, self.step_no = transport, 0
+        self.peer = None
+        if transport == "peer":
+            self.peer = PeerBuffers(lib, dist, dev, rank, world, self.seg.bytes, self.T * self.k * self.dim * 4)
+            # route, round, push, wait, unpack, tables, order, gate_up, round, down, scatter, wait, combine
+            self.kernels_per_step = 13
+        else:
+            self.kernels_per_step = 10  # route, round, unpack, tables, order, gate_up, round, down, scatter, combine
+
+    def close(self):
+        if self.peer:
+            self.peer.close(self.dist)
+            self.peer = None
 
     def step(self, x_home, logits_home, out_home, copy=0, stream=0, events=None):
         """x_home [T, dim], logits_home [T, n_exp], out_home [T, dim]: this rank's tokens; all on this GPU.
@@ -65,22 +129,40 @@ class EpMoeLane:
         ok = ok and lib.q8_round(x_home.data_ptr(), T, self.dim, self.dim, base + s.q, base + s.d, stream)
         if not ok:
             raise RuntimeError("libosmos_b200 refused a call (route / round)")
-        self.dist.all_gather_into_tensor(self.gathered, self.segment)
+        self.step_no += 1
+        P, n, half = self.peer, self.step_no, self.step_no & 1
+        if P:
+            ok = lib.ep_push(base, s.bytes, P.dst_seg[half].data_ptr(), P.flag[0].data_ptr(), self.world, n,
+                             P.counters.data_ptr(), stream)
+            ok = ok and lib.ep_wait(P.mine + P.off_flag[0], self.world, n, stream)
+            gathered = P.mine + P.off_seg[half]
+        else:
+            self.dist.all_gather_into_tensor(self.gathered, self.segment)
+            gathered = self.gathered.data_ptr()
         L = self.local
-        ok = lib.ep_unpack(self.gathered.data_ptr(), self.world, T, k, self.dim, self.ids_all.data_ptr(),
-                           self.wts_all.data_ptr(), self.q_all.data_ptr(), self.d_all.data_ptr(), stream)
+        ok = ok and lib.ep_unpack(gathered, self.world, T, k, self.dim, self.ids_all.data_ptr(),
+                                  self.wts_all.data_ptr(), self.q_all.data_ptr(), self.d_all.data_ptr(), stream)
         if events:
             events[0].record()
         ok = ok and lib.lane_ffn_rows(L.layers[copy % len(L.layers)], L.scratch, self.q_all.data_ptr(), self.d_all.data_ptr(),
                                       self.ids_all.data_ptr(), self.wts_all.data_ptr(), self.n_tok, self.e0, self.e1, stream)
         if events:
             events[1].record()
-        ok = ok and lib.ep_scatter_rows(L.scratch.ye, L.scratch.tab.row_of, self.n_tok * k, k, T, self.dim,
-                                        self.send.data_ptr(), stream)
+        if P:
+            ok = ok and lib.ep_scatter_rows_peer(L.scratch.ye, L.scratch.tab.row_of, self.n_tok * k, k, T, self.dim,
+                                                 P.dst_recv[half].data_ptr(), P.flag[1].data_ptr(), self.world, n,
+                                                 P.counters.data_ptr() + 4, stream)
+            ok = ok and lib.ep_wait(P.mine + P.off_flag[1], self.world, n, stream)
+            recv = P.mine + P.off_recv[half]
+        else:
+            ok = ok and lib.ep_scatter_rows(L.scratch.ye, L.scratch.tab.row_of, self.n_tok * k, k, T, self.dim,
+                                            self.send.data_ptr(), stream)
         if not ok:
             raise RuntimeError("libosmos_b200 refused a call (unpack / experts / scatter)")
-        self.dist.all_to_all_single(self.recv, self.send)
-        if not lib.ep_combine(self.recv.data_ptr(), base + s.ids, T, k, self.n_exp // self.world, self.dim, None,
+        if not P:
+            self.dist.all_to_all_single(self.recv, self.send)
+            recv = self.recv.data_ptr()
+        if not lib.ep_combine(recv, base + s.ids, T, k, self.n_exp // self.world, self.dim, None,
                               out_home.data_ptr(), stream):
             raise RuntimeError("libosmos_b200 refused a call (combine)")
 
@@ -94,7 +176,15 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
     n_tok, dim, k = cfg["n_tok"], cfg["dim"], cfg["k"]
     host = workloads.moe_layer_host(cfg)
     copies = 4
-    layer = EpMoeLane(lib, cfg, dev, rank, world, copies=copies, host_tensors=host)
+    import os
+    transport = os.environ.get("OSMOS_EP_TRANSPORT", "peer")
+    try:
+        layer = EpMoeLane(lib, cfg, dev, rank, world, copies=copies, host_tensors=host, transport=transport)
+    except RuntimeError as e:  # the peers' memory could not be mapped here: the exchanges go through NCCL
+        if transport != "peer":
+            raise
+        transport = "nccl (peer mapping unavailable: %s)" % e
+        layer = EpMoeLane(lib, cfg, dev, rank, world, copies=copies, host_tensors=host, transport="nccl")
     t0, t1 = home_tokens(rank, world, n_tok)
     n_inputs = 8
     hx, hl = zip(*[workloads.moe_inputs_host(cfg, s) for s in range(n_inputs)])
@@ -171,6 +261,7 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
                 "config": {"workload": cfg["name"], "tokens": n_tok, "experts": cfg["n_exp"], "top_k": k, "hidden": dim,
                            "expert_ff": cfg["ff"], "format": cfg["type"],
                            "parallelism": "ep%d: experts in contiguous ranges, tokens by home rank, all-gather dispatch, all-to-all combine" % world,
+                           "transport": transport,
                            "cold_cache": "%d copies of each rank's %d MB of expert weights cycled" % (copies, sum(per) * cfg["n_exp"] // world // 1000000)},
                 "e2e": {"value": n_tok * args.steps / t_e2e, "unit": unit,
                         "h2d_bytes_per_step": int((px[0].numel() + pl[0].numel()) * 4 * world),
@@ -182,5 +273,8 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
                              "us_per_launch": float(np.mean(k_ms) * 1e3)},
                 "cpu_baseline": None, "clocks": clocks.summary()}
         print(json.dumps(line), flush=True)
+    if lib.ep_wait_status():
+        raise SystemExit("bench: a wait on a peer's flag ran out on rank %d" % rank)
+    layer.close()
     dist.barrier()
     dist.destroy_process_group()

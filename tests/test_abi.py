@@ -78,6 +78,10 @@ def test_refusals_decided_on_the_host(lib):
     assert not lib.mv_fp4(16, 8, 64, 16, 64, 0, 16, 8, 1.0, None) and not lib.mv_fp4(16, 8, 96, 16, 96, 1, 16, 8, 1.0, None)
     assert not lib.mv_fp4_tok(16, 16, 16, 0, 8, 64, 16, 64, 16, 8, None)
     assert not lib.mv_fp4_tok(16, 16, 16, 1, 8, 64, 16, 66, 16, 8, None)
+    # the peer transport's launches (set-up calls need a GPU and are not made here)
+    assert not lib.ep_push(16, 24, 16, 16, 2, 1, 16, None) and not lib.ep_push(16, 32, 16, 16, 17, 1, 16, None)
+    assert not lib.ep_wait(16, 0, 1, None) and not lib.ep_wait(None, 2, 1, None)
+    assert not lib.ep_scatter_rows_peer(16, 16, 4, 2, 2, 6, 16, 16, 2, 1, 16, None)
     # q8 (reference: include/osmos/gpu/q8.h:26-44; tests/test_cpu_q8.c:226-229)
     assert not lib.q8_round(x, 1, 48, 48, x, x, None)
     assert not lib.q8_round(x, 1, 64, 32, x, x, None)
