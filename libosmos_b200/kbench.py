@@ -1,0 +1,79 @@
+"""Time one dense matvec entry point on a seeded synthetic matrix: the per-kernel counterpart of bench.py (the
+reference keeps such sweeps under tools/bench/).
+
+    python -m libosmos_b200.kbench q8_run Q4_0 49152 2048            # one token, graph-timed
+    python -m libosmos_b200.kbench mv_run Q8_0 6144 2048 --tokens 2
+    python -m libosmos_b200.kbench q8_run Q4_0 49152 2048 --plain 4  # four plain launches, nothing timed (for a profiler)
+
+Timing: 64 launches on successive cold copies of the matrix (more than 1 GiB cycled, so every launch reads HBM)
+captured in one CUDA graph and replayed 5 times; CUDA events around the replays; device time a launch.
+"""
+import argparse
+import json
+
+import numpy as np
+import torch
+
+import libosmos_b200
+from libosmos_b200 import synth
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["mv_run", "q8_run"])
+    ap.add_argument("type")
+    ap.add_argument("rows", type=int)
+    ap.add_argument("cols", type=int)
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--plain", type=int, default=0, help="this many plain launches on 4 copies instead of timing")
+    ap.add_argument("--generic", action="store_true", help="the generic kernels (mv_set_staged(0), q8_set_staged(0))")
+    args = ap.parse_args()
+    lib = libosmos_b200.load()
+    dev = torch.device("cuda", 0)
+    tid = synth.TYPE_ID[args.type]
+    w = synth.random_tensor(tid, args.rows, args.cols, synth.rng_for(1, tid, args.rows))
+    nb = int(w.size)
+    copies = 4 if args.plain else max(2, int(1.1 * 2 ** 30 // nb) + 1)
+    pool = torch.from_numpy(w).to(dev).repeat(copies)
+    x = torch.randn(args.tokens, args.cols, device=dev, generator=torch.Generator(device=dev).manual_seed(1017))
+    q = torch.zeros(args.tokens, args.cols, dtype=torch.int8, device=dev)
+    d = torch.zeros(args.tokens, args.cols // 32, device=dev)
+    y = torch.empty(args.tokens, args.rows, device=dev)
+    if args.generic:
+        lib.mv_set_staged(0), lib.q8_set_staged(0)
+    assert lib.q8_round(x.data_ptr(), args.tokens, args.cols, args.cols, q.data_ptr(), d.data_ptr(), None)
+    if args.op == "q8_run":
+        fn = lambda i, st: lib.q8_run(tid, pool.data_ptr() + (i % copies) * nb, args.rows, args.cols, q.data_ptr(),
+                                      d.data_ptr(), args.tokens, y.data_ptr(), args.rows, st)
+    else:
+        fn = lambda i, st: lib.mv_run(tid, pool.data_ptr() + (i % copies) * nb, args.rows, args.cols, x.data_ptr(),
+                                      args.tokens, y.data_ptr(), st)
+    for i in range(max(args.plain, 3)):
+        if not fn(i, None):
+            raise SystemExit("the library refused the call")
+    torch.cuda.synchronize()
+    status = lib.q8_status() | lib.mv_status()
+    if args.plain:
+        print("%d launches, status %d" % (args.plain, status))
+        return
+    n, reps = 64, 5
+    g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=st):
+        for i in range(n):
+            assert fn(i, st.cuda_stream)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (n * reps)
+    print(json.dumps({"op": args.op, "type": args.type, "rows": args.rows, "cols": args.cols, "tokens": args.tokens,
+                      "kernels": "generic" if args.generic else "default", "us_per_launch": us,
+                      "weight_bytes": nb, "weight_gbs": nb / us / 1e3, "status": status | lib.q8_status() | lib.mv_status()}))
+
+
+if __name__ == "__main__":
+    main()
