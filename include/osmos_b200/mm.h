@@ -1,8 +1,13 @@
 /* The f16 activation layout the prefill matrix products read, and the conversions into it.
  *
- * Drop-in for the activation side of the reference's include/osmos/gpu/mm.h: mm_x16 (:13), mm_x16_rows (:35),
- * mm_x16_heads (:37) and the layout function of kernels/mm.h:41-51 - same names, argument meaning, limits and
- * refusals. (The products themselves - mm_run, mm_run2, mm_tokens, mm_group - are not in this library yet.)
+ * Drop-in for the reference's include/osmos/gpu/mm.h: the activation side mm_x16 (:13), mm_x16_rows (:35),
+ * mm_x16_heads (:37) with the layout function of kernels/mm.h:41-51, and the products mm_known, mm_fits, mm_run,
+ * mm_run2, mm_tokens[_scaled], mm_group (:10-38) - same names, argument meaning, limits and refusals. The products
+ * compute what the reference's do - the weights' exact values rounded to f16, times the f16 activations,
+ * accumulated in F32 - on the tensor cores, with the tensor core's order of additions along K instead of the
+ * reference's wave partitions: results agree with the reference's within its own test bound
+ * ((cols / 16 + 20) 2^-24 sum |w16 x16|, tests/gpu/test_mm_gpu.hip:328-343), not bit for bit; a token's results are
+ * the same bits whatever it is batched with and wherever in the batch.
  *
  * x16 holds token t's column c, of rows xts values long, at half index
  *   (t / 16) * 16 * xts + (c / 16) * 256 + (t % 16) * 16 + c % 16
@@ -26,8 +31,14 @@ extern "C" {
 #define MM_TILE 16         /* reference: mm.h:7 */
 #define MM_MAX_TOKENS 2048 /* reference: mm.h:8 */
 
+#if defined(__CUDACC__)
+#define MM_HD __host__ __device__
+#else
+#define MM_HD
+#endif
+
 /* where token t's column c lies in a tiled x16 of rows xts long, in halves (reference: kernels/mm.h:47-49) */
-static inline uint64_t mm_x16_at(uint32_t t, uint32_t c, uint32_t xts) {
+static inline MM_HD uint64_t mm_x16_at(uint32_t t, uint32_t c, uint32_t xts) {
   return (uint64_t)(t / MM_TILE) * MM_TILE * xts + (uint64_t)(c / MM_TILE) * (MM_TILE * MM_TILE) + (t % MM_TILE) * MM_TILE +
          c % MM_TILE;
 }
@@ -47,6 +58,38 @@ bool mm_x16_rows(const float *x, uint32_t xs, const int32_t *idx, uint32_t slots
    16, hs or xs not a multiple of 4, x or x16 not 16-byte aligned, or a last head reaching past a row. */
 bool mm_x16_heads(const float *x, uint32_t xs, uint32_t n, uint32_t heads, uint32_t hs, uint32_t cols, void *x16,
                   int32_t *overflow, void *stream);
+
+/* whether `type` has a matrix-product kernel (every block type of qtype.h), and whether a rows x cols matrix of it
+   tiles: rows a multiple of 16, cols a multiple of 128 and whole blocks (reference: mm.h:10-11) */
+bool mm_known(uint32_t type);
+bool mm_fits(uint32_t type, uint32_t rows, uint32_t cols);
+/* y[t * ys + r] = sum_c W[r, c] x16[t][c], t < n <= MM_MAX_TOKENS; x16 as mm_x16 lays it (rows of cols values)
+   (reference: mm.h:15). false for a type without a kernel, a shape that does not tile, n 0 or past MM_MAX_TOKENS,
+   with more than one token ys shorter than a row, or x16 not 16-byte aligned. */
+bool mm_run(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const void *x16, uint32_t n, float *y,
+            uint32_t ys, void *stream);
+/* two matrices of one type and cols on the same x16, each the bits mm_run gives it alone (reference: mm.h:23);
+   refused as a whole when either would be */
+bool mm_run2(uint32_t type, const void *w0, uint32_t rows0, float *y0, uint32_t ys0, const void *w1, uint32_t rows1,
+             float *y1, uint32_t ys1, uint32_t cols, const void *x16, uint32_t n, void *stream);
+/* a matrix (w1 NULL) or two over any n tokens of F32 x: MM_MAX_TOKENS at a time through the one x16 - mm_x16 of the
+   chunk, then the products into its rows; `ready`: x16 already holds this x (n within one x16): the conversion is
+   skipped. _scaled: each matrix's sums times its scale as they are stored (reference: mm.h:17-22) */
+bool mm_tokens(uint32_t type, const void *w0, uint32_t rows0, float *y0, uint32_t ys0, const void *w1, uint32_t rows1,
+               float *y1, uint32_t ys1, uint32_t cols, const float *x, uint32_t xs, uint32_t n, void *x16,
+               int32_t *overflow, bool ready, void *stream);
+bool mm_tokens_scaled(uint32_t type, const void *w0, uint32_t rows0, float *y0, uint32_t ys0, float s0, const void *w1,
+                      uint32_t rows1, float *y1, uint32_t ys1, float s1, uint32_t cols, const float *x, uint32_t xs,
+                      uint32_t n, void *x16, int32_t *overflow, bool ready, void *stream);
+/* n_mat matrices of one type and shape: matrix m (w[m]) over the tiled x16 from x16 + xoff[m] halves (rows xts long),
+   its first cnt[m] <= max_cnt tokens' rows into y + yoff[m] + t * ys; w, cnt, xoff, yoff device arrays
+   (reference: mm.h:39-41). Each token the sums mm_run gives it. */
+bool mm_group(uint32_t type, const void *const *w, const int32_t *cnt, uint32_t n_mat, uint32_t max_cnt, uint32_t rows,
+              uint32_t cols, const void *x16, const uint32_t *xoff, uint32_t xts, float *y, const uint32_t *yoff,
+              uint32_t ys, void *stream);
+/* Not in the reference: the products' kernel never waits without a bound; reads and clears the current device's
+   record (synchronizes): bit 0 a wait ran out, the launch's outputs are not valid */
+uint32_t mm_status(void);
 
 #ifdef __cplusplus
 }

@@ -70,6 +70,14 @@ SIGNATURES = {
     "mm_x16": (B, [P, U32, U32, U32, P, P, P]),
     "mm_x16_rows": (B, [P, U32, P, U32, U32, P, P, P]),
     "mm_x16_heads": (B, [P, U32, U32, U32, U32, U32, P, P, P]),
+    "mm_known": (B, [U32]),
+    "mm_fits": (B, [U32, U32, U32]),
+    "mm_run": (B, [U32, P, U32, U32, P, U32, P, U32, P]),
+    "mm_run2": (B, [U32, P, U32, P, U32, P, U32, P, U32, U32, P, U32, P]),
+    "mm_tokens": (B, [U32, P, U32, P, U32, P, U32, P, U32, U32, P, U32, U32, P, P, C.c_bool, P]),
+    "mm_tokens_scaled": (B, [U32, P, U32, P, U32, C.c_float, P, U32, P, U32, C.c_float, U32, P, U32, U32, P, P, C.c_bool, P]),
+    "mm_group": (B, [U32, P, P, U32, U32, U32, U32, P, P, U32, P, P, U32, P]),
+    "mm_status": (U32, []),
     # q8.h
     "q8_round": (B, [P, U32, U32, U32, P, P, P]),
     "q8_0_round": (B, [P, U32, U32, U32, P, P, P]),

@@ -1,0 +1,343 @@
+// The prefill matrix products over f16 activations (include/osmos_b200/mm.h: mm_run, mm_run2, mm_group, mm_tokens)
+// on the 5th-generation tensor cores: tcgen05.mma kind::f16, F32 accumulators in tensor memory.
+//
+// The weights' exact values are rounded to f16 (nearest) as they are decoded, the activations are the caller's x16
+// (mm_x16's tiled f16), and every product is accumulated in F32 along K in one pass - the reference's arithmetic
+// (kernels/mm.h: f16 operands, F32 accumulation) with the tensor core's own order of additions instead of its waves'
+// partitions; a token's column is computed from that column alone, so its bits do not depend on the tokens beside
+// it or on where in the batch it stands.
+//
+// A block computes 128 weight rows x up to 512 tokens of one matrix, so a weight is decoded once for 512 tokens.
+// Thirteen warps, three roles:
+//   producers (8 warps)  per 64-value step of K: decode the rows' 8-value chunks to f16 and store them as the A
+//                        operand (four K = 16 sub-tiles of 128 rows, K-major core matrices of 8 rows x 16 bytes), and
+//                        cp.async the tokens' 16-byte pieces of x16 into the same layout (B, four sub-tiles a
+//                        128-token accumulator); a proxy fence and an arrive on the stage's "full" mbarrier. Two stages.
+//   issuer (1 warp)      per step and accumulator four tcgen05.mma M128 N128 K16 (the first of the whole K loop
+//                        overwrites, the rest accumulate), then tcgen05.commit onto the stage's "empty" mbarrier; after
+//                        the last step a commit onto "done".
+//   epilogue (4 warps)   thread = one weight row (its TMEM lane): tcgen05.ld the sums, scale, store y[t][row].
+// Every mbarrier wait is bounded (%globaltimer); a wait that runs out raises the status word, every role falls through
+// to the common exit and tensor memory is released.
+#include "decode.cuh"
+#include "dispatch.cuh"
+#include "osmos_b200/mm.h"
+#include "tma.cuh"
+
+namespace osmos {
+namespace mm_tc {
+namespace {
+
+using namespace tma;
+
+constexpr int kM = 128, kN = 128;  // rows a block; tokens an accumulator
+constexpr int kMaxAcc = 4;         // accumulators a block: 512 tokens
+constexpr int kEpiWarps = 4, kProdWarps = 8;
+constexpr int kIssuerWarp = kEpiWarps, kFirstProdWarp = kEpiWarps + 1;
+constexpr int kProdThreads = kProdWarps * kWarp;
+constexpr int kThreads = (kEpiWarps + 1 + kProdWarps) * kWarp;
+constexpr int kStep = 64;                        // values of K a stage
+constexpr int kSubTile = kM * 32;                // one K = 16 operand sub-tile: 128 rows x 32 bytes
+constexpr int kSubs = kStep / 16;                // sub-tiles a stage an operand: 4
+constexpr int kStageA = kSubs * kSubTile;        // 16 KB
+constexpr int kStageB = kMaxAcc * kSubs * kSubTile;  // 64 KB
+constexpr int kStageBytes = kStageA + kStageB;
+constexpr int kStages = 2;
+
+__device__ uint32_t g_status;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// shared-memory matrix descriptor of one sub-tile: K-major, no swizzle, core matrices of 8 rows x 16 bytes; the next
+// 16 bytes of K are 128 bytes on (leading offset), the next 8 rows 256 bytes on (stride offset)
+__device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
+  return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) (128u >> 4) << 16 | (uint64_t) (256u >> 4) << 32 | (uint64_t) 1 << 46;
+}
+// instruction descriptor: D F32, A and B f16, both K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t) (kN >> 3) << 17) | ((uint32_t) (kM >> 4) << 24);
+
+struct Args {
+  const uint8_t* w;          // one matrix (wt NULL)
+  const uint8_t* const* wt;  // grouped: the matrices
+  const int32_t* cnt;        // grouped: tokens a matrix
+  const uint32_t *xoff, *yoff;  // grouped: where a matrix's tokens start in x16 (halves) and y (floats)
+  const __half* x16;
+  float* y;
+  uint32_t rows, cols, n, xts, ys;
+  float scale;
+  uint32_t* status;
+};
+
+struct Shared {
+  uint64_t full[kStages], empty[kStages], done;
+  uint32_t tmem_base;
+  int fail;
+};
+
+template <uint32_t T>
+__global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ Shared sh;
+  __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
+  const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
+  const uint32_t m = blockIdx.y, row0 = blockIdx.x * kM, c0 = blockIdx.z * (kMaxAcc * kN);
+  const uint32_t n_tok = a.wt ? (uint32_t) (a.cnt[m] > 0 ? a.cnt[m] : 0) : a.n;
+  if (c0 >= n_tok) return;  // the whole block, before anything is allocated
+  const uint32_t n_valid = n_tok - c0 < (uint32_t) (kMaxAcc * kN) ? n_tok - c0 : (uint32_t) (kMaxAcc * kN);
+  const uint32_t n_valid16 = (n_valid + 15u) & ~15u;  // x16 holds whole tiles of 16 tokens
+  const uint32_t n_acc = (n_valid + kN - 1) / kN;
+  const uint32_t steps = a.cols / kStep;
+  const uint64_t row_bytes = (uint64_t) (a.cols / Fmt<T>::values) * Fmt<T>::bytes;
+  const uint8_t* w = a.wt ? a.wt[m] : a.w;
+  const __half* x16 = a.x16 + (a.wt ? a.xoff[m] : 0u);
+  float* y = a.y + (a.wt ? a.yoff[m] : 0u);
+
+  if (tid == 0) {
+    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdThreads), bar_init(&sh.empty[i], 1);
+    bar_init(&sh.done, 1);
+    sh.fail = 0;
+    bar_init_fence();
+  }
+  if (warp == (uint32_t) kIssuerWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sh.tmem_base)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  const Grids g = stage_grids<T>(tables);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sh.tmem_base;
+
+  if (warp >= (uint32_t) kFirstProdWarp) {
+    // ================= producers =================
+    const uint32_t pt = tid - kFirstProdWarp * kWarp;
+    for (uint32_t it = 0; it < steps; it++) {
+      const uint32_t stage = it % kStages, use = it / kStages;
+      if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
+        sh.fail = 1;
+        break;
+      }
+      uint8_t* sa = smem + stage * kStageBytes;
+      const uint32_t sb = smem_addr(sa + kStageA);
+      // B: token n's 8-value piece kc of this step, 16 bytes, to sub-tile (n / 128, kc / 2)
+      {
+        const uint32_t pieces = n_valid16 * (kStep / 8);
+        for (uint32_t i = pt; i < pieces; i += kProdThreads) {
+          const uint32_t kc = i & 7u, n = i >> 3, acc = n / kN, nn = n % kN;
+          cp_async16(sb + (acc * kSubs + (kc >> 1)) * kSubTile + (nn >> 3) * 256 + (kc & 1u) * 128 + (nn & 7u) * 16,
+                     x16 + mm_x16_at(c0 + n, it * kStep + kc * 8, a.xts));
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
+      // A: row r's chunk kc of this step decoded to 8 halves, 16 bytes, to sub-tile kc / 2 (a row past the matrix
+      // repeats the last row: computed, never stored)
+      for (uint32_t task = pt; task < (uint32_t) kM * (kStep / 8); task += kProdThreads) {
+        const uint32_t kc = task & 7u, r = task >> 3;
+        const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
+        const uint32_t cg = it * (kStep / kChunk) + kc;  // the chunk's index in its row
+        float v[kChunk];
+        decode8<T>(w + row * row_bytes + (uint64_t) (cg / Fmt<T>::chunks) * Fmt<T>::bytes, (int) (cg % Fmt<T>::chunks), v, g);
+        const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+        const __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+        uint4 out;
+        out.x = *(const uint32_t*) &h0, out.y = *(const uint32_t*) &h1, out.z = *(const uint32_t*) &h2, out.w = *(const uint32_t*) &h3;
+        *(uint4*) (sa + (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16) = out;
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      fence_async_smem();  // these writes before the tensor core's reads
+      bar_arrive(&sh.full[stage]);
+    }
+  } else if (warp == (uint32_t) kIssuerWarp) {
+    // ================= issuer =================
+    bool ok = true;
+    for (uint32_t it = 0; it < steps && !sh.fail; it++) {
+      const uint32_t stage = it % kStages, use = it / kStages;
+      if (!bar_wait(&sh.full[stage], use & 1u)) {
+        sh.fail = 1, ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        const uint32_t sa = smem_addr(smem + stage * kStageBytes), sb = sa + kStageA;
+        for (uint32_t acc = 0; acc < n_acc; acc++)
+          for (uint32_t q = 0; q < (uint32_t) kSubs; q++) {
+            const uint64_t da = tile_desc(sa + q * kSubTile), db = tile_desc(sb + (acc * kSubs + q) * kSubTile);
+            const uint32_t accumulate = (it | q) != 0 ? 1u : 0u;
+            asm volatile(
+                "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(
+                    tmem + acc * kN),
+                "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
+                : "memory");
+          }
+        // the stage's operands are free once these have run
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&sh.empty[stage]))
+                     : "memory");
+      }
+      __syncwarp();
+    }
+    if (ok && !sh.fail && lane == 0)
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&sh.done)) : "memory");
+    __syncwarp();
+  } else {
+    // ================= epilogue =================
+    const uint32_t row = 32u * warp + lane;  // this thread's weight row of the tile = its TMEM lane
+    const uint32_t lane_base = tmem + ((32u * warp) << 16);
+    if (!bar_wait(&sh.done, 0)) {
+      // (the K loop's own waits are 0.2 s each and can queue up: look again while nobody has given up)
+      bool landed = false;
+      for (uint32_t tries = 0; tries < 25u && !sh.fail && !landed; tries++) landed = bar_wait(&sh.done, 0);
+      if (!landed) sh.fail = 1;
+    }
+    if (!sh.fail) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (uint32_t acc = 0; acc < n_acc; acc++) {
+#pragma unroll 1
+        for (uint32_t c32 = 0; c32 < (uint32_t) kN; c32 += 32) {
+          if (acc * kN + c32 >= n_valid) break;
+          uint32_t r[32];
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+              "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+              : "r"(lane_base + acc * kN + c32)
+              : "memory");
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (row0 + row < a.rows) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+              const uint32_t t = acc * kN + c32 + i;
+              if (t < n_valid) {
+                const float v = __uint_as_float(r[i]);
+                y[(uint64_t) (c0 + t) * a.ys + row0 + row] = a.scale == 1.0f ? v : mul_rn(v, a.scale);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  // ================= common exit =================
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == (uint32_t) kIssuerWarp) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+  }
+  if (tid == 0 && sh.fail) atomicOr(a.status, 1u);
+}
+
+uint32_t* status_word() {
+  static uint32_t* at[64];
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return nullptr;
+  if (!at[d]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status) != cudaSuccess) return nullptr;
+    at[d] = (uint32_t*) p;
+  }
+  return at[d];
+}
+
+template <uint32_t T>
+bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
+  a.status = status_word();
+  if (!a.status) return false;
+  static bool sized = false;  // (one flag a template instance)
+  const int smem_bytes = kStages * kStageBytes;
+  if (!sized) {
+    if (cudaFuncSetAttribute(mm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return false;
+    sized = true;
+  }
+  const dim3 grid((a.rows + kM - 1) / kM, n_mat, (max_cnt + kMaxAcc * kN - 1) / (kMaxAcc * kN));
+  mm_tc_kernel<T><<<grid, kThreads, smem_bytes, s>>>(a);
+  return launched();
+}
+
+bool shape_ok(uint32_t type, uint32_t rows, uint32_t cols) {
+  const OsmosQTypeInfo* t = qtype_row(type);
+  return t && rows && rows % MM_TILE == 0 && cols && cols % 128 == 0 && cols % t->values == 0;
+}
+
+bool run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n, float* y, uint32_t ys,
+         float scale, void* stream) {
+  if (!w || !x16 || !y || !n || n > MM_MAX_TOKENS || !shape_ok(type, rows, cols) || (n > 1 && ys < rows)) return false;
+  if ((uintptr_t) x16 & 15u) return false;
+  Args a{};
+  a.w = (const uint8_t*) w, a.x16 = (const __half*) x16, a.y = y, a.rows = rows, a.cols = cols, a.n = n, a.xts = cols;
+  a.ys = ys, a.scale = scale;
+#define CASE(T) return launch<T>(a, 1, n, stream_of(stream));
+  OSMOS_SWITCH_QUANT(type, CASE, return false)
+#undef CASE
+}
+
+}  // namespace
+}  // namespace mm_tc
+}  // namespace osmos
+
+using namespace osmos;
+
+extern "C" bool mm_known(uint32_t type) { return qtype_row(type) != nullptr; }
+extern "C" bool mm_fits(uint32_t type, uint32_t rows, uint32_t cols) { return mm_tc::shape_ok(type, rows, cols); }
+extern "C" uint32_t mm_status(void) {
+  uint32_t* at = mm_tc::status_word();
+  if (!at) return 0x80000000u;
+  uint32_t v = 0, zero = 0;
+  if (cudaMemcpy(&v, at, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return 0x80000000u;
+  cudaMemcpy(at, &zero, sizeof zero, cudaMemcpyHostToDevice);
+  return v;
+}
+
+extern "C" bool mm_run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n, float* y,
+                       uint32_t ys, void* stream) {
+  return mm_tc::run(type, w, rows, cols, x16, n, y, ys, 1.0f, stream);
+}
+
+extern "C" bool mm_run2(uint32_t type, const void* w0, uint32_t rows0, float* y0, uint32_t ys0, const void* w1,
+                        uint32_t rows1, float* y1, uint32_t ys1, uint32_t cols, const void* x16, uint32_t n, void* stream) {
+  if (!w0 || !w1 || !y0 || !y1 || !x16 || !n || n > MM_MAX_TOKENS || !mm_tc::shape_ok(type, rows0, cols) ||
+      !mm_tc::shape_ok(type, rows1, cols) || (n > 1 && (ys0 < rows0 || ys1 < rows1)) || ((uintptr_t) x16 & 15u))
+    return false;  // (decided for both before either is queued)
+  return mm_tc::run(type, w0, rows0, cols, x16, n, y0, ys0, 1.0f, stream) &&
+         mm_tc::run(type, w1, rows1, cols, x16, n, y1, ys1, 1.0f, stream);
+}
+
+extern "C" bool mm_tokens_scaled(uint32_t type, const void* w0, uint32_t rows0, float* y0, uint32_t ys0, float s0,
+                                 const void* w1, uint32_t rows1, float* y1, uint32_t ys1, float s1, uint32_t cols,
+                                 const float* x, uint32_t xs, uint32_t n, void* x16, int32_t* overflow, bool ready,
+                                 void* stream) {
+  if (!w0 || !y0 || !x || !x16 || !overflow || !n || !mm_tc::shape_ok(type, rows0, cols) || (n > 1 && (xs < cols || ys0 < rows0)))
+    return false;
+  if (w1 && (!y1 || !mm_tc::shape_ok(type, rows1, cols) || (n > 1 && ys1 < rows1))) return false;
+  if ((uintptr_t) x16 & 15u) return false;
+  for (uint32_t t0 = 0; t0 < n; t0 += MM_MAX_TOKENS) {  // MM_MAX_TOKENS a time through the one x16
+    const uint32_t c = n - t0 < MM_MAX_TOKENS ? n - t0 : MM_MAX_TOKENS;
+    if (!(ready && n <= MM_MAX_TOKENS) && !mm_x16(x + (uint64_t) t0 * xs, xs, c, cols, x16, overflow, stream)) return false;
+    if (!mm_tc::run(type, w0, rows0, cols, x16, c, y0 + (uint64_t) t0 * ys0, ys0, s0, stream)) return false;
+    if (w1 && !mm_tc::run(type, w1, rows1, cols, x16, c, y1 + (uint64_t) t0 * ys1, ys1, s1, stream)) return false;
+  }
+  return true;
+}
+
+extern "C" bool mm_tokens(uint32_t type, const void* w0, uint32_t rows0, float* y0, uint32_t ys0, const void* w1,
+                          uint32_t rows1, float* y1, uint32_t ys1, uint32_t cols, const float* x, uint32_t xs, uint32_t n,
+                          void* x16, int32_t* overflow, bool ready, void* stream) {
+  return mm_tokens_scaled(type, w0, rows0, y0, ys0, 1.0f, w1, rows1, y1, ys1, 1.0f, cols, x, xs, n, x16, overflow, ready, stream);
+}
+
+extern "C" bool mm_group(uint32_t type, const void* const* w, const int32_t* cnt, uint32_t n_mat, uint32_t max_cnt,
+                         uint32_t rows, uint32_t cols, const void* x16, const uint32_t* xoff, uint32_t xts, float* y,
+                         const uint32_t* yoff, uint32_t ys, void* stream) {
+  if (!w || !cnt || !x16 || !xoff || !y || !yoff || !n_mat || n_mat > 65535 || !max_cnt || max_cnt > MM_MAX_TOKENS ||
+      !mm_tc::shape_ok(type, rows, cols) || xts < cols || xts % MM_TILE || ys < rows || ((uintptr_t) x16 & 15u))
+    return false;
+  mm_tc::Args a{};
+  a.wt = (const uint8_t* const*) w, a.cnt = cnt, a.xoff = xoff, a.yoff = yoff, a.x16 = (const __half*) x16, a.y = y;
+  a.rows = rows, a.cols = cols, a.xts = xts, a.ys = ys, a.scale = 1.0f;
+#define CASE(T) return mm_tc::launch<T>(a, n_mat, max_cnt, stream_of(stream));
+  OSMOS_SWITCH_QUANT(type, CASE, return false)
+#undef CASE
+}
