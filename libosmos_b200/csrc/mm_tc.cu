@@ -7,12 +7,14 @@
 // partitions; a token's column is computed from that column alone, so its bits do not depend on the tokens beside
 // it or on where in the batch it stands.
 //
-// A block computes 128 weight rows x up to 512 tokens of one matrix, so a weight is decoded once for 512 tokens.
-// Thirteen warps, three roles:
-//   producers (8 warps)  per 64-value step of K: decode the rows' 8-value chunks to f16 and store them as the A
+// A block computes 128 weight rows x 128, 256 or 512 tokens of one matrix (the most that still leaves every SM a
+// block), a weight decoded once a block.
+// Twenty-one warps, three roles:
+//   producers (16 warps) per 64-value step of K: decode the rows' 8-value chunks to f16 and store them as the A
 //                        operand (four K = 16 sub-tiles of 128 rows, K-major core matrices of 8 rows x 16 bytes), and
 //                        cp.async the tokens' 16-byte pieces of x16 into the same layout (B, four sub-tiles a
-//                        128-token accumulator); a proxy fence and an arrive on the stage's "full" mbarrier. Two stages.
+//                        128-token accumulator); a proxy fence and an arrive on the stage's "full" mbarrier. Two stages; the rows'
+//                        bytes reach the decoders through shared memory, 256 values of K at a time.
 //   issuer (1 warp)      per step and accumulator four tcgen05.mma M128 N128 K16 (the first of the whole K loop
 //                        overwrites, the rest accumulate), then tcgen05.commit onto the stage's "empty" mbarrier; after
 //                        the last step a commit onto "done".
@@ -32,7 +34,7 @@ using namespace tma;
 
 constexpr int kM = 128, kN = 128;  // rows a block; tokens an accumulator
 constexpr int kMaxAcc = 4;         // accumulators a block: 512 tokens
-constexpr int kEpiWarps = 4, kProdWarps = 8;
+constexpr int kEpiWarps = 4, kProdWarps = 16;
 constexpr int kIssuerWarp = kEpiWarps, kFirstProdWarp = kEpiWarps + 1;
 constexpr int kProdThreads = kProdWarps * kWarp;
 constexpr int kThreads = (kEpiWarps + 1 + kProdWarps) * kWarp;
@@ -40,8 +42,6 @@ constexpr int kStep = 64;                        // values of K a stage
 constexpr int kSubTile = kM * 32;                // one K = 16 operand sub-tile: 128 rows x 32 bytes
 constexpr int kSubs = kStep / 16;                // sub-tiles a stage an operand: 4
 constexpr int kStageA = kSubs * kSubTile;        // 16 KB
-constexpr int kStageB = kMaxAcc * kSubs * kSubTile;  // 64 KB
-constexpr int kStageBytes = kStageA + kStageB;
 constexpr int kStages = 2;
 
 __device__ uint32_t g_status;
@@ -65,6 +65,8 @@ struct Args {
   const __half* x16;
   float* y;
   uint32_t rows, cols, n, xts, ys;
+  uint32_t accs;  // accumulators (128 tokens each) a block: 1, 2 or 4
+  uint32_t stage_bytes, raw_off;  // an operand stage's bytes; where the raw weight buffers start
   float scale;
   uint32_t* status;
 };
@@ -81,10 +83,10 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
   __shared__ Shared sh;
   __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
-  const uint32_t m = blockIdx.y, row0 = blockIdx.x * kM, c0 = blockIdx.z * (kMaxAcc * kN);
+  const uint32_t m = blockIdx.y, row0 = blockIdx.x * kM, span = a.accs * kN, c0 = blockIdx.z * span;
   const uint32_t n_tok = a.wt ? (uint32_t) (a.cnt[m] > 0 ? a.cnt[m] : 0) : a.n;
   if (c0 >= n_tok) return;  // the whole block, before anything is allocated
-  const uint32_t n_valid = n_tok - c0 < (uint32_t) (kMaxAcc * kN) ? n_tok - c0 : (uint32_t) (kMaxAcc * kN);
+  const uint32_t n_valid = n_tok - c0 < span ? n_tok - c0 : span;
   const uint32_t n_valid16 = (n_valid + 15u) & ~15u;  // x16 holds whole tiles of 16 tokens
   const uint32_t n_acc = (n_valid + kN - 1) / kN;
   const uint32_t steps = a.cols / kStep;
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
   float* y = a.y + (a.wt ? a.yoff[m] : 0u);
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdThreads), bar_init(&sh.empty[i], 1);
+    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdWarps), bar_init(&sh.empty[i], 1);
     bar_init(&sh.done, 1);
     sh.fail = 0;
     bar_init_fence();
@@ -111,43 +113,77 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
 
   if (warp >= (uint32_t) kFirstProdWarp) {
     // ================= producers =================
+    // The rows' bytes come through shared memory 256 values of K at a time: 16-byte cp.async pieces of the aligned
+    // span around each row's bytes (a block may start anywhere in a 16-byte piece), two buffers, the next 256 values
+    // on their way while these are decoded - so the decoders' many narrow reads are shared-memory reads.
     const uint32_t pt = tid - kFirstProdWarp * kWarp;
+    constexpr uint32_t kKb = 256, kKbBytes = kKb / Fmt<T>::values * Fmt<T>::bytes, kSlot = (kKbBytes + 30u + 15u) & ~15u;
+    constexpr uint32_t kPieces = kSlot / 16;
+    uint8_t* raw = smem + a.raw_off;
+    const uint8_t* w_end = w + (uint64_t) a.rows * row_bytes;
+    const uint32_t kblocks = (a.cols + kKb - 1) / kKb;
+    auto fetch_raw = [&](uint32_t kb) {  // the rows' bytes of K block kb into buffer kb % 2
+      uint8_t* buf = raw + (kb & 1u) * (kM * kSlot);
+      for (uint32_t i = pt; i < (uint32_t) kM * kPieces; i += kProdThreads) {
+        const uint32_t r = i / kPieces, piece = i - r * kPieces;
+        const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
+        const uint8_t* src = (const uint8_t*) ((uintptr_t) (w + row * row_bytes + (uint64_t) kb * kKbBytes) & ~(uintptr_t) 15) + piece * 16u;
+        const uint32_t have = src >= w_end ? 0u : (w_end - src < 16 ? (uint32_t) (w_end - src) : 16u);  // (zero fill past the tensor)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(buf + r * kSlot + piece * 16u)), "l"(src), "r"(have)
+                     : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // B: token n's 8-value piece kc of step `it`, 16 bytes, to sub-tile (n / 128, kc / 2) of the step's stage
+    auto fetch_b = [&](uint32_t it) {
+      const uint32_t sb = smem_addr(smem + (it % kStages) * a.stage_bytes + kStageA);
+      const uint32_t pieces = n_valid16 * (kStep / 8);
+      for (uint32_t i = pt; i < pieces; i += kProdThreads) {
+        // (eight neighbouring threads: one K piece of eight neighbouring tokens - eight different 16-byte bank
+        // columns of the operand tile, so a store takes no more passes than its bytes need)
+        const uint32_t kc = (i >> 3) & 7u, n = (i >> 6) * 8u + (i & 7u), acc = n / kN, nn = n % kN;
+        cp_async16(sb + (acc * kSubs + (kc >> 1)) * kSubTile + (nn >> 3) * 256 + (kc & 1u) * 128 + (nn & 7u) * 16,
+                   x16 + mm_x16_at(c0 + n, it * kStep + kc * 8, a.xts));
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    bool dead = false;  // a wait ran out: no more work, but the producers' own barrier is still kept
+    fetch_raw(0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     for (uint32_t it = 0; it < steps; it++) {
-      const uint32_t stage = it % kStages, use = it / kStages;
-      if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
-        sh.fail = 1;
-        break;
-      }
-      uint8_t* sa = smem + stage * kStageBytes;
-      const uint32_t sb = smem_addr(sa + kStageA);
-      // B: token n's 8-value piece kc of this step, 16 bytes, to sub-tile (n / 128, kc / 2)
-      {
-        const uint32_t pieces = n_valid16 * (kStep / 8);
-        for (uint32_t i = pt; i < pieces; i += kProdThreads) {
-          const uint32_t kc = i & 7u, n = i >> 3, acc = n / kN, nn = n % kN;
-          cp_async16(sb + (acc * kSubs + (kc >> 1)) * kSubTile + (nn >> 3) * 256 + (kc & 1u) * 128 + (nn & 7u) * 16,
-                     x16 + mm_x16_at(c0 + n, it * kStep + kc * 8, a.xts));
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-      }
+      const uint32_t stage = it % kStages, use = it / kStages, kb = it / (kKb / kStep), sub = it % (kKb / kStep);
+      if (sub == 0) asm volatile("bar.sync 1, %0;" ::"n"(kProdThreads) : "memory");  // block kb has landed; kb - 1 is done with
+      if (!dead && use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) sh.fail = 1, dead = true;
+      if (dead) continue;
+      fetch_b(it);
+      const bool ahead = sub == 0 && kb + 1 < kblocks;
+      if (ahead) fetch_raw(kb + 1);
       // A: row r's chunk kc of this step decoded to 8 halves, 16 bytes, to sub-tile kc / 2 (a row past the matrix
       // repeats the last row: computed, never stored)
+      uint8_t* sa = smem + stage * a.stage_bytes;
+      const uint8_t* buf = raw + (kb & 1u) * (kM * kSlot);
+#pragma unroll
       for (uint32_t task = pt; task < (uint32_t) kM * (kStep / 8); task += kProdThreads) {
-        const uint32_t kc = task & 7u, r = task >> 3;
+        const uint32_t kc = (task >> 3) & 7u, r = (task >> 6) * 8u + (task & 7u);  // (the same dealing as B's)
         const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
-        const uint32_t cg = it * (kStep / kChunk) + kc;  // the chunk's index in its row
+        const uint32_t lead = (uint32_t) ((uintptr_t) (w + row * row_bytes + (uint64_t) kb * kKbBytes) & 15u);
+        const uint32_t cl = sub * (kStep / kChunk) + kc;  // the chunk's index in its K block
         float v[kChunk];
-        decode8<T>(w + row * row_bytes + (uint64_t) (cg / Fmt<T>::chunks) * Fmt<T>::bytes, (int) (cg % Fmt<T>::chunks), v, g);
+        decode8<T>(buf + r * kSlot + lead + (cl / Fmt<T>::chunks) * Fmt<T>::bytes, (int) (cl % Fmt<T>::chunks), v, g);
         const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
         const __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
         uint4 out;
         out.x = *(const uint32_t*) &h0, out.y = *(const uint32_t*) &h1, out.z = *(const uint32_t*) &h2, out.w = *(const uint32_t*) &h3;
         *(uint4*) (sa + (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16) = out;
       }
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      // this step's activations have landed (the next block's bytes, asked for after them, may still be on their way)
+      if (ahead) asm volatile("cp.async.wait_group 1;" ::: "memory");
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
       fence_async_smem();  // these writes before the tensor core's reads
-      bar_arrive(&sh.full[stage]);
+      __syncwarp();
+      if (lane == 0) bar_arrive(&sh.full[stage]);  // (one arrival a warp: 512 would queue on the one word)
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else if (warp == (uint32_t) kIssuerWarp) {
     // ================= issuer =================
     bool ok = true;
@@ -159,7 +195,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (lane == 0) {
-        const uint32_t sa = smem_addr(smem + stage * kStageBytes), sb = sa + kStageA;
+        const uint32_t sa = smem_addr(smem + stage * a.stage_bytes), sb = sa + kStageA;
         for (uint32_t acc = 0; acc < n_acc; acc++)
           for (uint32_t q = 0; q < (uint32_t) kSubs; q++) {
             const uint64_t da = tile_desc(sa + q * kSubTile), db = tile_desc(sb + (acc * kSubs + q) * kSubTile);
@@ -246,13 +282,28 @@ template <uint32_t T>
 bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   a.status = status_word();
   if (!a.status) return false;
+  // tokens a block: as many accumulators (a weight is decoded once a block) as still leave a block for every SM and
+  // fit shared memory beside the two raw weight buffers
+  int sms = 0, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return false;
+  constexpr uint32_t kSlot = ((256u / Fmt<T>::values * Fmt<T>::bytes) + 30u + 15u) & ~15u, kLimit = 224u * 1024u - (uint32_t) ((grid_smem_bytes<T>() + 1023) / 1024 * 1024);
+  const uint32_t row_tiles = (a.rows + kM - 1) / kM;
+  auto smem_for = [&](uint32_t k) { return kStages * (kStageA + k * kSubs * kSubTile) + 2u * kM * kSlot; };
+  a.accs = 1;
+  for (uint32_t k = kMaxAcc; k > 1; k >>= 1)
+    if (smem_for(k) <= kLimit && (uint64_t) row_tiles * n_mat * ((max_cnt + k * kN - 1) / (k * kN)) >= (uint64_t) sms) {
+      a.accs = k;
+      break;
+    }
+  a.stage_bytes = kStageA + a.accs * kSubs * kSubTile, a.raw_off = kStages * a.stage_bytes;
+  const int smem_bytes = (int) smem_for(a.accs);
   static bool sized = false;  // (one flag a template instance)
-  const int smem_bytes = kStages * kStageBytes;
   if (!sized) {
-    if (cudaFuncSetAttribute(mm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(mm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kLimit) != cudaSuccess) return false;
     sized = true;
   }
-  const dim3 grid((a.rows + kM - 1) / kM, n_mat, (max_cnt + kMaxAcc * kN - 1) / (kMaxAcc * kN));
+  const dim3 grid(row_tiles, n_mat, (max_cnt + a.accs * kN - 1) / (a.accs * kN));
   mm_tc_kernel<T><<<grid, kThreads, smem_bytes, s>>>(a);
   return launched();
 }

@@ -4,6 +4,8 @@ reference keeps such sweeps under tools/bench/).
     python -m libosmos_b200.kbench q8_run Q4_0 49152 2048            # one token, graph-timed
     python -m libosmos_b200.kbench mv_run Q8_0 6144 2048 --tokens 2
     python -m libosmos_b200.kbench q8_run Q4_0 49152 2048 --plain 4  # four plain launches, nothing timed (for a profiler)
+    python -m libosmos_b200.kbench mm_run Q4_K 4096 4096 --tokens 512  # the f16 prefill product (x16 made once)
+    python -m libosmos_b200.kbench mmq_group Q4_K 4096 4096 --tokens 512  # the int8 prefill product (x8 made once)
 
 Timing: 64 launches on successive cold copies of the matrix (more than 1 GiB cycled, so every launch reads HBM)
 captured in one CUDA graph and replayed 5 times; CUDA events around the replays; device time a launch.
@@ -20,7 +22,7 @@ from libosmos_b200 import synth
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["mv_run", "q8_run"])
+    ap.add_argument("op", choices=["mv_run", "q8_run", "mm_run", "mmq_group"])
     ap.add_argument("type")
     ap.add_argument("rows", type=int)
     ap.add_argument("cols", type=int)
@@ -42,7 +44,30 @@ def main():
     if args.generic:
         lib.mv_set_staged(0), lib.q8_set_staged(0)
     assert lib.q8_round(x.data_ptr(), args.tokens, args.cols, args.cols, q.data_ptr(), d.data_ptr(), None)
-    if args.op == "q8_run":
+    flops = None
+    if args.op in ("mm_run", "mmq_group"):
+        n16 = (args.tokens + 15) // 16 * 16
+        flops = 2.0 * args.rows * args.cols * args.tokens
+        if args.op == "mm_run":
+            x16 = torch.zeros(n16 * args.cols, dtype=torch.float16, device=dev)
+            flag = torch.zeros(1, dtype=torch.int32, device=dev)
+            assert lib.mm_x16(x.data_ptr(), args.cols, args.tokens, args.cols, x16.data_ptr(), flag.data_ptr(), None)
+            fn = lambda i, st: lib.mm_run(tid, pool.data_ptr() + (i % copies) * nb, args.rows, args.cols, x16.data_ptr(),
+                                          args.tokens, y.data_ptr(), args.rows, st)
+        else:
+            idx = torch.arange(args.tokens, dtype=torch.int32, device=dev)
+            x8 = torch.zeros(n16 * args.cols, dtype=torch.int8, device=dev)
+            dx = torch.zeros(n16 * args.cols // 32, device=dev)
+            sx = torch.zeros_like(dx)
+            assert lib.mmq_x8_rows(x.data_ptr(), args.cols, idx.data_ptr(), args.tokens, args.cols, x8.data_ptr(),
+                                   dx.data_ptr(), sx.data_ptr(), None)
+            tabs = [torch.tensor([pool.data_ptr() + c * nb], dtype=torch.int64, device=dev) for c in range(copies)]
+            cnt = torch.tensor([args.tokens], dtype=torch.int32, device=dev)
+            zero = torch.zeros(1, dtype=torch.int32, device=dev)
+            fn = lambda i, st: lib.mmq_group(tid, tabs[i % copies].data_ptr(), cnt.data_ptr(), 1, args.tokens, args.rows,
+                                             args.cols, x8.data_ptr(), dx.data_ptr(), sx.data_ptr(), zero.data_ptr(),
+                                             y.data_ptr(), zero.data_ptr(), args.rows, st)
+    elif args.op == "q8_run":
         fn = lambda i, st: lib.q8_run(tid, pool.data_ptr() + (i % copies) * nb, args.rows, args.cols, q.data_ptr(),
                                       d.data_ptr(), args.tokens, y.data_ptr(), args.rows, st)
     else:
@@ -52,7 +77,7 @@ def main():
         if not fn(i, None):
             raise SystemExit("the library refused the call")
     torch.cuda.synchronize()
-    status = lib.q8_status() | lib.mv_status()
+    status = lib.q8_status() | lib.mv_status() | lib.mm_status() | lib.mmq_status()
     if args.plain:
         print("%d launches, status %d" % (args.plain, status))
         return
@@ -72,7 +97,8 @@ def main():
     us = e0.elapsed_time(e1) * 1e3 / (n * reps)
     print(json.dumps({"op": args.op, "type": args.type, "rows": args.rows, "cols": args.cols, "tokens": args.tokens,
                       "kernels": "generic" if args.generic else "default", "us_per_launch": us,
-                      "weight_bytes": nb, "weight_gbs": nb / us / 1e3, "status": status | lib.q8_status() | lib.mv_status()}))
+                      "weight_bytes": nb, "weight_gbs": nb / us / 1e3, "tflops": None if flops is None else flops / us / 1e6,
+                      "status": status | lib.q8_status() | lib.mv_status() | lib.mm_status() | lib.mmq_status()}))
 
 
 if __name__ == "__main__":
