@@ -89,8 +89,9 @@ __device__ __forceinline__ void sub_codes(uint32_t sb, const LaneAt& at, LaneCod
   }
 }
 
-// L: lanes a row; NB: blocks a lane holds at most; NT: tokens a task carries
-template <uint32_t T, bool FUSED, int L, int NB, int NT>
+// L: lanes a row; NB: blocks a lane holds at most (EXACT: exactly - no test a block, so the blocks' loads can be
+// scheduled together); NT: tokens a task carries
+template <uint32_t T, bool FUSED, int L, int NB, int NT, bool EXACT>
 __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full[kWarps][kMaxSlots];
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
     constexpr int NTL = decltype(live_tag)::value;
 #pragma unroll
     for (int k = 0; k < NB; k++) {
-      if ((uint32_t) k < nbl) {
+      if (EXACT || (uint32_t) k < nbl) {
         LaneCodes c;
         sub_codes<T>(ra + sboff[k], at, c, luts);
 #pragma unroll
@@ -276,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
       for (int k = 0; k < NB; k++) {
         int4 lo = make_int4(0, 0, 0, 0), hi = lo;
         float dv = 0.0f;
-        if ((uint32_t) k < nbl) {
+        if (EXACT || (uint32_t) k < nbl) {
           const uint32_t s = sub + (uint32_t) L * k;
           const int4* xp = (const int4*) (a.q + xr * a.cols + s * 32u);
           lo = __ldg(xp), hi = __ldg(xp + 1), dv = __ldg(a.d + xr * nblk + s);
@@ -339,7 +340,7 @@ const Device* device_info() {
   return &devs[d];
 }
 
-template <uint32_t T, bool FUSED, int L, int NB, int NT>
+template <uint32_t T, bool FUSED, int L, int NB, int NT, bool EXACT>
 int launch(const Request& r, cudaStream_t s) {
   const Device* dev = device_info();
   if (!dev) return 0;
@@ -371,7 +372,7 @@ int launch(const Request& r, cudaStream_t s) {
   a.status = dev->status;
   const uint32_t total = a.ring_off + kWarps * slots * slot_bytes + 16u;
   static bool sized = false;  // (one flag a template instance)
-  auto kernel = lane_ring_kernel<T, FUSED, L, NB, NT>;
+  auto kernel = lane_ring_kernel<T, FUSED, L, NB, NT, EXACT>;
   if (!sized) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit) != cudaSuccess) return 0;
     sized = true;
@@ -386,14 +387,16 @@ int by_shape(const Request& r, cudaStream_t s) {
   if (r.cols < 4096) {
     if (nblk % 16) return 0;
     const uint32_t per = nblk / 16;
-    if (per == 1) return launch<T, FUSED, 16, 1, 2>(r, s);
-    if (per <= 4) return launch<T, FUSED, 16, 4, 2>(r, s);
+    if (per == 1) return launch<T, FUSED, 16, 1, 2, true>(r, s);
+    if (per == 4) return launch<T, FUSED, 16, 4, 2, true>(r, s);
+    if (per < 4) return launch<T, FUSED, 16, 4, 2, false>(r, s);
     return 0;
   }
   if (nblk % 32) return 0;
   const uint32_t per = nblk / 32;
-  if (per <= 4) return launch<T, FUSED, 32, 4, 2>(r, s);
-  if (per <= 8) return launch<T, FUSED, 32, 8, 1>(r, s);
+  if (per == 4) return launch<T, FUSED, 32, 4, 2, true>(r, s);
+  if (per < 4) return launch<T, FUSED, 32, 4, 2, false>(r, s);
+  if (per <= 8) return launch<T, FUSED, 32, 8, 1, false>(r, s);
   return 0;
 }
 
