@@ -200,6 +200,17 @@ __global__ void __launch_bounds__(kThreads) place_kernel(const int32_t* __restri
 }
 
 // ---- the int8 lane's tables (include/osmos_b200/lane.h) -----------------------------------------------------------
+__device__ __forceinline__ void order_token(const int32_t* row_of, uint32_t t, uint32_t k, int32_t* order) {
+  int32_t r[kMaxK];
+  for (uint32_t j = 0; j < k; j++) r[j] = row_of[t * k + j];
+  for (uint32_t a = 1; a < k; a++)
+    for (uint32_t c = a; c > 0 && (uint32_t) r[c] < (uint32_t) r[c - 1]; c--) {
+      const int32_t s = r[c];
+      r[c] = r[c - 1], r[c - 1] = s;
+    }
+  for (uint32_t j = 0; j < k; j++) order[t * k + j] = r[j];
+}
+
 __global__ void __launch_bounds__(kTableThreads) lane_tables_kernel(const int32_t* __restrict__ ids, uint32_t n,
                                                                     uint32_t k, uint32_t n_exp, const LaneExperts ex,
                                                                     const LaneTables t, uint32_t e0, uint32_t e1) {
@@ -245,6 +256,9 @@ __global__ void __launch_bounds__(kTableThreads) lane_tables_kernel(const int32_
     const int r = first_row[id] + rank_inline(sids, i);
     t.tok[r] = (int32_t) (i / k), t.pair[r] = (int32_t) i, t.row_of[i] = r;
   }
+  // each token's rows in order, in the same launch (the block's own writes, after its barrier)
+  __syncthreads();
+  for (uint32_t tk = threadIdx.x; tk < n / k; tk += kTableThreads) order_token(t.row_of, tk, k, t.order);
 }
 
 __global__ void __launch_bounds__(kThreads) lane_place_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_t k,
@@ -270,14 +284,7 @@ __global__ void lane_order_kernel(const int32_t* __restrict__ row_of, uint32_t n
                                   int32_t* __restrict__ order) {
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tok) return;
-  int32_t r[kMaxK];
-  for (uint32_t j = 0; j < k; j++) r[j] = row_of[t * k + j];
-  for (uint32_t a = 1; a < k; a++)
-    for (uint32_t c = a; c > 0 && (uint32_t) r[c] < (uint32_t) r[c - 1]; c--) {
-      const int32_t s = r[c];
-      r[c] = r[c - 1], r[c - 1] = s;
-    }
-  for (uint32_t j = 0; j < k; j++) order[t * k + j] = r[j];
+  order_token(row_of, t, k, order);
 }
 
 // ---- activation and combine ------------------------------------------------------------------------------------
@@ -428,6 +435,6 @@ extern "C" bool lane_tables(const int32_t* ids, uint32_t n, uint32_t k, uint32_t
     lane_place_kernel<<<n_exp, kThreads, 0, s>>>(ids, n, k, n_exp, *t, expert0, expert1);
     if (!launched()) return false;
   }
-  lane_order_kernel<<<blocks_for(n / k, 128), 128, 0, s>>>(t->row_of, n / k, k, t->order);
+  if (n > kInlinePicks) lane_order_kernel<<<blocks_for(n / k, 128), 128, 0, s>>>(t->row_of, n / k, k, t->order);
   return launched();
 }

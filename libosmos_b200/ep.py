@@ -110,10 +110,10 @@ class EpMoeLane:
         self.peer = None
         if transport == "peer":
             self.peer = PeerBuffers(lib, dist, dev, rank, world, self.seg.bytes, self.T * self.k * self.dim * 4)
-            # route, round, push, wait, unpack, tables, order, gate_up, round, down, scatter, wait, combine
-            self.kernels_per_step = 13
+            # route, round, push, wait, unpack, tables, gate_up, round, down, scatter, wait, combine
+            self.kernels_per_step = 12
         else:
-            self.kernels_per_step = 10  # route, round, unpack, tables, order, gate_up, round, down, scatter, combine
+            self.kernels_per_step = 9  # route, round, unpack, tables, gate_up, round, down, scatter, combine
 
     def close(self):
         if self.peer:

@@ -48,7 +48,7 @@ class MoeLane:
         self.ids = torch.zeros(picks, dtype=torch.int32, device=dev)
         self.wts = torch.zeros(picks, dtype=torch.float32, device=dev)
         self.rows = torch.zeros(picks, dtype=torch.int32, device=dev)
-        self.kernels_per_step = 8  # route, tables, order, round, gate_up, round, down, sum
+        self.kernels_per_step = 7  # route, tables (with the order), round, gate_up, round, down, sum
 
     def weight_bytes(self):
         return sum(t.numel() for t in self.weights[0])
