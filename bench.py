@@ -213,8 +213,6 @@ def run_ours(args):
     px = [torch.from_numpy(a).pin_memory() for a in hx]
     pl = [torch.from_numpy(a).pin_memory() for a in hl]
     out = torch.empty((n_tok, dim), dtype=torch.float32, device=dev)
-    pout = torch.empty((n_tok, dim), dtype=torch.float32).pin_memory()
-    sx, sl = torch.empty_like(dx[0]), torch.empty_like(dl[0])
     stream = torch.cuda.current_stream().cuda_stream
 
     # parity first: step 0 against the CPU oracle on a few tokens (the GPU tests hold the rest)
@@ -229,12 +227,14 @@ def run_ours(args):
         raise SystemExit("bench: the GPU layer's output differs from the CPU oracle's bits - not timing a wrong result")
     distinct = [len(np.unique(workloads.softmax_topk(l, cfg["k"])[0])) for l in hl]
 
-    def timed(fn, steps):
+    def timed(fn, steps, drain=None):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
         for s in range(steps):
             fn(s)
+        if drain:
+            drain()  # the side streams' last copies are inside the timed region
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / 1e3
@@ -242,17 +242,69 @@ def run_ours(args):
     def resident(s):
         layer.step(dx[s % n_inputs], dl[s % n_inputs], out, n_tok, s % copies, stream)
 
+    # end to end: every step's inputs come from pinned host memory and its output goes back to it, the copies on
+    # their own streams so that step s + 1's inputs and step s - 1's output move while step s computes (two buffers
+    # of each; events order a buffer's copy, its use and its reuse)
+    cin, cout = torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    bx = [torch.empty_like(dx[0]) for _ in range(2)]
+    bl = [torch.empty_like(dl[0]) for _ in range(2)]
+    bo = [torch.empty_like(out) for _ in range(2)]
+    bp = [torch.empty((n_tok, dim), dtype=torch.float32).pin_memory() for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    used = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    for e in used + out_done:
+        e.record(main)
+
     def end_to_end(s):
-        sx.copy_(px[s % n_inputs], non_blocking=True)
-        sl.copy_(pl[s % n_inputs], non_blocking=True)
-        layer.step(sx, sl, out, n_tok, s % copies, stream)
-        pout.copy_(out, non_blocking=True)
+        b = s & 1
+        cin.wait_event(used[b])  # the step that last read these input buffers is done
+        with torch.cuda.stream(cin):
+            bx[b].copy_(px[s % n_inputs], non_blocking=True)
+            bl[b].copy_(pl[s % n_inputs], non_blocking=True)
+            in_ready[b].record(cin)
+        main.wait_event(in_ready[b])
+        main.wait_event(out_done[b])  # the last output in bo[b] has reached the host
+        layer.step(bx[b], bl[b], bo[b], n_tok, s % copies, stream)
+        used[b].record(main)
+        cout.wait_event(used[b])
+        with torch.cuda.stream(cout):
+            bp[b].copy_(bo[b], non_blocking=True)
+            out_done[b].record(cout)
+
+    def e2e_drain():
+        main.wait_stream(cin), main.wait_stream(cout)
 
     for s in range(args.warmup):
         resident(s), end_to_end(s)
+    # the resident step as a user of the C ABI would run a decode loop: captured once per (input, weight copy) pair in
+    # a CUDA graph and replayed - the same seven launches, without the host's launch gaps
+    torch.cuda.synchronize()
+    graphs, side = [], torch.cuda.Stream()
+    for s in range(n_inputs):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            layer.step(dx[s], dl[s], out, n_tok, s % copies, side.cuda_stream)
+        graphs.append(g)
+
+    def resident_graph(s):
+        graphs[s % n_inputs].replay()
+
+    for s in range(args.warmup):
+        resident_graph(s)
+    torch.cuda.synchronize()
+    layer.step(dx[1], dl[1], out, n_tok, 1 % copies, stream)
+    torch.cuda.synchronize()
+    plain_bits = out.cpu().numpy().view(np.uint32).copy()
+    resident_graph(1)
+    torch.cuda.synchronize()
+    if not np.array_equal(plain_bits, out.cpu().numpy().view(np.uint32)):
+        raise SystemExit("bench: the graph-replayed step differs from the stream-launched one")
     with ClockSampler(local) as clocks:
-        t_res = timed(resident, args.steps)
-        t_e2e = timed(end_to_end, args.steps)
+        t_res = timed(resident_graph, args.steps)
+        t_res_stream = timed(resident, args.steps)
+        t_e2e = timed(end_to_end, args.steps, e2e_drain)
         # the dominant kernel alone: events around q8_gate_up inside the same step
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
         torch.cuda.synchronize()
@@ -286,10 +338,12 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
             "config": {"workload": cfg["name"], "tokens": n_tok, "experts": cfg["n_exp"], "top_k": cfg["k"], "hidden": dim,
                        "expert_ff": cfg["ff"], "format": cfg["type"], "parallelism": "1 gpu",
+                       "launch": "value: CUDA graph replay, one graph a (input, weight copy) pair; the same steps launched "
+                                 "on the stream take %.4f ms" % (1e3 * t_res_stream / args.steps),
                        "cold_cache": "%d copies of the layer's 616 MB of weights cycled; each step touches ~%d MB > 126 MB L2"
                                      % (copies, int(np.mean(distinct)) * sum(per) // 1000000)},
             "e2e": {"value": n_tok * args.steps / t_e2e, "unit": UNIT,
-                    "h2d_bytes_per_step": int(px[0].numel() * 4 + pl[0].numel() * 4), "d2h_bytes_per_step": int(pout.numel() * 4)},
+                    "h2d_bytes_per_step": int(px[0].numel() * 4 + pl[0].numel() * 4), "d2h_bytes_per_step": int(bp[0].numel() * 4)},
             "gpu_launches": layer.kernels_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": "q8_gate_up (lane_ring_kernel, IQ3_XXS, fused gate + up + activation)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
