@@ -36,18 +36,25 @@ def send_slot(pick, k, tokens_per_rank):
     return (t // tokens_per_rank) * tokens_per_rank * k + (t % tokens_per_rank) * k + j
 
 
+def peer_layout(world, seg_bytes, block_bytes):
+    """byte offsets inside a rank's exchange buffer: the two flag arrays (dispatch, combine; a word a sender), the two
+    halves of gathered segments (a segment a sender), the two halves of received row blocks (a block a sender); and
+    the buffer's size. Every region starts on 256 bytes."""
+    up = lambda v: (v + 255) // 256 * 256
+    off_flag = [0, 256]
+    off_seg = [512 + p * up(world * seg_bytes) for p in range(2)]
+    base_recv = 512 + 2 * up(world * seg_bytes)
+    off_recv = [base_recv + p * up(world * block_bytes) for p in range(2)]
+    return off_flag, off_seg, off_recv, base_recv + 2 * up(world * block_bytes)
+
+
 class PeerBuffers:
     """Every rank's exchange buffer, mapped into this process: [dispatch flags][combine flags][2 halves of gathered
     segments][2 halves of received rows]; and the device tables of addresses the pushing kernels take."""
 
     def __init__(self, lib, dist, dev, rank, world, seg_bytes, block_bytes):
         self.lib, self.rank, self.world = lib, rank, world
-        up = lambda v: (v + 255) // 256 * 256
-        self.off_flag = [0, 256]
-        self.off_seg = [512 + p * up(world * seg_bytes) for p in range(2)]
-        base_recv = 512 + 2 * up(world * seg_bytes)
-        self.off_recv = [base_recv + p * up(world * block_bytes) for p in range(2)]
-        total = base_recv + 2 * up(world * block_bytes)
+        self.off_flag, self.off_seg, self.off_recv, total = peer_layout(world, seg_bytes, block_bytes)
         mine, handle = C.c_void_p(), (C.c_uint8 * 64)()
         if not lib.ep_peer_alloc(total, C.byref(mine), handle):
             raise RuntimeError("ep_peer_alloc failed")

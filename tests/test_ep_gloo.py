@@ -92,3 +92,19 @@ def test_sharding_rules():
     slots = [ep.send_slot(i, k, T) for i in range(world * T * k)]
     assert sorted(slots) == list(range(world * T * k))
     assert all(ep.send_slot(i, k, T) // (T * k) == (i // k) // T for i in range(world * T * k))
+
+
+def test_peer_buffer_layout_regions_do_not_overlap():
+    """the exchange buffer every rank maps: flags, two halves of segments, two halves of row blocks - each sender its
+    own piece of each, nothing overlapping, everything 16-byte aligned (the pushing kernels store 16 bytes at a time)"""
+    from libosmos_b200 import ep
+    for world, seg, blk in ((2, 78000 // 16 * 16, 32 * 10 * 2048 * 4), (8, 19600 // 16 * 16, 8 * 10 * 2048 * 4), (16, 4800, 4 * 8 * 512 * 4)):
+        flag, segs, recv, total = ep.peer_layout(world, seg, blk)
+        spans = [(flag[0], world * 4), (flag[1], world * 4)]
+        spans += [(segs[p] + r * seg, seg) for p in range(2) for r in range(world)]
+        spans += [(recv[p] + r * blk, blk) for p in range(2) for r in range(world)]
+        spans.sort()
+        for (a, n), (b, _) in zip(spans, spans[1:]):
+            assert a + n <= b
+        assert spans[-1][0] + spans[-1][1] <= total and all(a % 16 == 0 for a, _ in spans[2:])
+        assert world * 4 <= 256
