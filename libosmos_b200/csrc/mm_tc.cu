@@ -57,6 +57,65 @@ __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
 // instruction descriptor: D F32, A and B f16, both K-major, N = 128, M = 128
 constexpr uint32_t kIdesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t) (kN >> 3) << 17) | ((uint32_t) (kM >> 4) << 24);
 
+// ---- the common types' chunks straight to f16 -----------------------------------------------------------------
+// Eight values of a block whose bytes lie in shared memory at `blk` (4-byte aligned here), as eight f16 in a uint4:
+// the same F32 value decode8 gives (each product rounded once), then rounded to f16. Small integers reach F32 by a
+// byte permute (byte n into bits 8 .. 15 of 0x47000000 = 32768 + n), and a product d n as fmaf(d, 32768 + n,
+// -32768 d): the subtrahend is a power of two times d, so the one rounding is the product's own.
+template <int J> __device__ __forceinline__ float biased(uint32_t bytes) {
+  return __uint_as_float(__byte_perm(bytes, 0x47000000u, 0x7404 | (J << 4)));
+}
+__device__ __forceinline__ uint32_t half2_bits(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *(const uint32_t*) &h;
+}
+template <uint32_t T> constexpr bool kFastChunk = (T == QTYPE_Q4_K || T == QTYPE_Q4_0 || T == QTYPE_Q8_0);
+
+template <uint32_t T>
+__device__ __forceinline__ uint4 fast_chunk(const uint8_t* blk, uint32_t k) {
+  uint4 out;
+  if constexpr (T == QTYPE_Q4_K) {
+    // chunk k of the 256-value block: group k / 4 (its 6-bit scale and min out of the 12 packed bytes), values
+    // 8 (k % 4) .. of the group: the low (even group) or high nibbles of 8 bytes
+    const uint32_t* wp = (const uint32_t*) blk;
+    const uint32_t grp = k >> 2, b8 = 8u * (grp & 3u);
+    const uint32_t hd = wp[0], a0 = (wp[1] >> b8) & 0xFFu, a1 = (wp[2] >> b8) & 0xFFu, a2 = (wp[3] >> b8) & 0xFFu;
+    const uint32_t sc = grp < 4 ? a0 & 63u : (a2 & 0x0Fu) | ((a0 >> 6) << 4);
+    const uint32_t mn = grp < 4 ? a1 & 63u : (a2 >> 4) | ((a1 >> 6) << 4);
+    const float ds = mul_rn(half_value(hd & 0xFFFFu), (float) sc), dm = mul_rn(half_value(hd >> 16), (float) mn);
+    const float c = mul_rn(ds, -32768.0f);
+    const uint32_t* q = wp + 4 + (grp >> 1) * 8 + (k & 3u) * 2;
+    const uint32_t s4 = 4u * (grp & 1u), m0 = (q[0] >> s4) & 0x0F0F0F0Fu, m1 = (q[1] >> s4) & 0x0F0F0F0Fu;
+    out.x = half2_bits(__fsub_rn(__fmaf_rn(ds, biased<0>(m0), c), dm), __fsub_rn(__fmaf_rn(ds, biased<1>(m0), c), dm));
+    out.y = half2_bits(__fsub_rn(__fmaf_rn(ds, biased<2>(m0), c), dm), __fsub_rn(__fmaf_rn(ds, biased<3>(m0), c), dm));
+    out.z = half2_bits(__fsub_rn(__fmaf_rn(ds, biased<0>(m1), c), dm), __fsub_rn(__fmaf_rn(ds, biased<1>(m1), c), dm));
+    out.w = half2_bits(__fsub_rn(__fmaf_rn(ds, biased<2>(m1), c), dm), __fsub_rn(__fmaf_rn(ds, biased<3>(m1), c), dm));
+  } else {
+    // a 32-value block with one f16 scale (2-byte aligned: read by halves): chunk k's 8 codes
+    const uint16_t* hp = (const uint16_t*) blk;
+    const float d = half_value(hp[0]);
+    uint32_t m0, m1;
+    float c;
+    if constexpr (T == QTYPE_Q4_0) {  // d (n - 8): bytes 8 (k % 2) .., low (k < 2) or high nibbles
+      const uint16_t* q = hp + 1 + 4 * (k & 1u);
+      const uint32_t s4 = 4u * (k >> 1);
+      m0 = (((uint32_t) q[0] | (uint32_t) q[1] << 16) >> s4) & 0x0F0F0F0Fu;
+      m1 = (((uint32_t) q[2] | (uint32_t) q[3] << 16) >> s4) & 0x0F0F0F0Fu;
+      c = mul_rn(d, -32776.0f);
+    } else {  // Q8_0: d q, the signed byte as q + 128
+      const uint16_t* q = hp + 1 + 4 * k;
+      m0 = ((uint32_t) q[0] | (uint32_t) q[1] << 16) ^ 0x80808080u;
+      m1 = ((uint32_t) q[2] | (uint32_t) q[3] << 16) ^ 0x80808080u;
+      c = mul_rn(d, -32896.0f);
+    }
+    out.x = half2_bits(__fmaf_rn(d, biased<0>(m0), c), __fmaf_rn(d, biased<1>(m0), c));
+    out.y = half2_bits(__fmaf_rn(d, biased<2>(m0), c), __fmaf_rn(d, biased<3>(m0), c));
+    out.z = half2_bits(__fmaf_rn(d, biased<0>(m1), c), __fmaf_rn(d, biased<1>(m1), c));
+    out.w = half2_bits(__fmaf_rn(d, biased<2>(m1), c), __fmaf_rn(d, biased<3>(m1), c));
+  }
+  return out;
+}
+
 struct Args {
   const uint8_t* w;          // one matrix (wt NULL)
   const uint8_t* const* wt;  // grouped: the matrices
@@ -168,12 +227,18 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
         const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
         const uint32_t lead = (uint32_t) ((uintptr_t) (w + row * row_bytes + (uint64_t) kb * kKbBytes) & 15u);
         const uint32_t cl = sub * (kStep / kChunk) + kc;  // the chunk's index in its K block
-        float v[kChunk];
-        decode8<T>(buf + r * kSlot + lead + (cl / Fmt<T>::chunks) * Fmt<T>::bytes, (int) (cl % Fmt<T>::chunks), v, g);
-        const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
-        const __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+        const uint8_t* blk = buf + r * kSlot + lead + (cl / Fmt<T>::chunks) * Fmt<T>::bytes;
         uint4 out;
-        out.x = *(const uint32_t*) &h0, out.y = *(const uint32_t*) &h1, out.z = *(const uint32_t*) &h2, out.w = *(const uint32_t*) &h3;
+        bool done = false;
+        if constexpr (kFastChunk<T>) {
+          if (T != QTYPE_Q4_K || ((uintptr_t) blk & 3u) == 0) out = fast_chunk<T>(blk, cl % Fmt<T>::chunks), done = true;
+        }
+        if (!done) {
+          float v[kChunk];
+          decode8<T>(blk, (int) (cl % Fmt<T>::chunks), v, g);
+          out.x = half2_bits(v[0], v[1]), out.y = half2_bits(v[2], v[3]);
+          out.z = half2_bits(v[4], v[5]), out.w = half2_bits(v[6], v[7]);
+        }
         *(uint4*) (sa + (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16) = out;
       }
       // this step's activations have landed (the next block's bytes, asked for after them, may still be on their way)
