@@ -24,6 +24,25 @@ __host__ inline unsigned blocks_for(uint64_t work, unsigned per_block) {
   return (unsigned) ((work + per_block - 1) / per_block);
 }
 
+// A launch that may begin before the kernel ahead of it on the stream has finished (programmatic stream
+// serialization): what such a kernel does before its `pdl_wait()` must not depend on that kernel's results - it is the
+// place for barrier initialisation, codebook tables and the first weight copies (no kernel writes weights). After
+// `pdl_wait()` the earlier kernel's writes are visible. `pdl_launch_next()` lets the kernel behind this one begin the
+// same way. Both are no-ops in a kernel launched the ordinary way.
+template <class... P, class... A>
+__host__ inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                             A... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // GGUF blocks are only 2-byte aligned in general (18, 34, 50, 66, 74, 82, 98 byte blocks; MXFP4's 17 is odd and is
 // read by bytes): these readers never assume more.
 __device__ __forceinline__ uint32_t ld8(const uint8_t* p) { return *p; }

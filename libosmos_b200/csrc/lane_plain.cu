@@ -72,6 +72,11 @@ __global__ void __launch_bounds__(W * kWarp, 1) plain_dense_kernel(const Args a)
     bar_init_fence();
     for (uint32_t i = 0; i < S; i++) issue(i);
   }
+  // Launched as a programmatic dependent of the kernel before it on the stream: this block may have started while
+  // that kernel was still finishing, and what ran so far touched only the weights (which no kernel writes). The
+  // activations may be that kernel's output: wait for it here. The kernel after this one may start the same way.
+  pdl_wait();
+  pdl_launch_next();
 
   // The lane's blocks are sub, sub + L, ...; it reads them in the order p -> block sub + L ((p + rot) % NB), where
   // the second row's lanes start half-way round: rows are a multiple of 128 bytes apart, so without the turn both
@@ -232,8 +237,7 @@ int launch(const Request& r, cudaStream_t s) {
   }
   uint32_t grid = (uint32_t) dev->sms;
   if (a.units < grid) grid = a.units;
-  kernel<<<grid, W * kWarp, total, s>>>(a);
-  return cudaGetLastError() == cudaSuccess ? 1 : -1;
+  return launch_dependent(kernel, dim3(grid), dim3(W * kWarp), total, s, a) == cudaSuccess ? 1 : -1;
 }
 
 // blocks a lane: the power of two that holds cols / 32 / L

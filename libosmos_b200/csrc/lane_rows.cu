@@ -66,6 +66,10 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
     bar_init_fence();
   }
   const RepLuts<T> luts = build_luts<T>(smem, kThreads);
+  // (a dependent launch: the tables and activations read from here on may be the output of the kernels ahead; the
+  // codebooks above are not)
+  pdl_wait();
+  pdl_launch_next();
 
   auto live_count = [&](uint32_t m) -> uint32_t {
     const int32_t c = a.cnt[m];
@@ -239,8 +243,7 @@ int launch(const Request& r, cudaStream_t s) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit) != cudaSuccess) return 0;
     sized = true;
   }
-  kernel<<<(uint32_t) dev->sms, kThreads, total, s>>>(a);
-  return cudaGetLastError() == cudaSuccess ? 1 : -1;
+  return launch_dependent(kernel, dim3((uint32_t) dev->sms), dim3(kThreads), total, s, a) == cudaSuccess ? 1 : -1;
 }
 
 }  // namespace

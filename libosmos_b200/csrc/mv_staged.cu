@@ -122,6 +122,8 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
     for (uint32_t i = 0; i < S; i++) issue(i);
   }
 
+  pdl_wait();  // (a dependent launch: x may be the output of the kernel ahead; the weight copies above are not)
+  pdl_launch_next();
   // the tokens' x (the live ones) and the codebooks, while the first copies fly
   const uint32_t live = a.n_tok < (uint32_t) NT ? a.n_tok : (uint32_t) NT;
   {
@@ -218,6 +220,8 @@ __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
     bar_init_fence();
     for (uint32_t i = 0; i < S; i++) issue(i);
   }
+  pdl_wait();  // (a dependent launch: x may be the output of the kernel ahead; the weight copies above are not)
+  pdl_launch_next();
   // the lane's x: chunk lane + 32 it of every stretch
   float xr[kRegIters][kChunk];
 #pragma unroll
@@ -314,8 +318,7 @@ int launch(const Request& r, const Device* dev, uint32_t slots, cudaStream_t s) 
   }
   uint32_t grid = (uint32_t) dev->sms;
   if (a.units < grid) grid = a.units;
-  kernel<<<grid, kThreads, total, s>>>(a);
-  return cudaGetLastError() == cudaSuccess ? 1 : -1;
+  return launch_dependent(kernel, dim3(grid), dim3(kThreads), total, s, a) == cudaSuccess ? 1 : -1;
 }
 
 template <uint32_t T>

@@ -126,6 +126,8 @@ bool by_tokens(const LaneArgs& a, uint32_t n, uint32_t grid_y, cudaStream_t s) {
 template <bool GGML>
 __global__ void __launch_bounds__(kThreads) round_kernel(const float* __restrict__ x, uint32_t rows, uint32_t cols,
                                                          uint32_t xs, int8_t* __restrict__ q, float* __restrict__ d) {
+  pdl_wait();  // (a dependent launch: x is usually the output of the kernel ahead)
+  pdl_launch_next();
   const uint32_t nblk = cols / 32;
   const uint64_t blk = (uint64_t) blockIdx.x * kWarps + threadIdx.x / kWarp;
   const int lane = threadIdx.x % kWarp;
@@ -154,8 +156,8 @@ template <bool GGML>
 bool round_rows(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d, cudaStream_t s) {
   if (!x || !q || !d || !rows || !cols || cols % 32 || xs < cols) return false;
   const uint64_t blocks = (uint64_t) rows * (cols / 32);
-  round_kernel<GGML><<<blocks_for(blocks, kWarps), kThreads, 0, s>>>(x, rows, cols, xs, q, d);
-  return launched();
+  return launch_dependent(round_kernel<GGML>, dim3(blocks_for(blocks, kWarps)), dim3(kThreads), 0, s, x, rows, cols, xs, q, d) ==
+         cudaSuccess;
 }
 
 int g_use_staged = 1;  // q8_set_staged: the tests run every kernel and compare their bits (0 generic only, 2 no ring)
