@@ -34,6 +34,8 @@ __global__ void __launch_bounds__(kThreads) route_kernel(const float* __restrict
                                                          int32_t* __restrict__ ids, float* __restrict__ w,
                                                          int32_t* __restrict__ rows) {
   __shared__ float p[kMaxExperts], scratch[kThreads];
+  pdl_wait();  // (a dependent launch: the step before may still be reading the ids and weights this one writes)
+  pdl_launch_next();
   const uint32_t t = blockIdx.x;
   const float* l = logits + (uint64_t) t * n_exp;
   float m = __int_as_float(0xFF800000);
@@ -114,6 +116,8 @@ __global__ void __launch_bounds__(kTableThreads) tiles_kernel(const int32_t* __r
                                                               const Q4xExpertTiles t, const Q4xExpertBounds bd) {
   __shared__ int count[kMaxExperts], first_place[kMaxExperts], first_slot[kMaxExperts], warp_sums[kWarp];
   __shared__ int32_t sids[kInlinePicks];
+  pdl_wait();  // (a dependent launch: ids are the router's output)
+  pdl_launch_next();
   const uint32_t e = threadIdx.x;
   count[e] = 0;
   __syncthreads();
@@ -216,6 +220,8 @@ __global__ void __launch_bounds__(kTableThreads) lane_tables_kernel(const int32_
                                                                     const LaneTables t, uint32_t e0, uint32_t e1) {
   __shared__ int count[kMaxExperts], first_row[kMaxExperts], warp_sums[kWarp];
   __shared__ int32_t sids[kInlinePicks];
+  pdl_wait();  // (a dependent launch: ids are the router's output)
+  pdl_launch_next();
   const uint32_t e = threadIdx.x;
   count[e] = 0;
   __syncthreads();
@@ -341,8 +347,8 @@ extern "C" bool q4x_route(const float* logits, uint32_t n_tok, uint32_t n_exp, u
                           int32_t* rows, void* stream) {
   if (!logits || !ids || !w || !rows || !n_tok || !n_exp || n_exp > kMaxExperts || !k || k > kMaxK || k > n_exp)
     return false;
-  route_kernel<<<n_tok, kThreads, 0, stream_of(stream)>>>(logits, n_exp, k, ids, w, rows);
-  return launched();
+  return launch_dependent(route_kernel, dim3(n_tok), dim3(kThreads), 0, stream_of(stream), logits, n_exp, k, ids, w, rows) ==
+         cudaSuccess;
 }
 
 extern "C" void q4x_expert_bounds(uint32_t n, uint32_t n_exp, Q4xExpertBounds* b) {
@@ -429,8 +435,9 @@ extern "C" bool lane_tables(const int32_t* ids, uint32_t n, uint32_t k, uint32_t
   for (int j = 0; j < 3; j++)
     if ((!ex->tab[j] && (!ex->base[j] || !ex->bytes[j])) || !t->w[j]) return false;
   const cudaStream_t s = stream_of(stream);
-  lane_tables_kernel<<<1, kTableThreads, 0, s>>>(ids, n, k, n_exp, *ex, *t, expert0, expert1);
-  if (!launched()) return false;
+  if (launch_dependent(lane_tables_kernel, dim3(1), dim3(kTableThreads), 0, s, ids, n, k, n_exp, *ex, *t, expert0, expert1) !=
+      cudaSuccess)
+    return false;
   if (n > kInlinePicks) {
     lane_place_kernel<<<n_exp, kThreads, 0, s>>>(ids, n, k, n_exp, *t, expert0, expert1);
     if (!launched()) return false;

@@ -74,6 +74,8 @@ __global__ void gather_rows_kernel(float* __restrict__ dst, const float* __restr
 
 __global__ void gather_sum_kernel(float* __restrict__ y, const float* __restrict__ src, const int32_t* __restrict__ idx,
                                   uint32_t m, uint64_t total, uint32_t dim, const float* __restrict__ add) {
+  pdl_wait();  // (a dependent launch: src and idx are the output of the kernels ahead)
+  pdl_launch_next();
   const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
   if (i >= total) return;
   const uint64_t t = i / dim, c = i % dim;
@@ -247,16 +249,16 @@ extern "C" bool ops_gather_sum(float* y, const float* src, const int32_t* idx, u
                                void* stream) {
   if (!y || !src || !idx || !m || !n || !dim) return false;
   const uint64_t total = (uint64_t) n * dim;
-  gather_sum_kernel<<<blocks_for(total, kThreads), kThreads, 0, stream_of(stream)>>>(y, src, idx, m, total, dim, nullptr);
-  return launched();
+  return launch_dependent(gather_sum_kernel, dim3(blocks_for(total, kThreads)), dim3(kThreads), 0, stream_of(stream), y, src, idx, m,
+                          total, dim, (const float*) nullptr) == cudaSuccess;
 }
 
 extern "C" bool ops_gather_sum_add(float* y, const float* src, const int32_t* idx, uint32_t m, uint32_t n, uint32_t dim,
                                    const float* add, void* stream) {
   if (!y || !src || !idx || !m || !n || !dim || !add) return false;
   const uint64_t total = (uint64_t) n * dim;
-  gather_sum_kernel<<<blocks_for(total, kThreads), kThreads, 0, stream_of(stream)>>>(y, src, idx, m, total, dim, add);
-  return launched();
+  return launch_dependent(gather_sum_kernel, dim3(blocks_for(total, kThreads)), dim3(kThreads), 0, stream_of(stream), y, src, idx, m,
+                          total, dim, add) == cudaSuccess;
 }
 
 extern "C" bool ops_copy_rows(float* dst, const float* src, const int32_t* idx, uint32_t n, uint32_t len, void* stream) {
