@@ -26,6 +26,8 @@ __host__ __device__ inline EpSegment segment_of(uint32_t tokens, uint32_t k, uin
 __global__ void unpack_kernel(const uint8_t* __restrict__ gathered, uint32_t n_ranks, uint32_t tokens, uint32_t k,
                               uint32_t dim, uint32_t* __restrict__ ids, uint32_t* __restrict__ weights,
                               uint32_t* __restrict__ q, uint32_t* __restrict__ d) {
+  pdl_wait();  // (a dependent launch: what this kernel reads is the output of the kernels ahead)
+  pdl_launch_next();
   const EpSegment s = segment_of(tokens, k, dim);
   const uint64_t w_ids = (uint64_t) tokens * k, w_q = (uint64_t) tokens * dim / 4, w_d = (uint64_t) tokens * (dim / 32);
   const uint64_t per_rank = 2 * w_ids + w_q + w_d;
@@ -54,6 +56,8 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ gathered, uint32_t n_r
 
 __global__ void scatter_rows_kernel(const float4* __restrict__ ye, const int32_t* __restrict__ row_of, uint32_t n_picks,
                                     uint32_t k, uint32_t tokens, uint32_t dim4, float4* __restrict__ send) {
+  pdl_wait();  // (a dependent launch: what this kernel reads is the output of the kernels ahead)
+  pdl_launch_next();
   const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
   if (i >= (uint64_t) n_picks * dim4) return;
   const uint32_t pick = (uint32_t) (i / dim4), c = (uint32_t) (i % dim4);
@@ -70,6 +74,8 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const float* __restri
                                                            uint32_t tokens, uint32_t k, uint32_t experts_per_rank,
                                                            uint32_t dim, const float* __restrict__ add,
                                                            float* __restrict__ out) {
+  pdl_wait();  // (a dependent launch: what this kernel reads is the output of the kernels ahead)
+  pdl_launch_next();
   __shared__ uint32_t slot[32];
   const uint32_t t = blockIdx.x;
   if (threadIdx.x == 0) {
@@ -115,6 +121,8 @@ __device__ __forceinline__ void publish(uint32_t* const* flag, uint32_t n_ranks,
 __global__ void __launch_bounds__(kThreads) push_kernel(const uint4* __restrict__ src, uint64_t n16, uint4* const* dst,
                                                         uint32_t* const* flag, uint32_t n_ranks, uint32_t step,
                                                         uint32_t* counter) {
+  pdl_wait();  // (a dependent launch: what this kernel reads is the output of the kernels ahead)
+  pdl_launch_next();
   for (uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x; i < n16; i += (uint64_t) gridDim.x * kThreads) {
     const uint4 v = src[i];
     for (uint32_t r = 0; r < n_ranks; r++) dst[r][i] = v;
@@ -127,6 +135,8 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_peer_kernel(const float
                                                                      uint32_t k, uint32_t tokens, uint32_t dim4,
                                                                      float4* const* recv, uint32_t* const* flag,
                                                                      uint32_t n_ranks, uint32_t step, uint32_t* counter) {
+  pdl_wait();  // (a dependent launch: what this kernel reads is the output of the kernels ahead)
+  pdl_launch_next();
   const uint64_t total = (uint64_t) n_picks * dim4;
   for (uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x; i < total; i += (uint64_t) gridDim.x * kThreads) {
     const uint32_t pick = (uint32_t) (i / dim4), c = (uint32_t) (i % dim4);
@@ -140,6 +150,8 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_peer_kernel(const float
 
 // thread r polls the flag rank r writes (this GPU's own memory), napping between looks, until it has reached `step`
 __global__ void peer_wait_kernel(const uint32_t* flags, uint32_t n_ranks, uint32_t step) {
+  pdl_wait();  // (a dependent launch: what this kernel reads is the output of the kernels ahead)
+  pdl_launch_next();
   if (threadIdx.x >= n_ranks) return;
   const uint32_t* f = flags + threadIdx.x;
   uint64_t t0;
@@ -198,15 +210,13 @@ extern "C" bool ep_push(const void* src, uint64_t bytes, void* const* dst, uint3
     return false;
   const uint64_t n16 = bytes / 16;
   const unsigned blocks = (unsigned) (n16 / kThreads < 1 ? 1 : (n16 / kThreads > 64 ? 64 : n16 / kThreads));
-  push_kernel<<<blocks, kThreads, 0, stream_of(stream)>>>((const uint4*) src, n16, (uint4* const*) dst, flag, n_ranks, step,
-                                                          counter);
-  return launched();
+  return launch_dependent(push_kernel, dim3(blocks), dim3(kThreads), 0, stream_of(stream), (const uint4*) src, n16,
+                          (uint4* const*) dst, flag, n_ranks, step, counter) == cudaSuccess;
 }
 
 extern "C" bool ep_wait(const uint32_t* flags, uint32_t n_ranks, uint32_t step, void* stream) {
   if (!flags || !n_ranks || n_ranks > EP_MAX_RANKS) return false;
-  peer_wait_kernel<<<1, 32, 0, stream_of(stream)>>>(flags, n_ranks, step);
-  return launched();
+  return launch_dependent(peer_wait_kernel, dim3(1), dim3(32), 0, stream_of(stream), flags, n_ranks, step) == cudaSuccess;
 }
 
 extern "C" uint32_t ep_wait_status(void) {
@@ -224,9 +234,8 @@ extern "C" bool ep_scatter_rows_peer(const float* ye, const int32_t* row_of, uin
     return false;
   const uint64_t work = (uint64_t) n_picks * (dim / 4);
   const unsigned blocks = (unsigned) (work / kThreads < 1 ? 1 : (work / kThreads > 592 ? 592 : work / kThreads));
-  scatter_rows_peer_kernel<<<blocks, kThreads, 0, stream_of(stream)>>>((const float4*) ye, row_of, n_picks, k, tokens, dim / 4,
-                                                                       (float4* const*) recv, flag, n_ranks, step, counter);
-  return launched();
+  return launch_dependent(scatter_rows_peer_kernel, dim3(blocks), dim3(kThreads), 0, stream_of(stream), (const float4*) ye,
+                          row_of, n_picks, k, tokens, dim / 4, (float4* const*) recv, flag, n_ranks, step, counter) == cudaSuccess;
 }
 
 extern "C" void ep_segment(uint32_t tokens, uint32_t k, uint32_t dim, EpSegment* s) { *s = segment_of(tokens, k, dim); }
@@ -235,9 +244,9 @@ extern "C" bool ep_unpack(const void* gathered, uint32_t n_ranks, uint32_t token
                           float* weights, int8_t* q, float* d, void* stream) {
   if (!gathered || !ids || !weights || !q || !d || !n_ranks || !tokens || !k || !dim || dim % 32) return false;
   const uint64_t words = ((uint64_t) tokens * k * 2 + (uint64_t) tokens * dim / 4 + (uint64_t) tokens * (dim / 32)) * n_ranks;
-  unpack_kernel<<<blocks_for(words, kThreads), kThreads, 0, stream_of(stream)>>>(
-      (const uint8_t*) gathered, n_ranks, tokens, k, dim, (uint32_t*) ids, (uint32_t*) weights, (uint32_t*) q, (uint32_t*) d);
-  return launched();
+  return launch_dependent(unpack_kernel, dim3(blocks_for(words, kThreads)), dim3(kThreads), 0, stream_of(stream),
+                          (const uint8_t*) gathered, n_ranks, tokens, k, dim, (uint32_t*) ids, (uint32_t*) weights, (uint32_t*) q,
+                          (uint32_t*) d) == cudaSuccess;
 }
 
 extern "C" bool ep_scatter_rows(const float* ye, const int32_t* row_of, uint32_t n_picks, uint32_t k, uint32_t tokens,
@@ -246,14 +255,13 @@ extern "C" bool ep_scatter_rows(const float* ye, const int32_t* row_of, uint32_t
       (((uintptr_t) ye | (uintptr_t) send) & 15u))
     return false;
   const uint64_t work = (uint64_t) n_picks * (dim / 4);
-  scatter_rows_kernel<<<blocks_for(work, kThreads), kThreads, 0, stream_of(stream)>>>((const float4*) ye, row_of, n_picks, k,
-                                                                                   tokens, dim / 4, (float4*) send);
-  return launched();
+  return launch_dependent(scatter_rows_kernel, dim3(blocks_for(work, kThreads)), dim3(kThreads), 0, stream_of(stream),
+                          (const float4*) ye, row_of, n_picks, k, tokens, dim / 4, (float4*) send) == cudaSuccess;
 }
 
 extern "C" bool ep_combine(const float* recv, const int32_t* ids, uint32_t tokens, uint32_t k, uint32_t experts_per_rank,
                            uint32_t dim, const float* add, float* out, void* stream) {
   if (!recv || !ids || !out || !tokens || !k || k > 32 || !experts_per_rank || !dim) return false;
-  combine_kernel<<<tokens, kThreads, 0, stream_of(stream)>>>(recv, ids, tokens, k, experts_per_rank, dim, add, out);
-  return launched();
+  return launch_dependent(combine_kernel, dim3(tokens), dim3(kThreads), 0, stream_of(stream), recv, ids, tokens, k,
+                          experts_per_rank, dim, add, out) == cudaSuccess;
 }
