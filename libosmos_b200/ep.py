@@ -200,8 +200,6 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
     px = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).pin_memory() for a in hx]
     pl = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).pin_memory() for a in hl]
     out = torch.empty((t1 - t0, dim), dtype=torch.float32, device=dev)
-    pout = torch.empty((t1 - t0, dim), dtype=torch.float32).pin_memory()
-    sx, sl = torch.empty_like(dx[0]), torch.empty_like(dl[0])
     stream = torch.cuda.current_stream().cuda_stream
 
     # parity first: this rank's first home token against the CPU oracle (same bits as on one GPU)
@@ -218,13 +216,15 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
     if int(flag.item()):
         raise SystemExit("bench: the expert-parallel layer's output differs from the CPU oracle's bits on some rank")
 
-    def timed(fn, steps):
+    def timed(fn, steps, drain=None):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         dist.barrier()
         torch.cuda.synchronize()
         e0.record()
         for s in range(steps):
             fn(s)
+        if drain:
+            drain()
         e1.record()
         torch.cuda.synchronize()
         dist.barrier()
@@ -235,17 +235,44 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
     def resident(s):
         layer.step(dx[s % n_inputs], dl[s % n_inputs], out, s % copies, stream)
 
+    # end to end: this rank's tokens come from pinned host memory and its output goes back, the copies on their own
+    # streams and double-buffered so that they overlap the neighbouring steps' compute (events order a buffer's copy,
+    # its use and its reuse); all of it inside the timed region
+    cin, cout = torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    bx, bl = [torch.empty_like(dx[0]) for _ in range(2)], [torch.empty_like(dl[0]) for _ in range(2)]
+    bo = [torch.empty_like(out) for _ in range(2)]
+    bp = [torch.empty((t1 - t0, dim), dtype=torch.float32).pin_memory() for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    used = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    for e in used + out_done:
+        e.record(main)
+
     def end_to_end(s):
-        sx.copy_(px[s % n_inputs], non_blocking=True)
-        sl.copy_(pl[s % n_inputs], non_blocking=True)
-        layer.step(sx, sl, out, s % copies, stream)
-        pout.copy_(out, non_blocking=True)
+        b = s & 1
+        cin.wait_event(used[b])
+        with torch.cuda.stream(cin):
+            bx[b].copy_(px[s % n_inputs], non_blocking=True)
+            bl[b].copy_(pl[s % n_inputs], non_blocking=True)
+            in_ready[b].record(cin)
+        main.wait_event(in_ready[b])
+        main.wait_event(out_done[b])
+        layer.step(bx[b], bl[b], bo[b], s % copies, stream)
+        used[b].record(main)
+        cout.wait_event(used[b])
+        with torch.cuda.stream(cout):
+            bp[b].copy_(bo[b], non_blocking=True)
+            out_done[b].record(cout)
+
+    def e2e_drain():
+        main.wait_stream(cin), main.wait_stream(cout)
 
     for s in range(args.warmup):
         resident(s), end_to_end(s)
     with ClockSampler(dev.index) as clocks:
         t_res = timed(resident, args.steps)
-        t_e2e = timed(end_to_end, args.steps)
+        t_e2e = timed(end_to_end, args.steps, e2e_drain)
         # rank 0's expert kernels alone (tables, gate + up + activation, round, down), by events inside the step
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
         for s, pair in enumerate(evs):
@@ -272,7 +299,7 @@ def run_bench(args, rank, world, dev, metric, unit, ClockSampler, measured_peaks
                            "cold_cache": "%d copies of each rank's %d MB of expert weights cycled" % (copies, sum(per) * cfg["n_exp"] // world // 1000000)},
                 "e2e": {"value": n_tok * args.steps / t_e2e, "unit": unit,
                         "h2d_bytes_per_step": int((px[0].numel() + pl[0].numel()) * 4 * world),
-                        "d2h_bytes_per_step": int(pout.numel() * 4 * world)},
+                        "d2h_bytes_per_step": int(bp[0].numel() * 4 * world)},
                 "gpu_launches": layer.kernels_per_step * args.steps * world,
                 "roofline": {"bound": "hbm", "kernel": "rank 0's expert kernels of a step (lane tables, q8_gate_up, q8_round, q8_group_tok)",
                              "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
