@@ -16,7 +16,8 @@
 //                         partition p the thread's sums go to y (p = 0) or are added to it (p > 0): the reference's
 //                         "partitions added in order", with y as the running sum.
 // The integer dots are exact whatever computes them, and every F32 operation is the generic kernel's (mmq.cu), so
-// the two give the same bits. Why the epilogue and not the tensor pipe sets the pace: see DESIGN.md.
+// the two give the same bits. The epilogue, not the tensor pipe, sets the pace: every 32-value group's dot leaves
+// tensor memory on its own and meets five CUDA-core instructions an element.
 //
 // Every mbarrier wait is bounded (%globaltimer); a wait that runs out raises the status word, every role falls
 // through to the common exit and tensor memory is released.

@@ -1,6 +1,6 @@
 """Generate the committed golden vectors. Run where the reference tree is mounted and gguf-py is installed:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [reference-tree]
 
 Writes (numpy .npz, a few hundred KB in all):
   dequant.npz   - for every block type: 48 random blocks (every scale/exponent byte random too) and the F32 values
