@@ -25,6 +25,8 @@ using namespace tma;
 using staged::build_luts;
 using staged::Rep;
 using staged::RepLuts;
+using staged::RepLuts2;
+using staged::build_luts2;
 using staged::Super;
 
 constexpr int kWarps = 16, kThreads = kWarps * kWarp;
@@ -68,7 +70,7 @@ struct LaneAt {
 
 // sub-block at.j of the superblock at shared address sb
 template <uint32_t T>
-__device__ __forceinline__ void sub_codes(uint32_t sb, const LaneAt& at, LaneCodes& c, const RepLuts<T>& lut) {
+__device__ __forceinline__ void sub_codes(uint32_t sb, const LaneAt& at, LaneCodes& c, const RepLuts2<T>& lut) {
   if constexpr (T == QTYPE_IQ3_XXS) {
     // the 8 grid indices and the sign / scale word, each out of the aligned words around it: both lie 2 mod 4 bytes
     // into the superblock, so they start mid-word when the superblock is aligned and on a word when it is not
@@ -80,7 +82,8 @@ __device__ __forceinline__ void sub_codes(uint32_t sb, const LaneAt& at, LaneCod
 #pragma unroll
     for (int k = 0; k < 4; k++) {
       const uint32_t i0 = __byte_perm(w[k >> 1], 0, 0x4440 + 2 * (k & 1)), i1 = __byte_perm(w[k >> 1], 0, 0x4441 + 2 * (k & 1));
-      apply_masks_carry(lut.grid32(i0), lut.grid32(i1), lut.sign_masks4((aux >> (7 * k)) & 0x7F), c.w[2 * k], c.w[2 * k + 1]);
+      const uint2 mm = lut.sign_masks2((aux >> (7 * k)) & 0x7F);
+      apply_masks(((uint64_t) lut.grid32(i1) << 32) | lut.grid32(i0), mm.x, mm.y, c.w[2 * k], c.w[2 * k + 1]);
     }
     c.s21[0] = c.s21[1] = 2 * (2 * (int) (aux >> 28) + 1);
     c.d = half_value(lds16(sb));
@@ -111,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
     for (uint32_t s = 0; s < S; s++) bar_init(&full[warp][s], 1);
     bar_init_fence();
   }
-  const RepLuts<T> luts = build_luts<T>(smem, kThreads);
+  const RepLuts2<T> luts = build_luts2<T>(smem, kThreads);
   // (a dependent launch: the tables and activations read from here on may be the output of the kernels ahead; the
   // codebooks above are not)
   pdl_wait();

@@ -22,7 +22,8 @@ namespace {
 using namespace tma;
 using staged::build_luts;
 using staged::Rep;
-using staged::RepLuts;
+using staged::RepLuts2;
+using staged::build_luts2;
 using staged::Super;
 
 constexpr int kWarps = 12, kThreads = kWarps * kWarp;
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
     for (int s = 0; s < kSlots; s++) bar_init(&full[warp][s], 1);
     bar_init_fence();
   }
-  const RepLuts<T> luts = build_luts<T>(smem, kThreads);
+  const RepLuts2<T> luts = build_luts2<T>(smem, kThreads);
   // (a dependent launch: the tables and activations read from here on may be the output of the kernels ahead; the
   // codebooks above are not)
   pdl_wait();

@@ -108,6 +108,35 @@ template <uint32_t T> __device__ inline RepLuts<T> build_luts(uint8_t* smem, int
   return l;
 }
 
+// The same tables with the sign masks as 8-byte (m0, m1) entries in 16 copies (a half-warp's lanes each their own
+// banks; an 8-byte read is half the shared-memory passes of the 16-byte one, the two "+ 1" words then cost an AND
+// each): for the kernels whose every lane looks masks up at once. Built over build_luts' 16 KB mask table; every
+// thread of the block calls it (two barriers).
+template <uint32_t T> struct RepLuts2 : RepLuts<T> {
+  uint32_t mask2;
+  __device__ __forceinline__ uint2 sign_masks2(uint32_t s7) const { return lds64(mask2 + s7 * 128u); }
+  __device__ __forceinline__ uint4 sign_masks4(uint32_t s7) const {
+    const uint2 m = sign_masks2(s7);
+    return make_uint4(m.x, m.y, m.x & 0x01010101u, m.y & 0x01010101u);
+  }
+};
+template <uint32_t T> __device__ inline RepLuts2<T> build_luts2(uint8_t* smem, int threads) {
+  RepLuts2<T> l;
+  (RepLuts<T>&) l = build_luts<T>(smem, threads);
+  l.mask2 = 0;
+  if constexpr (Rep<T>::mask > 0) {
+    const uint32_t lane = threadIdx.x % kWarp, base = l.mask - (lane & 7u) * 16u;
+    __syncthreads();  // the table's first form is complete and nobody reads it
+    for (uint32_t i = threadIdx.x; i < 128u * 16u; i += (uint32_t) threads) {
+      const uint32_t sg = osmos_ksigns[i / 16u];
+      asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(base + i * 8u), "r"(byte_mask4(sg)), "r"(byte_mask4(sg >> 4)) : "memory");
+    }
+    __syncthreads();
+    l.mask2 = base + (lane & 15u) * 8u;
+  }
+  return l;
+}
+
 // ---- arguments and shared-memory plan ---------------------------------------------------------------------------------
 struct Args {
   const uint8_t* w_dense;    // one matrix (tables NULL)
