@@ -92,6 +92,40 @@ __device__ __forceinline__ void sub_codes(uint32_t sb, const LaneAt& at, LaneCod
   }
 }
 
+// IQ3_XXS's block sums without negating a code: the signed dot sum s_i g_i x_i is dp4a(g, x) - 2 dp4a(g & m, x) (m the
+// byte mask of the negative values), so the mask costs one AND a word and a second dp4a a token instead of an XOR,
+// an addition and a carry word - the integer pipe is the busier one here. Exact integers, the contract's products:
+// the same bits as lane_block_sum.
+template <int NTL, int NT, int NB>
+__device__ __forceinline__ void iq3_block_sums(uint32_t sb, const LaneAt& at, const RepLuts2<QTYPE_IQ3_XXS>& lut,
+                                               const int (&xq)[NT][NB][8], int k, float* out) {
+  const uint32_t sh = at.sh, al = sb + at.qoff;
+  const uint32_t q0 = lds32(al), q1 = lds32(al + 4), q2 = lds32(al + 8);
+  const uint32_t ala = al + 64u - 4u * at.j;
+  const uint32_t aux = __funnelshift_r(lds32(ala), lds32(ala + 4), sh);
+  const uint32_t w[2] = {__funnelshift_r(q0, q1, sh), __funnelshift_r(q1, q2, sh)};
+  int pos[NTL][2], neg[NTL][2];  // a half's dots: all values, and the negative ones
+#pragma unroll
+  for (int t = 0; t < NTL; t++) pos[t][0] = pos[t][1] = neg[t][0] = neg[t][1] = 0;
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    const uint32_t i0 = __byte_perm(w[c >> 1], 0, 0x4440 + 2 * (c & 1)), i1 = __byte_perm(w[c >> 1], 0, 0x4441 + 2 * (c & 1));
+    const uint2 mm = lut.sign_masks2((aux >> (7 * c)) & 0x7F);
+    const int g0 = (int) lut.grid32(i0), g1 = (int) lut.grid32(i1);
+    const int n0 = g0 & (int) mm.x, n1 = g1 & (int) mm.y;
+#pragma unroll
+    for (int t = 0; t < NTL; t++) {
+      pos[t][c >> 1] = __dp4a(g1, xq[t][k][2 * c + 1], __dp4a(g0, xq[t][k][2 * c], pos[t][c >> 1]));
+      neg[t][c >> 1] = __dp4a(n1, xq[t][k][2 * c + 1], __dp4a(n0, xq[t][k][2 * c], neg[t][c >> 1]));
+    }
+  }
+  const int s21 = 2 * (2 * (int) (aux >> 28) + 1);
+  const float d = half_value(lds16(sb));
+#pragma unroll
+  for (int t = 0; t < NTL; t++)
+    out[t] = __fadd_rn(lane_part(d, s21, pos[t][0] - 2 * neg[t][0]), lane_part(d, s21, pos[t][1] - 2 * neg[t][1]));
+}
+
 // L: lanes a row; NB: blocks a lane holds at most (EXACT: exactly - no test a block, so the blocks' loads can be
 // scheduled together); NT: tokens a task carries
 template <uint32_t T, bool FUSED, int L, int NB, int NT, bool EXACT>
@@ -200,10 +234,17 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
 #pragma unroll
     for (int k = 0; k < NB; k++) {
       if (EXACT || (uint32_t) k < nbl) {
-        LaneCodes c;
-        sub_codes<T>(ra + sboff[k], at, c, luts);
+        if constexpr (T == QTYPE_IQ3_XXS) {
+          float bs[NTL];
+          iq3_block_sums<NTL, NT, NB>(ra + sboff[k], at, luts, xq, k, bs);
 #pragma unroll
-        for (int t = 0; t < NTL; t++) acc[t] = __fmaf_rn(xd[t][k], lane_block_sum<T>(c, xq[t][k]), acc[t]);
+          for (int t = 0; t < NTL; t++) acc[t] = __fmaf_rn(xd[t][k], bs[t], acc[t]);
+        } else {
+          LaneCodes c;
+          sub_codes<T>(ra + sboff[k], at, c, luts);
+#pragma unroll
+          for (int t = 0; t < NTL; t++) acc[t] = __fmaf_rn(xd[t][k], lane_block_sum<T>(c, xq[t][k]), acc[t]);
+        }
       }
     }
   };
