@@ -347,8 +347,8 @@ def run_ours(args):
             "gpu_launches": layer.kernels_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": "q8_gate_up (lane_ring_kernel, IQ3_XXS, fused gate + up + activation)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                         "traffic": 296837888, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch "
-                         "(step 6's experts: 291.7 MB + 5.1 MB), profiles/lane_ring_rows_iq3xxs_moe.md",
+                         "traffic": 296433152, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch "
+                         "(step 6's experts: 291.8 MB + 4.7 MB), profiles/lane_ring_rows_iq3xxs_moe.md",
                          "algorithmic_bytes_per_launch": float(np.mean(alg)),
                          "us_per_launch": float(np.mean(k_ms) * 1e3)},
             "cpu_baseline": cpu, "clocks": clocks.summary()}
