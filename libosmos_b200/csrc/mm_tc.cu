@@ -9,7 +9,9 @@
 //
 // A block computes 128 weight rows x 128, 256 or 512 tokens of one matrix (the most that still leaves every SM a
 // block), a weight decoded once a block.
-// Twenty-one warps, three roles:
+// Twenty-five warps, four roles:
+//   loader (4 warps)     cp.async of the tokens' 16-byte pieces of x16 into the B operand's layout, its arrivals on the
+//                        stage's second "full" mbarrier made by the hardware when the copies land
 //   producers (16 warps) per 64-value step of K: decode the rows' 8-value chunks to f16 and store them as the A
 //                        operand (four K = 16 sub-tiles of 128 rows, K-major core matrices of 8 rows x 16 bytes), and
 //                        cp.async the tokens' 16-byte pieces of x16 into the same layout (B, four sub-tiles a
@@ -35,14 +37,15 @@ using namespace tma;
 constexpr int kM = 128, kN = 128;  // rows a block; tokens an accumulator
 constexpr int kMaxAcc = 4;         // accumulators a block: 512 tokens
 constexpr int kEpiWarps = 4, kProdWarps = 16;
-constexpr int kIssuerWarp = kEpiWarps, kFirstProdWarp = kEpiWarps + 1;
-constexpr int kProdThreads = kProdWarps * kWarp;
-constexpr int kThreads = (kEpiWarps + 1 + kProdWarps) * kWarp;
+constexpr int kLoaderWarps = 4;
+constexpr int kIssuerWarp = kEpiWarps, kFirstLoaderWarp = kEpiWarps + 1, kFirstProdWarp = kFirstLoaderWarp + kLoaderWarps;
+constexpr int kProdThreads = kProdWarps * kWarp, kLoaderThreads = kLoaderWarps * kWarp;
+constexpr int kThreads = (kEpiWarps + 1 + kLoaderWarps + kProdWarps) * kWarp;
 constexpr int kStep = 64;                        // values of K a stage
 constexpr int kSubTile = kM * 32;                // one K = 16 operand sub-tile: 128 rows x 32 bytes
 constexpr int kSubs = kStep / 16;                // sub-tiles a stage an operand: 4
 constexpr int kStageA = kSubs * kSubTile;        // 16 KB
-constexpr int kStages = 2;
+constexpr int kMaxStages = 4;
 
 __device__ uint32_t g_status;
 
@@ -125,13 +128,13 @@ struct Args {
   float* y;
   uint32_t rows, cols, n, xts, ys;
   uint32_t accs;  // accumulators (128 tokens each) a block: 1, 2 or 4
-  uint32_t stage_bytes, raw_off;  // an operand stage's bytes; where the raw weight buffers start
+  uint32_t stages, stage_bytes, raw_off;  // the operand ring's depth, a stage's bytes; where the raw weight buffers start
   float scale;
   uint32_t* status;
 };
 
 struct Shared {
-  uint64_t full[kStages], empty[kStages], done;
+  uint64_t full_a[kMaxStages], full_b[kMaxStages], empty[kMaxStages], done;
   uint32_t tmem_base;
   int fail;
 };
@@ -155,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
   float* y = a.y + (a.wt ? a.yoff[m] : 0u);
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdWarps), bar_init(&sh.empty[i], 1);
+    for (int i = 0; i < kMaxStages; i++) bar_init(&sh.full_a[i], kProdWarps), bar_init(&sh.full_b[i], kLoaderThreads), bar_init(&sh.empty[i], 1);
     bar_init(&sh.done, 1);
     sh.fail = 0;
     bar_init_fence();
@@ -169,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sh.tmem_base;
+  const uint32_t S = a.stages;
 
   if (warp >= (uint32_t) kFirstProdWarp) {
     // ================= producers =================
@@ -193,30 +197,18 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    // B: token n's 8-value piece kc of step `it`, 16 bytes, to sub-tile (n / 128, kc / 2) of the step's stage
-    auto fetch_b = [&](uint32_t it) {
-      const uint32_t sb = smem_addr(smem + (it % kStages) * a.stage_bytes + kStageA);
-      const uint32_t pieces = n_valid16 * (kStep / 8);
-      for (uint32_t i = pt; i < pieces; i += kProdThreads) {
-        // (eight neighbouring threads: one K piece of eight neighbouring tokens - eight different 16-byte bank
-        // columns of the operand tile, so a store takes no more passes than its bytes need)
-        const uint32_t kc = (i >> 3) & 7u, n = (i >> 6) * 8u + (i & 7u), acc = n / kN, nn = n % kN;
-        cp_async16(sb + (acc * kSubs + (kc >> 1)) * kSubTile + (nn >> 3) * 256 + (kc & 1u) * 128 + (nn & 7u) * 16,
-                   x16 + mm_x16_at(c0 + n, it * kStep + kc * 8, a.xts));
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
     bool dead = false;  // a wait ran out: no more work, but the producers' own barrier is still kept
     fetch_raw(0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     for (uint32_t it = 0; it < steps; it++) {
-      const uint32_t stage = it % kStages, use = it / kStages, kb = it / (kKb / kStep), sub = it % (kKb / kStep);
-      if (sub == 0) asm volatile("bar.sync 1, %0;" ::"n"(kProdThreads) : "memory");  // block kb has landed; kb - 1 is done with
+      const uint32_t stage = it % S, use = it / S, kb = it / (kKb / kStep), sub = it % (kKb / kStep);
+      if (sub == 0) {  // this thread's pieces of block kb have landed; after the barrier everyone's have, and block
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // kb - 1's buffer is free for kb + 1
+        asm volatile("bar.sync 1, %0;" ::"n"(kProdThreads) : "memory");
+      }
       if (!dead && use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) sh.fail = 1, dead = true;
       if (dead) continue;
-      fetch_b(it);
-      const bool ahead = sub == 0 && kb + 1 < kblocks;
-      if (ahead) fetch_raw(kb + 1);
+      if (sub == 0 && kb + 1 < kblocks) fetch_raw(kb + 1);
       // A: row r's chunk kc of this step decoded to 8 halves, 16 bytes, to sub-tile kc / 2 (a row past the matrix
       // repeats the last row: computed, never stored)
       uint8_t* sa = smem + stage * a.stage_bytes;
@@ -241,23 +233,45 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
         }
         *(uint4*) (sa + (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16) = out;
       }
-      // this step's activations have landed (the next block's bytes, asked for after them, may still be on their way)
-      if (ahead) asm volatile("cp.async.wait_group 1;" ::: "memory");
-      else asm volatile("cp.async.wait_group 0;" ::: "memory");
       fence_async_smem();  // these writes before the tensor core's reads
       __syncwarp();
-      if (lane == 0) bar_arrive(&sh.full[stage]);  // (one arrival a warp: 512 would queue on the one word)
+      if (lane == 0) bar_arrive(&sh.full_a[stage]);  // (one arrival a warp: 512 would queue on the one word)
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (warp >= (uint32_t) kFirstLoaderWarp) {
+    // ================= the activations' loader =================
+    // token n's 8-value piece kc of step `it`, 16 bytes, to sub-tile (n / 128, kc / 2) of the step's stage; the warp
+    // never waits for its own copies: each thread's arrival on the stage's barrier is made by the hardware when that
+    // thread's copies have landed, so the loads run as far ahead of the tensor core as the ring is deep
+    const uint32_t lt = tid - kFirstLoaderWarp * kWarp;
+    for (uint32_t it = 0; it < steps; it++) {
+      const uint32_t stage = it % S, use = it / S;
+      if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
+        sh.fail = 1;
+        break;
+      }
+      const uint32_t sb = smem_addr(smem + stage * a.stage_bytes + kStageA);
+      const uint32_t pieces = n_valid16 * (kStep / 8);
+      for (uint32_t i = lt; i < pieces; i += kLoaderThreads) {
+        // (eight neighbouring threads: one K piece of eight neighbouring tokens - eight different 16-byte bank
+        // columns of the operand tile, so a store takes no more passes than its bytes need)
+        const uint32_t kc = (i >> 3) & 7u, n = (i >> 6) * 8u + (i & 7u), acc = n / kN, nn = n % kN;
+        cp_async16(sb + (acc * kSubs + (kc >> 1)) * kSubTile + (nn >> 3) * 256 + (kc & 1u) * 128 + (nn & 7u) * 16,
+                   x16 + mm_x16_at(c0 + n, it * kStep + kc * 8, a.xts));
+      }
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&sh.full_b[stage])) : "memory");
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == (uint32_t) kIssuerWarp) {
     // ================= issuer =================
     bool ok = true;
     for (uint32_t it = 0; it < steps && !sh.fail; it++) {
-      const uint32_t stage = it % kStages, use = it / kStages;
-      if (!bar_wait(&sh.full[stage], use & 1u)) {
+      const uint32_t stage = it % S, use = it / S;
+      if (!bar_wait(&sh.full_a[stage], use & 1u) || !bar_wait(&sh.full_b[stage], use & 1u)) {
         sh.fail = 1, ok = false;
         break;
       }
+      fence_async_smem();  // the loader's copies (seen through the barrier) before the tensor core's reads
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (lane == 0) {
         const uint32_t sa = smem_addr(smem + stage * a.stage_bytes), sb = sa + kStageA;
@@ -347,21 +361,24 @@ template <uint32_t T>
 bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   a.status = status_word();
   if (!a.status) return false;
-  // tokens a block: as many accumulators (a weight is decoded once a block) as still leave a block for every SM and
-  // fit shared memory beside the two raw weight buffers
   int sms = 0, dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return false;
   constexpr uint32_t kSlot = ((256u / Fmt<T>::values * Fmt<T>::bytes) + 30u + 15u) & ~15u, kLimit = 224u * 1024u - (uint32_t) ((grid_smem_bytes<T>() + 1023) / 1024 * 1024);
   const uint32_t row_tiles = (a.rows + kM - 1) / kM;
-  auto smem_for = [&](uint32_t k) { return kStages * (kStageA + k * kSubs * kSubTile) + 2u * kM * kSlot; };
+  auto stages_for = [&](uint32_t k) { return k >= 4 ? 2u : k == 2 ? 3u : 4u; };  // a deeper ring where a stage is small
+  auto smem_for = [&](uint32_t k) { return stages_for(k) * (kStageA + k * kSubs * kSubTile) + 2u * kM * kSlot; };
+  // tokens a block: the accumulator count (1, 2 or 4 of 128 tokens; a weight is decoded once a block) with the least
+  // estimated time - waves of blocks over the SMs times a block's time, which measured ~0.85 + 0.45 k a step
   a.accs = 1;
-  for (uint32_t k = kMaxAcc; k > 1; k >>= 1)
-    if (smem_for(k) <= kLimit && (uint64_t) row_tiles * n_mat * ((max_cnt + k * kN - 1) / (k * kN)) >= (uint64_t) sms) {
-      a.accs = k;
-      break;
-    }
-  a.stage_bytes = kStageA + a.accs * kSubs * kSubTile, a.raw_off = kStages * a.stage_bytes;
+  float best = 0.0f;
+  for (uint32_t k = 1; k <= (uint32_t) kMaxAcc; k <<= 1) {
+    if (smem_for(k) > kLimit) break;
+    const uint64_t blocks = (uint64_t) row_tiles * n_mat * ((max_cnt + k * kN - 1) / (k * kN));
+    const float cost = (float) ((blocks + sms - 1) / sms) * (0.85f + 0.45f * (float) k);
+    if (k == 1 || cost < best) best = cost, a.accs = k;
+  }
+  a.stages = stages_for(a.accs), a.stage_bytes = kStageA + a.accs * kSubs * kSubTile, a.raw_off = a.stages * a.stage_bytes;
   const int smem_bytes = (int) smem_for(a.accs);
   static bool sized = false;  // (one flag a template instance)
   if (!sized) {
