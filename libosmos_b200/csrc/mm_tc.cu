@@ -23,6 +23,10 @@
 //   epilogue (4 warps)   thread = one weight row (its TMEM lane): tcgen05.ld the sums, scale, store y[t][row].
 // Every mbarrier wait is bounded (%globaltimer); a wait that runs out raises the status word, every role falls through
 // to the common exit and tensor memory is released.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "decode.cuh"
 #include "dispatch.cuh"
 #include "osmos_b200/mm.h"
@@ -56,6 +60,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 // 16 bytes of K are 128 bytes on (leading offset), the next 8 rows 256 bytes on (stride offset)
 __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
   return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) (128u >> 4) << 16 | (uint64_t) (256u >> 4) << 32 | (uint64_t) 1 << 46;
+}
+// the same for a sub-tile a tensor-map copy wrote with the 32-byte swizzle: rows of 32 bytes (one MMA's K), the two
+// 16-byte halves of a row exchanged in every second group of four rows; 8 rows are 256 bytes
+__device__ __forceinline__ uint64_t tile_desc_sw32(uint32_t addr) {
+  return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) 1 << 16 | (uint64_t) (256u >> 4) << 32 | (uint64_t) 1 << 46 | (uint64_t) 6 << 61;
 }
 // instruction descriptor: D F32, A and B f16, both K-major, N = 128, M = 128
 constexpr uint32_t kIdesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t) (kN >> 3) << 17) | ((uint32_t) (kM >> 4) << 24);
@@ -128,6 +137,7 @@ struct Args {
   float* y;
   uint32_t rows, cols, n, xts, ys;
   uint32_t accs;  // accumulators (128 tokens each) a block: 1, 2 or 4
+  uint32_t use_tma;  // the activations come by tensor-map copies (mm_run), else by 16-byte cp.async (mm_group)
   uint32_t stages, stage_bytes, raw_off;  // the operand ring's depth, a stage's bytes; where the raw weight buffers start
   float scale;
   uint32_t* status;
@@ -140,7 +150,7 @@ struct Shared {
 };
 
 template <uint32_t T>
-__global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
+__global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ Shared sh;
   __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
@@ -158,7 +168,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
   float* y = a.y + (a.wt ? a.yoff[m] : 0u);
 
   if (tid == 0) {
-    for (int i = 0; i < kMaxStages; i++) bar_init(&sh.full_a[i], kProdWarps), bar_init(&sh.full_b[i], kLoaderThreads), bar_init(&sh.empty[i], 1);
+    for (int i = 0; i < kMaxStages; i++) bar_init(&sh.full_a[i], kProdWarps), bar_init(&sh.full_b[i], a.use_tma ? 1u : (uint32_t) kLoaderThreads), bar_init(&sh.empty[i], 1);
     bar_init(&sh.done, 1);
     sh.fail = 0;
     bar_init_fence();
@@ -244,6 +254,31 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
     // never waits for its own copies: each thread's arrival on the stage's barrier is made by the hardware when that
     // thread's copies have landed, so the loads run as far ahead of the tensor core as the ring is deep
     const uint32_t lt = tid - kFirstLoaderWarp * kWarp;
+    if (a.use_tma) {
+      // One warp, a tensor-map copy a (128 tokens, 16 values of K) sub-tile: the tiled x16 seen as [token tile][K
+      // fragment][token in tile][value in fragment], a box of 8 tiles x 1 fragment written with the 32-byte swizzle the
+      // MMA reads (tiles past the last are filled with zeros); the stage's barrier counts the bytes.
+      if (lt < (uint32_t) kWarp) {
+        const uint32_t ops = n_acc * kSubs;
+        for (uint32_t it = 0; it < steps; it++) {
+          const uint32_t stage = it % S, use = it / S;
+          if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
+            sh.fail = 1;
+            break;
+          }
+          if (lt == 0) bar_expect(&sh.full_b[stage], ops * kSubTile);
+          __syncwarp();
+          if (lt < ops) {
+            const uint32_t acc = lt / kSubs, q = lt % kSubs;
+            const uint32_t dst = smem_addr(smem + stage * a.stage_bytes + kStageA) + (acc * kSubs + q) * kSubTile;
+            asm volatile(
+                "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+                "l"(&tmap), "r"(0), "r"(0), "r"(it * kSubs + q), "r"(c0 / MM_TILE + acc * (kN / MM_TILE)), "r"(smem_addr(&sh.full_b[stage]))
+                : "memory");
+          }
+        }
+      }
+    } else
     for (uint32_t it = 0; it < steps; it++) {
       const uint32_t stage = it % S, use = it / S;
       if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
@@ -277,7 +312,8 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a) {
         const uint32_t sa = smem_addr(smem + stage * a.stage_bytes), sb = sa + kStageA;
         for (uint32_t acc = 0; acc < n_acc; acc++)
           for (uint32_t q = 0; q < (uint32_t) kSubs; q++) {
-            const uint64_t da = tile_desc(sa + q * kSubTile), db = tile_desc(sb + (acc * kSubs + q) * kSubTile);
+            const uint64_t da = tile_desc(sa + q * kSubTile);
+            const uint64_t db = a.use_tma ? tile_desc_sw32(sb + (acc * kSubs + q) * kSubTile) : tile_desc(sb + (acc * kSubs + q) * kSubTile);
             const uint32_t accumulate = (it | q) != 0 ? 1u : 0u;
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(
@@ -357,8 +393,38 @@ uint32_t* status_word() {
   return at[d];
 }
 
+// the driver's tensor-map encoder, looked up once (no link against the driver library)
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled) p;
+  }
+  return fn;
+}
+
+// the tiled x16 of n tokens (rows xts values long) as [token tile][K fragment][token in tile][value in fragment]
+bool x16_map(const void* x16, uint32_t n, uint32_t xts, CUtensorMap* tm) {
+  const EncodeTiled enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[4] = {MM_TILE, MM_TILE, xts / MM_TILE, (n + MM_TILE - 1) / MM_TILE};
+  const cuuint64_t strides[3] = {MM_TILE * 2, MM_TILE * MM_TILE * 2, (cuuint64_t) MM_TILE * xts * 2};
+  const cuuint32_t box[4] = {MM_TILE, MM_TILE, 1, kN / MM_TILE}, unit[4] = {1, 1, 1, 1};
+  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(x16), dims, strides, box, unit, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <uint32_t T>
 bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
+  alignas(64) CUtensorMap tmap;
+  memset(&tmap, 0, sizeof tmap);
+  a.use_tma = 0;
+  if (!a.wt && x16_map(a.x16, a.n, a.xts, &tmap)) a.use_tma = 1;
   a.status = status_word();
   if (!a.status) return false;
   int sms = 0, dev = 0;
@@ -386,7 +452,7 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
     sized = true;
   }
   const dim3 grid(row_tiles, n_mat, (max_cnt + a.accs * kN - 1) / (a.accs * kN));
-  mm_tc_kernel<T><<<grid, kThreads, smem_bytes, s>>>(a);
+  mm_tc_kernel<T><<<grid, kThreads, smem_bytes, s>>>(a, tmap);
   return launched();
 }
 
