@@ -435,13 +435,14 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   auto stages_for = [&](uint32_t k) { return k >= 4 ? 2u : k == 2 ? 3u : 4u; };  // a deeper ring where a stage is small
   auto smem_for = [&](uint32_t k) { return stages_for(k) * (kStageA + k * kSubs * kSubTile) + 2u * kM * kSlot; };
   // tokens a block: the accumulator count (1, 2 or 4 of 128 tokens; a weight is decoded once a block) with the least
-  // estimated time - waves of blocks over the SMs times a block's time, which measured ~0.85 + 0.45 k a step
+  // estimated time - waves of blocks over the SMs times a block's time, which measured ~0.85 + 0.45 k a step with the
+  // activations copied 16 bytes at a time and ~0.95 + 0.12 k with tensor-map copies
   a.accs = 1;
   float best = 0.0f;
   for (uint32_t k = 1; k <= (uint32_t) kMaxAcc; k <<= 1) {
     if (smem_for(k) > kLimit) break;
     const uint64_t blocks = (uint64_t) row_tiles * n_mat * ((max_cnt + k * kN - 1) / (k * kN));
-    const float cost = (float) ((blocks + sms - 1) / sms) * (0.85f + 0.45f * (float) k);
+    const float cost = (float) ((blocks + sms - 1) / sms) * (a.use_tma ? 0.95f + 0.12f * (float) k : 0.85f + 0.45f * (float) k);
     if (k == 1 || cost < best) best = cost, a.accs = k;
   }
   a.stages = stages_for(a.accs), a.stage_bytes = kStageA + a.accs * kSubs * kSubTile, a.raw_off = a.stages * a.stage_bytes;
