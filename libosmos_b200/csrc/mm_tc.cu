@@ -16,7 +16,7 @@
 //                        operand (four K = 16 sub-tiles of 128 rows, K-major core matrices of 8 rows x 16 bytes), and
 //                        cp.async the tokens' 16-byte pieces of x16 into the same layout (B, four sub-tiles a
 //                        128-token accumulator); a proxy fence and an arrive on the stage's "full" mbarrier. Two stages; the rows'
-//                        bytes reach the decoders through shared memory, 256 values of K at a time.
+//                        bytes reach the decoders through shared memory, 256 values of K at a time (128 of Q8_0).
 //   issuer (1 warp)      per step and accumulator four tcgen05.mma M128 N128 K16 (the first of the whole K loop
 //                        overwrites, the rest accumulate), then tcgen05.commit onto the stage's "empty" mbarrier; after
 //                        the last step a commit onto "done".
@@ -81,6 +81,12 @@ __device__ __forceinline__ uint32_t half2_bits(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *(const uint32_t*) &h;
 }
+// the rows' bytes come through shared memory this many values of K at a time (a whole number of blocks; fewer for the
+// widest type, whose two raw buffers would otherwise cost the ring a stage), in slots of an odd number of 16-byte
+// pieces a row
+template <uint32_t T> constexpr uint32_t kRawK = (T == QTYPE_Q8_0) ? 128u : 256u;
+template <uint32_t T> constexpr uint32_t kRawBytes = kRawK<T> / Fmt<T>::values * Fmt<T>::bytes;
+template <uint32_t T> constexpr uint32_t kRawSlot = ((kRawBytes<T> + 30u + 15u) & ~15u) | 16u;
 template <uint32_t T> constexpr bool kFastChunk = (T == QTYPE_Q4_K || T == QTYPE_Q4_0 || T == QTYPE_Q8_0);
 
 template <uint32_t T>
@@ -186,12 +192,12 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
 
   if (warp >= (uint32_t) kFirstProdWarp) {
     // ================= producers =================
-    // The rows' bytes come through shared memory 256 values of K at a time: 16-byte cp.async pieces of the aligned
-    // span around each row's bytes (a block may start anywhere in a 16-byte piece), two buffers, the next 256 values
+    // The rows' bytes come through shared memory kRawK values of K at a time: 16-byte cp.async pieces of the aligned
+    // span around each row's bytes (a block may start anywhere in a 16-byte piece), two buffers, the next block's values
     // on their way while these are decoded - so the decoders' many narrow reads are shared-memory reads.
     const uint32_t pt = tid - kFirstProdWarp * kWarp;
-    constexpr uint32_t kKb = 256, kKbBytes = kKb / Fmt<T>::values * Fmt<T>::bytes, kSlot = (kKbBytes + 30u + 15u) & ~15u;
-    constexpr uint32_t kPieces = kSlot / 16;
+    constexpr uint32_t kKb = kRawK<T>, kKbBytes = kRawBytes<T>, kSlot = kRawSlot<T>;
+    constexpr uint32_t kPieces = (kKbBytes + 30u + 15u) / 16u;  // (the slot may be one piece longer: an odd count)
     uint8_t* raw = smem + a.raw_off;
     const uint8_t* w_end = w + (uint64_t) a.rows * row_bytes;
     const uint32_t kblocks = (a.cols + kKb - 1) / kKb;
@@ -207,6 +213,20 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    // this thread's chunks of a step: chunk kc of rows 64 apart (eight neighbouring threads take one K piece of eight
+    // neighbouring rows - eight different 16-byte bank columns of the operand tile, and of the raw buffer, whose row
+    // slots are an odd number of 16-byte pieces); what does not change from step to step is worked out here
+    constexpr int kMine = kM * (kStep / 8) / kProdThreads;
+    static_assert(kMine * kProdThreads == kM * (kStep / 8), "every producer thread the same number of chunks");
+    const uint32_t kc = (pt >> 3) & 7u;
+    uint32_t slot_at[kMine], dst_at[kMine], base15[kMine];
+#pragma unroll
+    for (int u = 0; u < kMine; u++) {
+      const uint32_t task = pt + (uint32_t) u * kProdThreads, r = (task >> 6) * 8u + (task & 7u);
+      const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;  // (a row past the matrix repeats the last one)
+      slot_at[u] = r * kSlot, dst_at[u] = (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16;
+      base15[u] = (uint32_t) ((uintptr_t) (w + row * row_bytes) & 15u);
+    }
     bool dead = false;  // a wait ran out: no more work, but the producers' own barrier is still kept
     fetch_raw(0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -219,29 +239,27 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
       if (!dead && use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) sh.fail = 1, dead = true;
       if (dead) continue;
       if (sub == 0 && kb + 1 < kblocks) fetch_raw(kb + 1);
-      // A: row r's chunk kc of this step decoded to 8 halves, 16 bytes, to sub-tile kc / 2 (a row past the matrix
-      // repeats the last row: computed, never stored)
+      // A: the chunk decoded to 8 halves, 16 bytes, to sub-tile kc / 2 of the stage
       uint8_t* sa = smem + stage * a.stage_bytes;
       const uint8_t* buf = raw + (kb & 1u) * (kM * kSlot);
+      const uint32_t cl = sub * (kStep / kChunk) + kc;  // the chunk's index in its K block
+      const uint32_t in_blk = (cl / Fmt<T>::chunks) * Fmt<T>::bytes, k_in = cl % Fmt<T>::chunks;
+      const uint32_t kb15 = (kb * kKbBytes) & 15u;
 #pragma unroll
-      for (uint32_t task = pt; task < (uint32_t) kM * (kStep / 8); task += kProdThreads) {
-        const uint32_t kc = (task >> 3) & 7u, r = (task >> 6) * 8u + (task & 7u);  // (the same dealing as B's)
-        const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
-        const uint32_t lead = (uint32_t) ((uintptr_t) (w + row * row_bytes + (uint64_t) kb * kKbBytes) & 15u);
-        const uint32_t cl = sub * (kStep / kChunk) + kc;  // the chunk's index in its K block
-        const uint8_t* blk = buf + r * kSlot + lead + (cl / Fmt<T>::chunks) * Fmt<T>::bytes;
+      for (int u = 0; u < kMine; u++) {
+        const uint8_t* blk = buf + slot_at[u] + ((base15[u] + kb15) & 15u) + in_blk;
         uint4 out;
         bool done = false;
         if constexpr (kFastChunk<T>) {
-          if (T != QTYPE_Q4_K || ((uintptr_t) blk & 3u) == 0) out = fast_chunk<T>(blk, cl % Fmt<T>::chunks), done = true;
+          if (T != QTYPE_Q4_K || ((uintptr_t) blk & 3u) == 0) out = fast_chunk<T>(blk, k_in), done = true;
         }
         if (!done) {
           float v[kChunk];
-          decode8<T>(blk, (int) (cl % Fmt<T>::chunks), v, g);
+          decode8<T>(blk, (int) k_in, v, g);
           out.x = half2_bits(v[0], v[1]), out.y = half2_bits(v[2], v[3]);
           out.z = half2_bits(v[4], v[5]), out.w = half2_bits(v[6], v[7]);
         }
-        *(uint4*) (sa + (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16) = out;
+        *(uint4*) (sa + dst_at[u]) = out;
       }
       fence_async_smem();  // these writes before the tensor core's reads
       __syncwarp();
@@ -430,7 +448,7 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   int sms = 0, dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return false;
-  constexpr uint32_t kSlot = ((256u / Fmt<T>::values * Fmt<T>::bytes) + 30u + 15u) & ~15u, kLimit = 224u * 1024u - (uint32_t) ((grid_smem_bytes<T>() + 1023) / 1024 * 1024);
+  constexpr uint32_t kSlot = kRawSlot<T>, kLimit = 224u * 1024u - (uint32_t) ((grid_smem_bytes<T>() + 1023) / 1024 * 1024);
   const uint32_t row_tiles = (a.rows + kM - 1) / kM;
   auto stages_for = [&](uint32_t k) { return k >= 4 ? 2u : k == 2 ? 3u : 4u; };  // a deeper ring where a stage is small
   auto smem_for = [&](uint32_t k) { return stages_for(k) * (kStageA + k * kSubs * kSubTile) + 2u * kM * kSlot; };
