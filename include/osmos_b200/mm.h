@@ -87,6 +87,26 @@ bool mm_tokens_scaled(uint32_t type, const void *w0, uint32_t rows0, float *y0, 
 bool mm_group(uint32_t type, const void *const *w, const int32_t *cnt, uint32_t n_mat, uint32_t max_cnt, uint32_t rows,
               uint32_t cols, const void *x16, const uint32_t *xoff, uint32_t xts, float *y, const uint32_t *yoff,
               uint32_t ys, void *stream);
+/* NVFP4 weights times NVFP4 activations, W4A4 (reference: include/osmos/gpu/mm.h:45-61, kernels/mm_fp4.hip).
+   mm_fp4_ok: whether this device runs the path (the reference's answers true on sm_120a only; this one on sm_100a).
+   mm_fp4_quant: x's n rows (F32, or (bf16) BF16 as 16-bit words; stride xs elements) quantized under the input scale gs
+   (or *gs_dev, a device float) as ModelOpt's activations: every 16 values an E4M3 scale byte into sc (n x cols / 16),
+   E2M1 codes two a byte in k order, the low nibble first, into q (n x cols / 2); sr_seed 0 rounds to nearest (ties to
+   the even index), else stochastically under the seed. mm_fp4_act: F32, nearest, a host scale. Bit for bit the
+   reference's bytes. false without the device, for cols not whole 64s, a scale not above 0, xs shorter than a row,
+   or q not 8-byte aligned.
+   mm_fp4: y[t * ys + r] = scale * sum_c W[r, c] xq[t, c] over any n tokens, W an NVFP4 (QTYPE_NVFP4) matrix, xq the
+   values (q, sc) hold; the tensors' scales (the weight's and the input's) belong in `scale`. Both sides' values are
+   exact in f16 and go through the f16 tensor-core product (every product exact, F32 sums): within the reference's own
+   bound (1e-5 relative to float64 sums, tests/gpu/test_mm_fp4_gpu.hip:150), not its bits. Shapes as mm_fits takes
+   them (rows in 16s, cols in 128s; the reference: 8s and 64s). The step's f16 activations live in a stream-ordered
+   allocation made and freed by the call. */
+bool mm_fp4_ok(void);
+bool mm_fp4_act(const float *x, uint32_t xs, uint32_t n, uint32_t cols, float gs, void *q, void *sc, void *stream);
+bool mm_fp4_quant(const void *x, uint32_t bf16, uint32_t xs, uint32_t n, uint32_t cols, float gs, const float *gs_dev,
+                  uint32_t sr_seed, void *q, void *sc, void *stream);
+bool mm_fp4(const void *w, uint32_t rows, uint32_t cols, const void *q, const void *sc, uint32_t n, float scale,
+            float *y, uint32_t ys, void *stream);
 /* Not in the reference: the products' kernel never waits without a bound; reads and clears the current device's
    record (synchronizes): bit 0 a wait ran out, the launch's outputs are not valid */
 uint32_t mm_status(void);

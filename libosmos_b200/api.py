@@ -78,6 +78,10 @@ SIGNATURES = {
     "mm_tokens_scaled": (B, [U32, P, U32, P, U32, C.c_float, P, U32, P, U32, C.c_float, U32, P, U32, U32, P, P, C.c_bool, P]),
     "mm_group": (B, [U32, P, P, U32, U32, U32, U32, P, P, U32, P, P, U32, P]),
     "mm_status": (U32, []),
+    "mm_fp4_ok": (B, []),
+    "mm_fp4_act": (B, [P, U32, U32, U32, C.c_float, P, P, P]),
+    "mm_fp4_quant": (B, [P, U32, U32, U32, U32, C.c_float, P, U32, P, P, P]),
+    "mm_fp4": (B, [P, U32, U32, P, P, U32, C.c_float, P, U32, P]),
     # q8.h
     "q8_round": (B, [P, U32, U32, U32, P, P, P]),
     "q8_0_round": (B, [P, U32, U32, U32, P, P, P]),

@@ -29,6 +29,7 @@
 
 #include "decode.cuh"
 #include "dispatch.cuh"
+#include "mm_tc_api.h"
 #include "osmos_b200/mm.h"
 #include "tma.cuh"
 
@@ -475,6 +476,8 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   return launched();
 }
 
+}  // namespace
+
 bool shape_ok(uint32_t type, uint32_t rows, uint32_t cols) {
   const OsmosQTypeInfo* t = qtype_row(type);
   return t && rows && rows % MM_TILE == 0 && cols && cols % 128 == 0 && cols % t->values == 0;
@@ -492,7 +495,6 @@ bool run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void*
 #undef CASE
 }
 
-}  // namespace
 }  // namespace mm_tc
 }  // namespace osmos
 

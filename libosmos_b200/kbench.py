@@ -5,6 +5,7 @@ reference keeps such sweeps under tools/bench/).
     python -m libosmos_b200.kbench mv_run Q8_0 6144 2048 --tokens 2
     python -m libosmos_b200.kbench q8_run Q4_0 49152 2048 --plain 4  # four plain launches, nothing timed (for a profiler)
     python -m libosmos_b200.kbench mm_run Q4_K 4096 4096 --tokens 512  # the f16 prefill product (x16 made once)
+    python -m libosmos_b200.kbench mm_fp4 NVFP4 17408 5120 --tokens 2048  # W4A4: quantization + product a launch
     python -m libosmos_b200.kbench mmq_group Q4_K 4096 4096 --tokens 512  # the int8 prefill product (x8 made once)
 
 Timing: 64 launches on successive cold copies of the matrix (more than 1 GiB cycled, so every launch reads HBM)
@@ -22,7 +23,7 @@ from libosmos_b200 import synth
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["mv_run", "q8_run", "mm_run", "mmq_group"])
+    ap.add_argument("op", choices=["mv_run", "q8_run", "mm_run", "mmq_group", "mm_fp4"])
     ap.add_argument("type")
     ap.add_argument("rows", type=int)
     ap.add_argument("cols", type=int)
@@ -45,7 +46,14 @@ def main():
         lib.mv_set_staged(0), lib.q8_set_staged(0)
     assert lib.q8_round(x.data_ptr(), args.tokens, args.cols, args.cols, q.data_ptr(), d.data_ptr(), None)
     flops = None
-    if args.op in ("mm_run", "mmq_group"):
+    if args.op == "mm_fp4":  # the W4A4 step: the activations' quantization and the product (TYPE must be NVFP4)
+        flops = 2.0 * args.rows * args.cols * args.tokens
+        xq = torch.zeros(args.tokens, args.cols // 2, dtype=torch.uint8, device=dev)
+        xsc = torch.zeros(args.tokens, args.cols // 16, dtype=torch.uint8, device=dev)
+        fn = lambda i, st: (lib.mm_fp4_act(x.data_ptr(), args.cols, args.tokens, args.cols, 0.5, xq.data_ptr(), xsc.data_ptr(), st)
+                            and lib.mm_fp4(pool.data_ptr() + (i % copies) * nb, args.rows, args.cols, xq.data_ptr(),
+                                           xsc.data_ptr(), args.tokens, 1.0, y.data_ptr(), args.rows, st))
+    elif args.op in ("mm_run", "mmq_group"):
         n16 = (args.tokens + 15) // 16 * 16
         flops = 2.0 * args.rows * args.cols * args.tokens
         if args.op == "mm_run":

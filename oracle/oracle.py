@@ -189,6 +189,28 @@ class Oracle:
                                  C.c_int(int(scale is not None)), _p(y), C.c_uint32(rows))
         return y
 
+    def fp4_act(self, x, cols, gs, seed=0, bf16=False):
+        """(codes n x cols/2, scale bytes n x cols/16) of mm_fp4_act / mm_fp4_quant; x F32 rows, or (bf16) uint16 rows"""
+        x = np.ascontiguousarray(x, dtype=np.uint16 if bf16 else np.float32)
+        n, xs = x.shape
+        q = np.zeros((n, cols // 2), dtype=np.uint8)
+        sc = np.zeros((n, cols // 16), dtype=np.uint8)
+        self.lib.orc_fp4_act(_p(x), C.c_int(int(bf16)), C.c_uint32(xs), C.c_uint32(n), C.c_uint32(cols), C.c_float(gs),
+                             C.c_uint32(seed), _p(q), _p(sc))
+        return q, sc
+
+    def fp4_mm(self, w, rows, cols, q, sc, scale=1.0):
+        """(float64 sums, sums of magnitudes), n x rows, of mm_fp4 over the quantized operands"""
+        w = np.ascontiguousarray(w, dtype=np.uint8)
+        q = np.ascontiguousarray(q, dtype=np.uint8)
+        sc = np.ascontiguousarray(sc, dtype=np.uint8)
+        n = q.shape[0]
+        y = np.zeros((n, rows), dtype=np.float64)
+        mag = np.zeros((n, rows), dtype=np.float64)
+        self.lib.orc_fp4_mm(_p(w), C.c_uint32(rows), C.c_uint32(cols), _p(q), _p(sc), C.c_uint32(n), C.c_double(scale),
+                            _p(y), _p(mag))
+        return y, mag
+
     def fp8_round(self, x, dim=None):
         x = np.array(x, dtype=np.float32, copy=True).reshape(-1)
         packed = None

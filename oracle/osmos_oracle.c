@@ -959,3 +959,133 @@ ORC_API void orc_mv_fp4_rows(const uint8_t *w, uint32_t rows, uint32_t cols, con
       y[(uint64_t)t * ys + r] = use_scale ? acc[0] * scale : acc[0];
     }
 }
+
+/* ------------------------------------------------------------------------------------------------------------
+ * mm_fp4_act / mm_fp4_quant (kernels/mm_fp4.hip:23-104): the activations of the W4A4 product. Every 16 values one
+ * E4M3 scale - the code of min(amax / 6 / gs, 448) to nearest even (frexpf's fraction rounded to 3 bits; below 2^-6
+ * whole numbers of 2^-9) - and E2M1 codes of v / (scale gs) clamped to +-6: to nearest with a tie to the even index,
+ * or (seed != 0) up with probability (distance from the grid point below) / step under a hash of (seed, element).
+ * x: F32, or (bf16) the upper halves of F32. q: n x cols / 2 bytes, k order, low nibble first; sc: n x cols / 16.
+ * ---------------------------------------------------------------------------------------------------------- */
+static uint32_t fp4_scale_code(float v) /* mm_fp4.hip:26-43 */
+{
+  const float a = fminf(v, 448.0f);
+  if (!(a > 0.0f))
+    return 0;
+  int e;
+  const float m = frexpf(a, &e);
+  int E = e - 1 + 7;
+  if (E >= 1)
+  {
+    float q = rintf((m * 2.0f - 1.0f) * 8.0f);
+    if (q >= 8.0f)
+      q = 0.0f, E++;
+    if (E > 15 || (E == 15 && q > 6.0f))
+      return 0x7E;
+    return (uint32_t)(E << 3) | (uint32_t)q;
+  }
+  const float q = rintf(a / 0.001953125f);
+  return q >= 8.0f ? 0x08u : (uint32_t)q;
+}
+static float fp4_scale_value(uint32_t c) /* kernels/round.h:87-93, codes up to 0x7E */
+{
+  return c >> 3 ? ldexpf(1.0f + (float)(c & 7) / 8.0f, (int)(c >> 3) - 7) : (float)c * 0.001953125f;
+}
+static const float fp4_grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+static uint32_t fp4_code_nearest(float x) /* mm_fp4.hip:46-59 */
+{
+  const float a = fabsf(x);
+  uint32_t i;
+  if (a <= 0.25f) i = 0;
+  else if (a < 0.75f) i = 1;
+  else if (a <= 1.25f) i = 2;
+  else if (a < 1.75f) i = 3;
+  else if (a <= 2.5f) i = 4;
+  else if (a < 3.5f) i = 5;
+  else if (a <= 5.0f) i = 6;
+  else i = 7;
+  return i ? (x < 0.0f ? 8u : 0u) | i : 0u;
+}
+static float fp4_uniform(uint32_t seed, uint64_t i) /* mm_fp4.hip:64-69 */
+{
+  uint32_t h = (uint32_t)i * 0x9E3779B1u ^ (uint32_t)(i >> 32) * 0x85EBCA77u ^ seed;
+  h ^= h >> 16, h *= 0x85EBCA6Bu, h ^= h >> 13, h *= 0xC2B2AE35u, h ^= h >> 16;
+  return (float)(h >> 8) * (1.0f / 16777216.0f);
+}
+static uint32_t fp4_code_stochastic(float x, float u) /* mm_fp4.hip:73-81 */
+{
+  const float a = fabsf(x);
+  uint32_t i = 0;
+  while (i < 7 && a >= fp4_grid[i + 1])
+    i++;
+  if (i < 7 && u < (a - fp4_grid[i]) / (fp4_grid[i + 1] - fp4_grid[i]))
+    i++;
+  return i ? (x < 0.0f ? 8u : 0u) | i : 0u;
+}
+ORC_API void orc_fp4_act(const void *x, int bf16, uint32_t xs, uint32_t n, uint32_t cols, float gs, uint32_t seed,
+                         uint8_t *q, uint8_t *sc) /* mm_fp4.hip:84-112 */
+{
+  for (uint32_t t = 0; t < n; t++)
+    for (uint32_t b = 0; b < cols / 16; b++)
+    {
+      float v[16], amax = 0.0f;
+      for (int j = 0; j < 16; j++)
+      {
+        const uint64_t at = (uint64_t)t * xs + b * 16 + j;
+        if (bf16)
+        {
+          const uint32_t bits = (uint32_t)((const uint16_t *)x)[at] << 16;
+          memcpy(&v[j], &bits, 4);
+        }
+        else
+          v[j] = ((const float *)x)[at];
+        amax = fmaxf(amax, fabsf(v[j]));
+      }
+      const uint32_t s = fp4_scale_code(amax / 6.0f / gs);
+      const float sf = fp4_scale_value(s) * gs;
+      sc[(uint64_t)t * (cols / 16) + b] = (uint8_t)s;
+      uint8_t *o = q + (uint64_t)t * (cols / 2) + b * 8;
+      for (int j = 0; j < 16; j++)
+      {
+        const float c = sf > 0.0f ? fminf(fmaxf(v[j] / sf, -6.0f), 6.0f) : 0.0f;
+        const uint64_t k = (uint64_t)t * cols + b * 16 + j;
+        const uint32_t code = seed ? fp4_code_stochastic(c, fp4_uniform(seed, k)) : fp4_code_nearest(c);
+        if (j % 2 == 0)
+          o[j / 2] = (uint8_t)code;
+        else
+          o[j / 2] |= (uint8_t)(code << 4);
+      }
+    }
+}
+
+/* mm_fp4's sums the way the reference's test takes them (tests/gpu/test_mm_fp4_gpu.hip:129-153): double sums over the
+ * quantized values - weight (E2M1 value) (UE4M3 scale, its sign bit not read), activation (E2M1 value) (E4M3 scale) -
+ * times scale; also the sums of the products' magnitudes (for an error bound). y, mag: n x rows doubles. */
+ORC_API void orc_fp4_mm(const uint8_t *w, uint32_t rows, uint32_t cols, const uint8_t *q, const uint8_t *sc, uint32_t n,
+                        double scale, double *y, double *mag)
+{
+  const uint32_t nb = cols / 64;
+  for (uint32_t t = 0; t < n; t++)
+    for (uint32_t r = 0; r < rows; r++)
+    {
+      double s = 0.0, m = 0.0;
+      for (uint32_t b = 0; b < nb; b++)
+      {
+        const uint8_t *blk = w + ((uint64_t)r * nb + b) * 36;
+        for (int sb = 0; sb < 4; sb++)
+          for (int j = 0; j < 16; j++)
+          {
+            const uint8_t byte = blk[4 + 8 * sb + (j & 7)];
+            const uint32_t cw = (j < 8 ? byte : byte >> 4) & 15;
+            const double wv = (cw & 8 ? -1.0 : 1.0) * fp4_grid[cw & 7] * (double)ue4m3_value(blk[sb]);
+            const uint64_t c = (uint64_t)b * 64 + sb * 16 + j;
+            const uint32_t ca = (q[((uint64_t)t * cols + c) / 2] >> (4 * (c & 1))) & 15;
+            const double av = (ca & 8 ? -1.0 : 1.0) * fp4_grid[ca & 7] * (double)fp4_scale_value(sc[(uint64_t)t * (cols / 16) + c / 16] & 0x7F);
+            s += wv * av, m += fabs(wv * av);
+          }
+      }
+      y[(uint64_t)t * rows + r] = s * scale;
+      if (mag)
+        mag[(uint64_t)t * rows + r] = m * fabs(scale);
+    }
+}

@@ -78,6 +78,10 @@ def test_refusals_decided_on_the_host(lib):
     assert not lib.mv_fp4(16, 8, 64, 16, 64, 0, 16, 8, 1.0, None) and not lib.mv_fp4(16, 8, 96, 16, 96, 1, 16, 8, 1.0, None)
     assert not lib.mv_fp4_tok(16, 16, 16, 0, 8, 64, 16, 64, 16, 8, None)
     assert not lib.mv_fp4_tok(16, 16, 16, 1, 8, 64, 16, 66, 16, 8, None)
+    # W4A4 (reference: kernels/mm_fp4.hip:412-445): no device here, so every call is refused
+    assert not lib.mm_fp4_ok()
+    assert not lib.mm_fp4_act(16, 64, 1, 64, 1.0, 16, 16, None) and not lib.mm_fp4_quant(16, 1, 64, 1, 64, 1.0, None, 3, 16, 16, None)
+    assert not lib.mm_fp4(16, 128, 128, 16, 16, 1, 1.0, 16, 128, None)
     # the peer transport's launches (set-up calls need a GPU and are not made here)
     assert not lib.ep_push(16, 24, 16, 16, 2, 1, 16, None) and not lib.ep_push(16, 32, 16, 16, 17, 1, 16, None)
     assert not lib.ep_wait(16, 0, 1, None) and not lib.ep_wait(None, 2, 1, None)

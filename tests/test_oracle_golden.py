@@ -147,3 +147,74 @@ def test_mv_fp4_order_against_float64(oracle):
         assert np.array_equal(oracle.mv_fp4_rows(w, rows, cols, x[1:2], lanes).view(np.uint32), y[1:2].view(np.uint32))
         scaled = oracle.mv_fp4_rows(w, rows, cols, x, lanes, 0.25)
         assert np.array_equal(scaled, y * np.float32(0.25))
+
+
+def _e4m3_table():
+    """the values of E4M3's codes 0 .. 0x7E, from the format's definition (4 exponent bits, bias 7, 3 mantissa bits)"""
+    c = np.arange(0x7F)
+    e, m = c >> 3, c & 7
+    return np.where(e > 0, (1 + m / 8.0) * 2.0 ** (e - 7.0), m * 2.0 ** -9)
+
+
+def test_fp4_act_codes_against_nearest_value_search(oracle):
+    """the oracle's NVFP4 activation quantization (kernels/mm_fp4.hip:23-104 in the reference) pinned against an
+    independent statement of the same rule: the scale is the E4M3 value nearest amax / 6 / gs (a tie to the even code,
+    at most 448), a code the grid point nearest v / scale (a tie to the even index)"""
+    rng = np.random.default_rng(2024)
+    n, cols, gs = 24, 256, 0.05
+    x = (rng.standard_normal((n, cols)) * gs * 6).astype(np.float32)
+    x[0, :16] = 0
+    x[1, :16] *= 1e5
+    x[2, 16:32] *= 1e-4
+    q, sc = oracle.fp4_act(x, cols, gs)
+    table = _e4m3_table()
+    grid = np.array([0, .5, 1, 1.5, 2, 3, 4, 6])
+    for t in range(n):
+        for b in range(cols // 16):
+            v = x[t, 16 * b:16 * b + 16]
+            target = min(float(np.float32(np.float32(np.abs(v).max() / np.float32(6.0)) / np.float32(gs))), 448.0)
+            d = np.abs(table - target)
+            best = np.flatnonzero(d == d.min())
+            code = best[0] if best.size == 1 else [k for k in best if k % 2 == 0][0]
+            assert sc[t, b] == code, (t, b, target)
+            sf = np.float32(np.float32(table[code]) * np.float32(gs))
+            for j in range(16):
+                a = float(np.clip(np.float32(v[j]) / sf, -6, 6)) if sf > 0 else 0.0
+                dd = np.abs(grid - abs(a))
+                bi = np.flatnonzero(dd == dd.min())
+                i = bi[0] if bi.size == 1 else [k for k in bi if k % 2 == 0][0]
+                want = (8 if a < 0 and i else 0) | i
+                got = (q[t, (16 * b + j) // 2] >> (4 * (j & 1))) & 15
+                assert got == want, (t, b, j, a)
+
+
+def test_fp4_act_stochastic_is_unbiased_and_seeded(oracle):
+    x = np.full((1, 64 * 512), 0.8, np.float32)
+    x[0, ::16] = 6.0  # every group's scale is 1
+    q1, _ = oracle.fp4_act(x, x.shape[1], 1.0, seed=7)
+    q2, _ = oracle.fp4_act(x, x.shape[1], 1.0, seed=7)
+    q3, _ = oracle.fp4_act(x, x.shape[1], 1.0, seed=8)
+    assert np.array_equal(q1, q2) and not np.array_equal(q1, q3)
+    codes = np.stack([q1 & 15, q1 >> 4], -1).reshape(-1)
+    codes = codes[np.arange(codes.size) % 16 != 0]
+    assert set(np.unique(codes)) == {1, 2}  # 0.5 or 1.0
+    up = (codes == 2).mean()   # 0.8 lies 0.6 of the way from 0.5 to 1
+    assert abs(up - 0.6) < 0.01
+
+
+def test_fp4_mm_sums(oracle):
+    """the float64 sums over the quantized operands equal the dequantized weights times the decoded activations"""
+    from libosmos_b200 import synth
+    tid = TYPES["NVFP4"]
+    rows, cols, n = 16, 256, 5
+    w = synth.random_tensor(tid, rows, cols, synth.rng_for(43))
+    x = np.random.default_rng(5).standard_normal((n, cols)).astype(np.float32)
+    q, sc = oracle.fp4_act(x, cols, 0.2)
+    y, mag = oracle.fp4_mm(w, rows, cols, q, sc, scale=0.5)
+    wv = oracle.dequant(tid, w, rows * cols).reshape(rows, cols).astype(np.float64)
+    grid = np.array([0, .5, 1, 1.5, 2, 3, 4, 6])
+    codes = np.stack([q & 15, q >> 4], -1).reshape(n, cols)
+    xv = np.where(codes & 8, -1.0, 1.0) * grid[codes & 7] * np.repeat(_e4m3_table()[sc], 16, axis=1)
+    assert np.allclose(y, 0.5 * xv @ wv.T, rtol=1e-12, atol=1e-300) and (mag >= np.abs(y)).all()
+    # the quantized activations stay close to x under its scale: |x - xq gs| <= the step of the group's scale
+    assert np.abs(xv * 0.2 - x).max() < 0.2 * np.abs(x).max()
