@@ -63,6 +63,11 @@ bool mm_x16_heads(const float *x, uint32_t xs, uint32_t n, uint32_t heads, uint3
    tiles: rows a multiple of 16, cols a multiple of 128 and whole blocks (reference: mm.h:10-11) */
 bool mm_known(uint32_t type);
 bool mm_fits(uint32_t type, uint32_t rows, uint32_t cols);
+/* the launch class of a matrix with n tokens - how many 128-token accumulators a block carries at most: 1, 2 or 4; 0
+   for a type without a kernel (reference: mm.h:12, kernels/mm.hip:161-167, 455-465, where it is the column tiles a
+   block takes). A caller sorts mm_group's matrices by count and makes one launch a run of equal classes
+   (src/run/hip_ffn.c:110-127), so that a matrix of few tokens is not run in a kernel sized for many. */
+uint32_t mm_col_tiles(uint32_t type, uint32_t n);
 /* y[t * ys + r] = sum_c W[r, c] x16[t][c], t < n <= MM_MAX_TOKENS; x16 as mm_x16 lays it (rows of cols values)
    (reference: mm.h:15). false for a type without a kernel, a shape that does not tile, n 0 or past MM_MAX_TOKENS,
    with more than one token ys shorter than a row, or x16 not 16-byte aligned. */

@@ -72,6 +72,7 @@ SIGNATURES = {
     "mm_x16_heads": (B, [P, U32, U32, U32, U32, U32, P, P, P]),
     "mm_known": (B, [U32]),
     "mm_fits": (B, [U32, U32, U32]),
+    "mm_col_tiles": (U32, [U32, U32]),
     "mm_run": (B, [U32, P, U32, U32, P, U32, P, U32, P]),
     "mm_run2": (B, [U32, P, U32, P, U32, P, U32, P, U32, U32, P, U32, P]),
     "mm_tokens": (B, [U32, P, U32, P, U32, P, U32, P, U32, U32, P, U32, U32, P, P, C.c_bool, P]),

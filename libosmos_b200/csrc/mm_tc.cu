@@ -502,6 +502,10 @@ using namespace osmos;
 
 extern "C" bool mm_known(uint32_t type) { return qtype_row(type) != nullptr; }
 extern "C" bool mm_fits(uint32_t type, uint32_t rows, uint32_t cols) { return mm_tc::shape_ok(type, rows, cols); }
+extern "C" uint32_t mm_col_tiles(uint32_t type, uint32_t n) {
+  if (!qtype_row(type)) return 0;
+  return n <= (uint32_t) mm_tc::kN ? 1u : n <= 2u * mm_tc::kN ? 2u : (uint32_t) mm_tc::kMaxAcc;
+}
 extern "C" uint32_t mm_status(void) {
   uint32_t* at = mm_tc::status_word();
   if (!at) return 0x80000000u;

@@ -80,6 +80,7 @@ def test_refusals_decided_on_the_host(lib):
     assert not lib.mv_fp4_tok(16, 16, 16, 1, 8, 64, 16, 66, 16, 8, None)
     # W4A4 (reference: kernels/mm_fp4.hip:412-445): no device here, so every call is refused
     assert not lib.mm_fp4_ok()
+    assert [lib.mm_col_tiles(12, n) for n in (1, 128, 129, 256, 257, 2048)] == [1, 1, 2, 2, 4, 4] and lib.mm_col_tiles(99, 5) == 0
     assert not lib.mm_fp4_act(16, 64, 1, 64, 1.0, 16, 16, None) and not lib.mm_fp4_quant(16, 1, 64, 1, 64, 1.0, None, 3, 16, 16, None)
     assert not lib.mm_fp4(16, 128, 128, 16, 16, 1, 1.0, 16, 128, None)
     # the peer transport's launches (set-up calls need a GPU and are not made here)
