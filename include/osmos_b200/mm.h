@@ -59,6 +59,17 @@ bool mm_x16_rows(const float *x, uint32_t xs, const int32_t *idx, uint32_t slots
 bool mm_x16_heads(const float *x, uint32_t xs, uint32_t n, uint32_t heads, uint32_t hs, uint32_t cols, void *x16,
                   int32_t *overflow, void *stream);
 
+/* the attention's output to f16 on the way to its output projection (reference: mm.h:14-15, kernels/mm.hip:105-135,
+   480-491): of every head (head_dim values of a row) the last rope_dim values rotated back - the pair (2i, 2i + 1) by
+   the angle pos[t] * freqs[i], as (a cos + b sin, b cos - a sin) - then every 32 values rounded to E4M3 under the
+   scale 2^ceil(log2(max(amax, 1e-4) / 448)) (ops_fp8_round's rule), then to f16 in mm_x16's layout and with its
+   overflow flag. false for n 0 or past MM_MAX_TOKENS, cols not a multiple of head_dim, head_dim or head_dim - rope_dim
+   not a multiple of 32, rope_dim odd or past head_dim, xs shorter than a row. The cosine and sine are the device
+   library's: a result can differ from another library's by one E4M3 step where the rotated value lies on a
+   rounding boundary. */
+bool mm_x16_attn(const float *x, uint32_t xs, uint32_t n, uint32_t cols, uint32_t head_dim, uint32_t rope_dim,
+                 const float *freqs, const int32_t *pos, void *x16, int32_t *overflow, void *stream);
+
 /* whether `type` has a matrix-product kernel (every block type of qtype.h), and whether a rows x cols matrix of it
    tiles: rows a multiple of 16, cols a multiple of 128 and whole blocks (reference: mm.h:10-11) */
 bool mm_known(uint32_t type);

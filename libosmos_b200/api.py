@@ -70,6 +70,7 @@ SIGNATURES = {
     "mm_x16": (B, [P, U32, U32, U32, P, P, P]),
     "mm_x16_rows": (B, [P, U32, P, U32, U32, P, P, P]),
     "mm_x16_heads": (B, [P, U32, U32, U32, U32, U32, P, P, P]),
+    "mm_x16_attn": (B, [P, U32, U32, U32, U32, U32, P, P, P, P, P]),
     "mm_known": (B, [U32]),
     "mm_fits": (B, [U32, U32, U32]),
     "mm_col_tiles": (U32, [U32, U32]),

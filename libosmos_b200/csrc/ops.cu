@@ -3,6 +3,7 @@
 #include <cuda/atomic>
 
 #include "decode.cuh"
+#include "osmos_b200/mm.h"
 #include "osmos_b200/ops.h"
 #include "topk.cuh"
 
@@ -197,6 +198,36 @@ __global__ void __launch_bounds__(kThreads) fp8_kernel(float* x, uint64_t blocks
   if (j % 32 == 0) row[dim + j / 32] = (uint8_t) (ilogbf(s) + 127);
 }
 
+// mm_x16_attn: a warp a 32-value block of a token's row, a lane a value - each head's last rope_dim values rotated back
+// by the token's position (a pair's lanes trade values), the block rounded to E4M3 under its power-of-two scale, then
+// to f16 in the tiled layout; the tile's rows past the last token zero (kernels/mm.hip:105-135 in the reference)
+__global__ void __launch_bounds__(kThreads) x16_attn_kernel(const float* __restrict__ x, uint32_t xs, uint32_t n, uint32_t n16,
+                                                            uint32_t cols, uint32_t head_dim, uint32_t rope_dim,
+                                                            const float* __restrict__ freqs, const int32_t* __restrict__ pos,
+                                                            __half* __restrict__ x16, int32_t* overflow) {
+  const uint64_t blk = (uint64_t) blockIdx.x * (kThreads / kWarp) + threadIdx.x / kWarp;
+  const uint32_t lane = threadIdx.x % kWarp, per_row = cols / 32;
+  const uint32_t t = (uint32_t) (blk / per_row), c = (uint32_t) (blk % per_row) * 32 + lane;
+  if (t >= n16) return;  // (the whole warp: a block is one token's)
+  float v = 0.0f;
+  if (t < n) {
+    v = x[(uint64_t) t * xs + c];
+    const uint32_t d = c % head_dim, r0 = head_dim - rope_dim;
+    if (d >= r0) {  // the whole block lies in the rotated part (r0 is a multiple of 32)
+      const float other = __shfl_xor_sync(0xFFFFFFFFu, v, 1, kWarp);
+      const float ang = mul_rn((float) pos[t], freqs[(d - r0) / 2]);
+      const float cs = cosf(ang), sn = -sinf(ang);
+      const float a = lane & 1 ? other : v, b = lane & 1 ? v : other;
+      v = lane & 1 ? __fadd_rn(mul_rn(a, sn), mul_rn(b, cs)) : __fsub_rn(mul_rn(a, cs), mul_rn(b, sn));
+    }
+    const float amax = warp_amax(fabsf(v));
+    const float s = exp2f(ceilf(log2f(__fdiv_rn(fmaxf(amax, 1e-4f), 448.0f))));
+    v = mul_rn(e4m3_round(fminf(fmaxf(__fdiv_rn(v, s), -448.0f), 448.0f)), s);
+  }
+  if (!(fabsf(v) <= 65504.0f)) atomicOr(overflow, 1);
+  x16[mm_x16_at(t, c, cols)] = __float2half_rn(v);
+}
+
 uint32_t g_wait_limit_ms = 2000;
 
 }  // namespace
@@ -290,6 +321,18 @@ extern "C" bool ops_fp4_round(float* x, uint64_t n, uint32_t block, bool e4m3_sc
   if (packed && (!dim || dim % block || dim % 4 || n % dim || block != (e4m3_scale ? 16u : 32u))) return false;
   fp4_kernel<<<blocks_for(n / block, kThreads / kWarp), kThreads, 0, stream_of(stream)>>>(x, n / block, block, e4m3_scale,
                                                                                        (uint8_t*) packed, dim);
+  return launched();
+}
+
+extern "C" bool mm_x16_attn(const float* x, uint32_t xs, uint32_t n, uint32_t cols, uint32_t head_dim, uint32_t rope_dim,
+                            const float* freqs, const int32_t* pos, void* x16, int32_t* overflow, void* stream) {
+  if (!x || !x16 || !overflow || !n || n > MM_MAX_TOKENS || !cols || cols % MM_TILE || (n > 1 && xs < cols) || !head_dim ||
+      cols % head_dim || head_dim % 32 || rope_dim > head_dim || rope_dim % 2 || (head_dim - rope_dim) % 32 ||
+      (rope_dim && (!freqs || !pos)))
+    return false;
+  const uint32_t n16 = (n + MM_TILE - 1) / MM_TILE * MM_TILE;
+  x16_attn_kernel<<<blocks_for((uint64_t) n16 * (cols / 32), kThreads / kWarp), kThreads, 0, stream_of(stream)>>>(
+      x, xs, n, n16, cols, head_dim, rope_dim, freqs, pos, (__half*) x16, overflow);
   return launched();
 }
 

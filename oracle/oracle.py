@@ -62,6 +62,7 @@ class Oracle:
         L.orc_mmq_x8_rows.restype = C.c_int
         L.orc_mmq_rows.restype = C.c_int
         L.orc_fp4_round.restype = C.c_int
+        L.orc_x16_attn.restype = C.c_int
         L.orc_fp8_round.restype = C.c_int
         L.orc_lane_exp.restype = C.c_float
         L.orc_lane_exp.argtypes = [C.c_float]
@@ -177,6 +178,17 @@ class Oracle:
         out = np.zeros(padded * cols, dtype=np.uint16)
         ip = None if idx is None else np.ascontiguousarray(idx, dtype=np.int32)
         over = self.lib.orc_x16_rows(_p(x), C.c_uint32(xs), _p(ip), C.c_uint32(slots), C.c_uint32(cols), _p(out))
+        return out, int(over)
+
+    def x16_attn(self, x, n, cols, head_dim, rope_dim, freqs, pos):
+        """(tiled f16 bits, overflow flag) of mm_x16_attn"""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        freqs = np.ascontiguousarray(freqs, dtype=np.float32)
+        pos = np.ascontiguousarray(pos, dtype=np.int32)
+        out = np.zeros((n + 15) // 16 * 16 * cols, dtype=np.uint16)
+        over = self.lib.orc_x16_attn(_p(x), C.c_uint32(x.shape[1]), C.c_uint32(n), C.c_uint32(cols), C.c_uint32(head_dim),
+                                     C.c_uint32(rope_dim), _p(freqs), _p(pos), _p(out))
+        assert over >= 0
         return out, int(over)
 
     def mv_fp4_rows(self, w, rows, cols, x, lanes=32, scale=None):

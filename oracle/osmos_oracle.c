@@ -1089,3 +1089,44 @@ ORC_API void orc_fp4_mm(const uint8_t *w, uint32_t rows, uint32_t cols, const ui
         mag[(uint64_t)t * rows + r] = m * fabs(scale);
     }
 }
+
+/* ------------------------------------------------------------------------------------------------------------
+ * mm_x16_attn (kernels/mm.hip:105-135): each head's last rope_dim values rotated back - pair (2i, 2i + 1) at angle
+ * pos[t] freqs[i]: with cs = cos, sn = -sin, (a cs - b sn, a sn + b cs) - then every 32 values to E4M3 under their
+ * power-of-two scale (orc_fp8_round's rule), then f16 in the tiled layout; rows up to the next multiple of 16 zero.
+ * Returns the overflow flag.
+ * ---------------------------------------------------------------------------------------------------------- */
+ORC_API int orc_x16_attn(const float *x, uint32_t xs, uint32_t n, uint32_t cols, uint32_t head_dim, uint32_t rope_dim,
+                         const float *freqs, const int32_t *pos, uint16_t *x16)
+{
+  int over = 0;
+  const uint32_t padded = (n + 15) / 16 * 16, r0 = head_dim - rope_dim;
+  for (uint32_t t = 0; t < padded; t++)
+    for (uint32_t c0 = 0; c0 < cols; c0 += 32)
+    {
+      float v[32];
+      for (uint32_t j = 0; j < 32; j++)
+        v[j] = t < n ? x[(uint64_t)t * xs + c0 + j] : 0.0f;
+      if (t < n)
+      {
+        if (c0 % head_dim >= r0)
+          for (uint32_t j = 0; j < 32; j += 2)
+          {
+            const float ang = (float)pos[t] * freqs[((c0 + j) % head_dim - r0) / 2];
+            const float cs = cosf(ang), sn = -sinf(ang), a = v[j], b = v[j + 1];
+            const float lo = a * cs, lo2 = b * sn, hi = a * sn, hi2 = b * cs;
+            v[j] = lo - lo2, v[j + 1] = hi + hi2;
+          }
+        if (!orc_fp8_round(v, 32, NULL, 0))
+          return -1;
+      }
+      for (uint32_t j = 0; j < 32; j++)
+      {
+        const uint32_t c = c0 + j;
+        if (!(fabsf(v[j]) <= 65504.0f))
+          over = 1;
+        x16[(uint64_t)(t / 16) * 16 * cols + (uint64_t)(c / 16) * 256 + (t % 16) * 16 + c % 16] = half_bits(v[j]);
+      }
+    }
+  return over;
+}

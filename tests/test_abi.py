@@ -75,6 +75,7 @@ def test_refusals_decided_on_the_host(lib):
     assert not lib.mm_x16(8, 64, 2, 72, 8, 8, None) and not lib.mm_x16(8, 32, 2, 64, 8, 8, None)
     assert not lib.mm_x16_rows(16, 66, 8, 4, 64, 8, 8, None) and not lib.mm_x16_rows(8, 64, 8, 4, 64, 8, 8, None)
     assert not lib.mm_x16_heads(16, 64, 4, 3, 32, 16, 16, 8, None)  # the last head reaches past a row
+    assert not lib.mm_x16_attn(16, 128, 2, 128, 48, 0, 16, 16, 16, 16, None) and not lib.mm_x16_attn(16, 128, 2, 128, 64, 33, 16, 16, 16, 16, None)
     assert not lib.mv_fp4(16, 8, 64, 16, 64, 0, 16, 8, 1.0, None) and not lib.mv_fp4(16, 8, 96, 16, 96, 1, 16, 8, 1.0, None)
     assert not lib.mv_fp4_tok(16, 16, 16, 0, 8, 64, 16, 64, 16, 8, None)
     assert not lib.mv_fp4_tok(16, 16, 16, 1, 8, 64, 16, 66, 16, 8, None)

@@ -154,3 +154,59 @@ def test_mv_fp4_tok_entries(lib, dev, oracle, cols, lanes):
     sync()
     assert same_bits(y1.cpu().numpy(), got)
     assert not lib.mv_fp4_tok(None, None, None, 1, 16, 64, None, 64, None, 16, None)
+
+
+def _attn_case(n, heads, head_dim, rope_dim, seed, pos_zero=False):
+    rng = synth.rng_for(33, n, heads, head_dim, rope_dim, seed)
+    cols = heads * head_dim
+    x = (rng.standard_normal((n, cols)) * 3).astype(np.float32)
+    freqs = (10000.0 ** (-np.arange(max(rope_dim // 2, 1)) / max(rope_dim // 2, 1))).astype(np.float32)
+    pos = np.zeros(n, np.int32) if pos_zero else rng.integers(0, 4000, n).astype(np.int32)
+    return x, cols, freqs, pos
+
+
+def _run_attn(lib, dev, x, n, cols, head_dim, rope_dim, freqs, pos):
+    out, flag = _tiled(dev, n, cols), torch.zeros(1, dtype=torch.int32, device=dev)
+    assert lib.mm_x16_attn(ptr(to_dev(x, dev)), x.shape[1], n, cols, head_dim, rope_dim, ptr(to_dev(freqs, dev)),
+                           ptr(to_dev(pos, dev)), ptr(out), ptr(flag), None)
+    sync()
+    return out.cpu().numpy().view(np.uint16), int(flag.item())
+
+
+@pytest.mark.parametrize("n,heads,head_dim,rope_dim,pos_zero", [(5, 2, 64, 0, False), (16, 3, 128, 64, True), (37, 2, 192, 64, True)])
+def test_mm_x16_attn_exact_cases(lib, dev, oracle, n, heads, head_dim, rope_dim, pos_zero):
+    """no rotation, or a rotation by angle 0 (cos 1, sin 0 in every library): the oracle's bits"""
+    x, cols, freqs, pos = _attn_case(n, heads, head_dim, rope_dim, 1, pos_zero)
+    want, over = oracle.x16_attn(x, n, cols, head_dim, rope_dim, freqs, pos)
+    got, flag = _run_attn(lib, dev, x, n, cols, head_dim, rope_dim, freqs, pos)
+    assert np.array_equal(got, want) and flag == over == 0
+
+
+def test_mm_x16_attn_rotated(lib, dev, oracle):
+    """general positions: the device's cosine and sine may differ from the host library's in the last place, which moves
+    a value across an E4M3 rounding boundary now and then - by one step at most, in well under 1 % of the values"""
+    n, heads, head_dim, rope_dim = 50, 4, 128, 64
+    x, cols, freqs, pos = _attn_case(n, heads, head_dim, rope_dim, 2)
+    want, over = oracle.x16_attn(x, n, cols, head_dim, rope_dim, freqs, pos)
+    got, flag = _run_attn(lib, dev, x, n, cols, head_dim, rope_dim, freqs, pos)
+    assert flag == over == 0
+    g, w = got.view(np.float16).astype(np.float64), want.view(np.float16).astype(np.float64)
+    off = g != w
+    assert off.mean() < 0.01
+    assert (np.abs(g - w)[off] <= 0.126 * np.maximum(np.abs(w[off]), 2.0 ** -6)).all()
+    # the part of every head that is not rotated has the oracle's bits everywhere
+    keep = np.zeros((64, cols), bool)
+    keep[:, [c for c in range(cols) if c % head_dim < head_dim - rope_dim]] = True
+    idx = [(t // 16) * 16 * cols + (c // 16) * 256 + (t % 16) * 16 + c % 16 for t in range(n) for c in range(cols) if keep[t, c]]
+    assert np.array_equal(got[idx], want[idx])
+    assert not got[[(48 // 16) * 16 * cols + (c // 16) * 256 + (t % 16) * 16 + c % 16 for t in range(50, 64) for c in range(cols)]].any()
+
+
+def test_mm_x16_attn_refusals(lib, dev):
+    a = torch.zeros(4096, dtype=torch.float32, device=dev)
+    f = torch.zeros(1, dtype=torch.int32, device=dev)
+    args = lambda n, cols, hd, rd, xs=None: (ptr(a), xs or cols, n, cols, hd, rd, ptr(a), ptr(f), ptr(a), ptr(f), None)
+    assert not lib.mm_x16_attn(*args(0, 128, 64, 32)) and not lib.mm_x16_attn(*args(2049, 128, 64, 32))
+    assert not lib.mm_x16_attn(*args(2, 128, 48, 0)) and not lib.mm_x16_attn(*args(2, 128, 64, 48))
+    assert not lib.mm_x16_attn(*args(2, 128, 64, 33)) and not lib.mm_x16_attn(*args(2, 128, 64, 96))
+    assert not lib.mm_x16_attn(*args(2, 192, 128, 64)) and not lib.mm_x16_attn(*args(2, 128, 64, 32, xs=64))

@@ -218,3 +218,35 @@ def test_fp4_mm_sums(oracle):
     assert np.allclose(y, 0.5 * xv @ wv.T, rtol=1e-12, atol=1e-300) and (mag >= np.abs(y)).all()
     # the quantized activations stay close to x under its scale: |x - xq gs| <= the step of the group's scale
     assert np.abs(xv * 0.2 - x).max() < 0.2 * np.abs(x).max()
+
+
+def test_x16_attn_against_numpy(oracle):
+    """mm_x16_attn's restatement against the same steps taken with numpy: rotate, round 32 at a time, tile"""
+    n, heads, head_dim, rope_dim = 6, 2, 64, 32
+    cols = heads * head_dim
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((n, cols)) * 2).astype(np.float32)
+    freqs = (100.0 ** (-np.arange(rope_dim // 2) / (rope_dim // 2))).astype(np.float32)
+    pos = rng.integers(0, 50, n).astype(np.int32)
+    got, over = oracle.x16_attn(x, n, cols, head_dim, rope_dim, freqs, pos)
+    assert over == 0
+    v = x.copy().reshape(n, heads, head_dim)
+    ang = pos[:, None].astype(np.float32) * freqs[None, :]
+    cs, sn = np.cos(ang.astype(np.float64)), np.sin(ang.astype(np.float64))
+    a, b = v[:, :, head_dim - rope_dim::2].astype(np.float64), v[:, :, head_dim - rope_dim + 1::2].astype(np.float64)
+    v[:, :, head_dim - rope_dim::2] = a * cs[:, None, :] + b * sn[:, None, :]
+    v[:, :, head_dim - rope_dim + 1::2] = b * cs[:, None, :] - a * sn[:, None, :]
+    want = oracle.fp8_round(v.reshape(-1))[0].reshape(n, cols)
+    tiled = got.view(np.float16).astype(np.float32)
+    back = np.zeros((16, cols), np.float32)
+    for t in range(16):
+        for c in range(cols):
+            back[t, c] = tiled[(t // 16) * 16 * cols + (c // 16) * 256 + (t % 16) * 16 + c % 16]
+    assert not back[n:].any()
+    # the unrotated part is exactly the FP8 rounding of x; the rotated part agrees with the float64 rotation to one
+    # E4M3 step (the F32 rotation rounds differently in the last place)
+    keep = (np.arange(cols) % head_dim) < head_dim - rope_dim
+    ref16 = want.astype(np.float16).astype(np.float32)
+    assert np.array_equal(back[:n][:, keep], ref16[:, keep])
+    assert (np.abs(back[:n] - ref16) <= 0.126 * np.maximum(np.abs(ref16), 2.0 ** -6)).all()
+    assert (back[:n] != ref16).mean() < 0.02
