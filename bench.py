@@ -356,6 +356,10 @@ def run_ours(args):
         line["matvec"] = matvec_leg(lib, dev, peak)
     except Exception as e:  # a second figure beside the headline: reported, never required
         line["matvec"] = {"unavailable": str(e)[:160]}
+    try:
+        line["prefill"] = prefill_leg(lib, dev)
+    except Exception as e:
+        line["prefill"] = {"unavailable": str(e)[:160]}
     print(json.dumps(line), flush=True)
 
 
@@ -410,6 +414,74 @@ def matvec_leg(lib, dev, peak):
         del pool
     if lib.q8_status() or lib.mv_status():
         raise SystemExit("bench: a staged matvec kernel reported a copy that never landed")
+    return out
+
+
+def prefill_leg(lib, dev):
+    """BASELINE's second configuration beside the headline: a Q4_K 4096 x 4096 matrix over 512 tokens through the
+    int8 product in the reference's order of sums (mmq_group, bit-exact) and through the f16 product (mm_run), and
+    the f16 product again at 2048 tokens. Activations converted once, outside the timed launches; 64 launches on
+    successive cold copies of the matrix in one CUDA graph, replayed; device time a launch; the fraction is of the
+    measured bf16 burst peak."""
+    import torch
+
+    from libosmos_b200 import synth
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tf_peak, kind = float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        tf_peak, kind = 1590.0, "fallback"
+    tid, rows, cols = synth.TYPE_ID["Q4_K"], 4096, 4096
+    w = synth.random_tensor(tid, rows, cols, synth.rng_for(2, tid, rows))
+    nb = int(w.size)
+    copies = 24  # 226 MB cycled: more than the 126 MB L2
+    pool = torch.from_numpy(w).to(dev).repeat(copies)
+    out = {"format": "Q4_K", "rows": rows, "cols": cols, "peak_tflops": tf_peak, "peak_kind": kind, "cases": []}
+    for op, tokens in (("mmq_group", 512), ("mm_run", 512), ("mm_run", 2048)):
+        n16 = (tokens + 15) // 16 * 16
+        x = torch.randn(tokens, cols, device=dev)
+        y = torch.empty(tokens, rows, device=dev)
+        if op == "mm_run":
+            x16 = torch.zeros(n16 * cols, dtype=torch.float16, device=dev)
+            flag = torch.zeros(1, dtype=torch.int32, device=dev)
+            assert lib.mm_x16(x.data_ptr(), cols, tokens, cols, x16.data_ptr(), flag.data_ptr(), None)
+            fn = lambda i, st: lib.mm_run(tid, pool.data_ptr() + (i % copies) * nb, rows, cols, x16.data_ptr(), tokens,
+                                          y.data_ptr(), rows, st)
+        else:
+            idx = torch.arange(tokens, dtype=torch.int32, device=dev)
+            x8 = torch.zeros(n16 * cols, dtype=torch.int8, device=dev)
+            dx = torch.zeros(n16 * cols // 32, device=dev)
+            sx = torch.zeros_like(dx)
+            assert lib.mmq_x8_rows(x.data_ptr(), cols, idx.data_ptr(), tokens, cols, x8.data_ptr(), dx.data_ptr(),
+                                   sx.data_ptr(), None)
+            tabs = [torch.tensor([pool.data_ptr() + c * nb], dtype=torch.int64, device=dev) for c in range(copies)]
+            cnt = torch.tensor([tokens], dtype=torch.int32, device=dev)
+            zero = torch.zeros(1, dtype=torch.int32, device=dev)
+            fn = lambda i, st: lib.mmq_group(tid, tabs[i % copies].data_ptr(), cnt.data_ptr(), 1, tokens, rows, cols,
+                                             x8.data_ptr(), dx.data_ptr(), sx.data_ptr(), zero.data_ptr(), y.data_ptr(),
+                                             zero.data_ptr(), rows, st)
+        for i in range(3):
+            assert fn(i, None)
+        torch.cuda.synchronize()
+        n, reps = 64, 5
+        g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(n):
+                assert fn(i, st.cuda_stream)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (n * reps)
+        tf = 2.0 * rows * cols * tokens / us / 1e6
+        out["cases"].append({"op": op, "tokens": tokens, "us_per_launch": us, "tflops": tf, "frac_of_bf16_peak": tf / tf_peak,
+                             "tokens_per_s": tokens / us * 1e6})
+    if lib.mm_status() or lib.mmq_status():
+        raise SystemExit("bench: a tensor-core product reported a wait that ran out")
     return out
 
 
