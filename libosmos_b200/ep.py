@@ -55,23 +55,41 @@ class PeerBuffers:
     def __init__(self, lib, dist, dev, rank, world, seg_bytes, block_bytes):
         self.lib, self.rank, self.world = lib, rank, world
         self.off_flag, self.off_seg, self.off_recv, total = peer_layout(world, seg_bytes, block_bytes)
+        # Every rank takes every step of the set-up whether or not its own part worked, and the ranks then agree on the
+        # outcome: either all of them hold all the mappings or all of them raise (and the caller takes NCCL) - a rank
+        # that left alone would leave the others waiting in the next collective.
         mine, handle = C.c_void_p(), (C.c_uint8 * 64)()
-        if not lib.ep_peer_alloc(total, C.byref(mine), handle):
-            raise RuntimeError("ep_peer_alloc failed")
-        self.mine = mine.value
+        failed = None if lib.ep_peer_alloc(total, C.byref(mine), handle) else "ep_peer_alloc failed"
+        self.mine = mine.value if failed is None else None
         all_handles = torch.empty(world * 64, dtype=torch.uint8, device=dev)
         dist.all_gather_into_tensor(all_handles, torch.tensor(list(handle), dtype=torch.uint8, device=dev))
+        ok = torch.tensor([int(failed is None)], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         all_handles = all_handles.cpu().numpy().reshape(world, 64)
-        self.base = []
-        for r in range(world):
-            if r == rank:
-                self.base.append(self.mine)
-                continue
-            p = C.c_void_p()
-            h = (C.c_uint8 * 64)(*[int(b) for b in all_handles[r]])
-            if not lib.ep_peer_open(h, C.byref(p)):
-                raise RuntimeError("ep_peer_open failed for rank %d" % r)
-            self.base.append(p.value)
+        self.base = [None] * world
+        if int(ok.item()):
+            for r in range(world):
+                if r == rank:
+                    self.base[r] = self.mine
+                    continue
+                p = C.c_void_p()
+                h = (C.c_uint8 * 64)(*[int(b) for b in all_handles[r]])
+                if not lib.ep_peer_open(h, C.byref(p)):
+                    failed = "ep_peer_open failed for rank %d" % r
+                    break
+                self.base[r] = p.value
+        else:
+            failed = failed or "ep_peer_alloc failed on another rank"
+        ok = torch.tensor([int(failed is None)], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if not int(ok.item()):
+            for r, b in enumerate(self.base):
+                if r != rank and b is not None:
+                    lib.ep_peer_close(b)
+            dist.barrier()  # nobody's buffer is freed while a peer still maps it
+            if self.mine is not None:
+                lib.ep_peer_free(self.mine)
+            raise RuntimeError(failed or "a peer could not map the exchange buffers")
         tbl = lambda f: torch.tensor([f(r) for r in range(world)], dtype=torch.int64, device=dev)
         # where this rank's piece goes in rank r's buffer, and the flag this rank owns there
         self.dst_seg = [tbl(lambda r, p=p: self.base[r] + self.off_seg[p] + rank * seg_bytes) for p in range(2)]
