@@ -365,7 +365,8 @@ def run_ours(args):
 
 def matvec_leg(lib, dev, peak):
     """BASELINE's first metric beside the headline: the decode matvec's weight-GB/s. Config 1's matrix (Q4_0
-    6144 x 2048, 7 MB: a launch is latency-bound) and the same rows eight times over, each through the int8 lane
+    6144 x 2048, 7 MB: a launch is latency-bound), the same rows eight times over, and a 302 MB matrix (131072 x 4096:
+    what a launch reaches once its start and end no longer count), each through the int8 lane
     form (q8_run: x rounded once by q8_round) and the F32 form in the reference's order (mv_run). 64 launches on
     successive cold copies (more than 1 GiB cycled) captured in one CUDA graph, replayed; device time a launch."""
     import torch
@@ -374,7 +375,7 @@ def matvec_leg(lib, dev, peak):
     tid = synth.TYPE_ID["Q4_0"]
     out = {"format": "Q4_0", "tokens": 1, "timing": "64 launches on successive copies (> 1 GiB cycled) in a CUDA graph, replayed 5 times",
            "cases": []}
-    for rows, cols in ((6144, 2048), (49152, 2048)):
+    for rows, cols in ((6144, 2048), (49152, 2048), (131072, 4096)):
         w = synth.random_tensor(tid, rows, cols, synth.rng_for(1, tid, rows))
         nb = int(w.size)
         copies = max(2, int(1.1 * 2 ** 30 // nb) + 1)

@@ -54,6 +54,23 @@ __device__ __forceinline__ void scaled4(uint32_t bytes, float d, float c, float*
   v[2] = __fmaf_rn(d, biased<2>(bytes), c), v[3] = __fmaf_rn(d, biased<3>(bytes), c);
 }
 
+// Two F32 fused multiply-adds in one instruction (sm_100's packed F32 pipe): element by element the same IEEE
+// operation as fmaf, so the same bits - one issue slot for two rows' chains instead of two.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+template <uint32_t T> constexpr bool kPlainPair = (T == QTYPE_Q4_0 || T == QTYPE_Q8_0);
+
 // ---- what of a row a lane reads, worked out once: the lane's chunk of each 256-value stretch is at a fixed place ----
 template <uint32_t T> struct LanePlan {  // any type: decode8 through a pointer
   static constexpr uint32_t kStretch = Fmt<T>::bytes * (256 / Fmt<T>::values);
@@ -78,6 +95,13 @@ template <> struct LanePlan<QTYPE_Q4_0> {
     scaled4((__funnelshift_r(r0, r1, sh) >> s4) & 0x0F0F0F0Fu, d, neg, v);
     scaled4((__funnelshift_r(r1, r2, sh) >> s4) & 0x0F0F0F0Fu, d, neg, v + 4);
   }
+  // the same chunk undecoded: its eight codes as bytes of m[0], m[1]; value j is fmaf(d, 32768 + byte j, neg)
+  __device__ __forceinline__ void codes(uint32_t row, uint32_t it, uint32_t* m, float& d, float& neg) const {
+    const uint32_t base = row + it * kStretch;
+    const uint32_t r0 = lds32(base + al), r1 = lds32(base + al + 4), r2 = lds32(base + al + 8);
+    d = half_value(lds16(base + doff)), neg = mul_rn(d, -32776.0f);
+    m[0] = (__funnelshift_r(r0, r1, sh) >> s4) & 0x0F0F0F0Fu, m[1] = (__funnelshift_r(r1, r2, sh) >> s4) & 0x0F0F0F0Fu;
+  }
 };
 template <> struct LanePlan<QTYPE_Q8_0> {
   static constexpr uint32_t kStretch = 272;
@@ -92,6 +116,12 @@ template <> struct LanePlan<QTYPE_Q8_0> {
     const float d = half_value(lds16(base + doff)), neg = mul_rn(d, -32896.0f);
     scaled4(__funnelshift_r(r0, r1, sh) ^ 0x80808080u, d, neg, v);
     scaled4(__funnelshift_r(r1, r2, sh) ^ 0x80808080u, d, neg, v + 4);
+  }
+  __device__ __forceinline__ void codes(uint32_t row, uint32_t it, uint32_t* m, float& d, float& neg) const {
+    const uint32_t base = row + it * kStretch;
+    const uint32_t r0 = lds32(base + al), r1 = lds32(base + al + 4), r2 = lds32(base + al + 8);
+    d = half_value(lds16(base + doff)), neg = mul_rn(d, -32896.0f);
+    m[0] = __funnelshift_r(r0, r1, sh) ^ 0x80808080u, m[1] = __funnelshift_r(r1, r2, sh) ^ 0x80808080u;
   }
 };
 
@@ -251,17 +281,40 @@ __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
     float acc[RW];
 #pragma unroll
     for (int q = 0; q < RW; q++) acc[q] = 0.0f;
+    if constexpr (kPlainPair<T> && RW == 2) {
+      // the two rows' chains side by side in the packed F32 instructions: every element the same fmaf as below
+      uint64_t acc2 = pack2(0.0f, 0.0f);
 #pragma unroll
-    for (int it = 0; it < kRegIters; it++) {
-      if ((uint32_t) it < ni) {
+      for (int it = 0; it < kRegIters; it++) {
+        if ((uint32_t) it < ni) {
+          uint32_t m0[2], m1[2];
+          float d0, n0, d1, n1;
+          plan.codes(sa, (uint32_t) it, m0, d0, n0);
+          plan.codes(sa + row_bytes, (uint32_t) it, m1, d1, n1);
+          const uint64_t dd = pack2(d0, d1), nn = pack2(n0, n1);
 #pragma unroll
-        for (int q = 0; q < RW; q++) {
-          float v[kChunk];
-          plan.values(sa + q * row_bytes, sp + q * row_bytes, (uint32_t) it, v, g);
-          float s = acc[q];
+          for (int j = 0; j < kChunk; j++) {
+            const uint32_t sel = 0x7404u | ((uint32_t) (j & 3) << 4);
+            const uint64_t b = pack2(__uint_as_float(__byte_perm(m0[j >> 2], 0x47000000u, sel)),
+                                     __uint_as_float(__byte_perm(m1[j >> 2], 0x47000000u, sel)));
+            acc2 = fma2(fma2(dd, b, nn), pack2(xr[it][j], xr[it][j]), acc2);
+          }
+        }
+      }
+      unpack2(acc2, acc[0], acc[1]);
+    } else {
 #pragma unroll
-          for (int j = 0; j < kChunk; j++) s = __fmaf_rn(v[j], xr[it][j], s);
-          acc[q] = s;
+      for (int it = 0; it < kRegIters; it++) {
+        if ((uint32_t) it < ni) {
+#pragma unroll
+          for (int q = 0; q < RW; q++) {
+            float v[kChunk];
+            plan.values(sa + q * row_bytes, sp + q * row_bytes, (uint32_t) it, v, g);
+            float s = acc[q];
+#pragma unroll
+            for (int j = 0; j < kChunk; j++) s = __fmaf_rn(v[j], xr[it][j], s);
+            acc[q] = s;
+          }
         }
       }
     }
