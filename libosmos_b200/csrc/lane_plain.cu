@@ -46,7 +46,7 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {  // unsigned 
 
 // L: lanes a row; NB: blocks a lane holds (a power of two, cols <= 32 L NB); NT: tokens; W: warps a block
 template <uint32_t T, int L, int NB, int NT, int W>
-__global__ void __launch_bounds__(W * kWarp, 1) plain_dense_kernel(const Args a) {
+__global__ void __launch_bounds__(W * kWarp, (W <= 12 ? 2 : 1)) plain_dense_kernel(const Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full[W][kMaxSlots];
   constexpr int RU = kWarp / L;  // rows a warp sums at once
@@ -222,12 +222,19 @@ int launch(const Request& r, cudaStream_t s) {
     slot_rows = rows_k, slots = n > (uint32_t) kMaxSlots ? (uint32_t) kMaxSlots : n;
     break;
   }
-  if (slots < 2) return 0;
+  if (slots < 1) return 0;
   Args a{};
   a.w = (const uint8_t*) r.w, a.q = r.q, a.d = r.d, a.y = r.y, a.rows = r.rows, a.cols = r.cols, a.ys = r.ys;
   a.n_tok = r.n_tok, a.slots = slots, a.slot_rows = slot_rows, a.slot_bytes = slot_rows * row_bytes;
   a.units = (r.rows + slot_rows - 1) / slot_rows;
   a.status = dev->status;
+  {
+    // no more slots than a warp has units: a small matrix then leaves shared memory for the next launch's blocks,
+    // which start their weight copies beside this launch's (a programmatic dependent waits only for its activations)
+    const uint32_t blocks = a.units < (uint32_t) dev->sms ? a.units : (uint32_t) dev->sms;
+    const uint32_t per_warp = ((a.units + blocks - 1) / blocks + W - 1) / W;
+    if (per_warp < slots) slots = per_warp, a.slots = per_warp;
+  }
   const uint32_t total = W * slots * a.slot_bytes + 16u;  // + the word read past a last block
   static bool sized = false;  // (one flag a template instance)
   auto kernel = plain_dense_kernel<T, L, NB, NT, W>;
@@ -244,6 +251,16 @@ int launch(const Request& r, cudaStream_t s) {
 template <uint32_t T, int L, int NT>
 int by_blocks(const Request& r, cudaStream_t s) {
   const uint32_t per = (r.cols / 32 + L - 1) / L;
+  if constexpr (NT == 1) {
+    // a matrix of at most two passes a warp of the small block: twelve warps, two blocks a multiprocessor, so that the
+    // launch behind this one is resident (its copies in flight) while this one computes
+    const Device* dev = device_info();
+    if (dev && (uint64_t) r.rows <= 2ull * (kWarp / L) * 12u * (uint32_t) dev->sms) {
+      if (per <= 1) return launch<T, L, 1, 1, 12>(r, s);
+      if (per <= 2) return launch<T, L, 2, 1, 12>(r, s);
+      if (per <= 4) return launch<T, L, 4, 1, 12>(r, s);
+    }
+  }
   if (per <= 1) return launch<T, L, 1, NT, (NT == 1 ? 24 : 16)>(r, s);
   if (per <= 2) return launch<T, L, 2, NT, (NT == 1 ? 24 : 16)>(r, s);
   if (per <= 4) return launch<T, L, 4, NT, (NT == 1 ? 24 : 16)>(r, s);
