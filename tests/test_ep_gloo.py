@@ -1,17 +1,18 @@
-"""The expert-parallel step's protocol on CPU: 2 `gloo` ranks run the same sharding, slot and ordering rules as
+"""The expert-parallel step's protocol on CPU: 2 and 4 `gloo` ranks run the same sharding, slot and ordering rules as
 libosmos_b200/ep.py (its index functions are the ones used here) with the CPU oracle standing in for the kernels, and
 the combined result must equal the single-rank layer bit for bit."""
 import os
 import socket
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from libosmos_b200 import ep, runner, synth, workloads
 
-CFG = dict(workloads.MOE_IQ3, name="ep_test", n_exp=8, k=3, n_tok=6, dim=256, ff=256)
+CFG = dict(workloads.MOE_IQ3, name="ep_test", n_exp=8, k=3, n_tok=8, dim=256, ff=256)  # (both divide by 2 and 4 ranks)
 
 
 def _free_port():
@@ -79,9 +80,10 @@ def _rank_main(rank, world, port, result_path):
     dist.destroy_process_group()
 
 
-def test_two_ranks_equal_one_rank(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_equal_one_rank(tmp_path, world):
     result = str(tmp_path / "ok.npy")
-    mp.spawn(_rank_main, args=(2, _free_port(), result), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(world, _free_port(), result), nprocs=world, join=True)
     assert bool(np.load(result)[0])
 
 
