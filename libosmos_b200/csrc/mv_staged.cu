@@ -125,6 +125,35 @@ template <> struct LanePlan<QTYPE_Q8_0> {
   }
 };
 
+template <> struct LanePlan<QTYPE_Q4_K> {
+  // lane l's chunk of a 144-byte block: group l / 4 (its 6-bit scale and min among the 12 packed bytes), values
+  // 8 (l % 4) .. of the group - the low (even group) or high nibbles of 8 bytes; everything but the bytes themselves
+  // is worked out once. A row starts on 16 bytes and a block is 144 long, so every read is aligned.
+  static constexpr uint32_t kStretch = 144;
+  uint32_t qoff, s4, b8, upper;
+  __device__ __forceinline__ explicit LanePlan(uint32_t l) {
+    const uint32_t grp = l >> 2;
+    qoff = 16u + (grp >> 1) * 32u + (l & 3u) * 8u, s4 = 4u * (grp & 1u), b8 = 8u * (grp & 3u), upper = grp >> 2;
+  }
+  __device__ __forceinline__ void values(uint32_t row, const uint8_t*, uint32_t it, float* v, const Grids&) const {
+    const uint32_t base = row + it * kStretch;
+    const uint32_t hd = lds32(base);
+    const uint32_t a0 = (lds32(base + 4) >> b8) & 0xFFu, a1 = (lds32(base + 8) >> b8) & 0xFFu, a2 = (lds32(base + 12) >> b8) & 0xFFu;
+    const uint32_t sc = upper ? (a2 & 0x0Fu) | ((a0 >> 6) << 4) : a0 & 63u;
+    const uint32_t mn = upper ? (a2 >> 4) | ((a1 >> 6) << 4) : a1 & 63u;
+    // d sc has at most 17 significant bits and a code 4: the product is exact, so one fmaf against the biased code
+    // gives the bits of mul_rn(d sc, n); then the min is taken off, rounded once - decode8's value
+    const float ds = mul_rn(half_value(hd & 0xFFFFu), (float) sc), dm = mul_rn(half_value(hd >> 16), (float) mn);
+    const float c = mul_rn(ds, -32768.0f);
+    const uint2 q = lds64(base + qoff);
+    const uint32_t m0 = (q.x >> s4) & 0x0F0F0F0Fu, m1 = (q.y >> s4) & 0x0F0F0F0Fu;
+    v[0] = __fsub_rn(__fmaf_rn(ds, biased<0>(m0), c), dm), v[1] = __fsub_rn(__fmaf_rn(ds, biased<1>(m0), c), dm);
+    v[2] = __fsub_rn(__fmaf_rn(ds, biased<2>(m0), c), dm), v[3] = __fsub_rn(__fmaf_rn(ds, biased<3>(m0), c), dm);
+    v[4] = __fsub_rn(__fmaf_rn(ds, biased<0>(m1), c), dm), v[5] = __fsub_rn(__fmaf_rn(ds, biased<1>(m1), c), dm);
+    v[6] = __fsub_rn(__fmaf_rn(ds, biased<2>(m1), c), dm), v[7] = __fsub_rn(__fmaf_rn(ds, biased<3>(m1), c), dm);
+  }
+};
+
 template <uint32_t T, int NT, int RW>
 __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -158,9 +187,11 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
   const uint32_t live = a.n_tok < (uint32_t) NT ? a.n_tok : (uint32_t) NT;
   {
     const uint32_t per = a.cols / 4;
+    // a token's chunks as two planes - every chunk's first four values, then every chunk's last four - so that a
+    // warp's 16-byte reads of one plane are contiguous (chunk after chunk 32 bytes apart, they would pair up on banks)
     for (uint32_t i = tid; i < live * per; i += kThreads) {
       const uint32_t t = i / per, j = i - t * per;
-      ((float4*) smem)[i] = __ldg((const float4*) (a.x + (uint64_t) t * a.xs) + j);
+      ((float4*) smem)[t * per + (j & 1u) * (per / 2) + (j >> 1)] = __ldg((const float4*) (a.x + (uint64_t) t * a.xs) + j);
     }
   }
   const Grids g = stage_grids<T>(tables);
@@ -193,8 +224,8 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
       for (int q = 0; q < RW; q++) plan.values(sa + q * row_bytes, sp + q * row_bytes, it, v[q], g);
 #pragma unroll
       for (int t = 0; t < NT; t++) {
-        const uint32_t xc = xa[t] + (lane + 32u * it) * 32u;
-        const float4 lo = lds128f(xc), hi = lds128f(xc + 16u);
+        const uint32_t xc = xa[t] + (lane + 32u * it) * 16u;
+        const float4 lo = lds128f(xc), hi = lds128f(xc + a.cols * 2u);
 #pragma unroll
         for (int q = 0; q < RW; q++) {
           float s = acc[q][t];
