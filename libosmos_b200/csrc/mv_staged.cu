@@ -154,10 +154,37 @@ template <> struct LanePlan<QTYPE_Q4_K> {
   }
 };
 
+template <> struct LanePlan<QTYPE_MXFP4> {
+  // lane l's chunk of a 136-byte stretch: block l / 4 (17 bytes: the scale's exponent, then 16 bytes of codes), its
+  // bytes 8 (l % 2) .., the low (l % 4 < 2) or high nibbles. The codes' values (doubled) come from a 16-entry F32 table
+  // in shared memory (`tbl`, set by the kernel): sixteen different banks, where the constant bank would serve a warp's
+  // different codes one after another.
+  static constexpr uint32_t kStretch = 136;
+  uint32_t al, sh, eoff, s4, tbl;
+  __device__ __forceinline__ explicit LanePlan(uint32_t l) : tbl(0) {
+    const uint32_t b = l >> 2, k = l & 3u, a0 = b * 17u + 1u + 8u * (k & 1u);
+    al = a0 & ~3u, sh = (a0 & 3u) * 8u, eoff = b * 17u, s4 = 4u * (k >> 1);
+  }
+  __device__ __forceinline__ void values(uint32_t row, const uint8_t*, uint32_t it, float* v, const Grids&) const {
+    const uint32_t base = row + it * kStretch;
+    const uint32_t r0 = lds32(base + al), r1 = lds32(base + al + 4), r2 = lds32(base + al + 8);
+    const uint32_t e = lds8(base + eoff);
+    const float dd = __uint_as_float(e >= 2 ? (e - 1) << 23 : 0x00200000u << e);
+    // a code's table offset (4 code) in each byte
+    const uint32_t w[2] = {((__funnelshift_r(r0, r1, sh) >> s4) & 0x0F0F0F0Fu) << 2, ((__funnelshift_r(r1, r2, sh) >> s4) & 0x0F0F0F0Fu) << 2};
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = mul_rn(dd, ldsf(tbl + ((w[j >> 2] >> (8 * (j & 3))) & 0xFFu)));
+  }
+};
+
 template <uint32_t T, int NT, int RW>
 __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
+  __shared__ float e2m1_values[16];  // MXFP4: a code's value, doubled
+  if constexpr (T == QTYPE_MXFP4) {
+    if (threadIdx.x < 16) e2m1_values[threadIdx.x] = (float) osmos_e2m1_doubled[threadIdx.x];
+  }
   __shared__ __align__(8) uint64_t full[kWarps][kMaxSlots];
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
   const uint32_t row_bytes = a.cols / Fmt<T>::values * Fmt<T>::bytes;
@@ -201,7 +228,8 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
 #pragma unroll
   for (int t = 0; t < NT; t++) xa[t] = smem_addr(smem) + ((uint32_t) t < live ? (uint32_t) t : live - 1) * a.cols * 4u;
   const uint32_t ni = a.cols / 256;
-  const LanePlan<T> plan(lane);
+  LanePlan<T> plan(lane);
+  if constexpr (T == QTYPE_MXFP4) plan.tbl = smem_addr(e2m1_values);
 
   for (uint32_t i = 0;; i++) {
     const uint32_t u = u_lo + warp + i * kWarps;
@@ -260,6 +288,10 @@ template <uint32_t T, int RW>
 __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
+  __shared__ float e2m1_values[16];  // MXFP4: a code's value, doubled
+  if constexpr (T == QTYPE_MXFP4) {
+    if (threadIdx.x < 16) e2m1_values[threadIdx.x] = (float) osmos_e2m1_doubled[threadIdx.x];
+  }
   __shared__ __align__(8) uint64_t full[kWarps][kMaxSlots];
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
   const uint32_t row_bytes = a.cols / Fmt<T>::values * Fmt<T>::bytes;
@@ -297,7 +329,8 @@ __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
   }
   const Grids g = stage_grids<T>(tables);
   __syncthreads();  // the barriers' initialisation, seen by every lane that will wait on them
-  const LanePlan<T> plan(lane);
+  LanePlan<T> plan(lane);
+  if constexpr (T == QTYPE_MXFP4) plan.tbl = smem_addr(e2m1_values);
 
   for (uint32_t i = 0;; i++) {
     const uint32_t u = u_lo + warp + i * kWarps;
