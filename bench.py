@@ -364,7 +364,7 @@ def run_ours(args):
 
 
 def matvec_leg(lib, dev, peak):
-    """BASELINE's first metric beside the headline: the decode matvec's weight-GB/s. Config 1's matrix (Q4_0
+    """The decode matvec's weight-GB/s, the second figure beside the headline: the reference's dense decode matrix (Q4_0
     6144 x 2048, 7 MB: a launch is latency-bound), the same rows eight times over, and a 302 MB matrix (131072 x 4096:
     what a launch reaches once its start and end no longer count), each through the int8 lane
     form (q8_run: x rounded once by q8_round) and the F32 form in the reference's order (mv_run). 64 launches on
@@ -419,7 +419,7 @@ def matvec_leg(lib, dev, peak):
 
 
 def prefill_leg(lib, dev):
-    """BASELINE's second configuration beside the headline: a Q4_K 4096 x 4096 matrix over 512 tokens through the
+    """The prefill product beside the headline: a Q4_K 4096 x 4096 matrix over 512 tokens through the
     int8 product in the reference's order of sums (mmq_group, bit-exact) and through the f16 product (mm_run), and
     the f16 product again at 2048 tokens. Activations converted once, outside the timed launches; 64 launches on
     successive cold copies of the matrix in one CUDA graph, replayed; device time a launch; the fraction is of the
