@@ -10,8 +10,8 @@
 //
 // Two kernels. One token and rows of at most 2048 values (the decode step's usual shape): every lane keeps its 64
 // values of x in registers for the whole launch, so shared memory serves only the weights (mv_regx_kernel). Else x
-// lies in shared memory and is read a chunk at a time (mv_staged_kernel; one or two tokens - more go to the generic
-// kernel, which then reads x less often a row).
+// lies in shared memory and is read a chunk at a time (mv_staged_kernel; up to eight tokens, each its own chain of
+// the same order, so a token's bits do not depend on how many ride along).
 #include "mv_staged_api.h"
 
 #include "decode.cuh"
@@ -444,7 +444,7 @@ int by_shape(const Request& r, cudaStream_t s) {
   if (!dev) return 0;
   const uint32_t row_bytes = r.cols / Fmt<T>::values * Fmt<T>::bytes;
   if (r.cols % 256 || row_bytes % 16u) return 0;  // whole 256-value stretches; a row's bytes are a bulk copy's
-  if (r.n_tok > 2) return 0;  // the generic kernel reads x less often a row then
+  if (r.n_tok > 8) return 0;
   const bool regx = r.n_tok == 1 && r.cols <= 256u * kRegIters;
   const uint32_t budget = kSmemLimit<T> - 16u;
   const uint32_t x_bytes = regx ? 0u : (r.n_tok * r.cols * 4u + 127u) & ~127u;
@@ -460,7 +460,10 @@ int by_shape(const Request& r, cudaStream_t s) {
   if (slots < 2) return 0;
   if (regx) return pair ? launch<T, 1, 2, true>(r, dev, slots, s) : launch<T, 1, 1, true>(r, dev, slots, s);
   if (r.n_tok <= 1) return pair ? launch<T, 1, 2, false>(r, dev, slots, s) : launch<T, 1, 1, false>(r, dev, slots, s);
-  return pair ? launch<T, 2, 2, false>(r, dev, slots, s) : launch<T, 2, 1, false>(r, dev, slots, s);
+  if (r.n_tok <= 2) return pair ? launch<T, 2, 2, false>(r, dev, slots, s) : launch<T, 2, 1, false>(r, dev, slots, s);
+  // 3 .. 8 tokens: a chunk is decoded once and meets every token's values (four or eight chains a row)
+  if (r.n_tok <= 4) return pair ? launch<T, 4, 2, false>(r, dev, slots, s) : launch<T, 4, 1, false>(r, dev, slots, s);
+  return pair ? launch<T, 8, 2, false>(r, dev, slots, s) : launch<T, 8, 1, false>(r, dev, slots, s);
 }
 
 }  // namespace

@@ -104,11 +104,11 @@ def test_mv_staged_row_pairs(lib, dev, oracle, name):
     """a matrix tall enough that a warp sums two rows at once; an odd row count leaves the last unit one row"""
     tid = TYPES[name]
     rows, cols = 8 * 16 * 160 + 3, 512
-    w, x = _mv_case(tid, rows, cols, 2, 2)
+    w, x = _mv_case(tid, rows, cols, 8, 2)
     want = oracle.mv_rows(tid, w, rows, cols, x)
     wd, xd = to_dev(w, dev), to_dev(x, dev)
     lib.mv_status()
-    for n in (1, 2):
+    for n in (1, 2, 3, 4, 7, 8):
         y = torch.full((n, rows), np.nan, dtype=torch.float32, device=dev)
         assert lib.mv_run(tid, ptr(wd), rows, cols, ptr(xd), n, ptr(y), None)
         sync()
