@@ -1,18 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-weight matrix path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py --kernel OP TYPE ROWS COLS [--tokens T] [--plain L] [--generic]    # one kernel alone
 
-Workload (config.workload): the Qwen-style MoE FFN layer in IQ3_XXS - 512 experts, 64 tokens routed top-10, hidden
-2048, expert width 512 - run as the int8 lane: softmax router, activations rounded to int8 per 32, fused gate + up +
-activation over the picked experts, the activations rounded again, down, each token's rows summed in ascending
+Default workload (config.workload): the Qwen-style MoE FFN layer in IQ3_XXS - 512 experts, 64 tokens routed top-10,
+hidden 2048, expert width 512 - run as the int8 lane: softmax router, activations rounded to int8 per 32, fused gate +
+up + activation over the picked experts, the activations rounded again, down, each token's rows summed in ascending
 expert id. A step is one pass of the layer over one 64-token batch; successive steps use successive cold copies of
-the layer's weights (a model's next layer), 616 MB each, so no step finds its weights in L2.
+the layer's weights (a model's next layer), so no step finds its weights in L2. On N GPUs the layer runs
+expert-parallel (libosmos_b200/ep.py): the same 64 tokens, experts and home tokens split over the ranks.
 
-Prints ONE JSON line: tokens/s through the layer (value: inputs resident in HBM; e2e: host buffers in, host
-buffer out through the C ABI), the dominant kernel's weight-GB/s against the measured HBM peak (roofline), and the
-reference's own CPU lane on this host's cores beside it (cpu_baseline). `--impl reference` times only that CPU
-path.
+Prints ONE JSON line: tokens/s through the layer (value: inputs resident in HBM; e2e: pinned host buffers in, host
+buffer out, through the C ABI), the dominant kernel's weight-GB/s against the measured HBM peak (roofline), a
+per-stage breakdown, and the reference's own CPU lane on this host's cores beside it (cpu_baseline).
+`--impl reference` times only that CPU path. Every figure is preceded, in the same run, by a bit-for-bit check of the
+GPU result against the CPU checker.
 """
 import argparse
 import json
@@ -28,6 +31,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC, UNIT = "moe_layer_tokens_per_s", "tokens/s"
+REGIONS = 5  # timed regions of exactly --steps steps each; value is their median
 
 
 def measured_peaks():
@@ -39,8 +43,16 @@ def measured_peaks():
         return 6650.0, "fallback"
 
 
+def measured_tflops():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 class ClockSampler:
-    """nvidia-smi's SM clock and throttle reasons sampled while the timed region runs"""
+    """nvidia-smi's SM clock and throttle reasons sampled while the timed regions run"""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -51,7 +63,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
             self.thread.start()
@@ -91,15 +103,19 @@ def dist_env():
     return rank, world, int(os.environ.get("LOCAL_RANK", str(rank)))
 
 
+def workload_config(cfg):
+    """the workload's description: the same keys in both arms"""
+    return {"workload": cfg["name"], "tokens": cfg["n_tok"], "experts": cfg["n_exp"], "top_k": cfg["k"],
+            "hidden": cfg["dim"], "expert_ff": cfg["ff"], "format": cfg["type"]}
+
+
 # ---------------------------------------------------------------------------------------------------------------------
-# the reference arm: the reference's CPU lane (oracle/_ref, its sources compiled unmodified) or, where that library
-# is missing or this CPU lacks its AVX-512 VNNI kernels, this repository's scalar restatement of it
+# the CPU checker and the reference arm: the reference's CPU lane (oracle/_ref, its sources compiled unmodified) or,
+# where that library is missing or this CPU lacks its AVX-512 VNNI kernels, this repository's scalar restatement
 # ---------------------------------------------------------------------------------------------------------------------
-def cpu_step_inputs(cfg, step):
-    from libosmos_b200 import workloads
-    x, logits = workloads.moe_inputs_host(cfg, step)
-    ids, wts = workloads.softmax_topk(logits, cfg["k"])
-    # rows by (expert, pick): the lane's layout (a row an expert's copy of its token's input)
+def lane_rows_of(cfg, x, ids, wts):
+    """a step's rows by (expert, pick) - the lane's layout, a row an expert's copy of its token's input: the rows'
+    inputs and routed weights, the experts' (id, first row, count), and each row's pick"""
     flat = ids.reshape(-1)
     order = np.argsort(flat, kind="stable")
     xr = np.ascontiguousarray(x[order // cfg["k"]])
@@ -112,19 +128,27 @@ def cpu_step_inputs(cfg, step):
     return xr, sc, experts, order
 
 
+def cpu_step_inputs(cfg, step):
+    from libosmos_b200 import workloads
+    x, logits = workloads.moe_inputs_host(cfg, step)
+    ids, wts = workloads.softmax_topk(logits, cfg["k"])
+    return lane_rows_of(cfg, x, ids, wts)
+
+
 class CpuArm:
-    def __init__(self, cfg, host_tensors, threads=None):
+    def __init__(self, cfg, host_tensors, threads=None, pin=True):
         from libosmos_b200 import synth, workloads
         from oracle.oracle import Oracle, Reference
         self.cfg, self.host = cfg, host_tensors
         self.tid = synth.TYPE_ID[cfg["type"]]
         self.per = workloads.moe_expert_bytes(cfg)
-        self.cores = os.cpu_count() or 1
+        avail = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
         self.kind = "reference" if Reference.available() else "port"
+        self.pinned = []
         if self.kind == "reference":
             self.ref = Reference()
-            self.threads = min(64, threads or self.cores)
-            self.pool = self.ref.lib.cpu_lane_create(self.threads, None, cfg["n_tok"] * cfg["k"], cfg["dim"], cfg["ff"])
+            self.threads = max(1, min(64, threads or avail))
+            self.pool, self.pinned = self.ref.lane_pool(self.threads, cfg["n_tok"] * cfg["k"], cfg["dim"], cfg["ff"], pin)
             if not self.pool:
                 self.kind = "port"
         if self.kind == "port":
@@ -133,16 +157,22 @@ class CpuArm:
     def parts(self, e):
         return [self.host[m][e * self.per[m]:(e + 1) * self.per[m]] for m in range(3)]
 
-    def run(self, xr, sc, experts, limit_rows=None):
-        """one step's expert FFN rows on the CPU; returns (seconds, rows done, y)"""
+    def job(self, xr, sc, experts):
+        cfg = self.cfg
+        ex = [tuple(self.parts(e)) + (r0, c) for e, r0, c in experts]
+        return self.ref.lane_job(self.tid, self.tid, cfg["dim"], cfg["ff"], cfg["lim"], xr, sc, ex)
+
+    def rows(self, xr, sc, experts, limit_rows=None):
+        """one step's expert FFN rows on the CPU; returns (seconds, rows done, y). The reference's job is built before
+        the clock starts."""
         cfg = self.cfg
         if self.kind == "reference":
-            ex = [tuple(self.parts(e)) + (r0, c) for e, r0, c in experts]
+            job = self.job(xr, sc, experts)
             t0 = time.perf_counter()
-            y = self.ref.lane_ffn(self.threads, self.tid, self.tid, cfg["dim"], cfg["ff"], cfg["lim"], xr, sc, ex, pool=self.pool)
+            ok = job.run(self.pool)
             dt = time.perf_counter() - t0
-            assert y is not None, "the reference's cpu_lane refused the job"
-            return dt, xr.shape[0], y
+            assert ok, "the reference's cpu_lane refused or failed the job"
+            return dt, xr.shape[0], job.y
         done, t0 = 0, time.perf_counter()
         y = np.zeros((xr.shape[0], cfg["dim"]), np.float32)
         for e, r0, c in experts:
@@ -154,30 +184,52 @@ class CpuArm:
                 break
         return time.perf_counter() - t0, done, y
 
+    def layer(self, x, ids, wts):
+        """the whole layer's output for tokens x with the given picks: the rows, then each token's rows added in
+        ascending expert id (the checker of the GPU step)"""
+        cfg = self.cfg
+        xr, sc, experts, order = lane_rows_of(cfg, x, ids, wts)
+        _, done, y = self.rows(xr, sc, experts)
+        assert done == xr.shape[0]
+        out = np.zeros((x.shape[0], cfg["dim"]), np.float32)
+        tok = order // cfg["k"]
+        for r in range(xr.shape[0]):  # rows ascend with the expert id
+            out[tok[r]] = (out[tok[r]] + y[r]).astype(np.float32)
+        return out
+
+    def timed(self, steps, warmup, first_step=0):
+        """tokens/s over `steps` steps after `warmup`; each step's job is built outside its clock"""
+        cfg, limit = self.cfg, (None if self.kind == "reference" else 24)
+        times, rows = [], 0
+        for s in range(warmup + steps):
+            xr, sc, experts, _ = cpu_step_inputs(cfg, first_step + s)
+            dt, done, _ = self.rows(xr, sc, experts, limit)
+            if s >= warmup:
+                times.append(dt), (rows := rows + done)
+        sample = ("%d full steps of %d tokens (%d expert rows each) after %d warm-up" % (steps, cfg["n_tok"], cfg["n_tok"] * cfg["k"], warmup)
+                  if limit is None else "the first %d expert rows of %d steps, scaled to tokens" % (limit, steps))
+        return rows / cfg["k"] / sum(times), 1e3 * sum(times) / len(times), sample
+
 
 def run_reference(args):
     from libosmos_b200 import workloads
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    cfg = workloads.MOE_IQ3
-    arm = CpuArm(cfg, workloads.moe_layer_host(cfg))
-    limit = None if arm.kind == "reference" else 24  # the scalar port: a bounded sample of a step's rows
-    times, rows = [], 0
-    for s in range(args.warmup + args.steps):
-        xr, sc, experts, _ = cpu_step_inputs(cfg, s)
-        dt, done, _ = arm.run(xr, sc, experts, limit)
-        if s >= args.warmup:
-            times.append(dt), (rows := rows + done)
-    tok_s = rows / cfg["k"] / sum(times)
-    sample = ("full steps of %d tokens (%d expert rows each)" % (cfg["n_tok"], cfg["n_tok"] * cfg["k"])
-              if limit is None else "the first %d expert rows of each step, scaled to tokens" % limit)
+    cfg = workloads.BY_NAME[args.workload]
+    host = workloads.moe_layer_host(cfg)
+    arm = CpuArm(cfg, host)
+    tok_s, ms, sample = arm.timed(args.steps, args.warmup)
+    one = None
+    if arm.kind == "reference":  # the single-thread figure beside it
+        one_arm = CpuArm(cfg, host, threads=1)
+        one = one_arm.timed(max(1, min(3, args.steps)), 1)[0]
     line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
-            "config": {"workload": cfg["name"], "tokens": cfg["n_tok"], "experts": cfg["n_exp"], "top_k": cfg["k"],
-                       "hidden": cfg["dim"], "expert_ff": cfg["ff"], "format": cfg["type"]},
-            "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": arm.threads, "kind": arm.kind, "sample": sample},
+            "config": workload_config(cfg),
+            "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": arm.threads, "kind": arm.kind, "sample": sample,
+                             "pinned_cpus": arm.pinned, "one_thread_value": one},
             "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -189,46 +241,71 @@ def run_ours(args):
     import torch
 
     import libosmos_b200
-    from libosmos_b200 import runner, workloads
+    from libosmos_b200 import ep, workloads
     rank, world, local = dist_env()
     assert world == args.gpus or world == 1, "launch N ranks for --gpus N"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    dist = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-        from libosmos_b200 import ep
-        return ep.run_bench(args, rank, world, dev, METRIC, UNIT, ClockSampler, measured_peaks)
-
     lib = libosmos_b200.load()
-    cfg = workloads.MOE_IQ3
-    n_tok, dim = cfg["n_tok"], cfg["dim"]
+    cfg = workloads.BY_NAME[args.workload]
+    n_tok, dim, k = cfg["n_tok"], cfg["dim"], cfg["k"]
     host = workloads.moe_layer_host(cfg)
+    per = workloads.moe_expert_bytes(cfg)
     copies = 4
-    layer = runner.MoeLane(lib, cfg, dev, copies=copies, host_tensors=host)
+    transport = os.environ.get("OSMOS_EP_TRANSPORT", "peer")
+    try:
+        layer = ep.EpMoeLane(lib, cfg, dev, rank, world, copies=copies, host_tensors=host, transport=transport, dist=dist)
+    except RuntimeError as e:  # the peers' memory could not be mapped here: the exchanges go through NCCL
+        if transport != "peer" or world == 1:
+            raise
+        transport = "nccl (peer mapping unavailable: %s)" % e
+        layer = ep.EpMoeLane(lib, cfg, dev, rank, world, copies=copies, host_tensors=host, transport="nccl", dist=dist)
+    fused = layer.transport == "peer"
+    t0, t1 = ep.home_tokens(rank, world, n_tok)
+    T = t1 - t0
     n_inputs = 8
     hx, hl = zip(*[workloads.moe_inputs_host(cfg, s) for s in range(n_inputs)])
-    dx = [torch.from_numpy(a).to(dev) for a in hx]
-    dl = [torch.from_numpy(a).to(dev) for a in hl]
-    px = [torch.from_numpy(a).pin_memory() for a in hx]
-    pl = [torch.from_numpy(a).pin_memory() for a in hl]
-    out = torch.empty((n_tok, dim), dtype=torch.float32, device=dev)
+    dx = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).to(dev) for a in hx]
+    dl = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).to(dev) for a in hl]
+    px = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).pin_memory() for a in hx]
+    pl = [torch.from_numpy(np.ascontiguousarray(a[t0:t1])).pin_memory() for a in hl]
+    out = torch.empty((T, dim), dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
 
-    # parity first: step 0 against the CPU oracle on a few tokens (the GPU tests hold the rest)
-    from oracle.oracle import Oracle
-    layer.step(dx[0], dl[0], out, n_tok, 0, stream)
+    def all_ok(ok):
+        if world == 1:
+            return ok
+        flag = torch.tensor([0 if ok else 1], device=dev)
+        dist.all_reduce(flag)
+        return int(flag.item()) == 0
+
+    # parity first: EVERY home token of step 0 against the CPU checker's bits (the reference's own CPU lane where it
+    # runs, else the scalar restatement), with the picks the GPU made (checked equal to a double-precision softmax)
+    layer.step(dx[0], dl[0], out, 0, stream)
     torch.cuda.synchronize()
-    ids = layer.ids.cpu().numpy().reshape(n_tok, cfg["k"])
-    wts = layer.wts.cpu().numpy().reshape(n_tok, cfg["k"])
-    want = runner.moe_oracle(Oracle(), cfg, host, hx[0][:2], ids[:2], wts[:2])
-    got = out.cpu().numpy()[:2]
-    if not np.array_equal(got.view(np.uint32), want.view(np.uint32)):
-        raise SystemExit("bench: the GPU layer's output differs from the CPU oracle's bits - not timing a wrong result")
-    distinct = [len(np.unique(workloads.softmax_topk(l, cfg["k"])[0])) for l in hl]
+    got_ids, got_wts = layer.last_picks()
+    want_ids, want_wts = workloads.softmax_topk(hl[0][t0:t1], k)
+    arm = CpuArm(cfg, host)
+    ok = np.array_equal(got_ids, want_ids) and np.allclose(got_wts, want_wts, rtol=1e-5, atol=0)
+    want = arm.layer(hx[0][t0:t1], got_ids, got_wts)
+    ok = ok and np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    if not all_ok(ok):
+        raise SystemExit("bench: the GPU layer's output differs from the CPU checker's bits on some rank - not timing a wrong result")
+    parity = "all %d home tokens of step 0 on every rank, bit-equal to the %s" % (
+        T, "reference's cpu_lane_submit" if arm.kind == "reference" else "scalar restatement of the reference's CPU lane")
+    distinct = [np.unique(workloads.softmax_topk(l, k)[0]) for l in hl]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
 
     def timed(fn, steps, drain=None):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
         torch.cuda.synchronize()
         e0.record()
         for s in range(steps):
@@ -237,20 +314,26 @@ def run_ours(args):
             drain()  # the side streams' last copies are inside the timed region
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / 1e3
+        barrier()
+        t = e0.elapsed_time(e1) / 1e3
+        if world > 1:
+            tt = torch.tensor([t], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
+        return t
 
     def resident(s):
-        layer.step(dx[s % n_inputs], dl[s % n_inputs], out, n_tok, s % copies, stream)
+        layer.step(dx[s % n_inputs], dl[s % n_inputs], out, s % copies, stream)
 
     # end to end: every step's inputs come from pinned host memory and its output goes back to it, the copies on
     # their own streams so that step s + 1's inputs and step s - 1's output move while step s computes (two buffers
-    # of each; events order a buffer's copy, its use and its reuse)
+    # of each; events order a buffer's copy, its use and its reuse); all of it inside the timed region
     cin, cout = torch.cuda.Stream(), torch.cuda.Stream()
     main = torch.cuda.current_stream()
     bx = [torch.empty_like(dx[0]) for _ in range(2)]
     bl = [torch.empty_like(dl[0]) for _ in range(2)]
     bo = [torch.empty_like(out) for _ in range(2)]
-    bp = [torch.empty((n_tok, dim), dtype=torch.float32).pin_memory() for _ in range(2)]
+    bp = [torch.empty((T, dim), dtype=torch.float32).pin_memory() for _ in range(2)]
     in_ready = [torch.cuda.Event() for _ in range(2)]
     used = [torch.cuda.Event() for _ in range(2)]
     out_done = [torch.cuda.Event() for _ in range(2)]
@@ -266,7 +349,7 @@ def run_ours(args):
             in_ready[b].record(cin)
         main.wait_event(in_ready[b])
         main.wait_event(out_done[b])  # the last output in bo[b] has reached the host
-        layer.step(bx[b], bl[b], bo[b], n_tok, s % copies, stream)
+        layer.step(bx[b], bl[b], bo[b], s % copies, stream)
         used[b].record(main)
         cout.wait_event(used[b])
         with torch.cuda.stream(cout):
@@ -279,108 +362,171 @@ def run_ours(args):
     for s in range(args.warmup):
         resident(s), end_to_end(s)
     # the resident step as a user of the C ABI would run a decode loop: captured once per (input, weight copy) pair in
-    # a CUDA graph and replayed - the same seven launches, without the host's launch gaps
-    torch.cuda.synchronize()
-    graphs, side = [], torch.cuda.Stream()
-    for s in range(n_inputs):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=side):
-            layer.step(dx[s], dl[s], out, n_tok, s % copies, side.cuda_stream)
-        graphs.append(g)
+    # a CUDA graph and replayed - the same launches (the fused step keeps its step number on the device, so a captured
+    # step is valid for every replay), without the host's launch gaps
+    graphs = []
+    if fused:
+        torch.cuda.synchronize()
+        barrier()
+        side = torch.cuda.Stream()
+        for s in range(n_inputs):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                layer.step(dx[s], dl[s], out, s % copies, side.cuda_stream)
+            graphs.append(g)
+        torch.cuda.synchronize()
+        barrier()
 
     def resident_graph(s):
         graphs[s % n_inputs].replay()
 
-    for s in range(args.warmup):
-        resident_graph(s)
-    torch.cuda.synchronize()
-    layer.step(dx[1], dl[1], out, n_tok, 1 % copies, stream)
-    torch.cuda.synchronize()
-    plain_bits = out.cpu().numpy().view(np.uint32).copy()
-    resident_graph(1)
-    torch.cuda.synchronize()
-    if not np.array_equal(plain_bits, out.cpu().numpy().view(np.uint32)):
-        raise SystemExit("bench: the graph-replayed step differs from the stream-launched one")
+    best = resident_graph if graphs else resident
+    if graphs:
+        for s in range(args.warmup):
+            resident_graph(s)
+        torch.cuda.synchronize()
+        layer.step(dx[1], dl[1], out, 1 % copies, stream)
+        torch.cuda.synchronize()
+        plain_bits = out.cpu().numpy().view(np.uint32).copy()
+        resident_graph(1)
+        torch.cuda.synchronize()
+        if not all_ok(np.array_equal(plain_bits, out.cpu().numpy().view(np.uint32))):
+            raise SystemExit("bench: the graph-replayed step differs from the stream-launched one")
     with ClockSampler(local) as clocks:
-        t_res = timed(resident_graph, args.steps)
-        t_res_stream = timed(resident, args.steps)
-        t_e2e = timed(end_to_end, args.steps, e2e_drain)
-        # the dominant kernel alone: events around q8_gate_up inside the same step
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        # about a second of the same steps first, so that the clock sampler sees the GPU under this load (the same
+        # count on every rank: a rank's steps pair with its peers')
+        n_warm = int(min(20000, max(args.steps, 1.0 / (timed(best, args.steps) / args.steps))))
+        for s in range(n_warm):
+            best(s)
+            if s % 256 == 255:
+                torch.cuda.synchronize()
         torch.cuda.synchronize()
-        for s, (a, b) in enumerate(evs):
-            layer.step_timed_gate_up(dx[s % n_inputs], dl[s % n_inputs], out, n_tok, s % copies, a, b, stream)
-        torch.cuda.synchronize()
-    k_ms = [a.elapsed_time(b) for a, b in evs]
-    per = workloads.moe_expert_bytes(cfg)
-    alg = [distinct[s % n_inputs] * (per[0] + per[1]) for s in range(args.steps)]
-    achieved = float(np.sum(alg) / (np.sum(k_ms) * 1e-3) / 1e9)
-    peak, peak_kind = measured_peaks()
+        t_regions = [timed(best, args.steps) for _ in range(REGIONS)]
+        t_stream = [timed(resident, args.steps) for _ in range(REGIONS)]
+        t_e2e = [timed(end_to_end, args.steps, e2e_drain) for _ in range(REGIONS)]
+        # the stages of a step by events inside the step (fused transport), max over ranks of each stage's mean
+        stage_names = ["route+round+dispatch", "wait+tables", "gate_up", "round", "down+push", "wait+combine"]
+        stage_ms = None
+        if fused:
+            n_ev = min(args.steps, 50)
+            evs = [[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(n_ev)]
+            barrier()
+            torch.cuda.synchronize()
+            for s, e in enumerate(evs):
+                layer.step_phases(dx[s % n_inputs], dl[s % n_inputs], out, s % copies, stream, e)
+            torch.cuda.synchronize()
+            stage = np.array([[e[i].elapsed_time(e[i + 1]) for i in range(6)] for e in evs])
+            stage_ms = stage.mean(axis=0)
+            if world > 1:
+                tt = torch.tensor(stage_ms, device=dev)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                stage_ms = tt.cpu().numpy()
+    t_res, t_str, t_ee = float(np.median(t_regions)), float(np.median(t_stream)), float(np.median(t_e2e))
+    if lib.ep_wait_status() or lib.q8_status():
+        raise SystemExit("bench: a bounded wait ran out on rank %d" % rank)
+    if rank == 0:
+        e0, e1 = ep.expert_range(rank, world, cfg["n_exp"])
+        peak, peak_kind = measured_peaks()
+        roof = {"bound": "hbm", "peak": peak, "unit": "GB/s", "peak_kind": peak_kind}
+        if fused:
+            # rank 0's gate + up + activation kernel: the distinct experts of the steps it was timed on, that it owns
+            alg = [int(((distinct[s % n_inputs] >= e0) & (distinct[s % n_inputs] < e1)).sum()) * (per[0] + per[1])
+                   for s in range(len(evs))]
+            k_ms = stage[:, 2]
+            achieved = float(np.sum(alg) / (np.sum(k_ms) * 1e-3) / 1e9)
+            roof.update({"kernel": "q8_gate_up (lane_ring_kernel, %s, fused gate + up + activation) on rank 0" % cfg["type"],
+                         "achieved": achieved, "frac": achieved / peak,
+                         "traffic": 296433152 if (world == 1 and cfg["name"] == workloads.MOE_IQ3["name"]) else None,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, profiles/lane_ring_rows_iq3xxs_moe.md"
+                         if world == 1 else None,
+                         "algorithmic_bytes_per_launch": float(np.mean(alg)), "us_per_launch": float(np.mean(k_ms) * 1e3)})
+        cpu = None
+        try:
+            tok_s, _, sample = arm.timed(5 if arm.kind == "reference" else 1, 1)
+            cpu = {"value": tok_s, "unit": UNIT, "cores": arm.threads, "kind": arm.kind, "sample": sample}
+        except Exception as e:  # the baseline is reported, never required
+            cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "unavailable", "sample": str(e)[:120]}
+        line = {"metric": METRIC, "value": n_tok * args.steps / t_res, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic", "config": workload_config(cfg),
+                "run": {"parallelism": "1 gpu" if world == 1 else
+                        "ep%d: experts in contiguous ranges, tokens by home rank; dispatch and combine by peer stores from the producing kernels" % world,
+                        "transport": transport if world > 1 else "none",
+                        "launch": ("value: CUDA graph replay, one graph a (input, weight copy) pair" if graphs else "value: launched on the stream")
+                                  + "; the same steps launched on the stream take %.4f ms" % (1e3 * t_str / args.steps),
+                        "cold_cache": "%d copies of each rank's %d MB of expert weights cycled; a step touches ~%d MB in all (> 126 MB L2 at 1 GPU)"
+                                      % (copies, sum(per) * cfg["n_exp"] // world // 1000000,
+                                         int(np.mean([len(d) for d in distinct])) * sum(per) // 1000000),
+                        "timing": "median of %d regions of exactly %d steps, CUDA events, max over ranks" % (REGIONS, args.steps),
+                        "regions_ms_per_step": [1e3 * t / args.steps for t in t_regions],
+                        "parity": parity},
+                "e2e": {"value": n_tok * args.steps / t_ee, "unit": UNIT,
+                        "h2d_bytes_per_step": int((px[0].numel() + pl[0].numel()) * 4 * world),
+                        "d2h_bytes_per_step": int(bp[0].numel() * 4 * world)},
+                "gpu_launches": layer.kernels_per_step * args.steps * world,
+                "roofline": roof,
+                "stages_ms": None if stage_ms is None else dict(zip(stage_names, [float(v) for v in stage_ms])),
+                "cpu_baseline": cpu, "clocks": clocks.summary()}
+        if world == 1 and cfg["name"] == workloads.MOE_IQ3["name"]:
+            try:
+                line["matvec"] = matvec_leg(lib, dev, peak)
+            except Exception as e:  # a second figure beside the headline: reported, never required
+                line["matvec"] = {"unavailable": str(e)[:160]}
+            try:
+                line["prefill"] = prefill_leg(lib, dev)
+            except Exception as e:
+                line["prefill"] = {"unavailable": str(e)[:160]}
+        print(json.dumps(line), flush=True)
+    layer.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
-    # the CPU baseline beside it: the reference's CPU lane on this host, one to three steps
-    cpu = None
-    try:
-        arm = CpuArm(cfg, host)
-        limit = None if arm.kind == "reference" else 24
-        tt, rows = 0.0, 0
-        for s in range(3 if arm.kind == "reference" else 1):
-            xr, sc, experts, _ = cpu_step_inputs(cfg, s)
-            dt, done, _ = arm.run(xr, sc, experts, limit)
-            if s or arm.kind != "reference":
-                tt, rows = tt + dt, rows + done
-        cpu = {"value": rows / cfg["k"] / tt, "unit": UNIT, "cores": arm.threads, "kind": arm.kind,
-               "sample": "2 full 64-token steps after 1 warm-up" if limit is None else "24 expert rows of one step, scaled"}
-    except Exception as e:  # the baseline is reported, never required
-        cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "unavailable", "sample": str(e)[:120]}
 
-    line = {"metric": METRIC, "value": n_tok * args.steps / t_res, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
-            "config": {"workload": cfg["name"], "tokens": n_tok, "experts": cfg["n_exp"], "top_k": cfg["k"], "hidden": dim,
-                       "expert_ff": cfg["ff"], "format": cfg["type"], "parallelism": "1 gpu",
-                       "launch": "value: CUDA graph replay, one graph a (input, weight copy) pair; the same steps launched "
-                                 "on the stream take %.4f ms" % (1e3 * t_res_stream / args.steps),
-                       "cold_cache": "%d copies of the layer's 616 MB of weights cycled; each step touches ~%d MB > 126 MB L2"
-                                     % (copies, int(np.mean(distinct)) * sum(per) // 1000000)},
-            "e2e": {"value": n_tok * args.steps / t_e2e, "unit": UNIT,
-                    "h2d_bytes_per_step": int(px[0].numel() * 4 + pl[0].numel() * 4), "d2h_bytes_per_step": int(bp[0].numel() * 4)},
-            "gpu_launches": layer.kernels_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "q8_gate_up (lane_ring_kernel, IQ3_XXS, fused gate + up + activation)",
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                         "traffic": 296433152, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch "
-                         "(step 6's experts: 291.8 MB + 4.7 MB), profiles/lane_ring_rows_iq3xxs_moe.md",
-                         "algorithmic_bytes_per_launch": float(np.mean(alg)),
-                         "us_per_launch": float(np.mean(k_ms) * 1e3)},
-            "cpu_baseline": cpu, "clocks": clocks.summary()}
-    try:
-        line["matvec"] = matvec_leg(lib, dev, peak)
-    except Exception as e:  # a second figure beside the headline: reported, never required
-        line["matvec"] = {"unavailable": str(e)[:160]}
-    try:
-        line["prefill"] = prefill_leg(lib, dev)
-    except Exception as e:
-        line["prefill"] = {"unavailable": str(e)[:160]}
-    print(json.dumps(line), flush=True)
+def graph_time(fn, n=64, reps=5):
+    """device microseconds a launch: n launches (fn(i, stream)) captured in one CUDA graph, replayed reps times"""
+    import torch
+    for i in range(3):
+        assert fn(i, None), "the library refused the call"
+    torch.cuda.synchronize()
+    g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=st):
+        for i in range(n):
+            assert fn(i, st.cuda_stream)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (n * reps)
 
 
 def matvec_leg(lib, dev, peak):
     """The decode matvec's weight-GB/s, the second figure beside the headline: the reference's dense decode matrix (Q4_0
     6144 x 2048, 7 MB: a launch is latency-bound), the same rows eight times over, and a 302 MB matrix (131072 x 4096:
-    what a launch reaches once its start and end no longer count), each through the int8 lane
-    form (q8_run: x rounded once by q8_round) and the F32 form in the reference's order (mv_run). 64 launches on
-    successive cold copies (more than 1 GiB cycled) captured in one CUDA graph, replayed; device time a launch."""
+    what a launch reaches once its start and end no longer count), each through the int8 lane form (q8_run: x rounded
+    once by q8_round) and the F32 form in the reference's order (mv_run). Each case's first launch is compared with the
+    CPU checker's bits (a sample of rows for the large matrices) before anything is timed. 64 launches on successive
+    cold copies (more than 1 GiB cycled) captured in one CUDA graph, replayed; device time a launch."""
     import torch
 
     from libosmos_b200 import synth
+    from oracle.oracle import Oracle
+    orc = Oracle()
     tid = synth.TYPE_ID["Q4_0"]
     out = {"format": "Q4_0", "tokens": 1, "timing": "64 launches on successive copies (> 1 GiB cycled) in a CUDA graph, replayed 5 times",
+           "parity": "first launch of every case bit-equal to the CPU checker (all rows at 6144, 4096 sampled rows above)",
            "cases": []}
     for rows, cols in ((6144, 2048), (49152, 2048), (131072, 4096)):
         w = synth.random_tensor(tid, rows, cols, synth.rng_for(1, tid, rows))
         nb = int(w.size)
         copies = max(2, int(1.1 * 2 ** 30 // nb) + 1)
         pool = torch.from_numpy(w).to(dev).repeat(copies)
-        x = torch.randn(1, cols, device=dev)
+        xh = synth.rng_for(5, rows).standard_normal((1, cols)).astype(np.float32)
+        x = torch.from_numpy(xh).to(dev)
         q = torch.zeros(1, cols, dtype=torch.int8, device=dev)
         d = torch.zeros(1, cols // 32, device=dev)
         y = torch.empty(1, rows, device=dev)
@@ -391,25 +537,20 @@ def matvec_leg(lib, dev, peak):
             "mv_run": lambda i, st: lib.mv_run(tid, pool.data_ptr() + (i % copies) * nb, rows, cols, x.data_ptr(), 1,
                                                y.data_ptr(), st),
         }
+        # the checker's rows: all of a small matrix, else a seeded sample
+        pick = np.arange(rows) if rows <= 8192 else np.sort(synth.rng_for(6, rows).choice(rows, 4096, replace=False))
+        rb = nb // rows
+        wsel = np.ascontiguousarray(w.reshape(rows, rb)[pick]).reshape(-1)
+        qh, dh = orc.q8_round(xh)
+        want = {"q8_run": orc.q8_rows(tid, wsel, len(pick), cols, qh, dh), "mv_run": orc.mv_rows(tid, wsel, len(pick), cols, xh)}
         case = {"rows": rows, "cols": cols, "weight_bytes": nb}
         for name, fn in calls.items():
-            for i in range(3):
-                assert fn(i, None)
+            y.zero_()
+            assert fn(1, None)
             torch.cuda.synchronize()
-            n, reps = 64, 5
-            g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
-            with torch.cuda.graph(g, stream=st):
-                for i in range(n):
-                    assert fn(i, st.cuda_stream)
-            g.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                g.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (n * reps)
+            if not np.array_equal(y.cpu().numpy()[:, pick].view(np.uint32), want[name].view(np.uint32)):
+                raise SystemExit("bench: %s at %dx%d differs from the CPU checker's bits" % (name, rows, cols))
+            us = graph_time(fn)
             case[name] = {"us_per_launch": us, "weight_gbs": nb / us / 1e3, "frac_of_hbm_peak": nb / us / 1e3 / peak}
         out["cases"].append(case)
         del pool
@@ -419,29 +560,37 @@ def matvec_leg(lib, dev, peak):
 
 
 def prefill_leg(lib, dev):
-    """The prefill product beside the headline: a Q4_K 4096 x 4096 matrix over 512 tokens through the
-    int8 product in the reference's order of sums (mmq_group, bit-exact) and through the f16 product (mm_run), and
-    the f16 product again at 2048 tokens. Activations converted once, outside the timed launches; 64 launches on
-    successive cold copies of the matrix in one CUDA graph, replayed; device time a launch; the fraction is of the
-    measured bf16 burst peak."""
+    """The prefill product beside the headline: a Q4_K 4096 x 4096 matrix over 512 tokens through the int8 product in
+    the reference's order of sums (mmq_group, bit-exact) and through the f16 product (mm_run), and the f16 product
+    again at 2048 tokens. Before timing, mmq_group's output is compared bit for bit with the CPU checker on 256 sampled
+    rows x all tokens, and mm_run's with a double-precision sum over the f16-rounded operands on the same rows, within
+    the reference test's bound. Activations converted once, outside the timed launches; 64 launches on successive cold
+    copies of the matrix in one CUDA graph, replayed; device time a launch. The int8 fraction is of twice the measured
+    bf16 burst (the nominal ratio of the int8 to the bf16 tensor rate; no int8 peak is measured here)."""
     import torch
 
     from libosmos_b200 import synth
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            tf_peak, kind = float(json.load(f)["bf16_tflops"]), "measured"
-    except Exception:
-        tf_peak, kind = 1590.0, "fallback"
+    from oracle.oracle import Oracle
+    orc = Oracle()
+    tf_peak, kind = measured_tflops()
     tid, rows, cols = synth.TYPE_ID["Q4_K"], 4096, 4096
     w = synth.random_tensor(tid, rows, cols, synth.rng_for(2, tid, rows))
     nb = int(w.size)
     copies = 24  # 226 MB cycled: more than the 126 MB L2
     pool = torch.from_numpy(w).to(dev).repeat(copies)
-    out = {"format": "Q4_K", "rows": rows, "cols": cols, "peak_tflops": tf_peak, "peak_kind": kind, "cases": []}
+    pick = np.sort(synth.rng_for(7).choice(rows, 256, replace=False))
+    rb = nb // rows
+    wsel = np.ascontiguousarray(w.reshape(rows, rb)[pick]).reshape(-1)
+    wf = orc.dequant(tid, wsel, len(pick) * cols).reshape(len(pick), cols)
+    out = {"format": "Q4_K", "rows": rows, "cols": cols, "peak_tflops": tf_peak, "peak_kind": kind,
+           "int8_peak_tops": 2 * tf_peak, "int8_peak_kind": "nominal: twice the %s bf16 burst" % kind,
+           "parity": "mmq_group bit-equal to the CPU checker, mm_run within (cols/16+20) 2^-24 sum|w16 x16| of a float64 sum, 256 sampled rows x all tokens",
+           "cases": []}
     for op, tokens in (("mmq_group", 512), ("mm_run", 512), ("mm_run", 2048)):
         n16 = (tokens + 15) // 16 * 16
-        x = torch.randn(tokens, cols, device=dev)
-        y = torch.empty(tokens, rows, device=dev)
+        xh = synth.rng_for(8, tokens).standard_normal((tokens, cols)).astype(np.float32)
+        x = torch.from_numpy(xh).to(dev)
+        y = torch.zeros(tokens, rows, device=dev)
         if op == "mm_run":
             x16 = torch.zeros(n16 * cols, dtype=torch.float16, device=dev)
             flag = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -461,29 +610,113 @@ def prefill_leg(lib, dev):
             fn = lambda i, st: lib.mmq_group(tid, tabs[i % copies].data_ptr(), cnt.data_ptr(), 1, tokens, rows, cols,
                                              x8.data_ptr(), dx.data_ptr(), sx.data_ptr(), zero.data_ptr(), y.data_ptr(),
                                              zero.data_ptr(), rows, st)
-        for i in range(3):
-            assert fn(i, None)
+        assert fn(1, None)
         torch.cuda.synchronize()
-        n, reps = 64, 5
-        g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
-        with torch.cuda.graph(g, stream=st):
-            for i in range(n):
-                assert fn(i, st.cuda_stream)
-        g.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            g.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (n * reps)
+        got = y.cpu().numpy()[:, pick]
+        if op == "mmq_group":
+            hx8, hdx, hsx = orc.mmq_x8_rows(xh, np.arange(tokens, dtype=np.int32), cols)
+            want = orc.mmq_rows(wsel, len(pick), cols, hx8, hdx, hsx, 0, tokens)
+            good = np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        else:
+            w16 = wf.astype(np.float16).astype(np.float64)
+            h16 = xh.astype(np.float16).astype(np.float64)
+            want = h16 @ w16.T
+            bound = (cols / 16 + 20) * 2.0 ** -24 * (np.abs(h16) @ np.abs(w16).T)
+            good = bool((np.abs(got.astype(np.float64) - want) <= bound).all())
+        if not good:
+            raise SystemExit("bench: %s at %d tokens fails its check against the CPU checker" % (op, tokens))
+        us = graph_time(fn)
         tf = 2.0 * rows * cols * tokens / us / 1e6
-        out["cases"].append({"op": op, "tokens": tokens, "us_per_launch": us, "tflops": tf, "frac_of_bf16_peak": tf / tf_peak,
-                             "tokens_per_s": tokens / us * 1e6})
+        case = {"op": op, "tokens": tokens, "us_per_launch": us, "tflops": tf, "tokens_per_s": tokens / us * 1e6}
+        if op == "mmq_group":
+            case["frac_of_int8_peak"], case["peak_kind"] = tf / (2 * tf_peak), out["int8_peak_kind"]
+        else:
+            case["frac_of_bf16_peak"] = tf / tf_peak
+        out["cases"].append(case)
     if lib.mm_status() or lib.mmq_status():
         raise SystemExit("bench: a tensor-core product reported a wait that ran out")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# one kernel alone (the per-kernel counterpart of the step; the reference keeps such sweeps under tools/bench/)
+# ---------------------------------------------------------------------------------------------------------------------
+def run_kernel(args):
+    """python bench.py --kernel q8_run Q4_0 49152 2048              one token, graph-timed
+       python bench.py --kernel mv_run Q8_0 6144 2048 --tokens 2
+       python bench.py --kernel q8_run Q4_0 49152 2048 --plain 4    four plain launches, nothing timed (for a profiler)
+       python bench.py --kernel mm_run Q4_K 4096 4096 --tokens 512  the f16 prefill product (x16 made once)
+       python bench.py --kernel mm_fp4 NVFP4 17408 5120 --tokens 2048   W4A4: quantization + product a launch
+       python bench.py --kernel mmq_group Q4_K 4096 4096 --tokens 512   the int8 prefill product (x8 made once)
+    64 launches on successive cold copies of the matrix (more than 1 GiB cycled) in one CUDA graph, replayed 5 times."""
+    import torch
+
+    import libosmos_b200
+    from libosmos_b200 import synth
+    op, tname, rows, cols = args.kernel[0], args.kernel[1], int(args.kernel[2]), int(args.kernel[3])
+    lib = libosmos_b200.load()
+    dev = torch.device("cuda", 0)
+    tid = synth.TYPE_ID[tname]
+    tokens = args.tokens
+    w = synth.random_tensor(tid, rows, cols, synth.rng_for(1, tid, rows))
+    nb = int(w.size)
+    copies = 4 if args.plain else max(2, int(1.1 * 2 ** 30 // nb) + 1)
+    pool = torch.from_numpy(w).to(dev).repeat(copies)
+    x = torch.randn(tokens, cols, device=dev, generator=torch.Generator(device=dev).manual_seed(1017))
+    q = torch.zeros(tokens, cols, dtype=torch.int8, device=dev)
+    d = torch.zeros(tokens, cols // 32, device=dev)
+    y = torch.empty(tokens, rows, device=dev)
+    if args.generic:
+        lib.mv_set_staged(0), lib.q8_set_staged(0)
+    assert lib.q8_round(x.data_ptr(), tokens, cols, cols, q.data_ptr(), d.data_ptr(), None)
+    flops = None
+    if op == "mm_fp4":  # the W4A4 step: the activations' quantization and the product (TYPE must be NVFP4)
+        flops = 2.0 * rows * cols * tokens
+        xq = torch.zeros(tokens, cols // 2, dtype=torch.uint8, device=dev)
+        xsc = torch.zeros(tokens, cols // 16, dtype=torch.uint8, device=dev)
+        fn = lambda i, st: (lib.mm_fp4_act(x.data_ptr(), cols, tokens, cols, 0.5, xq.data_ptr(), xsc.data_ptr(), st)
+                            and lib.mm_fp4(pool.data_ptr() + (i % copies) * nb, rows, cols, xq.data_ptr(),
+                                           xsc.data_ptr(), tokens, 1.0, y.data_ptr(), rows, st))
+    elif op in ("mm_run", "mmq_group"):
+        n16 = (tokens + 15) // 16 * 16
+        flops = 2.0 * rows * cols * tokens
+        if op == "mm_run":
+            x16 = torch.zeros(n16 * cols, dtype=torch.float16, device=dev)
+            flag = torch.zeros(1, dtype=torch.int32, device=dev)
+            assert lib.mm_x16(x.data_ptr(), cols, tokens, cols, x16.data_ptr(), flag.data_ptr(), None)
+            fn = lambda i, st: lib.mm_run(tid, pool.data_ptr() + (i % copies) * nb, rows, cols, x16.data_ptr(),
+                                          tokens, y.data_ptr(), rows, st)
+        else:
+            idx = torch.arange(tokens, dtype=torch.int32, device=dev)
+            x8 = torch.zeros(n16 * cols, dtype=torch.int8, device=dev)
+            dx = torch.zeros(n16 * cols // 32, device=dev)
+            sx = torch.zeros_like(dx)
+            assert lib.mmq_x8_rows(x.data_ptr(), cols, idx.data_ptr(), tokens, cols, x8.data_ptr(), dx.data_ptr(), sx.data_ptr(), None)
+            tabs = [torch.tensor([pool.data_ptr() + c * nb], dtype=torch.int64, device=dev) for c in range(copies)]
+            cnt = torch.tensor([tokens], dtype=torch.int32, device=dev)
+            zero = torch.zeros(1, dtype=torch.int32, device=dev)
+            fn = lambda i, st: lib.mmq_group(tid, tabs[i % copies].data_ptr(), cnt.data_ptr(), 1, tokens, rows, cols,
+                                             x8.data_ptr(), dx.data_ptr(), sx.data_ptr(), zero.data_ptr(), y.data_ptr(),
+                                             zero.data_ptr(), rows, st)
+    elif op == "q8_run":
+        fn = lambda i, st: lib.q8_run(tid, pool.data_ptr() + (i % copies) * nb, rows, cols, q.data_ptr(), d.data_ptr(),
+                                      tokens, y.data_ptr(), rows, st)
+    elif op == "mv_run":
+        fn = lambda i, st: lib.mv_run(tid, pool.data_ptr() + (i % copies) * nb, rows, cols, x.data_ptr(), tokens, y.data_ptr(), st)
+    else:
+        raise SystemExit("unknown kernel %r" % op)
+    if args.plain:
+        for i in range(args.plain):
+            if not fn(i, None):
+                raise SystemExit("the library refused the call")
+        torch.cuda.synchronize()
+        print("%d launches, status %d" % (args.plain, lib.q8_status() | lib.mv_status() | lib.mm_status() | lib.mmq_status()))
+        return
+    us = graph_time(fn)
+    print(json.dumps({"op": op, "type": tname, "rows": rows, "cols": cols, "tokens": tokens,
+                      "kernels": "generic" if args.generic else "default", "us_per_launch": us, "weight_bytes": nb,
+                      "weight_gbs": nb / us / 1e3, "tflops": None if flops is None else flops / us / 1e6,
+                      "status": lib.q8_status() | lib.mv_status() | lib.mm_status() | lib.mmq_status()}))
 
 
 def main():
@@ -492,7 +725,14 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="moe_iq3xxs_512e_top10")
+    ap.add_argument("--kernel", nargs=4, metavar=("OP", "TYPE", "ROWS", "COLS"), help="time one kernel alone")
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--plain", type=int, default=0, help="--kernel: this many plain launches on 4 copies instead of timing")
+    ap.add_argument("--generic", action="store_true", help="--kernel: the generic kernels")
     args = ap.parse_args()
+    if args.kernel:
+        return run_kernel(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -76,6 +76,59 @@ bool ep_scatter_rows_peer(const float *ye, const int32_t *row_of, uint32_t n_pic
                           uint32_t dim, float *const *recv, uint32_t *const *flag, uint32_t n_ranks, uint32_t step,
                           uint32_t *counter, void *stream);
 
+/* ---- the whole step in five dependent launches and one C call ---------------------------------------------------
+ * The peer transport with each exchange folded into the kernel that produces or consumes its data:
+ *   1. ep_route_round_push   q4x_route + q8_round of the home tokens, every result stored straight into EVERY rank's
+ *                            exchange buffer (token-major over all tokens of the step: nothing is unpacked later),
+ *                            then this rank's dispatch flag released in every buffer;
+ *   2. ep_lane_tables        a bounded wait on all dispatch flags at its head, then lane_tables for this rank's
+ *                            experts and, for each row, the address of its place in its token's home rank;
+ *   3. ep_gate_up            q8_gate_up on the gathered tokens;          4. q8_round of the activations;
+ *   5. ep_down_push          q8_group_tok (down) whose epilogue stores each finished row into its home rank's
+ *                            receive block, the last block releasing this rank's combine flag in every buffer;
+ *   6. ep_combine_wait       a bounded wait on all combine flags, then each home token's k rows added in ascending
+ *                            expert id (+ add).
+ * The step number lives on the device (launch 1 advances it), and the buffers' halves are chosen from its parity
+ * inside the kernels, so a step's launches never change and can be captured in a CUDA graph. A wait that runs out
+ * (2 s) sets bit 0 of ep_wait_status() and lets the stream go on. With one rank the same launches run with the flags
+ * always already there: the single-GPU layer is this step with n_ranks = 1. */
+typedef struct EpLayout /* byte offsets inside a rank's exchange buffer; the same on every rank */
+{
+  uint64_t flags_dispatch, flags_combine; /* n_ranks words each: word s written by rank s */
+  uint64_t ids[2], weights[2], q[2], d[2]; /* all tokens' picks, routed weights, int8 rows, scales; by step parity */
+  uint64_t recv[2];                        /* this rank's home tokens' rows [tokens * k][dim] F32; by step parity */
+  uint64_t bytes;
+} EpLayout;
+/* n_tok tokens in all (a multiple of n_ranks), k picks a token, rows of dim values. false for a shape it refuses. */
+bool ep_layout(uint32_t n_ranks, uint32_t n_tok, uint32_t k, uint32_t dim, EpLayout *l);
+
+typedef struct EpPlan /* host memory; made once, read by every step */
+{
+  uint32_t rank, n_ranks;
+  uint32_t n_tok;            /* tokens of a step over all ranks; rank r is home to [r, r + 1) * n_tok / n_ranks */
+  uint32_t expert0, expert1; /* this rank's experts */
+  EpLayout lay;
+  void *peer[EP_MAX_RANKS]; /* every rank's exchange buffer (lay.bytes, zeroed, 256-byte aligned) as mapped here */
+  uint32_t *sync;           /* device, this rank's: 4 zeroed words ([0] the step counter, [1] [2] publish counters) */
+  float **rows;             /* device scratch [n_tok * k]: where each of this rank's rows goes */
+  LaneLayer layer;          /* the layer (its experts' addresses as this rank holds them) */
+  LaneScratch scratch;      /* lane_scratch_bind's, for n_tok tokens */
+} EpPlan;
+
+/* x, logits, add (or NULL), out: this rank's home tokens ([n_tok / n_ranks][dim], [..][n_exp], [..][dim]).
+   false = refused, nothing queued (a plan, type or shape the fused kernels do not take: use the unfused entries). */
+bool ep_layer_step(const EpPlan *p, const float *x, const float *logits, const float *add, float *out, void *stream);
+/* true when ep_layer_step takes the plan (checked by ep_layer_step itself before its first launch) */
+bool ep_plan_ok(const EpPlan *p);
+/* the step's stages, queued one after another by ep_layer_step (libosmos_b200/host/ep_step.c) */
+bool ep_route_round_push(const EpPlan *p, const float *x, const float *logits, void *stream);
+bool ep_lane_tables(const EpPlan *p, void *stream);
+bool ep_gate_up(const EpPlan *p, void *stream);
+bool ep_down_push(const EpPlan *p, void *stream);
+bool ep_combine_wait(const EpPlan *p, const float *add, float *out, void *stream);
+/* this rank's picks of the last step copied to host arrays [n_tok / n_ranks][k] (for checks; synchronizes the device) */
+bool ep_last_picks(const EpPlan *p, int32_t *ids, float *weights);
+
 /* lane_ffn's middle for one rank: tokens already rounded (q, d, token-major), the rows of experts [e0, e1) into
    s->ye (row r = the r-th of those picks sorted by (expert, pick)); s->tab.row_of says which row a pick got */
 bool lane_ffn_rows(const LaneLayer *l, const LaneScratch *s, const int8_t *q, const float *d, const int32_t *ids,

@@ -79,6 +79,12 @@ bool q4x_expert_tiles_static(const int32_t *ids, uint32_t n, uint32_t k, uint32_
                              const Q4xExpertTiles *t, void *stream);
 /* y = silu(g) * u (libm expf), also to side when not NULL (reference: q4x_ops.h:157, q4x_moe.hip:167-170,253-259) */
 bool q4x_swiglu(const float *g, const float *u, uint64_t n, float *y, const Q4xX16 *side, void *stream);
+/* the activation straight into down's tiled f16 input: slot s (of `slots`, whole tiles of 16 included) gets
+   silu(g[idx[s]][c]) * u[idx[s]][c] for c < ff as f16 at (s / 16) * 16 * ff + (c / 16) * 256 + (s % 16) * 16 + c % 16, a
+   pad slot (idx[s] < 0) zeros; a value past f16's range sets *overflow. false for ff not a multiple of 16
+   (reference: q4x_ops.h:159-160, kernels/q4x_moe.hip:236-259). */
+bool q4x_swiglu_rows(const float *g, const float *u, uint32_t ff, const int32_t *idx, uint32_t slots, void *x16,
+                     int32_t *overflow, void *stream);
 /* out[t][d] = sum_j y[where[t k + j]][d] * w[t k + j] in pick order from 0, + shared[t][d] * sigmoid(shared_logit[t])
    (reference: q4x_ops.h:161-162, kernels/q4x_moe.hip:172-200,274-285) */
 bool q4x_moe_sum(const float *y, const int32_t *where, const float *w, uint32_t n_tok, uint32_t k, uint32_t dim,

@@ -46,6 +46,9 @@ bool q8_gate_up(uint32_t type, const void *const *wg, const void *const *wu, con
 
 /* ---- extensions: no counterpart in the reference -------------------------------------------------------------- */
 
+/* true for the types q8_group_tok and q8_gate_up take (the reference's int8 lane types) */
+bool q8_known(uint32_t type);
+
 /* One dense matrix over n_tok >= 1 int8 rows: y[t * ys + r] from q row t / d row t - q8_group_tok's sums without
    the tables. Takes the lane types and, beyond the reference, the plain 32-value blocks Q4_0 and Q8_0, for which
    the block value is d_w * (float)isum with isum the whole block's exact integer dot (the lane's rules applied to

@@ -48,6 +48,16 @@ class EpSegment(C.Structure):
     _fields_ = [("ids", U64), ("weights", U64), ("q", U64), ("d", U64), ("bytes", U64)]
 
 
+class EpLayout(C.Structure):
+    _fields_ = [("flags_dispatch", U64), ("flags_combine", U64), ("ids", U64 * 2), ("weights", U64 * 2), ("q", U64 * 2),
+                ("d", U64 * 2), ("recv", U64 * 2), ("bytes", U64)]
+
+
+class EpPlan(C.Structure):
+    _fields_ = [("rank", U32), ("n_ranks", U32), ("n_tok", U32), ("expert0", U32), ("expert1", U32), ("lay", EpLayout),
+                ("peer", P * 16), ("sync", P), ("rows", P), ("layer", LaneLayer), ("scratch", LaneScratch)]
+
+
 class QTypeInfo(C.Structure):
     _fields_ = [("id", U32), ("values", U32), ("bytes", U32), ("paths", U32), ("name", C.c_char_p)]
 
@@ -90,6 +100,7 @@ SIGNATURES = {
     "q8_group_tok": (B, [U32, P, P, P, P, U32, U32, U32, U32, P, P, P, U32, P]),
     "q8_gate_up": (B, [U32, P, P, P, P, P, P, U32, U32, U32, U32, P, P, P, F32, P, U32, P]),
     "q8_run": (B, [U32, P, U32, U32, P, P, U32, P, U32, P]),
+    "q8_known": (B, [U32]),
     "mv_set_staged": (None, [C.c_int]),
     "mv_status": (U32, []),
     "q8_set_staged": (None, [C.c_int]),
@@ -106,6 +117,7 @@ SIGNATURES = {
     "q4x_expert_tiles": (B, [P, U32, U32, U32, U32, U32, C.POINTER(Q4xExpertTiles), P]),
     "q4x_expert_tiles_static": (B, [P, U32, U32, U32, U32, U32, C.POINTER(Q4xExpertTiles), P]),
     "q4x_swiglu": (B, [P, P, U64, P, C.POINTER(Q4xX16), P]),
+    "q4x_swiglu_rows": (B, [P, P, U32, P, U32, P, P, P]),
     "q4x_moe_sum": (B, [P, P, P, U32, U32, U32, P, P, P, P]),
     # ops.h
     "ops_router": (B, [P, P, U32, U32, F32, U32, P, P, P]),
@@ -141,6 +153,15 @@ SIGNATURES = {
     "ep_wait": (B, [P, U32, U32, P]),
     "ep_wait_status": (U32, []),
     "ep_scatter_rows_peer": (B, [P, P, U32, U32, U32, U32, P, P, U32, U32, P, P]),
+    "ep_layout": (B, [U32, U32, U32, U32, C.POINTER(EpLayout)]),
+    "ep_plan_ok": (B, [C.POINTER(EpPlan)]),
+    "ep_layer_step": (B, [C.POINTER(EpPlan), P, P, P, P, P]),
+    "ep_route_round_push": (B, [C.POINTER(EpPlan), P, P, P]),
+    "ep_lane_tables": (B, [C.POINTER(EpPlan), P]),
+    "ep_gate_up": (B, [C.POINTER(EpPlan), P]),
+    "ep_down_push": (B, [C.POINTER(EpPlan), P]),
+    "ep_combine_wait": (B, [C.POINTER(EpPlan), P, P, P]),
+    "ep_last_picks": (B, [C.POINTER(EpPlan), P, P]),
     "lane_ffn_rows": (B, [C.POINTER(LaneLayer), C.POINTER(LaneScratch), P, P, P, P, U32, U32, U32, P]),
 }
 

@@ -40,6 +40,16 @@ __host__ inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, di
   cfg.attrs = attr, cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
+// A kernel's dynamic shared-memory limit is an attribute of the kernel on ONE device: set it once per device. `done`
+// is the caller's per-kernel record (a static array, one flag a device). false when the attribute was refused.
+template <class K>
+__host__ inline bool allow_dynamic_smem(K kernel, int bytes, bool (&done)[64]) {
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return false;
+  if (done[d]) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  return done[d] = true;
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -4,7 +4,13 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "ep_sync.cuh"
+#include "moe_api.h"
 #include "osmos_b200/ep.h"
+#include "osmos_b200/q8.h"
+#include "q8_api.h"
+#include "q8_round.cuh"
+#include "route.cuh"
 
 namespace osmos {
 namespace {
@@ -170,10 +176,216 @@ __global__ void peer_wait_kernel(const uint32_t* flags, uint32_t n_ranks, uint32
   }
 }
 
+// ---- the fused step --------------------------------------------------------------------------------------------------
+__host__ __device__ inline uint64_t up256(uint64_t v) { return (v + 255u) & ~(uint64_t) 255u; }
+
+struct StepArgs {
+  EpPeers peers;
+  EpLayout lay;
+  uint32_t rank, n_ranks, tokens, k, dim, n_exp;
+  uint32_t* sync;  // [0] step, [1] [2] publish counters
+};
+
+// A block a home token. Its first warp routes it (route.cuh) while all eight round its row to int8 (q8_round.cuh);
+// every result goes straight to its token-major place in every rank's buffer. The last block to finish releases this
+// rank's dispatch flag everywhere and advances the step counter.
+template <int R>
+__global__ void __launch_bounds__(256) route_round_push_kernel(const StepArgs a, const float* __restrict__ x,
+                                                               const float* __restrict__ logits) {
+  pdl_wait();  // (a dependent launch: the step before may still be reading what this one writes)
+  pdl_launch_next();
+  const uint32_t step = a.sync[0] + 1u, half = step & 1u;
+  const uint32_t tl = blockIdx.x, t = a.rank * a.tokens + tl, lane = threadIdx.x % kWarp;
+  if (threadIdx.x < kWarp) {
+    const route::Pick p = route::softmax_topk<R>(logits + (uint64_t) tl * a.n_exp, a.n_exp, a.k, lane);
+    if (lane < a.k)
+      for (uint32_t r = 0; r < a.n_ranks; r++) {
+        ((int32_t*) (a.peers.base[r] + a.lay.ids[half]))[t * a.k + lane] = (int32_t) p.id;
+        ((float*) (a.peers.base[r] + a.lay.weights[half]))[t * a.k + lane] = p.w;
+      }
+  }
+  const uint32_t per = a.dim / 8;
+  for (uint32_t c0 = 0; c0 < per; c0 += blockDim.x) {  // (whole warps: per is a multiple of 4, the bound is the block's)
+    const uint32_t c = c0 + threadIdx.x;
+    const bool live = c < per;
+    float v[8], scale;
+    load8(x + (uint64_t) tl * a.dim + (uint64_t) (live ? c : 0) * 8, v);
+    const uint2 codes = round_block8<false>(v, &scale);
+    if (!live) continue;
+    for (uint32_t r = 0; r < a.n_ranks; r++) {
+      *(uint2*) (a.peers.base[r] + a.lay.q[half] + (uint64_t) t * a.dim + (uint64_t) c * 8) = codes;
+      if (c % 4 == 0) ((float*) (a.peers.base[r] + a.lay.d[half]))[(uint64_t) t * (a.dim / 32) + c / 4] = scale;
+    }
+  }
+  publish_step(a.peers, a.lay.flags_dispatch, a.rank, a.n_ranks, step, a.sync + 1, a.sync);
+}
+
+// A block a home token: a bounded wait on every rank's combine flag, the token's picks ordered by expert id (k is
+// small: one thread sorts by insertion), then every thread its columns, the rows added in that order from 0.
+__global__ void __launch_bounds__(kThreads) combine_wait_kernel(const StepArgs a, const float* __restrict__ add,
+                                                                float* __restrict__ out) {
+  __shared__ uint32_t order[32];
+  pdl_wait();  // (a dependent launch)
+  pdl_launch_next();
+  const uint32_t step = a.sync[0], half = step & 1u;
+  uint8_t* mine = a.peers.base[a.rank];
+  if (threadIdx.x < a.n_ranks && !flag_wait((const uint32_t*) (mine + a.lay.flags_combine) + threadIdx.x, step))
+    atomicOr(&g_peer_wait_status, 1u);
+  const uint32_t tl = blockIdx.x, k = a.k;
+  if (threadIdx.x == 0) {
+    const int32_t* ids = (const int32_t*) (mine + a.lay.ids[half]) + (uint64_t) (a.rank * a.tokens + tl) * k;
+    int32_t e[32];
+    for (uint32_t j = 0; j < k; j++) e[j] = ids[j], order[j] = j;
+    for (uint32_t i = 1; i < k; i++)
+      for (uint32_t c = i; c > 0 && e[c] < e[c - 1]; c--) {
+        const int32_t se = e[c];
+        const uint32_t sj = order[c];
+        e[c] = e[c - 1], e[c - 1] = se, order[c] = order[c - 1], order[c - 1] = sj;
+      }
+  }
+  __syncthreads();
+  const float4* recv = (const float4*) (mine + a.lay.recv[half]) + (uint64_t) tl * k * (a.dim / 4);
+  for (uint32_t c = threadIdx.x; c < a.dim / 4; c += kThreads) {
+    float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (uint32_t j = 0; j < k; j++) {
+      const float4 v = recv[(uint64_t) order[j] * (a.dim / 4) + c];
+      s.x = __fadd_rn(s.x, v.x), s.y = __fadd_rn(s.y, v.y), s.z = __fadd_rn(s.z, v.z), s.w = __fadd_rn(s.w, v.w);
+    }
+    if (add) {
+      const float4 v = ((const float4*) add)[(uint64_t) tl * (a.dim / 4) + c];
+      s.x = __fadd_rn(s.x, v.x), s.y = __fadd_rn(s.y, v.y), s.z = __fadd_rn(s.z, v.z), s.w = __fadd_rn(s.w, v.w);
+    }
+    ((float4*) out)[(uint64_t) tl * (a.dim / 4) + c] = s;
+  }
+}
+
+StepArgs step_args(const EpPlan* p) {
+  StepArgs a{};
+  for (uint32_t r = 0; r < p->n_ranks; r++) a.peers.base[r] = (uint8_t*) p->peer[r];
+  a.lay = p->lay, a.rank = p->rank, a.n_ranks = p->n_ranks, a.tokens = p->n_tok / p->n_ranks, a.k = p->layer.k;
+  a.dim = p->layer.dim, a.n_exp = p->layer.n_exp, a.sync = p->sync;
+  return a;
+}
+
+// the lane kernels' extras for the step: inputs by parity out of this rank's own buffer
+LaneEp lane_ep(const EpPlan* p, bool gathered_inputs, bool push) {
+  LaneEp e{};
+  e.step = p->sync;
+  if (gathered_inputs)
+    e.half_q = p->lay.q[1] - p->lay.q[0], e.half_d = p->lay.d[1] - p->lay.d[0], e.half_scale = p->lay.weights[1] - p->lay.weights[0];
+  if (push) {
+    e.out_rows = p->rows, e.publish = true, e.flags_off = p->lay.flags_combine, e.rank = p->rank, e.n_ranks = p->n_ranks;
+    e.counter = p->sync + 2;
+    for (uint32_t r = 0; r < p->n_ranks; r++) e.peers.base[r] = (uint8_t*) p->peer[r];
+  }
+  return e;
+}
+
 }  // namespace
 }  // namespace osmos
 
 using namespace osmos;
+
+extern "C" bool ep_layout(uint32_t n_ranks, uint32_t n_tok, uint32_t k, uint32_t dim, EpLayout* l) {
+  if (!l || !n_ranks || n_ranks > EP_MAX_RANKS || !n_tok || n_tok % n_ranks || !k || k > 32 || !dim || dim % 32) return false;
+  const uint64_t picks = (uint64_t) n_tok * k, tokens = n_tok / n_ranks;
+  uint64_t at = 0;
+  l->flags_dispatch = at, at += 256;
+  l->flags_combine = at, at += 256;
+  for (int h = 0; h < 2; h++) {
+    l->ids[h] = at, at += up256(picks * 4);
+    l->weights[h] = at, at += up256(picks * 4);
+    l->q[h] = at, at += up256((uint64_t) n_tok * dim);
+    l->d[h] = at, at += up256((uint64_t) n_tok * (dim / 32) * 4);
+  }
+  for (int h = 0; h < 2; h++) l->recv[h] = at, at += up256(tokens * k * dim * 4);
+  l->bytes = at;
+  return true;
+}
+
+extern "C" bool ep_plan_ok(const EpPlan* p) {
+  if (!p || !p->n_ranks || p->n_ranks > EP_MAX_RANKS || p->rank >= p->n_ranks || !p->n_tok || p->n_tok % p->n_ranks ||
+      !p->sync || !p->rows || p->expert0 >= p->expert1 || p->expert1 > p->layer.n_exp)
+    return false;
+  const LaneLayer& l = p->layer;
+  EpLayout want;
+  if (!l.dim || l.dim % 256 || !l.ff || l.ff % 256 || !l.k || l.k > 32 || !l.n_exp || l.n_exp > 1024 || l.k > l.n_exp ||
+      (uint64_t) p->n_tok * l.k > 1024 || !ep_layout(p->n_ranks, p->n_tok, l.k, l.dim, &want) ||
+      memcmp(&want, &p->lay, sizeof want) != 0 || p->scratch.max_tok < p->n_tok)
+    return false;
+  for (uint32_t r = 0; r < p->n_ranks; r++)
+    if (!p->peer[r] || ((uintptr_t) p->peer[r] & 255u)) return false;
+  const uint32_t ents = p->scratch.tab.max_entries;
+  return q8_gate_up_ep(l.type_gu, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, ents, LANE_MAX_TOKENS, l.ff, l.dim,
+                       nullptr, nullptr, nullptr, l.lim, nullptr, l.ff, LaneEp{}, true, nullptr) &&
+         q8_group_tok_ep(l.type_down, nullptr, nullptr, nullptr, nullptr, ents, LANE_MAX_TOKENS, l.dim, l.ff, nullptr, nullptr,
+                         nullptr, l.dim, LaneEp{}, true, nullptr);
+}
+
+extern "C" bool ep_route_round_push(const EpPlan* p, const float* x, const float* logits, void* stream) {
+  if (!p || !x || !logits) return false;
+  const StepArgs a = step_args(p);
+  const dim3 grid(a.tokens), block(256);
+  const cudaStream_t s = stream_of(stream);
+  switch (route::regs_for(a.n_exp)) {
+    case 4: return launch_dependent(route_round_push_kernel<4>, grid, block, 0, s, a, x, logits) == cudaSuccess;
+    case 8: return launch_dependent(route_round_push_kernel<8>, grid, block, 0, s, a, x, logits) == cudaSuccess;
+    case 16: return launch_dependent(route_round_push_kernel<16>, grid, block, 0, s, a, x, logits) == cudaSuccess;
+    default: return launch_dependent(route_round_push_kernel<32>, grid, block, 0, s, a, x, logits) == cudaSuccess;
+  }
+}
+
+extern "C" bool ep_lane_tables(const EpPlan* p, void* stream) {
+  if (!p) return false;
+  uint8_t* mine = (uint8_t*) p->peer[p->rank];
+  LaneTablesSync sy;
+  sy.flags = (const uint32_t*) (mine + p->lay.flags_dispatch), sy.step = p->sync, sy.n_ranks = p->n_ranks;
+  sy.half_bytes = p->lay.ids[1] - p->lay.ids[0];
+  void* status = nullptr;
+  if (cudaGetSymbolAddress(&status, g_peer_wait_status) != cudaSuccess) return false;
+  sy.status = (uint32_t*) status;
+  LaneRowHomes homes;
+  homes.rows = p->rows, homes.recv[0] = p->lay.recv[0], homes.recv[1] = p->lay.recv[1];
+  homes.tokens = p->n_tok / p->n_ranks, homes.dim = p->layer.dim;
+  for (uint32_t r = 0; r < p->n_ranks; r++) homes.base[r] = (uint8_t*) p->peer[r];
+  return lane_tables_launch((const int32_t*) (mine + p->lay.ids[0]), p->n_tok * p->layer.k, p->layer.k, p->layer.n_exp,
+                            p->expert0, p->expert1, &p->layer.experts, &p->scratch.tab, sy, homes, stream_of(stream));
+}
+
+extern "C" bool ep_gate_up(const EpPlan* p, void* stream) {
+  if (!p) return false;
+  const LaneLayer& l = p->layer;
+  const LaneTables& t = p->scratch.tab;
+  const uint8_t* mine = (const uint8_t*) p->peer[p->rank];
+  return q8_gate_up_ep(l.type_gu, t.w[0], t.w[1], t.cnt, t.xrow, t.tok, t.pair, t.max_entries, LANE_MAX_TOKENS, l.ff, l.dim,
+                       (const int8_t*) (mine + p->lay.q[0]), (const float*) (mine + p->lay.d[0]),
+                       (const float*) (mine + p->lay.weights[0]), l.lim, p->scratch.hh, l.ff, lane_ep(p, true, false), false,
+                       stream_of(stream));
+}
+
+extern "C" bool ep_down_push(const EpPlan* p, void* stream) {
+  if (!p) return false;
+  const LaneLayer& l = p->layer;
+  const LaneTables& t = p->scratch.tab;
+  return q8_group_tok_ep(l.type_down, t.w[2], t.cnt, t.xrow, nullptr, t.max_entries, LANE_MAX_TOKENS, l.dim, l.ff,
+                         p->scratch.hq, p->scratch.hqd, nullptr, l.dim, lane_ep(p, false, true), false, stream_of(stream));
+}
+
+extern "C" bool ep_combine_wait(const EpPlan* p, const float* add, float* out, void* stream) {
+  if (!p || !out || (((uintptr_t) out | (uintptr_t) add) & 15u)) return false;
+  const StepArgs a = step_args(p);
+  return launch_dependent(combine_wait_kernel, dim3(a.tokens), dim3(kThreads), 0, stream_of(stream), a, add, out) == cudaSuccess;
+}
+
+extern "C" bool ep_last_picks(const EpPlan* p, int32_t* ids, float* weights) {
+  if (!p || !ids || !weights || cudaDeviceSynchronize() != cudaSuccess) return false;
+  uint32_t step = 0;
+  if (cudaMemcpy(&step, p->sync, sizeof step, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+  const uint8_t* mine = (const uint8_t*) p->peer[p->rank];
+  const uint64_t n = (uint64_t) (p->n_tok / p->n_ranks) * p->layer.k, first = (uint64_t) p->rank * n;
+  return cudaMemcpy(ids, (const int32_t*) (mine + p->lay.ids[step & 1u]) + first, n * 4, cudaMemcpyDeviceToHost) == cudaSuccess &&
+         cudaMemcpy(weights, (const float*) (mine + p->lay.weights[step & 1u]) + first, n * 4, cudaMemcpyDeviceToHost) == cudaSuccess;
+}
 
 extern "C" bool ep_peer_alloc(uint64_t bytes, void** ptr, uint8_t handle[EP_HANDLE_BYTES]) {
   static_assert(sizeof(cudaIpcMemHandle_t) == EP_HANDLE_BYTES, "a CUDA IPC handle is 64 bytes");

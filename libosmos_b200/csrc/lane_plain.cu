@@ -236,12 +236,9 @@ int launch(const Request& r, cudaStream_t s) {
     if (per_warp < slots) slots = per_warp, a.slots = per_warp;
   }
   const uint32_t total = W * slots * a.slot_bytes + 16u;  // + the word read past a last block
-  static bool sized = false;  // (one flag a template instance)
+  static bool sized[64] = {};  // (one record a template instance, one flag a device)
   auto kernel = plain_dense_kernel<T, L, NB, NT, W>;
-  if (!sized) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit + 16) != cudaSuccess) return 0;
-    sized = true;
-  }
+  if (!allow_dynamic_smem(kernel, (int) kSmemLimit + 16, sized)) return 0;
   uint32_t grid = (uint32_t) dev->sms;
   if (a.units < grid) grid = a.units;
   return launch_dependent(kernel, dim3(grid), dim3(W * kWarp), total, s, a) == cudaSuccess ? 1 : -1;

@@ -49,6 +49,7 @@ struct Args {
   uint32_t slots, slot_rows, task_slots, slot_bytes;  // a slot: slot_rows rows (of each matrix); a task: task_slots slots
   uint32_t list_off, ptr_off, ring_off;               // byte offsets into dynamic shared memory
   uint32_t* status;
+  LaneEp ep;
 };
 
 // a superblock's bytes through shared-memory loads at run-time offsets (2-byte aligned at best)
@@ -153,6 +154,14 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
   // codebooks above are not)
   pdl_wait();
   pdl_launch_next();
+  // (the expert-parallel step: the activations and weights of an odd step lie in the buffers' second halves)
+  const uint32_t parity = a.ep.step ? (*a.ep.step & 1u) : 0u;
+  const int8_t* const in_q = a.q + parity * a.ep.half_q;
+  const float* const in_d = (const float*) ((const uint8_t*) a.d + parity * a.ep.half_d);
+  const float* const in_scale = (const float*) ((const uint8_t*) a.scale + parity * a.ep.half_scale);
+  auto out_row_ptr = [&](uint32_t r) -> float* {
+    return a.ep.out_rows ? a.ep.out_rows[r] : a.out + (uint64_t) r * a.out_stride;
+  };
 
   // the live (entry, token group) list in entry order, and every entry's matrix pointers
   auto live_count = [&](uint32_t m) -> uint32_t {
@@ -297,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
 #pragma unroll
         for (int t = 0; t < NTL; t++) {
           const float v = tree(acc[t]);
-          if (sub == 0) a.out[(uint64_t) (out_row + t) * a.out_stride + row0 + p + grp] = v;
+          if (sub == 0) out_row_ptr(out_row + t)[row0 + p + grp] = v;
         }
       }
     }
@@ -320,15 +329,15 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
       const uint32_t r = r0 + ((uint32_t) t < live ? (uint32_t) t : live - 1);
       const uint64_t xr = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
       scale[t] = 0.0f;
-      if constexpr (FUSED) scale[t] = a.scale[a.win ? a.win[r] : r];
+      if constexpr (FUSED) scale[t] = in_scale[a.win ? a.win[r] : r];
 #pragma unroll
       for (int k = 0; k < NB; k++) {
         int4 lo = make_int4(0, 0, 0, 0), hi = lo;
         float dv = 0.0f;
         if (EXACT || (uint32_t) k < nbl) {
           const uint32_t s = sub + (uint32_t) L * k;
-          const int4* xp = (const int4*) (a.q + xr * a.cols + s * 32u);
-          lo = __ldg(xp), hi = __ldg(xp + 1), dv = __ldg(a.d + xr * nblk + s);
+          const int4* xp = (const int4*) (in_q + xr * a.cols + s * 32u);
+          lo = __ldg(xp), hi = __ldg(xp + 1), dv = __ldg(in_d + xr * nblk + s);
         }
         xq[t][k][0] = lo.x, xq[t][k][1] = lo.y, xq[t][k][2] = lo.z, xq[t][k][3] = lo.w;
         xq[t][k][4] = hi.x, xq[t][k][5] = hi.y, xq[t][k][6] = hi.z, xq[t][k][7] = hi.w;
@@ -363,14 +372,16 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
 #pragma unroll
         for (int t = 0; t < NT; t++)
           if ((uint32_t) t < live)
-            a.out[(uint64_t) (r0 + t) * a.out_stride + task_row0 + lane] = lane_swiglu(hg[t], hu[t], a.lim, scale[t]);
+            out_row_ptr(r0 + t)[task_row0 + lane] = lane_swiglu(hg[t], hu[t], a.lim, scale[t]);
       }
     }
   }
+  if (a.ep.publish)  // (every thread of every block comes here: a block that stood down above has left already)
+    publish_step(a.ep.peers, a.ep.flags_off, a.ep.rank, a.ep.n_ranks, *a.ep.step, a.ep.counter, nullptr);
 }
 
 struct Device {
-  int sms = 0;
+  int sms = 0, index = 0;
   uint32_t* status = nullptr;
 };
 
@@ -383,7 +394,7 @@ const Device* device_info() {
     int sms = 0;
     if (cudaGetSymbolAddress(&at, g_status) != cudaSuccess || !at) return nullptr;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || sms <= 0) return nullptr;
-    devs[d].sms = sms, devs[d].status = (uint32_t*) at;
+    devs[d].sms = sms, devs[d].index = d, devs[d].status = (uint32_t*) at;
   }
   return &devs[d];
 }
@@ -418,13 +429,12 @@ int launch(const Request& r, cudaStream_t s) {
   a.out_stride = r.out_stride, a.n_entries = r.n_entries, a.max_cnt = r.max_cnt;
   a.slots = slots, a.slot_rows = rc, a.task_slots = ts, a.slot_bytes = slot_bytes;
   a.status = dev->status;
+  a.ep = r.ep;
   const uint32_t total = a.ring_off + kWarps * slots * slot_bytes + 16u;
-  static bool sized = false;  // (one flag a template instance)
+  if (r.dry) return 1;
+  static bool sized[64] = {};  // (per template instance and device: the attribute belongs to a device's context)
   auto kernel = lane_ring_kernel<T, FUSED, L, NB, NT, EXACT>;
-  if (!sized) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit) != cudaSuccess) return 0;
-    sized = true;
-  }
+  if (!allow_dynamic_smem(kernel, (int) kSmemLimit, sized)) return 0;
   return launch_dependent(kernel, dim3((uint32_t) dev->sms), dim3(kThreads), total, s, a) == cudaSuccess ? 1 : -1;
 }
 

@@ -2,6 +2,8 @@
 #pragma once
 #include <cstdint>
 
+#include "lane_ep.h"
+
 namespace osmos {
 namespace ring {
 
@@ -16,6 +18,8 @@ struct Request {
   float lim;
   float* out;
   uint32_t rows, cols, out_stride, n_entries, max_cnt;
+  LaneEp ep;  // the expert-parallel step's extras (lane_ep.h); zero: none
+  bool dry = false;  // only answer whether the kernel takes the type and shape (1 / 0): nothing is queued
 };
 
 // 1: queued on the stream; 0: not a type / shape this kernel takes (nothing queued); -1: the launch was refused

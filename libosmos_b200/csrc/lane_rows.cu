@@ -45,6 +45,7 @@ struct Args {
   uint32_t rows, out_stride, n_entries, max_cnt;
   uint32_t list_off, ptr_off, x_off, ring_off, slot_bytes;
   uint32_t* status;
+  LaneEp ep;
 };
 
 template <uint32_t T>
@@ -71,6 +72,13 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
   // codebooks above are not)
   pdl_wait();
   pdl_launch_next();
+  // (the expert-parallel step: inputs of an odd step in the buffers' second halves, rows stored where a table says)
+  const uint32_t parity = a.ep.step ? (*a.ep.step & 1u) : 0u;
+  const int8_t* const in_q = a.q + parity * a.ep.half_q;
+  const float* const in_d = (const float*) ((const uint8_t*) a.d + parity * a.ep.half_d);
+  auto out_row_ptr = [&](uint32_t r) -> float* {
+    return a.ep.out_rows ? a.ep.out_rows[r] : a.out + (uint64_t) r * a.out_stride;
+  };
 
   auto live_count = [&](uint32_t m) -> uint32_t {
     const int32_t c = a.cnt[m];
@@ -163,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       for (int o = kBlocks / 2; o > 0; o >>= 1)
 #pragma unroll
         for (int l = 0; l < o; l++) prod[t][l] = __fadd_rn(prod[t][l], prod[t][l + o]);
-      a.out[(uint64_t) (out_row + t) * a.out_stride + row] = prod[t][0];
+      out_row_ptr(out_row + t)[row] = prod[t][0];
     }
   };
 
@@ -183,8 +191,8 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       if ((uint32_t) t < live) {
         const uint32_t r = r0 + t;
         const uint64_t xr = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
-        ((int4*) (xs + t * kCols))[lane] = __ldg((const int4*) (a.q + xr * kCols) + lane);
-        if (lane < (uint32_t) kBlocks) ((float*) (xs + kNT * kCols))[t * kBlocks + lane] = __ldg(a.d + xr * kBlocks + lane);
+        ((int4*) (xs + t * kCols))[lane] = __ldg((const int4*) (in_q + xr * kCols) + lane);
+        if (lane < (uint32_t) kBlocks) ((float*) (xs + kNT * kCols))[t * kBlocks + lane] = __ldg(in_d + xr * kBlocks + lane);
       }
     }
     __syncwarp();
@@ -202,10 +210,12 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       issue(n + kSlots);
     }
   }
+  if (a.ep.publish)  // (every thread of every block comes here: a block that stood down above has left already)
+    publish_step(a.ep.peers, a.ep.flags_off, a.ep.rank, a.ep.n_ranks, *a.ep.step, a.ep.counter, nullptr);
 }
 
 struct Device {
-  int sms = 0;
+  int sms = 0, index = 0;
   uint32_t* status = nullptr;
 };
 
@@ -218,7 +228,7 @@ const Device* device_info() {
     int sms = 0;
     if (cudaGetSymbolAddress(&at, g_status) != cudaSuccess || !at) return nullptr;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || sms <= 0) return nullptr;
-    devs[d].sms = sms, devs[d].status = (uint32_t*) at;
+    devs[d].sms = sms, devs[d].index = d, devs[d].status = (uint32_t*) at;
   }
   return &devs[d];
 }
@@ -238,12 +248,11 @@ int launch(const Request& r, cudaStream_t s) {
   a.w = (const uint8_t* const*) r.w, a.cnt = r.cnt, a.xrow = r.xrow, a.xin = r.xin, a.q = r.q, a.d = r.d, a.out = r.out;
   a.rows = r.rows, a.out_stride = r.out_stride, a.n_entries = r.n_entries, a.max_cnt = r.max_cnt;
   a.status = dev->status;
-  static bool sized = false;  // (one flag a template instance)
+  a.ep = r.ep;
+  if (r.dry) return 1;
+  static bool sized[64] = {};  // (per template instance and device: the attribute belongs to a device's context)
   auto kernel = lane_rows_kernel<T>;
-  if (!sized) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit) != cudaSuccess) return 0;
-    sized = true;
-  }
+  if (!allow_dynamic_smem(kernel, (int) kSmemLimit, sized)) return 0;
   return launch_dependent(kernel, dim3((uint32_t) dev->sms), dim3(kThreads), total, s, a) == cudaSuccess ? 1 : -1;
 }
 

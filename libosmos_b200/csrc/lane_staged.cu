@@ -53,12 +53,9 @@ int launch(const Request& r, cudaStream_t s) {
   uint32_t stages = 2;  // as deep a ring as shared memory holds
   while (stages < (uint32_t) kMaxStages && make_plan<T>(r.cols, tr, M, stages + 1).total <= kSmemLimit) stages++;
   const Plan p = make_plan<T>(r.cols, tr, M, stages);
-  static bool sized = false;  // (one flag a template instance)
+  static bool sized[64] = {};  // (one record a template instance, one flag a device)
   auto kernel = lane_staged_kernel<T, FUSED, DENSE>;
-  if (!sized) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit) != cudaSuccess) return 0;
-    sized = true;
-  }
+  if (!allow_dynamic_smem(kernel, (int) kSmemLimit, sized)) return 0;
   Args a{};
   a.w_dense = (const uint8_t*) r.w_dense, a.wg = (const uint8_t* const*) r.wg, a.wu = (const uint8_t* const*) r.wu;
   a.cnt = r.cnt, a.xrow = r.xrow, a.xin = r.xin, a.win = r.win, a.q = r.q, a.d = r.d, a.scale = r.scale, a.lim = r.lim;

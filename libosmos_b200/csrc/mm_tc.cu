@@ -466,11 +466,8 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   }
   a.stages = stages_for(a.accs), a.stage_bytes = kStageA + a.accs * kSubs * kSubTile, a.raw_off = a.stages * a.stage_bytes;
   const int smem_bytes = (int) smem_for(a.accs);
-  static bool sized = false;  // (one flag a template instance)
-  if (!sized) {
-    if (cudaFuncSetAttribute(mm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kLimit) != cudaSuccess) return false;
-    sized = true;
-  }
+  static bool sized[64] = {};  // (one record a template instance, one flag a device)
+  if (!allow_dynamic_smem(mm_tc_kernel<T>, (int) kLimit, sized)) return false;
   const dim3 grid(row_tiles, n_mat, (max_cnt + a.accs * kN - 1) / (a.accs * kN));
   mm_tc_kernel<T><<<grid, kThreads, smem_bytes, s>>>(a, tmap);
   return launched();

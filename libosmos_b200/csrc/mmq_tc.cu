@@ -385,12 +385,9 @@ int try_launch(const void* const* w, const int32_t* cnt, uint32_t n_mat, uint32_
   if (rows % kM || cols % kBlockValues || (((uintptr_t) x8 | (uintptr_t) dx | (uintptr_t) sx) & 15u)) return 0;
   uint32_t* status = status_word();
   if (!status) return 0;
-  static bool sized = false;
+  static bool sized[64] = {};  // (one flag a device)
   const int smem_bytes = kStages * kStageBytes;
-  if (!sized) {
-    if (cudaFuncSetAttribute(q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return 0;
-    sized = true;
-  }
+  if (!allow_dynamic_smem(q4k_tc_kernel, smem_bytes, sized)) return 0;
   Args a{(const uint8_t* const*) w, cnt, x8, dx, sx, soff, yoff, y, cols, ys, status};
   const dim3 grid(rows / kM, n_mat, (max_cnt + kN - 1) / kN);
   q4k_tc_kernel<<<grid, kThreads, smem_bytes, (cudaStream_t) stream>>>(a);

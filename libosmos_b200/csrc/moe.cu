@@ -1,152 +1,147 @@
 // Routing, expert tables, activation and combine of an MoE layer (include/osmos_b200/moe.h), and the device-built
 // tables of the int8 lane (include/osmos_b200/lane.h). Everything here is built on the GPU: no host round trip
 // between the router and the experts.
+//
+// The router is a warp a token (route.cuh). The tables are one block of 1024 threads: a thread an expert for the
+// counts and the prefix sums (every sum of the block in ONE pass of shuffles, whatever their number), and the picks'
+// places by the first warp walking the picks 32 at a time in pick order - lanes with the same expert find each other
+// with match.any, the group's first lane reserves the group's places in the expert's running fill - which is the
+// stable sort by expert without a thread ever scanning the picks before its own.
+#include "moe_api.h"
+
 #include "decode.cuh"
-#include "osmos_b200/lane.h"
 #include "osmos_b200/moe.h"
-#include "topk.cuh"
+#include "route.cuh"
 
 namespace osmos {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr uint32_t kMaxExperts = 1024, kMaxK = 32;
-constexpr float kSumFloor = 6.103515625e-5f;  // 2^-14: the floor under the picked probabilities' sum
 
-// a block's reductions by one fixed tree (thread i's partial first, then halving strides): every thread gets the
-// result, and the result depends on nothing but the inputs' places
-template <bool MAX>
-__device__ __forceinline__ float block_reduce(float v, float* scratch) {
-  scratch[threadIdx.x] = v;
-  __syncthreads();
-  for (int s = kThreads / 2; s > 0; s >>= 1) {
-    if (threadIdx.x < s)
-      scratch[threadIdx.x] = MAX ? fmaxf(scratch[threadIdx.x], scratch[threadIdx.x + s])
-                                 : __fadd_rn(scratch[threadIdx.x], scratch[threadIdx.x + s]);
-    __syncthreads();
-  }
-  const float r = scratch[0];
-  __syncthreads();
-  return r;
-}
+// ---- the router ----------------------------------------------------------------------------------------------------
+constexpr int kRouteWarps = 4;  // tokens a block
 
-__global__ void __launch_bounds__(kThreads) route_kernel(const float* __restrict__ logits, uint32_t n_exp, uint32_t k,
-                                                         int32_t* __restrict__ ids, float* __restrict__ w,
-                                                         int32_t* __restrict__ rows) {
-  __shared__ float p[kMaxExperts], scratch[kThreads];
+template <int R>
+__global__ void __launch_bounds__(kRouteWarps* kWarp) route_kernel(const float* __restrict__ logits, uint32_t n_tok,
+                                                                   uint32_t n_exp, uint32_t k, int32_t* __restrict__ ids,
+                                                                   float* __restrict__ w, int32_t* __restrict__ rows) {
   pdl_wait();  // (a dependent launch: the step before may still be reading the ids and weights this one writes)
   pdl_launch_next();
-  const uint32_t t = blockIdx.x;
-  const float* l = logits + (uint64_t) t * n_exp;
-  float m = __int_as_float(0xFF800000);
-  for (uint32_t i = threadIdx.x; i < n_exp; i += kThreads) m = fmaxf(m, l[i]);
-  m = block_reduce<true>(m, scratch);
-  float sum = 0.0f;
-  for (uint32_t i = threadIdx.x; i < n_exp; i += kThreads) {
-    p[i] = expf(__fsub_rn(l[i], m));
-    sum = __fadd_rn(sum, p[i]);
-  }
-  const float inv = __fdiv_rn(1.0f, block_reduce<false>(sum, scratch));
-  for (uint32_t i = threadIdx.x; i < n_exp; i += kThreads) p[i] = mul_rn(p[i], inv);
-  __syncthreads();
-  if (threadIdx.x >= kWarp) return;
-  const uint32_t lane = threadIdx.x;
-  constexpr int kMine = kMaxExperts / kWarp;
-  float mine[kMine];
-#pragma unroll
-  for (int r = 0; r < kMine; r++) mine[r] = lane + 32u * r < n_exp ? order_key(p[lane + 32u * r]) : 0.0f;
-  uint32_t taken = 0;
-  float pick[kMaxK], total = 0.0f;
-  for (uint32_t j = 0; j < k; j++) {
-    float best;
-    const int e = warp_pick<kMine>(mine, n_exp, taken, best);
-    pick[j] = best, total = __fadd_rn(total, best);
-    if (!lane) ids[t * k + j] = e, rows[t * k + j] = (int32_t) t;
-  }
-  if (lane) return;
-  const float div = fmaxf(total, kSumFloor);
-  for (uint32_t j = 0; j < k; j++) w[t * k + j] = __fdiv_rn(pick[j], div);
+  const uint32_t t = blockIdx.x * kRouteWarps + threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+  if (t >= n_tok) return;  // (the whole warp)
+  const route::Pick p = route::softmax_topk<R>(logits + (uint64_t) t * n_exp, n_exp, k, lane);
+  if (lane < k) ids[t * k + lane] = (int32_t) p.id, w[t * k + lane] = p.w, rows[t * k + lane] = (int32_t) t;
 }
 
-// ---- per-expert tables -----------------------------------------------------------------------------------------
+// ---- per-expert tables ---------------------------------------------------------------------------------------------
 constexpr int kTableThreads = 1024;  // a thread an expert
+constexpr int kTableWarps = kTableThreads / kWarp;
 constexpr int kPart = MM_TILE << (Q4X_TILE_RUNS - 1);  // an entry's most tokens (128)
 constexpr uint32_t kInlinePicks = 1024;  // up to this many picks are placed by the table kernel itself
 
-__device__ __forceinline__ int run_of(int c) { return c <= 16 ? 0 : c <= 32 ? 1 : c <= 64 ? 2 : 3; }
+__device__ __forceinline__ int tile_run(int c) { return c <= 16 ? 0 : c <= 32 ? 1 : c <= 64 ? 2 : 3; }
 
-// exclusive prefix sums over the block's kTableThreads values (thread i's value v): returns the sum of the values
-// of the threads before i; *total the sum of all. integers: any order gives the same result
-__device__ __forceinline__ int block_exclusive(int v, int* warp_sums, int* total) {
+// N exclusive prefix sums over the block's kTableThreads threads at once: v[i] becomes the sum of the v[i] of the
+// threads before this one, total[i] the sum over all threads. One pass: a shuffle scan in each warp, the warps' sums
+// through shared memory, the first N warps scanning one array each. Integers: any order gives the same result.
+template <int N>
+__device__ __forceinline__ void block_exclusive(int (&v)[N], int (&total)[N], int (*warp_sums)[kTableWarps]) {
+  static_assert(N <= kTableWarps, "one warp scans one array of warp sums");
   const int lane = threadIdx.x % kWarp, wid = threadIdx.x / kWarp;
-  int inc = v;
+  int inc[N];
 #pragma unroll
-  for (int o = 1; o < kWarp; o <<= 1) {
-    const int up = __shfl_up_sync(0xFFFFFFFFu, inc, o, kWarp);
-    if (lane >= o) inc += up;
+  for (int i = 0; i < N; i++) {
+    inc[i] = v[i];
+#pragma unroll
+    for (int o = 1; o < kWarp; o <<= 1) {
+      const int up = __shfl_up_sync(0xFFFFFFFFu, inc[i], o, kWarp);
+      if (lane >= o) inc[i] += up;
+    }
   }
   __syncthreads();  // the scratch free of its last use
-  if (lane == kWarp - 1) warp_sums[wid] = inc;
+  if (lane == kWarp - 1)
+#pragma unroll
+    for (int i = 0; i < N; i++) warp_sums[i][wid] = inc[i];
   __syncthreads();
-  if (wid == 0) {
-    int s = warp_sums[lane];
+  if (wid < N) {
+    int s = warp_sums[wid][lane];
 #pragma unroll
     for (int o = 1; o < kWarp; o <<= 1) {
       const int up = __shfl_up_sync(0xFFFFFFFFu, s, o, kWarp);
       if (lane >= o) s += up;
     }
-    warp_sums[lane] = s;
+    warp_sums[wid][lane] = s;
   }
   __syncthreads();
-  *total = warp_sums[kWarp - 1];
-  return inc - v + (wid ? warp_sums[wid - 1] : 0);
+#pragma unroll
+  for (int i = 0; i < N; i++) {
+    total[i] = warp_sums[i][kWarp - 1];
+    v[i] = inc[i] - v[i] + (wid ? warp_sums[i][wid - 1] : 0);
+  }
 }
 
-// pick i's rank among the picks of its own expert before it (the stable sort's order), for few picks: every thread
-// walks the picks before its own in shared memory
-__device__ __forceinline__ int rank_inline(const int32_t* sids, uint32_t i) {
-  const int32_t e = sids[i];
-  int r = 0;
-  for (uint32_t j = 0; j < i; j++) r += sids[j] == e;
-  return r;
+// The picks' ranks inside their experts, in pick order, by the calling warp alone: sids[i] the pick's expert (or -1: not
+// placed), fill[e] the places of expert e handed out so far (zero on entry). rank[i] = how many picks of the same expert
+// come before pick i.
+__device__ __forceinline__ void rank_picks(const int32_t* sids, uint32_t n, int* fill, uint16_t* rank) {
+  const uint32_t lane = threadIdx.x % kWarp;
+  for (uint32_t i0 = 0; i0 < n; i0 += kWarp) {
+    const uint32_t i = i0 + lane;
+    const int32_t id = i < n ? sids[i] : -1;
+    const uint32_t same = __match_any_sync(0xFFFFFFFFu, id);
+    const uint32_t first = (uint32_t) __ffs((int) same) - 1u;
+    int base = 0;
+    if (lane == first && id >= 0) {
+      base = fill[id];
+      fill[id] = base + __popc(same);
+    }
+    __syncwarp();
+    base = __shfl_sync(0xFFFFFFFFu, base, (int) first, kWarp);
+    if (id >= 0) rank[i] = (uint16_t) (base + __popc(same & ((1u << lane) - 1u)));
+  }
 }
 
 __global__ void __launch_bounds__(kTableThreads) tiles_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_t k,
                                                               uint32_t n_exp, uint32_t dim, uint32_t ff,
                                                               const Q4xExpertTiles t, const Q4xExpertBounds bd) {
-  __shared__ int count[kMaxExperts], first_place[kMaxExperts], first_slot[kMaxExperts], warp_sums[kWarp];
+  __shared__ int count[kMaxExperts], place0[kMaxExperts], slot0[kMaxExperts], warp_sums[2 + Q4X_TILE_RUNS][kTableWarps];
   __shared__ int32_t sids[kInlinePicks];
+  __shared__ uint16_t rank[kInlinePicks];
   pdl_wait();  // (a dependent launch: ids are the router's output)
   pdl_launch_next();
   const uint32_t e = threadIdx.x;
+  const bool inline_place = n <= kInlinePicks;
   count[e] = 0;
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < n; i += kTableThreads) {
     const int32_t id = ids[i];
-    atomicAdd(&count[id], 1);
-    if (n <= kInlinePicks) sids[i] = id;
+    const bool known = (uint32_t) id < n_exp;  // (an id outside the experts has no place: it is left out)
+    if (known) atomicAdd(&count[id], 1);
+    if (inline_place) sids[i] = known ? id : -1;
   }
   __syncthreads();
   const int c = e < n_exp ? count[e] : 0;
-  const int slots = (c + MM_TILE - 1) / MM_TILE * MM_TILE, rem = c % kPart;
-  int live_slots, dummy, live_run[Q4X_TILE_RUNS], at[Q4X_TILE_RUNS];
-  const int p0 = block_exclusive(c, warp_sums, &dummy);
-  const int s0 = block_exclusive(slots, warp_sums, &live_slots);
+  const int padded = (c + MM_TILE - 1) / MM_TILE * MM_TILE, last = c % kPart;
+  // the expert's first place, first slot, and first entry in each run of tile counts
+  int first[2 + Q4X_TILE_RUNS], total[2 + Q4X_TILE_RUNS];
+  first[0] = c, first[1] = padded;
 #pragma unroll
-  for (int r = 0; r < Q4X_TILE_RUNS; r++) {
-    const int mine = (r == Q4X_TILE_RUNS - 1 ? c / kPart : 0) + (rem && run_of(rem) == r);
-    at[r] = (int) bd.first[r] + block_exclusive(mine, warp_sums, &live_run[r]);
-  }
-  first_place[e] = p0, first_slot[e] = s0;
+  for (int r = 0; r < Q4X_TILE_RUNS; r++)
+    first[2 + r] = (r == Q4X_TILE_RUNS - 1 ? c / kPart : 0) + (last && tile_run(last) == r);
+  block_exclusive(first, total, warp_sums);
+  place0[e] = first[0], slot0[e] = first[1];
+  count[e] = 0;  // (the fill counters of the ranking below)
   if (e < n_exp) {
-    t.off[e] = p0, t.off[n_exp + e] = s0, t.off[2 * n_exp + e] = c;
-    for (int s = s0 + c; s < s0 + slots; s++) t.gidx[s] = -1, t.hidx[s] = -1;
-    for (int part = 0; part * kPart < c; part++) {
-      const int m = c - part * kPart < kPart ? c - part * kPart : kPart, en = at[run_of(m)]++;
-      const int slot = s0 + part * kPart, place = p0 + part * kPart;
+    t.off[e] = first[0], t.off[n_exp + e] = first[1], t.off[2 * n_exp + e] = c;
+    for (int s = first[1] + c; s < first[1] + padded; s++) t.gidx[s] = -1, t.hidx[s] = -1;
+    // the expert's tokens in parts of at most 128, each an entry of the run its tile count belongs to
+    for (int done = 0; done < c; done += kPart) {
+      const int m = c - done < kPart ? c - done : kPart, r = tile_run(m);
+      const uint32_t en = bd.first[r] + (uint32_t) first[2 + r]++;
+      const uint32_t slot = (uint32_t) (first[1] + done), place = (uint32_t) (first[0] + done);
       t.cnt[en] = m;
-      t.xg[en] = (uint32_t) slot * dim, t.xd[en] = (uint32_t) slot * ff;
-      t.yg[en] = (uint32_t) place * ff, t.yd[en] = (uint32_t) place * dim;
+      t.xg[en] = slot * dim, t.xd[en] = slot * ff, t.yg[en] = place * ff, t.yd[en] = place * dim;
 #pragma unroll
       for (int j = 0; j < Q4X_GROUP_TENSORS; j++)
         t.ptr[j][en] = t.tab[j] ? t.tab[j][e] : (const uint8_t*) t.base[j] + (uint64_t) e * t.bytes[j];
@@ -155,13 +150,16 @@ __global__ void __launch_bounds__(kTableThreads) tiles_kernel(const int32_t* __r
   // the tables' tails, launched to their bounds: entries of no tokens, slots of no token
 #pragma unroll
   for (int r = 0; r < Q4X_TILE_RUNS; r++)
-    for (uint32_t i = (uint32_t) live_run[r] + threadIdx.x; i < bd.count[r]; i += kTableThreads) t.cnt[bd.first[r] + i] = 0;
-  for (uint32_t s = (uint32_t) live_slots + threadIdx.x; s < bd.slots; s += kTableThreads) t.gidx[s] = -1, t.hidx[s] = -1;
-  if (n > kInlinePicks) return;  // place_kernel's
+    for (uint32_t i = (uint32_t) total[2 + r] + threadIdx.x; i < bd.count[r]; i += kTableThreads) t.cnt[bd.first[r] + i] = 0;
+  for (uint32_t s = (uint32_t) total[1] + threadIdx.x; s < bd.slots; s += kTableThreads) t.gidx[s] = -1, t.hidx[s] = -1;
+  if (!inline_place) return;  // place_kernel's
+  __syncthreads();
+  if (threadIdx.x < kWarp) rank_picks(sids, n, count, rank);
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < n; i += kTableThreads) {
     const int32_t id = sids[i];
-    const int q = first_place[id] + rank_inline(sids, i), s = first_slot[id] + q - first_place[id];
+    if (id < 0) continue;
+    const int q = place0[id] + rank[i], s = slot0[id] + rank[i];
     t.where[i] = q, t.gidx[s] = (int32_t) (i / k), t.hidx[s] = q;
   }
 }
@@ -204,9 +202,12 @@ __global__ void __launch_bounds__(kThreads) place_kernel(const int32_t* __restri
 }
 
 // ---- the int8 lane's tables (include/osmos_b200/lane.h) -----------------------------------------------------------
-__device__ __forceinline__ void order_token(const int32_t* row_of, uint32_t t, uint32_t k, int32_t* order) {
+// a token's rows in ascending row (= ascending expert id), the picks without a row here (-1) last: k is small, one
+// thread sorts by insertion
+template <class Rows>
+__device__ __forceinline__ void order_token(Rows row_of, uint32_t t, uint32_t k, int32_t* order) {
   int32_t r[kMaxK];
-  for (uint32_t j = 0; j < k; j++) r[j] = row_of[t * k + j];
+  for (uint32_t j = 0; j < k; j++) r[j] = row_of(t * k + j);
   for (uint32_t a = 1; a < k; a++)
     for (uint32_t c = a; c > 0 && (uint32_t) r[c] < (uint32_t) r[c - 1]; c--) {
       const int32_t s = r[c];
@@ -215,56 +216,73 @@ __device__ __forceinline__ void order_token(const int32_t* row_of, uint32_t t, u
   for (uint32_t j = 0; j < k; j++) order[t * k + j] = r[j];
 }
 
+// where row (token t, pick j) of the exchange goes: its home rank's receive block, row (t % tokens) * k + j
+__device__ __forceinline__ float* home_row(const LaneRowHomes& h, uint32_t half, uint32_t i, uint32_t k) {
+  const uint32_t t = i / k, j = i % k;
+  return (float*) (h.base[t / h.tokens] + h.recv[half]) + ((uint64_t) (t % h.tokens) * k + j) * h.dim;
+}
+
 __global__ void __launch_bounds__(kTableThreads) lane_tables_kernel(const int32_t* __restrict__ ids, uint32_t n,
                                                                     uint32_t k, uint32_t n_exp, const LaneExperts ex,
-                                                                    const LaneTables t, uint32_t e0, uint32_t e1) {
-  __shared__ int count[kMaxExperts], first_row[kMaxExperts], warp_sums[kWarp];
-  __shared__ int32_t sids[kInlinePicks];
+                                                                    const LaneTables t, uint32_t e0, uint32_t e1,
+                                                                    const LaneTablesSync sy, const LaneRowHomes homes) {
+  __shared__ int count[kMaxExperts], first_row[kMaxExperts], warp_sums[2][kTableWarps];
+  __shared__ int32_t sids[kInlinePicks], srow[kInlinePicks];
+  __shared__ uint16_t rank[kInlinePicks];
   pdl_wait();  // (a dependent launch: ids are the router's output)
   pdl_launch_next();
   const uint32_t e = threadIdx.x;
+  const bool inline_place = n <= kInlinePicks;
   count[e] = 0;
+  uint32_t step = 0;
+  if (sy.flags) {  // expert-parallel: the picks are the peers' - every peer's flag must have reached this step
+    step = *sy.step;
+    if (threadIdx.x < sy.n_ranks && !flag_wait(sy.flags + threadIdx.x, step)) atomicOr(sy.status, 1u);
+    ids = (const int32_t*) ((const uint8_t*) ids + (step & 1u) * sy.half_bytes);
+  }
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < n; i += kTableThreads) {
     const int32_t id = ids[i];
     const bool own = (uint32_t) id >= e0 && (uint32_t) id < e1;  // experts outside [e0, e1) are another rank's
     if (own) atomicAdd(&count[id], 1);
-    if (n <= kInlinePicks) sids[i] = own ? id : -1;
+    if (inline_place) sids[i] = own ? id : -1;
   }
   __syncthreads();
   const int c = e < n_exp ? count[e] : 0;
-  const int ents = (c + LANE_MAX_TOKENS - 1) / LANE_MAX_TOKENS;
-  int rows, live;
-  const int r0 = block_exclusive(c, warp_sums, &rows);
-  const int en0 = block_exclusive(ents, warp_sums, &live);
-  first_row[e] = r0;
+  int first[2] = {c, (c + LANE_MAX_TOKENS - 1) / LANE_MAX_TOKENS}, total[2];
+  const int parts = first[1];
+  block_exclusive(first, total, warp_sums);
+  first_row[e] = first[0];
+  count[e] = 0;  // (the fill counters of the ranking below)
   if (e < n_exp) {
-    t.off[e] = r0, t.off[n_exp + e] = c;
-    for (int part = 0; part < ents; part++) {
-      const int en = en0 + part;
-      t.cnt[en] = c - part * LANE_MAX_TOKENS < LANE_MAX_TOKENS ? c - part * LANE_MAX_TOKENS : LANE_MAX_TOKENS;
-      t.xrow[en] = r0 + part * LANE_MAX_TOKENS;
+    t.off[e] = first[0], t.off[n_exp + e] = c;
+    for (int part = 0; part < parts; part++) {
+      const int en = first[1] + part, left = c - part * LANE_MAX_TOKENS;
+      t.cnt[en] = left < LANE_MAX_TOKENS ? left : LANE_MAX_TOKENS;
+      t.xrow[en] = first[0] + part * LANE_MAX_TOKENS;
 #pragma unroll
       for (int j = 0; j < 3; j++)
         t.w[j][en] = ex.tab[j] ? ex.tab[j][e] : (const uint8_t*) ex.base[j] + (uint64_t) e * ex.bytes[j];
     }
   }
-  for (uint32_t i = (uint32_t) live + threadIdx.x; i < t.max_entries; i += kTableThreads) t.cnt[i] = 0;
-  if (threadIdx.x == 0) t.counts[0] = live, t.counts[1] = rows;
-  if (n > kInlinePicks) return;  // lane_place_kernel's
+  for (uint32_t i = (uint32_t) total[1] + threadIdx.x; i < t.max_entries; i += kTableThreads) t.cnt[i] = 0;
+  if (threadIdx.x == 0) t.counts[0] = total[1], t.counts[1] = total[0];
+  if (!inline_place) return;  // lane_place_kernel's
+  __syncthreads();
+  if (threadIdx.x < kWarp) rank_picks(sids, n, count, rank);
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < n; i += kTableThreads) {
     const int32_t id = sids[i];
-    if (id < 0) {
-      t.row_of[i] = -1;
-      continue;
-    }
-    const int r = first_row[id] + rank_inline(sids, i);
-    t.tok[r] = (int32_t) (i / k), t.pair[r] = (int32_t) i, t.row_of[i] = r;
+    const int r = id < 0 ? -1 : first_row[id] + rank[i];
+    srow[i] = r, t.row_of[i] = r;
+    if (r < 0) continue;
+    t.tok[r] = (int32_t) (i / k), t.pair[r] = (int32_t) i;
+    if (homes.rows) homes.rows[r] = home_row(homes, step & 1u, i, k);
   }
-  // each token's rows in order, in the same launch (the block's own writes, after its barrier)
+  // each token's rows in order, in the same launch
   __syncthreads();
-  for (uint32_t tk = threadIdx.x; tk < n / k; tk += kTableThreads) order_token(t.row_of, tk, k, t.order);
+  for (uint32_t tk = threadIdx.x; tk < n / k; tk += kTableThreads)
+    order_token([&](uint32_t i) { return srow[i]; }, tk, k, t.order);
 }
 
 __global__ void __launch_bounds__(kThreads) lane_place_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_t k,
@@ -284,32 +302,74 @@ __global__ void __launch_bounds__(kThreads) lane_place_kernel(const int32_t* __r
   });
 }
 
-// a token's rows in ascending expert id (rows ascend with the expert, so ascending row): its k picks' rows sorted,
-// the picks without a row here (-1) last
 __global__ void lane_order_kernel(const int32_t* __restrict__ row_of, uint32_t n_tok, uint32_t k,
                                   int32_t* __restrict__ order) {
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tok) return;
-  order_token(row_of, t, k, order);
+  order_token([&](uint32_t i) { return row_of[i]; }, t, k, order);
 }
 
 // ---- activation and combine ------------------------------------------------------------------------------------
 __device__ __forceinline__ float sigmoidf(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 __device__ __forceinline__ float siluf(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
 
-__device__ __forceinline__ void x16_put(const Q4xX16& side, uint64_t i, float v) {
-  if (!side.x16) return;
-  const uint32_t t = side.row0 + (uint32_t) (i / side.cols), c = (uint32_t) (i % side.cols);
-  if (!(fabsf(v) <= 65504.0f)) atomicOr(side.overflow, 1);
-  ((__half*) side.x16)[(uint64_t) (t / 16) * 16 * side.cols + (c / 16) * 256 + (t % 16) * 16 + c % 16] = __float2half_rn(v);
+// value (token t, column c) of a cols-wide activation into the 16 x 16 tiled f16 layout, a value past f16 flagged
+__device__ __forceinline__ void x16_store(__half* x16, int32_t* overflow, uint32_t t, uint32_t c, uint32_t cols, float v) {
+  if (!(fabsf(v) <= 65504.0f)) atomicOr(overflow, 1);
+  x16[(uint64_t) (t / 16) * 16 * cols + (c / 16) * 256 + (t % 16) * 16 + c % 16] = __float2half_rn(v);
 }
 
-__global__ void swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u, uint64_t n, float* __restrict__ y,
-                              const Q4xX16 side) {
-  const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
+// four neighbouring values a thread where the addresses allow it (VEC 4), else one
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u, uint64_t n,
+                                                          float* __restrict__ y, const Q4xX16 side) {
+  const uint64_t i = ((uint64_t) blockIdx.x * kThreads + threadIdx.x) * VEC;
   if (i >= n) return;
-  y[i] = mul_rn(siluf(g[i]), u[i]);
-  x16_put(side, i, y[i]);
+  float gv[VEC], uv[VEC], out[VEC];
+  if constexpr (VEC == 4) {
+    const float4 a = *(const float4*) (g + i), b = *(const float4*) (u + i);
+    gv[0] = a.x, gv[1] = a.y, gv[2] = a.z, gv[3] = a.w, uv[0] = b.x, uv[1] = b.y, uv[2] = b.z, uv[3] = b.w;
+  } else {
+    gv[0] = g[i], uv[0] = u[i];
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; v++) out[v] = mul_rn(siluf(gv[v]), uv[v]);
+  if constexpr (VEC == 4) *(float4*) (y + i) = make_float4(out[0], out[1], out[2], out[3]);
+  else y[i] = out[0];
+  if (side.x16)
+#pragma unroll
+    for (int v = 0; v < VEC; v++)
+      x16_store((__half*) side.x16, side.overflow, side.row0 + (uint32_t) ((i + v) / side.cols), (uint32_t) ((i + v) % side.cols),
+                side.cols, out[v]);
+}
+
+// the activation straight into down's tiled f16 input: slot s takes row idx[s] of g and u (a pad slot, -1, zeros); a
+// thread eight neighbouring columns of a slot - half a tile row, one 16-byte store
+__global__ void __launch_bounds__(kThreads) swiglu_rows_kernel(const float* __restrict__ g, const float* __restrict__ u, uint32_t ff,
+                                                               const int32_t* __restrict__ idx, uint32_t slots,
+                                                               __half* __restrict__ x16, int32_t* overflow) {
+  const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
+  const uint32_t per = ff / 8;
+  if (i >= (uint64_t) slots * per) return;
+  const uint32_t s = (uint32_t) (i / per), c = (uint32_t) (i % per) * 8;
+  const int32_t r = idx[s];
+  __align__(16) __half h[8];
+  bool over = false;
+  if (r >= 0) {
+    const float* gp = g + (uint64_t) r * ff + c;
+    const float* up = u + (uint64_t) r * ff + c;
+#pragma unroll
+    for (int v = 0; v < 8; v++) {
+      const float o = mul_rn(siluf(gp[v]), up[v]);
+      over |= !(fabsf(o) <= 65504.0f);
+      h[v] = __float2half_rn(o);
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < 8; v++) h[v] = __float2half_rn(0.0f);
+  }
+  if (over) atomicOr(overflow, 1);
+  *(uint4*) (x16 + (uint64_t) (s / 16) * 16 * ff + (c / 16) * 256 + (s % 16) * 16 + c % 16) = *(const uint4*) h;
 }
 
 template <int VEC>
@@ -339,6 +399,29 @@ __global__ void moe_sum_kernel(const float* __restrict__ y, const int32_t* __res
 }
 
 }  // namespace
+
+// the lane tables with the expert-parallel step's extras (moe_api.h); sy.flags / homes.rows NULL: the plain tables
+bool lane_tables_launch(const int32_t* ids, uint32_t n, uint32_t k, uint32_t n_exp, uint32_t expert0, uint32_t expert1,
+                        const LaneExperts* ex, const LaneTables* t, const LaneTablesSync& sy, const LaneRowHomes& homes,
+                        cudaStream_t s) {
+  if (!ids || !n || !k || n % k || k > kMaxK || !n_exp || n_exp > kMaxExperts || expert0 >= expert1 ||
+      expert1 > n_exp || !ex || !t || !t->cnt || !t->xrow || !t->tok || !t->pair || !t->row_of || !t->order ||
+      !t->off || !t->counts || t->max_entries < lane_max_entries(n, n_exp))
+    return false;
+  for (int j = 0; j < 3; j++)
+    if ((!ex->tab[j] && (!ex->base[j] || !ex->bytes[j])) || !t->w[j]) return false;
+  if ((sy.flags || homes.rows) && n > kInlinePicks) return false;  // (the exchange's step is a decode step: few picks)
+  if (launch_dependent(lane_tables_kernel, dim3(1), dim3(kTableThreads), 0, s, ids, n, k, n_exp, *ex, *t, expert0, expert1,
+                       sy, homes) != cudaSuccess)
+    return false;
+  if (n > kInlinePicks) {
+    lane_place_kernel<<<n_exp, kThreads, 0, s>>>(ids, n, k, n_exp, *t, expert0, expert1);
+    if (!launched()) return false;
+    lane_order_kernel<<<blocks_for(n / k, 128), 128, 0, s>>>(t->row_of, n / k, k, t->order);
+  }
+  return launched();
+}
+
 }  // namespace osmos
 
 using namespace osmos;
@@ -347,15 +430,28 @@ extern "C" bool q4x_route(const float* logits, uint32_t n_tok, uint32_t n_exp, u
                           int32_t* rows, void* stream) {
   if (!logits || !ids || !w || !rows || !n_tok || !n_exp || n_exp > kMaxExperts || !k || k > kMaxK || k > n_exp)
     return false;
-  return launch_dependent(route_kernel, dim3(n_tok), dim3(kThreads), 0, stream_of(stream), logits, n_exp, k, ids, w, rows) ==
-         cudaSuccess;
+  const dim3 grid(blocks_for(n_tok, kRouteWarps)), block(kRouteWarps * kWarp);
+  const cudaStream_t s = stream_of(stream);
+  switch (route::regs_for(n_exp)) {
+    case 4: return launch_dependent(route_kernel<4>, grid, block, 0, s, logits, n_tok, n_exp, k, ids, w, rows) == cudaSuccess;
+    case 8: return launch_dependent(route_kernel<8>, grid, block, 0, s, logits, n_tok, n_exp, k, ids, w, rows) == cudaSuccess;
+    case 16: return launch_dependent(route_kernel<16>, grid, block, 0, s, logits, n_tok, n_exp, k, ids, w, rows) == cudaSuccess;
+    default: return launch_dependent(route_kernel<32>, grid, block, 0, s, logits, n_tok, n_exp, k, ids, w, rows) == cudaSuccess;
+  }
 }
 
 extern "C" void q4x_expert_bounds(uint32_t n, uint32_t n_exp, Q4xExpertBounds* b) {
+  // a run r holds the entries of 2^r tiles: an expert gives one entry to the run of its last part (at most one an
+  // expert, and it needs more than 16 * 2^(r-1) tokens), and all its full 128-token parts to the last run
   const uint32_t most = n < n_exp ? n : n_exp;
-  const uint32_t cap[Q4X_TILE_RUNS] = {most, n / 17 < most ? n / 17 : most, n / 33 < most ? n / 33 : most, n / 65};
-  b->entries = 0;
-  for (int r = 0; r < Q4X_TILE_RUNS; r++) b->first[r] = b->entries, b->count[r] = cap[r], b->entries += cap[r];
+  uint32_t at = 0;
+  for (uint32_t r = 0; r < Q4X_TILE_RUNS; r++) {
+    const uint32_t need = r ? (MM_TILE << (r - 1)) + 1u : 1u;  // the fewest tokens of an entry of this run
+    uint32_t cap = n / need < most ? n / need : most;
+    if (r == Q4X_TILE_RUNS - 1) cap = n / need;  // (full parts: not bounded by the experts)
+    b->first[r] = at, b->count[r] = cap, at += cap;
+  }
+  b->entries = at;
   b->slots = n + (MM_TILE - 1) * most;
 }
 
@@ -402,7 +498,18 @@ extern "C" bool q4x_expert_tiles_static(const int32_t* ids, uint32_t n, uint32_t
 extern "C" bool q4x_swiglu(const float* g, const float* u, uint64_t n, float* y, const Q4xX16* side, void* stream) {
   if (!g || !u || !y || !n) return false;
   const Q4xX16 s = side ? *side : Q4xX16{nullptr, nullptr, 1, 0};
-  swiglu_kernel<<<blocks_for(n, kThreads), kThreads, 0, stream_of(stream)>>>(g, u, n, y, s);
+  if (n % 4 == 0 && ((uintptr_t) g | (uintptr_t) u | (uintptr_t) y) % 16 == 0)
+    swiglu_kernel<4><<<blocks_for(n / 4, kThreads), kThreads, 0, stream_of(stream)>>>(g, u, n, y, s);
+  else
+    swiglu_kernel<1><<<blocks_for(n, kThreads), kThreads, 0, stream_of(stream)>>>(g, u, n, y, s);
+  return launched();
+}
+
+extern "C" bool q4x_swiglu_rows(const float* g, const float* u, uint32_t ff, const int32_t* idx, uint32_t slots, void* x16,
+                                int32_t* overflow, void* stream) {
+  if (!g || !u || !idx || !x16 || !overflow || !slots || !ff || ff % MM_TILE || ((uintptr_t) x16 & 15u)) return false;
+  const uint64_t work = (uint64_t) slots * (ff / 8);
+  swiglu_rows_kernel<<<blocks_for(work, kThreads), kThreads, 0, stream_of(stream)>>>(g, u, ff, idx, slots, (__half*) x16, overflow);
   return launched();
 }
 
@@ -428,20 +535,5 @@ extern "C" uint32_t lane_max_entries(uint32_t n, uint32_t n_exp) {
 
 extern "C" bool lane_tables(const int32_t* ids, uint32_t n, uint32_t k, uint32_t n_exp, uint32_t expert0,
                             uint32_t expert1, const LaneExperts* ex, const LaneTables* t, void* stream) {
-  if (!ids || !n || !k || n % k || k > kMaxK || !n_exp || n_exp > kMaxExperts || expert0 >= expert1 ||
-      expert1 > n_exp || !ex || !t || !t->cnt || !t->xrow || !t->tok || !t->pair || !t->row_of || !t->order ||
-      !t->off || !t->counts || t->max_entries < lane_max_entries(n, n_exp))
-    return false;
-  for (int j = 0; j < 3; j++)
-    if ((!ex->tab[j] && (!ex->base[j] || !ex->bytes[j])) || !t->w[j]) return false;
-  const cudaStream_t s = stream_of(stream);
-  if (launch_dependent(lane_tables_kernel, dim3(1), dim3(kTableThreads), 0, s, ids, n, k, n_exp, *ex, *t, expert0, expert1) !=
-      cudaSuccess)
-    return false;
-  if (n > kInlinePicks) {
-    lane_place_kernel<<<n_exp, kThreads, 0, s>>>(ids, n, k, n_exp, *t, expert0, expert1);
-    if (!launched()) return false;
-  }
-  if (n > kInlinePicks) lane_order_kernel<<<blocks_for(n / k, 128), 128, 0, s>>>(t->row_of, n / k, k, t->order);
-  return launched();
+  return lane_tables_launch(ids, n, k, n_exp, expert0, expert1, ex, t, LaneTablesSync{}, LaneRowHomes{}, stream_of(stream));
 }

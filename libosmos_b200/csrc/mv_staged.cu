@@ -425,14 +425,11 @@ int launch(const Request& r, const Device* dev, uint32_t slots, cudaStream_t s) 
   a.units = (r.rows + RW - 1) / RW;
   a.status = dev->status;
   const uint32_t total = a.ring_off + kWarps * slots * a.slot_bytes + 16u;  // + the window's read past a last block
-  static bool sized = false;  // (one flag a template instance)
+  static bool sized[64] = {};  // (one record a template instance, one flag a device)
   void (*kernel)(const Args);
   if constexpr (REGX) kernel = mv_regx_kernel<T, RW>;
   else kernel = mv_staged_kernel<T, NT, RW>;
-  if (!sized) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemLimit<T>) != cudaSuccess) return 0;
-    sized = true;
-  }
+  if (!allow_dynamic_smem(kernel, (int) kSmemLimit<T>, sized)) return 0;
   uint32_t grid = (uint32_t) dev->sms;
   if (a.units < grid) grid = a.units;
   return launch_dependent(kernel, dim3(grid), dim3(kThreads), total, s, a) == cudaSuccess ? 1 : -1;

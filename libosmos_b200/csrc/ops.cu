@@ -5,7 +5,9 @@
 #include "decode.cuh"
 #include "osmos_b200/mm.h"
 #include "osmos_b200/ops.h"
-#include "topk.cuh"
+#include "route.cuh"
+
+#include <initializer_list>
 
 namespace osmos {
 namespace {
@@ -14,83 +16,113 @@ constexpr int kThreads = 256;
 
 __device__ __forceinline__ float sigmoidf(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 __device__ __forceinline__ float siluf(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
-__device__ __forceinline__ float softplusf(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
-// a block a token: every expert's score and key through shared memory, then the first warp picks
+// a warp a token (route.cuh): scores and keys in the warp's registers, four tokens a block
+constexpr int kRouteWarps = 4;
+template <int R, int SCORE>
+__global__ void __launch_bounds__(kRouteWarps* kWarp) router_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                                    uint32_t n_tok, uint32_t n_exp, uint32_t k, float scale,
+                                                                    int32_t* __restrict__ idx, float* __restrict__ w) {
+  const uint32_t t = blockIdx.x * kRouteWarps + threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+  if (t >= n_tok) return;  // (the whole warp)
+  const route::Pick p = route::scored_topk<R, SCORE>(logits + (uint64_t) t * n_exp, bias, n_exp, k, scale, lane);
+  if (lane < k) idx[t * k + lane] = (int32_t) p.id, w[t * k + lane] = p.w;
+}
+
 template <int SCORE>
-__global__ void __launch_bounds__(kThreads) router_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                                          uint32_t n_exp, uint32_t k, float scale,
-                                                          int32_t* __restrict__ idx, float* __restrict__ w) {
-  __shared__ float score[OPS_MAX_EXPERTS], key[OPS_MAX_EXPERTS];
-  const uint32_t t = blockIdx.x;
-  for (uint32_t e = threadIdx.x; e < n_exp; e += kThreads) {
-    const float l = logits[(uint64_t) t * n_exp + e];
-    score[e] = SCORE == OPS_SCORE_SIGMOID ? sigmoidf(l) : sqrtf(softplusf(l));
-    key[e] = order_key(__fadd_rn(score[e], bias[e]));
+bool launch_router(const float* logits, const float* bias, uint32_t n_exp, uint32_t k, float scale, uint32_t n_tok, int32_t* idx,
+                   float* w, cudaStream_t s) {
+  const dim3 grid(blocks_for(n_tok, kRouteWarps)), block(kRouteWarps * kWarp);
+  switch (route::regs_for(n_exp)) {
+    case 4: router_kernel<4, SCORE><<<grid, block, 0, s>>>(logits, bias, n_tok, n_exp, k, scale, idx, w); break;
+    case 8: router_kernel<8, SCORE><<<grid, block, 0, s>>>(logits, bias, n_tok, n_exp, k, scale, idx, w); break;
+    case 16: router_kernel<16, SCORE><<<grid, block, 0, s>>>(logits, bias, n_tok, n_exp, k, scale, idx, w); break;
+    default: router_kernel<32, SCORE><<<grid, block, 0, s>>>(logits, bias, n_tok, n_exp, k, scale, idx, w); break;
   }
-  __syncthreads();
-  if (threadIdx.x >= kWarp) return;
-  const uint32_t lane = threadIdx.x;
-  constexpr int kMine = OPS_MAX_EXPERTS / kWarp;
-  float mine[kMine];
-#pragma unroll
-  for (int r = 0; r < kMine; r++) mine[r] = lane + 32u * r < n_exp ? key[lane + 32u * r] : 0.0f;
-  uint32_t taken = 0;
-  int32_t pick[OPS_MAX_TOPK];
-  for (uint32_t s = 0; s < k; s++) {
-    float best;
-    pick[s] = warp_pick<kMine>(mine, n_exp, taken, best);
-  }
-  if (lane) return;
-  float wt[OPS_MAX_TOPK], sum = 0.0f;
-  for (uint32_t s = 0; s < k; s++) {
-    wt[s] = (uint32_t) pick[s] < n_exp ? score[pick[s]] : 0.0f;
-    sum = __fadd_rn(sum, wt[s]);
-  }
-  for (uint32_t s = 0; s < k; s++) {
-    idx[t * k + s] = pick[s];
-    w[t * k + s] = mul_rn(__fdiv_rn(wt[s], __fadd_rn(sum, 1e-20f)), scale);
-  }
+  return launched();
 }
 
-template <bool LANE>
-__global__ void swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u, uint32_t n, float lim,
-                              const float* __restrict__ scale, uint64_t total, float* __restrict__ h) {
-  const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
+// The elementwise steps take rows of n (or len, dim) values. Where the rows and every address are whole 16-byte words a
+// thread handles four neighbouring values of one row (VEC 4: one load / store a tensor), else one (VEC 1). The
+// operations on each value are the same either way, so are the bits.
+template <int VEC> struct Pack;
+template <> struct Pack<1> {
+  float v[1];
+  __device__ __forceinline__ void load(const float* p) { v[0] = *p; }
+  __device__ __forceinline__ void store(float* p) const { *p = v[0]; }
+};
+template <> struct Pack<4> {
+  float v[4];
+  __device__ __forceinline__ void load(const float* p) {
+    const float4 a = *(const float4*) p;
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+  }
+  __device__ __forceinline__ void store(float* p) const { *(float4*) p = make_float4(v[0], v[1], v[2], v[3]); }
+};
+__host__ inline bool words16(uint32_t row_len, std::initializer_list<const void*> ptrs) {
+  if (row_len % 4) return false;
+  for (const void* p : ptrs)
+    if ((uintptr_t) p & 15u) return false;
+  return true;
+}
+
+template <bool LANE, int VEC>
+__global__ void __launch_bounds__(kThreads) swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u, uint32_t n,
+                                                          float lim, const float* __restrict__ scale, uint64_t total,
+                                                          float* __restrict__ h) {
+  const uint64_t i = ((uint64_t) blockIdx.x * kThreads + threadIdx.x) * VEC;
   if (i >= total) return;
-  if constexpr (LANE) {
-    h[i] = lane_swiglu(g[i], u[i], lim, scale[i / n]);
-  } else {
-    const float gv = fminf(g[i], lim), uv = fminf(fmaxf(u[i], -lim), lim);
-    const float v = mul_rn(siluf(gv), uv);
-    h[i] = scale ? mul_rn(v, scale[i / n]) : v;
+  Pack<VEC> a, b, o;
+  a.load(g + i), b.load(u + i);
+  const float sc = scale ? scale[i / n] : 1.0f;
+#pragma unroll
+  for (int j = 0; j < VEC; j++) {
+    if constexpr (LANE) {
+      o.v[j] = lane_swiglu(a.v[j], b.v[j], lim, sc);
+    } else {
+      const float gv = fminf(a.v[j], lim), uv = fminf(fmaxf(b.v[j], -lim), lim);
+      const float v = mul_rn(siluf(gv), uv);
+      o.v[j] = scale ? mul_rn(v, sc) : v;
+    }
   }
+  o.store(h + i);
 }
 
-__global__ void gather_rows_kernel(float* __restrict__ dst, const float* __restrict__ src, const int32_t* __restrict__ idx,
-                                   uint64_t total, uint32_t len) {
-  const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
-  if (i < total) dst[i] = src[(uint64_t) idx[i / len] * len + i % len];
+// dst[i][:] = src[idx[i]][:] (SCATTER false), or rows idx[i] of src to the same rows of dst (SCATTER true)
+template <bool SCATTER, int VEC>
+__global__ void __launch_bounds__(kThreads) rows_kernel(float* __restrict__ dst, const float* __restrict__ src,
+                                                        const int32_t* __restrict__ idx, uint64_t total, uint32_t len) {
+  const uint64_t i = ((uint64_t) blockIdx.x * kThreads + threadIdx.x) * VEC;
+  if (i >= total) return;
+  const uint64_t from = (uint64_t) idx[i / len] * len + i % len;
+  Pack<VEC> v;
+  v.load(src + from);
+  v.store(dst + (SCATTER ? from : i));
 }
 
-__global__ void gather_sum_kernel(float* __restrict__ y, const float* __restrict__ src, const int32_t* __restrict__ idx,
-                                  uint32_t m, uint64_t total, uint32_t dim, const float* __restrict__ add) {
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) gather_sum_kernel(float* __restrict__ y, const float* __restrict__ src,
+                                                              const int32_t* __restrict__ idx, uint32_t m, uint64_t total,
+                                                              uint32_t dim, const float* __restrict__ add) {
   pdl_wait();  // (a dependent launch: src and idx are the output of the kernels ahead)
   pdl_launch_next();
-  const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
+  const uint64_t i = ((uint64_t) blockIdx.x * kThreads + threadIdx.x) * VEC;
   if (i >= total) return;
   const uint64_t t = i / dim, c = i % dim;
-  float s = 0.0f;
-  for (uint32_t j = 0; j < m; j++) s = __fadd_rn(s, src[(uint64_t) idx[t * m + j] * dim + c]);
-  y[i] = add ? __fadd_rn(s, add[i]) : s;
-}
-
-__global__ void copy_rows_kernel(float* __restrict__ dst, const float* __restrict__ src, const int32_t* __restrict__ idx,
-                                 uint64_t total, uint32_t len) {
-  const uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
-  if (i >= total) return;
-  const uint64_t at = (uint64_t) idx[i / len] * len + i % len;
-  dst[at] = src[at];
+  Pack<VEC> s, v;
+#pragma unroll
+  for (int j = 0; j < VEC; j++) s.v[j] = 0.0f;
+  for (uint32_t j = 0; j < m; j++) {  // the rows in j's order, from 0
+    v.load(src + (uint64_t) idx[t * m + j] * dim + c);
+#pragma unroll
+    for (int q = 0; q < VEC; q++) s.v[q] = __fadd_rn(s.v[q], v.v[q]);
+  }
+  if (add) {
+    v.load(add + i);
+#pragma unroll
+    for (int q = 0; q < VEC; q++) s.v[q] = __fadd_rn(s.v[q], v.v[q]);
+  }
+  s.store(y + i);
 }
 
 // bit 0: a wait ran out. one word a device (device memory: each device that loads the library has its own copy)
@@ -239,13 +271,10 @@ extern "C" bool ops_router_scored(const float* logits, const float* bias, uint32
                                   OpsScore score, uint32_t n_tok, int32_t* idx, float* w, void* stream) {
   if (!logits || !bias || !idx || !w || !n_exp || n_exp > OPS_MAX_EXPERTS || !k || k > OPS_MAX_TOPK || k > n_exp || !n_tok)
     return false;
-  if (score == OPS_SCORE_SIGMOID)
-    router_kernel<OPS_SCORE_SIGMOID><<<n_tok, kThreads, 0, stream_of(stream)>>>(logits, bias, n_exp, k, scale, idx, w);
-  else if (score == OPS_SCORE_SQRT_SOFTPLUS)
-    router_kernel<OPS_SCORE_SQRT_SOFTPLUS><<<n_tok, kThreads, 0, stream_of(stream)>>>(logits, bias, n_exp, k, scale, idx, w);
-  else
-    return false;
-  return launched();
+  if (score == OPS_SCORE_SIGMOID) return launch_router<route::kSigmoid>(logits, bias, n_exp, k, scale, n_tok, idx, w, stream_of(stream));
+  if (score == OPS_SCORE_SQRT_SOFTPLUS)
+    return launch_router<route::kSqrtSoftplus>(logits, bias, n_exp, k, scale, n_tok, idx, w, stream_of(stream));
+  return false;
 }
 
 extern "C" bool ops_router(const float* logits, const float* bias, uint32_t n_exp, uint32_t k, float scale,
@@ -253,50 +282,69 @@ extern "C" bool ops_router(const float* logits, const float* bias, uint32_t n_ex
   return ops_router_scored(logits, bias, n_exp, k, scale, OPS_SCORE_SQRT_SOFTPLUS, n_tok, idx, w, stream);
 }
 
+template <bool LANE>
+static bool swiglu_rows(const float* g, const float* u, uint32_t n, float lim, const float* scale, uint32_t n_tok, float* h,
+                        cudaStream_t s) {
+  const uint64_t total = (uint64_t) n * n_tok;
+  if (words16(n, {g, u, h}))
+    swiglu_kernel<LANE, 4><<<blocks_for(total / 4, kThreads), kThreads, 0, s>>>(g, u, n, lim, scale, total, h);
+  else
+    swiglu_kernel<LANE, 1><<<blocks_for(total, kThreads), kThreads, 0, s>>>(g, u, n, lim, scale, total, h);
+  return launched();
+}
+
 extern "C" bool ops_swiglu_lane(const float* g, const float* u, uint32_t n, float lim, const float* scale, uint32_t n_tok,
                                 float* h, void* stream) {
   if (!g || !u || !h || !n || !n_tok || !scale) return false;
-  const uint64_t total = (uint64_t) n * n_tok;
-  swiglu_kernel<true><<<blocks_for(total, kThreads), kThreads, 0, stream_of(stream)>>>(g, u, n, lim, scale, total, h);
-  return launched();
+  return swiglu_rows<true>(g, u, n, lim, scale, n_tok, h, stream_of(stream));
 }
 
 extern "C" bool ops_swiglu(const float* g, const float* u, uint32_t n, float lim, const float* scale, uint32_t n_tok,
                            float* h, void* stream) {
   if (!g || !u || !h || !n || !n_tok) return false;
-  const uint64_t total = (uint64_t) n * n_tok;
-  swiglu_kernel<false><<<blocks_for(total, kThreads), kThreads, 0, stream_of(stream)>>>(g, u, n, lim, scale, total, h);
+  return swiglu_rows<false>(g, u, n, lim, scale, n_tok, h, stream_of(stream));
+}
+
+template <bool SCATTER>
+static bool move_rows(float* dst, const float* src, const int32_t* idx, uint32_t n, uint32_t len, cudaStream_t s) {
+  const uint64_t total = (uint64_t) n * len;
+  if (words16(len, {dst, src}))
+    rows_kernel<SCATTER, 4><<<blocks_for(total / 4, kThreads), kThreads, 0, s>>>(dst, src, idx, total, len);
+  else
+    rows_kernel<SCATTER, 1><<<blocks_for(total, kThreads), kThreads, 0, s>>>(dst, src, idx, total, len);
   return launched();
 }
 
 extern "C" bool ops_gather_rows(float* dst, const float* src, const int32_t* idx, uint32_t n, uint32_t len, void* stream) {
   if (!dst || !src || !idx || !n || !len) return false;
-  const uint64_t total = (uint64_t) n * len;
-  gather_rows_kernel<<<blocks_for(total, kThreads), kThreads, 0, stream_of(stream)>>>(dst, src, idx, total, len);
-  return launched();
+  return move_rows<false>(dst, src, idx, n, len, stream_of(stream));
+}
+
+static bool gather_sum(float* y, const float* src, const int32_t* idx, uint32_t m, uint32_t n, uint32_t dim, const float* add,
+                       cudaStream_t s) {
+  const uint64_t total = (uint64_t) n * dim;
+  if (words16(dim, {y, src, add}))
+    return launch_dependent(gather_sum_kernel<4>, dim3(blocks_for(total / 4, kThreads)), dim3(kThreads), 0, s, y, src, idx, m, total,
+                            dim, add) == cudaSuccess;
+  return launch_dependent(gather_sum_kernel<1>, dim3(blocks_for(total, kThreads)), dim3(kThreads), 0, s, y, src, idx, m, total, dim,
+                          add) == cudaSuccess;
 }
 
 extern "C" bool ops_gather_sum(float* y, const float* src, const int32_t* idx, uint32_t m, uint32_t n, uint32_t dim,
                                void* stream) {
   if (!y || !src || !idx || !m || !n || !dim) return false;
-  const uint64_t total = (uint64_t) n * dim;
-  return launch_dependent(gather_sum_kernel, dim3(blocks_for(total, kThreads)), dim3(kThreads), 0, stream_of(stream), y, src, idx, m,
-                          total, dim, (const float*) nullptr) == cudaSuccess;
+  return gather_sum(y, src, idx, m, n, dim, nullptr, stream_of(stream));
 }
 
 extern "C" bool ops_gather_sum_add(float* y, const float* src, const int32_t* idx, uint32_t m, uint32_t n, uint32_t dim,
                                    const float* add, void* stream) {
   if (!y || !src || !idx || !m || !n || !dim || !add) return false;
-  const uint64_t total = (uint64_t) n * dim;
-  return launch_dependent(gather_sum_kernel, dim3(blocks_for(total, kThreads)), dim3(kThreads), 0, stream_of(stream), y, src, idx, m,
-                          total, dim, add) == cudaSuccess;
+  return gather_sum(y, src, idx, m, n, dim, add, stream_of(stream));
 }
 
 extern "C" bool ops_copy_rows(float* dst, const float* src, const int32_t* idx, uint32_t n, uint32_t len, void* stream) {
   if (!dst || !src || !idx || !n || !len) return false;
-  const uint64_t total = (uint64_t) n * len;
-  copy_rows_kernel<<<blocks_for(total, kThreads), kThreads, 0, stream_of(stream)>>>(dst, src, idx, total, len);
-  return launched();
+  return move_rows<true>(dst, src, idx, n, len, stream_of(stream));
 }
 
 extern "C" void ops_wait_set_limit_ms(uint32_t ms) { g_wait_limit_ms = ms ? ms : 1; }

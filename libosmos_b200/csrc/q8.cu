@@ -12,6 +12,8 @@
 #include "lane_staged_api.h"
 #include "osmos_b200/mv.h"
 #include "osmos_b200/q8.h"
+#include "q8_api.h"
+#include "q8_round.cuh"
 
 namespace osmos {
 namespace {
@@ -122,41 +124,36 @@ bool by_tokens(const LaneArgs& a, uint32_t n, uint32_t grid_y, cudaStream_t s) {
   return launch<T, 8, FUSED, DENSE>(a, grid_y, s);
 }
 
-// a warp a block of 32 values: the block's largest magnitude by the warp's tree, each lane its code
+// four lanes a block of 32 values, eight values a lane (q8_round.cuh)
 template <bool GGML>
 __global__ void __launch_bounds__(kThreads) round_kernel(const float* __restrict__ x, uint32_t rows, uint32_t cols,
                                                          uint32_t xs, int8_t* __restrict__ q, float* __restrict__ d) {
   pdl_wait();  // (a dependent launch: x is usually the output of the kernel ahead)
   pdl_launch_next();
-  const uint32_t nblk = cols / 32;
-  const uint64_t blk = (uint64_t) blockIdx.x * kWarps + threadIdx.x / kWarp;
-  const int lane = threadIdx.x % kWarp;
-  if (blk >= (uint64_t) rows * nblk) return;  // the whole warp
-  const uint32_t r = (uint32_t) (blk / nblk), s = (uint32_t) (blk % nblk);
-  const float v = x[(uint64_t) r * xs + (uint64_t) s * 32 + lane];
-  float amax = fabsf(v);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o, kWarp));
-  int code;
-  float scale;
-  if constexpr (GGML) {
-    const float dd = __fdiv_rn(amax, 127.0f), id = dd != 0.0f ? __fdiv_rn(1.0f, dd) : 0.0f;
-    code = (int) roundf(mul_rn(v, id));
-    scale = __half2float(__float2half_rn(dd));
+  const uint32_t per = cols / 8;  // lanes a row
+  const uint64_t total = (uint64_t) rows * per, i = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
+  const bool live = i < total;  // (a block of four lanes is live or not as a whole; the warp's shuffles want every lane)
+  const uint64_t at = live ? i : 0;
+  const uint32_t r = (uint32_t) (at / per), c = (uint32_t) (at % per);
+  float v[8], scale;
+  load8(x + (uint64_t) r * xs + (uint64_t) c * 8, v);
+  const uint2 codes = round_block8<GGML>(v, &scale);
+  if (!live) return;
+  int8_t* out = q + (uint64_t) r * cols + (uint64_t) c * 8;
+  if (((uintptr_t) out & 7u) == 0) {
+    *(uint2*) out = codes;
   } else {
-    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    code = (int) rintf(mul_rn(v, inv));
-    scale = __fdiv_rn(amax, 127.0f);
+#pragma unroll
+    for (int j = 0; j < 8; j++) out[j] = (int8_t) ((j < 4 ? codes.x >> (8 * j) : codes.y >> (8 * (j - 4))) & 0xFF);
   }
-  q[(uint64_t) r * cols + (uint64_t) s * 32 + lane] = (int8_t) code;
-  if (lane == 0) d[(uint64_t) r * nblk + s] = scale;
+  if (c % 4 == 0) d[(uint64_t) r * (cols / 32) + c / 4] = scale;
 }
 
 template <bool GGML>
 bool round_rows(const float* x, uint32_t rows, uint32_t cols, uint32_t xs, int8_t* q, float* d, cudaStream_t s) {
   if (!x || !q || !d || !rows || !cols || cols % 32 || xs < cols) return false;
-  const uint64_t blocks = (uint64_t) rows * (cols / 32);
-  return launch_dependent(round_kernel<GGML>, dim3(blocks_for(blocks, kWarps)), dim3(kThreads), 0, s, x, rows, cols, xs, q, d) ==
+  const uint64_t lanes = (uint64_t) rows * (cols / 8);
+  return launch_dependent(round_kernel<GGML>, dim3(blocks_for(lanes, kThreads)), dim3(kThreads), 0, s, x, rows, cols, xs, q, d) ==
          cudaSuccess;
 }
 
@@ -184,10 +181,40 @@ int staged_first(uint32_t type, const LaneArgs& a, bool fused, bool dense, uint3
 }
 
 }  // namespace
+
+bool q8_gate_up_ep(uint32_t type, const void* const* wg, const void* const* wu, const int32_t* cnt, const int32_t* xrow,
+                   const int32_t* xin, const int32_t* win, uint32_t n, uint32_t max_cnt, uint32_t rows, uint32_t cols,
+                   const int8_t* q, const float* d, const float* scale, float lim, float* h, uint32_t hs, const LaneEp& ep,
+                   bool dry, cudaStream_t s) {
+  if (!n || n > MV_MAX_GROUP || !rows || !max_cnt || max_cnt > MV_MAX_TOKENS || !cols || cols % 256 || hs < rows) return false;
+  if (!dry && (!wg || !wu || !cnt || !xrow || !q || !d || !h || !scale)) return false;
+  if (!qtype_row(type) || !(qtype_row(type)->paths & QTYPE_PATH_Q8)) return false;
+  ring::Request r{};
+  r.fused = true, r.wg = wg, r.wu = wu, r.cnt = cnt, r.xrow = xrow, r.xin = xin, r.win = win, r.q = q, r.d = d;
+  r.scale = scale, r.lim = lim, r.out = h, r.rows = rows, r.cols = cols, r.out_stride = hs, r.n_entries = n;
+  r.max_cnt = max_cnt, r.ep = ep, r.dry = dry;
+  return ring::try_launch(type, r, s) > 0;
+}
+
+bool q8_group_tok_ep(uint32_t type, const void* const* w, const int32_t* cnt, const int32_t* xrow, const int32_t* xin,
+                     uint32_t n, uint32_t max_cnt, uint32_t rows, uint32_t cols, const int8_t* q, const float* d, float* y,
+                     uint32_t ys, const LaneEp& ep, bool dry, cudaStream_t s) {
+  if (!n || n > MV_MAX_GROUP || !rows || !max_cnt || max_cnt > MV_MAX_TOKENS || !cols || cols % 256) return false;
+  if (!dry && (!w || !cnt || !xrow || !q || !d || (!y && !ep.out_rows))) return false;
+  if (!qtype_row(type) || !(qtype_row(type)->paths & QTYPE_PATH_Q8)) return false;
+  rows::Request rr{w, cnt, xrow, xin, q, d, y, rows, cols, ys, n, max_cnt, ep, dry};
+  if (const int st = rows::try_launch(type, rr, s)) return st > 0;
+  ring::Request r{};
+  r.fused = false, r.wg = w, r.cnt = cnt, r.xrow = xrow, r.xin = xin, r.q = q, r.d = d, r.out = y, r.rows = rows;
+  r.cols = cols, r.out_stride = ys, r.n_entries = n, r.max_cnt = max_cnt, r.ep = ep, r.dry = dry;
+  return ring::try_launch(type, r, s) > 0;
+}
+
 }  // namespace osmos
 
 using namespace osmos;
 
+extern "C" bool q8_known(uint32_t type) { return qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8); }
 extern "C" void q8_set_staged(int on) { g_use_staged = on; }
 extern "C" uint32_t q8_status(void) { return staged::read_status() | plain::read_status() | ring::read_status() | rows::read_status(); }
 
@@ -211,7 +238,7 @@ extern "C" bool q8_group_tok(uint32_t type, const void* const* w, const int32_t*
   a.rows = rows, a.cols = cols, a.out_stride = ys;
   if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8)) {
     if (g_use_staged == 1) {  // 512-column matrices: a thread a row
-      const rows::Request r{w, cnt, xrow, xin, q, d, y, rows, cols, ys, n, max_cnt};
+      const rows::Request r{w, cnt, xrow, xin, q, d, y, rows, cols, ys, n, max_cnt, LaneEp{}, false};
       if (const int st = rows::try_launch(type, r, stream)) return st > 0;
     }
     if (const int st = ring_first(type, a, false, n, max_cnt, stream)) return st > 0;

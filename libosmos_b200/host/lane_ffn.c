@@ -47,9 +47,29 @@ static uint64_t carve(const LaneLayer *l, uint32_t max_tok, uint8_t *mem, LaneSc
   return at;
 }
 
+/* every refusal of every stage (lane_tables, q8_round, q8_gate_up, q8_group_tok, ops_gather_sum[_add]) that depends on
+   the layer alone: checked before the first launch, so false means nothing was queued */
 static bool layer_ok(const LaneLayer *l)
 {
-  return l && l->dim && l->ff && l->dim % 256 == 0 && l->ff % 256 == 0 && l->n_exp && l->k && l->k <= 32;
+  return l && l->dim && l->ff && l->dim % 256 == 0 && l->ff % 256 == 0 && l->n_exp && l->n_exp <= 1024 && l->k &&
+         l->k <= 32 && l->k <= l->n_exp && q8_known(l->type_down) && (!l->type_gu || q8_known(l->type_gu));
+}
+
+static bool experts_ok(const LaneExperts *e)
+{
+  for (int j = 0; j < 3; j++)
+    if (!e->tab[j] && (!e->base[j] || !e->bytes[j]))
+      return false;
+  return true;
+}
+
+static bool scratch_ok(const LaneLayer *l, const LaneScratch *s, uint32_t n_tok)
+{
+  const LaneTables *t = s ? &s->tab : NULL;
+  const uint64_t picks = (uint64_t)n_tok * (l ? l->k : 0);
+  return s && n_tok && n_tok <= s->max_tok && s->xq && s->xqd && s->hh && s->hq && s->hqd && s->ye && t->w[0] && t->w[1] &&
+         t->w[2] && t->cnt && t->xrow && t->tok && t->pair && t->row_of && t->order && t->off && t->counts &&
+         t->max_entries >= lane_max_entries((uint32_t)picks, l->n_exp) && t->max_entries <= 65535u;
 }
 
 uint64_t lane_scratch_bytes(const LaneLayer *l, uint32_t max_tok)
@@ -70,7 +90,7 @@ bool lane_scratch_bind(const LaneLayer *l, uint32_t max_tok, void *mem, uint64_t
 bool lane_ffn(const LaneLayer *l, const LaneScratch *s, const float *x, const int32_t *ids, const float *weights,
               uint32_t n_tok, const float *add, float *out, void *stream)
 {
-  if (!layer_ok(l) || !s || !x || !ids || !weights || !out || !n_tok || n_tok > s->max_tok)
+  if (!layer_ok(l) || !experts_ok(&l->experts) || !scratch_ok(l, s, n_tok) || !x || !ids || !weights || !out)
     return false;
   const uint32_t picks = n_tok * l->k, D = l->dim, FF = l->ff;
   const LaneTables *t = &s->tab;
@@ -96,7 +116,8 @@ bool lane_ffn(const LaneLayer *l, const LaneScratch *s, const float *x, const in
 bool lane_ffn_rows(const LaneLayer *l, const LaneScratch *s, const int8_t *q, const float *d, const int32_t *ids,
                    const float *weights, uint32_t n_tok, uint32_t e0, uint32_t e1, void *stream)
 {
-  if (!layer_ok(l) || !s || !q || !d || !ids || !weights || !n_tok || n_tok > s->max_tok || e0 >= e1 || e1 > l->n_exp)
+  if (!layer_ok(l) || !l->type_gu || !experts_ok(&l->experts) || !scratch_ok(l, s, n_tok) || !q || !d || !ids ||
+      !weights || e0 >= e1 || e1 > l->n_exp)
     return false;
   const uint32_t picks = n_tok * l->k, D = l->dim, FF = l->ff;
   const LaneTables *t = &s->tab;

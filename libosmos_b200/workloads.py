@@ -11,6 +11,10 @@ MOE_IQ3 = dict(name="moe_iq3xxs_512e_top10", type="IQ3_XXS", n_exp=512, k=10, n_
                sigma=0.005, lim=1.0e30)
 # the decode matvec: Q4_0 W[6144 x 2048], one token
 MV_Q4_0 = dict(name="mv_q4_0_6144x2048", type="Q4_0", rows=6144, cols=2048, sigma=0.01)
+# the prefill product: Q4_K W[4096 x 4096] over 512 tokens
+MM_Q4_K = dict(name="mm_q4_k_4096x4096x512", type="Q4_K", rows=4096, cols=4096, tokens=512, sigma=0.01)
+
+BY_NAME = {MOE_IQ3["name"]: MOE_IQ3}
 
 
 def moe_layer_host(cfg, layer=0):

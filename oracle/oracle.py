@@ -23,14 +23,30 @@ BLOCK = {2: (32, 18), 8: (32, 34), 10: (256, 84), 12: (256, 144), 16: (256, 66),
 LANE_TYPES = ("IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ1_S", "IQ2_S", "IQ1_M", "Q2_K")
 
 
-def build(ref_tree="/root/reference"):
-    """Compile the restatement, and the reference's CPU lane when its tree is present."""
+def reference_tree():
+    """Where the reference's sources are mounted: $OSMOS_REF, else the `reference_path` the benchmark description at
+    the repository's root (BASELINE.json) names; None when neither points at a tree that holds src/cpu."""
+    import json
+    cand = os.environ.get("OSMOS_REF")
+    if not cand:
+        try:
+            with open(os.path.join(HERE, "..", "BASELINE.json")) as f:
+                cand = json.load(f).get("reference_path")
+        except (OSError, ValueError):
+            cand = None
+    return cand if cand and os.path.isdir(os.path.join(cand, "src", "cpu")) else None
+
+
+def build(ref_tree=None):
+    """Compile the restatement, and the reference's CPU lane when its tree is present (ref_tree, else
+    reference_tree())."""
+    ref_tree = ref_tree or reference_tree()
     grids = os.path.join(HERE, "..", "libosmos_b200", "csrc", "_gen", "osmos_grids.h")
     if not os.path.exists(grids):
         os.makedirs(os.path.dirname(grids), exist_ok=True)
         subprocess.check_call(["python", os.path.join(HERE, "..", "libosmos_b200", "csrc", "gen_grids.py"), grids])
     subprocess.check_call(["make", "-s", "-C", HERE])
-    if os.path.isdir(os.path.join(ref_tree, "src", "cpu")):
+    if ref_tree and os.path.isdir(os.path.join(ref_tree, "src", "cpu")):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + ref_tree])
 
 
@@ -292,6 +308,44 @@ class Reference:
         ok = self.lib.cpu_mv_rows(C.c_uint32(type_id), _p(w), C.c_uint32(cols), C.c_uint32(0), C.c_uint32(rows),
                                   _p(x), C.c_uint32(x.shape[1]), C.c_uint32(n), _p(y), C.c_uint32(rows))
         return y if ok else None
+
+    def lane_pool(self, threads, max_rows, dim, ff, pin=True):
+        """cpu_lane_create with worker i pinned to the i-th CPU this process may run on (pin False: the scheduler's
+        to place); returns (pool handle or None, the CPUs used)"""
+        cpus = sorted(os.sched_getaffinity(0))[:threads] if pin and hasattr(os, "sched_getaffinity") else []
+        if pin and len(cpus) == threads:
+            arr = (C.c_int * threads)(*cpus)
+            pool = self.lib.cpu_lane_create(threads, arr, max_rows, dim, ff)
+            if pool:
+                return pool, cpus
+        return self.lib.cpu_lane_create(threads, None, max_rows, dim, ff), []
+
+    def lane_job(self, type_gu, type_down, dim, ff, lim, x, scale, experts):
+        """a cpu_lane job built once: returns an object whose .run(pool) submits it and waits (True when it was done)
+        and whose .y holds the rows; everything the job points to is kept alive by the object"""
+        ref = self
+
+        class Job:
+            def __init__(self):
+                self.x = np.ascontiguousarray(x, dtype=np.float32)
+                self.scale = np.ascontiguousarray(scale, dtype=np.float32)
+                self.y = np.zeros((self.x.shape[0], dim), dtype=np.float32)
+                self.parts = experts
+                self.arr = (CpuLaneExpert * len(experts))()
+                for i, (g, u, dn, row0, cnt) in enumerate(experts):
+                    self.arr[i] = CpuLaneExpert(g.ctypes.data, u.ctypes.data, dn.ctypes.data, row0, cnt)
+                self.seq = np.zeros(1, dtype=np.uint32)
+                self.n = 0
+                self.job = CpuLaneJob(type_gu, type_down, dim, ff, lim, self.x.ctypes.data, self.scale.ctypes.data,
+                                      self.x.shape[0], self.arr, len(experts), self.y.ctypes.data, self.seq.ctypes.data, 0)
+
+            def run(self, pool):
+                self.n += 1
+                self.job.value = self.n
+                ok = ref.lib.cpu_lane_submit(pool, C.byref(self.job)) and ref.lib.cpu_lane_wait(pool)
+                return bool(ok) and int(self.seq[0]) == self.n
+
+        return Job()
 
     def lane_ffn(self, threads, type_gu, type_down, dim, ff, lim, x, scale, experts, pool=None):
         """experts: list of (gate, up, down, row0, cnt) numpy byte arrays; x [n_rows, dim]; returns y [n_rows, dim].

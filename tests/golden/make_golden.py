@@ -94,7 +94,9 @@ def ffn_golden(ref):
 
 
 if __name__ == "__main__":
-    tree = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    tree = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("OSMOS_REF")
+    if not tree or not os.path.isdir(os.path.join(tree, "src", "cpu")):
+        raise SystemExit("make_golden.py: pass the reference tree (argument or $OSMOS_REF)")
     orc.build(tree)
     ref = orc.Reference()
     assert ref.lib.cpu_q8_ready(), "this CPU lacks AVX-512 VNNI: the reference's int8 lane refuses"

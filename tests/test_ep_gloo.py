@@ -47,7 +47,8 @@ def _rank_main(rank, world, port, result_path):
     flat = ids.reshape(-1)
     order = [i for i in np.argsort(flat, kind="stable") if e0 <= flat[i] < e1]
     tid = synth.TYPE_ID[cfg["type"]]
-    send = np.zeros((world * T * k, dim), np.float32)
+    # 4. each row goes straight to its token's home rank: row (t % T) * k + j of that rank's receive block
+    contrib = np.zeros((world, T * k, dim), np.float32)  # what this rank stores into each home's block
     for i in order:
         e, t = int(flat[i]), i // k
         parts = [host[m][e * per[m]:(e + 1) * per[m]] for m in range(3)]
@@ -56,18 +57,18 @@ def _rank_main(rank, world, port, result_path):
         h = orc.swiglu_lane(g, u, cfg["lim"], wts.reshape(-1)[i:i + 1])
         hq, hd = orc.q8_round(h)
         y = orc.q8_rows(tid, parts[2], dim, ff, hq, hd)
-        send[ep.send_slot(i, k, T)] = y[0]  # 4. scatter
-    # 5. combine exchange: block h of every rank's send buffer goes to rank h
-    blocks = [torch.zeros(world * T * k, dim) for _ in range(world)]
-    dist.all_gather(blocks, torch.from_numpy(send))
-    recv = np.stack([b.numpy().reshape(world, T * k, dim)[rank] for b in blocks])  # recv[o] = rank o's rows for my tokens
+        home, row = ep.recv_row(i, k, T)
+        contrib[home, row] = y[0]
+    # 5. the stores of all ranks land in the homes' blocks: every row has exactly one writer, so the block is the sum
+    blocks = [torch.zeros(world, T * k, dim) for _ in range(world)]
+    dist.all_gather(blocks, torch.from_numpy(contrib))
+    recv = sum(b.numpy()[rank] for b in blocks)
     # 6. each home token's rows in ascending expert id
     out = np.zeros((T, dim), np.float32)
     for t in range(T):
         acc = np.zeros(dim, np.float32)
         for j in np.argsort(ids_home[t], kind="stable"):
-            owner = int(ids_home[t, j]) // (cfg["n_exp"] // world)
-            acc = (acc + recv[owner, t * k + j]).astype(np.float32)
+            acc = (acc + recv[t * k + j]).astype(np.float32)
         out[t] = acc
     outs = [torch.zeros(T, dim) for _ in range(world)]
     dist.all_gather(outs, torch.from_numpy(out))
@@ -96,17 +97,32 @@ def test_sharding_rules():
     assert all(ep.send_slot(i, k, T) // (T * k) == (i // k) // T for i in range(world * T * k))
 
 
-def test_peer_buffer_layout_regions_do_not_overlap():
-    """the exchange buffer every rank maps: flags, two halves of segments, two halves of row blocks - each sender its
-    own piece of each, nothing overlapping, everything 16-byte aligned (the pushing kernels store 16 bytes at a time)"""
-    from libosmos_b200 import ep
-    for world, seg, blk in ((2, 78000 // 16 * 16, 32 * 10 * 2048 * 4), (8, 19600 // 16 * 16, 8 * 10 * 2048 * 4), (16, 4800, 4 * 8 * 512 * 4)):
-        flag, segs, recv, total = ep.peer_layout(world, seg, blk)
-        spans = [(flag[0], world * 4), (flag[1], world * 4)]
-        spans += [(segs[p] + r * seg, seg) for p in range(2) for r in range(world)]
-        spans += [(recv[p] + r * blk, blk) for p in range(2) for r in range(world)]
+def test_recv_rows_are_distinct_per_home():
+    k, T, world = 10, 8, 8
+    seen = set()
+    for i in range(world * T * k):
+        home, row = ep.recv_row(i, k, T)
+        assert home == (i // k) // T and 0 <= row < T * k and (home, row) not in seen
+        seen.add((home, row))
+
+
+def test_exchange_buffer_layout_regions_do_not_overlap():
+    """the exchange buffer every rank maps (ep_layout, host code of the library): two flag arrays, two halves of the
+    token-major dispatch arrays, two halves of the home rows - nothing overlapping, everything 256-byte aligned"""
+    import libosmos_b200
+    from libosmos_b200 import api
+    lib = libosmos_b200.load()
+    for world, n_tok, k, dim in ((1, 64, 10, 2048), (2, 64, 10, 2048), (8, 64, 10, 2048), (16, 32, 8, 7168)):
+        lay = api.EpLayout()
+        assert lib.ep_layout(world, n_tok, k, dim, lay)
+        picks, T = n_tok * k, n_tok // world
+        spans = [(lay.flags_dispatch, world * 4), (lay.flags_combine, world * 4)]
+        for h in range(2):
+            spans += [(lay.ids[h], picks * 4), (lay.weights[h], picks * 4), (lay.q[h], n_tok * dim), (lay.d[h], n_tok * dim // 32 * 4),
+                      (lay.recv[h], T * k * dim * 4)]
         spans.sort()
         for (a, n), (b, _) in zip(spans, spans[1:]):
             assert a + n <= b
-        assert spans[-1][0] + spans[-1][1] <= total and all(a % 16 == 0 for a, _ in spans[2:])
-        assert world * 4 <= 256
+        assert spans[-1][0] + spans[-1][1] <= lay.bytes and all(a % 256 == 0 for a, _ in spans)
+        # the halves are the same distance apart for every array the lane kernels read by parity
+        assert lay.q[1] - lay.q[0] == lay.d[1] - lay.d[0] == lay.ids[1] - lay.ids[0] == lay.weights[1] - lay.weights[0]

@@ -1,6 +1,6 @@
-"""The expert-parallel layer on two GPUs, both transports: each rank checks its output against the CPU oracle's bits
-inside bench.py before timing (it exits non-zero on a mismatch or a wait that ran out). Needs two GPUs; skipped on
-one."""
+"""The expert-parallel layer on two GPUs, both transports: each rank checks all its home tokens' output against the CPU
+checker's bits inside bench.py before timing (it exits non-zero on a mismatch or a wait that ran out). Needs two GPUs;
+skipped on one."""
 import json
 import os
 import subprocess
@@ -25,4 +25,4 @@ def test_two_rank_layer_matches_oracle(transport):
     run = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
     line = json.loads([l for l in run.stdout.splitlines() if l.startswith("{")][-1])
-    assert line["n_gpus"] == 2 and line["value"] > 0 and line["config"]["transport"].startswith(transport)
+    assert line["n_gpus"] == 2 and line["value"] > 0 and line["run"]["transport"].startswith(transport)

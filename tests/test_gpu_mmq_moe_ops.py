@@ -245,6 +245,38 @@ def test_swiglu_and_moe_sum(lib, dev):
             assert same_bits(first, got)  # both paths: the same operations, the same bits
 
 
+def test_swiglu_side_and_swiglu_rows(lib, dev, oracle):
+    """q4x_swiglu's f16 side output and q4x_swiglu_rows: the bits mm_x16 / mm_x16_rows make of q4x_swiglu's F32 output"""
+    rng = synth.rng_for(38)
+    rows, ff = 21, 48
+    g = (rng.standard_normal((rows, ff)) * 3).astype(np.float32)
+    u = rng.standard_normal((rows, ff)).astype(np.float32)
+    g[3, 5], u[3, 5] = 90.0, 1.0e4  # past f16's range: the overflow flag
+    gd, ud = to_dev(g, dev), to_dev(u, dev)
+    y = torch.empty((rows, ff), dtype=torch.float32, device=dev)
+    row0, padded = 16, 48
+    side16 = torch.zeros(padded * ff, dtype=torch.float16, device=dev)
+    over = torch.zeros(1, dtype=torch.int32, device=dev)
+    side = api.Q4xX16(side16.data_ptr(), over.data_ptr(), ff, row0)
+    assert lib.q4x_swiglu(ptr(gd), ptr(ud), rows * ff, ptr(y), side, None)
+    sync()
+    yh = y.cpu().numpy()
+    want16, want_over = oracle.x16_rows(np.concatenate([np.zeros((row0, ff), np.float32), yh, np.zeros((padded - row0 - rows, ff), np.float32)]), padded, ff)
+    assert np.array_equal(side16.cpu().numpy().view(np.uint16), want16) and int(over.item()) == 1 == want_over
+    # the rows form: slots name rows of g / u, -1 a pad slot of zeros
+    idx = np.array([4, -1, 0, 20, 7, 7, -1, 2, 9, 11, 13, 1, 19, 18, 17, 16, 15, -1, 3], dtype=np.int32)
+    slots = 32
+    full = np.concatenate([idx, -np.ones(slots - idx.size, np.int32)])
+    x16 = torch.full((slots * ff,), 5.0, dtype=torch.float16, device=dev)
+    over.zero_()
+    assert lib.q4x_swiglu_rows(ptr(gd), ptr(ud), ff, ptr(to_dev(full, dev)), slots, ptr(x16), ptr(over), None)
+    sync()
+    want16, want_over = oracle.x16_rows(yh, slots, ff, idx=full)
+    assert np.array_equal(x16.cpu().numpy().view(np.uint16), want16) and int(over.item()) == want_over == 1
+    assert not lib.q4x_swiglu_rows(ptr(gd), ptr(ud), 40, ptr(to_dev(full, dev)), slots, ptr(x16), ptr(over), None)
+    assert not lib.q4x_swiglu_rows(ptr(gd), ptr(ud), ff, 0, slots, ptr(x16), ptr(over), None)
+
+
 # ---- lane ops ---------------------------------------------------------------------------------------------------------
 def test_swiglu_lane_and_gathers(lib, dev, oracle):
     rng = synth.rng_for(36)

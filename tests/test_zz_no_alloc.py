@@ -48,8 +48,13 @@ def test_static_scratch_matches_caller_scratch_twice(lib, dev):
         t0, want = _tables(lib, dev, n, n_exp, with_off=True)
         t1, got = _tables(lib, dev, n, n_exp, with_off=False)
         assert lib.q4x_expert_tiles(ptr(ids_d), n, k, n_exp, dim, ff, t0, None)
+        if call == 0:  # the first call on the device looks the array's address up: no allocation belongs to it either
+            assert lib.q4x_expert_tiles_static(ptr(ids_d), n, k, n_exp, dim, ff, t1, None)
+            sync()
+        free_before = torch.cuda.mem_get_info()[0]
         assert lib.q4x_expert_tiles_static(ptr(ids_d), n, k, n_exp, dim, ff, t1, None)
         sync()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         live = want["cnt"].cpu().numpy() > 0
         assert live.any()
         for name, _ in FIELDS:
