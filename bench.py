@@ -359,6 +359,17 @@ def run_ours(args):
     def e2e_drain():
         main.wait_stream(cin), main.wait_stream(cout)
 
+    if args.profile:  # for a profiler: the checked step, then W + K plain steps on the stream, nothing timed or printed
+        for s in range(args.warmup + args.steps):
+            resident(s)
+        torch.cuda.synchronize()
+        if lib.ep_wait_status() or lib.q8_status():
+            raise SystemExit("bench: a bounded wait ran out on rank %d" % rank)
+        layer.close()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     for s in range(args.warmup):
         resident(s), end_to_end(s)
     # the resident step as a user of the C ABI would run a decode loop: captured once per (input, weight copy) pair in
@@ -730,6 +741,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--plain", type=int, default=0, help="--kernel: this many plain launches on 4 copies instead of timing")
     ap.add_argument("--generic", action="store_true", help="--kernel: the generic kernels")
+    ap.add_argument("--profile", action="store_true",
+                    help="for a profiler: the parity-checked step, then warmup + steps plain steps on the stream; nothing is timed")
     args = ap.parse_args()
     if args.kernel:
         return run_kernel(args)

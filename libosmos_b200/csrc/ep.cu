@@ -232,16 +232,12 @@ __global__ void __launch_bounds__(kThreads) combine_wait_kernel(const StepArgs a
   if (threadIdx.x < a.n_ranks && !flag_wait((const uint32_t*) (mine + a.lay.flags_combine) + threadIdx.x, step))
     atomicOr(&g_peer_wait_status, 1u);
   const uint32_t tl = blockIdx.x, k = a.k;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < kWarp) {  // pick j's place in the sum: how many of the token's picks have a lower expert id
     const int32_t* ids = (const int32_t*) (mine + a.lay.ids[half]) + (uint64_t) (a.rank * a.tokens + tl) * k;
-    int32_t e[32];
-    for (uint32_t j = 0; j < k; j++) e[j] = ids[j], order[j] = j;
-    for (uint32_t i = 1; i < k; i++)
-      for (uint32_t c = i; c > 0 && e[c] < e[c - 1]; c--) {
-        const int32_t se = e[c];
-        const uint32_t sj = order[c];
-        e[c] = e[c - 1], e[c - 1] = se, order[c] = order[c - 1], order[c - 1] = sj;
-      }
+    const int32_t e = threadIdx.x < k ? ids[threadIdx.x] : 0x7FFFFFFF;
+    uint32_t place = 0;
+    for (uint32_t j = 0; j < k; j++) place += __shfl_sync(0xFFFFFFFFu, e, (int) j, kWarp) < e;
+    if (threadIdx.x < k) order[place] = threadIdx.x;  // (a token picks an expert once: the places are distinct)
   }
   __syncthreads();
   const float4* recv = (const float4*) (mine + a.lay.recv[half]) + (uint64_t) tl * k * (a.dim / 4);

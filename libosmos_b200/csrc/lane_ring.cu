@@ -155,10 +155,8 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
   pdl_wait();
   pdl_launch_next();
   // (the expert-parallel step: the activations and weights of an odd step lie in the buffers' second halves)
+  // (one register: the addresses are formed where a task loads its tokens, once a task)
   const uint32_t parity = a.ep.step ? (*a.ep.step & 1u) : 0u;
-  const int8_t* const in_q = a.q + parity * a.ep.half_q;
-  const float* const in_d = (const float*) ((const uint8_t*) a.d + parity * a.ep.half_d);
-  const float* const in_scale = (const float*) ((const uint8_t*) a.scale + parity * a.ep.half_scale);
   auto out_row_ptr = [&](uint32_t r) -> float* {
     return a.ep.out_rows ? a.ep.out_rows[r] : a.out + (uint64_t) r * a.out_stride;
   };
@@ -266,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
   // a slot's rows, for NTL live tokens
   // fused: a row's gate and up sums are kept by the lane whose index is the row's place in the task (hg, hu); the
   // task's rows get their activation together at its end, a lane a row
-  auto do_slot = [&](auto live_tag, uint32_t sa, uint32_t row0, uint32_t place0, uint32_t out_row,
+  auto do_slot = [&](auto live_tag, uint32_t sa, uint32_t row0, uint32_t place0, float* const (&orow)[NT],
                      const int (&xq)[NT][NB][8], const float (&xd)[NT][NB], float* hg, float* hu) {
     constexpr int NTL = decltype(live_tag)::value;
     const uint32_t half_bytes = RC * row_bytes;  // fused: the up rows follow the gate rows
@@ -306,7 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
 #pragma unroll
         for (int t = 0; t < NTL; t++) {
           const float v = tree(acc[t]);
-          if (sub == 0) out_row_ptr(out_row + t)[row0 + p + grp] = v;
+          if (sub == 0) orow[t][row0 + p + grp] = v;
         }
       }
     }
@@ -324,12 +322,16 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
     // the task's tokens: the lane's blocks of their int8 rows, their scales, the routed weights
     int xq[NT][NB][8];
     float xd[NT][NB], scale[NT];
+    float* orow[NT];  // where each token's results go: looked up now, used when the task's rows are done
+    const int8_t* const in_q = a.q + parity * a.ep.half_q;
+    const float* const in_d = (const float*) ((const uint8_t*) a.d + parity * a.ep.half_d);
 #pragma unroll
     for (int t = 0; t < NT; t++) {
       const uint32_t r = r0 + ((uint32_t) t < live ? (uint32_t) t : live - 1);
       const uint64_t xr = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
+      orow[t] = out_row_ptr(r);
       scale[t] = 0.0f;
-      if constexpr (FUSED) scale[t] = in_scale[a.win ? a.win[r] : r];
+      if constexpr (FUSED) scale[t] = ((const float*) ((const uint8_t*) a.scale + parity * a.ep.half_scale))[a.win ? a.win[r] : r];
 #pragma unroll
       for (int k = 0; k < NB; k++) {
         int4 lo = make_int4(0, 0, 0, 0), hi = lo;
@@ -355,8 +357,8 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
         break;
       }
       const uint32_t sa = smem_addr(ring + slot * a.slot_bytes);
-      if (NT > 1 && live == (uint32_t) NT) do_slot(I2{}, sa, task_row0 + ss * RC, ss * RC, r0, xq, xd, hg, hu);
-      else do_slot(I1{}, sa, task_row0 + ss * RC, ss * RC, r0, xq, xd, hg, hu);
+      if (NT > 1 && live == (uint32_t) NT) do_slot(I2{}, sa, task_row0 + ss * RC, ss * RC, orow, xq, xd, hg, hu);
+      else do_slot(I1{}, sa, task_row0 + ss * RC, ss * RC, orow, xq, xd, hg, hu);
       __syncwarp();  // every lane is done reading the slot: refill it
       if (lane == 0) {
         fence_async_smem();
@@ -372,7 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
 #pragma unroll
         for (int t = 0; t < NT; t++)
           if ((uint32_t) t < live)
-            out_row_ptr(r0 + t)[task_row0 + lane] = lane_swiglu(hg[t], hu[t], a.lim, scale[t]);
+            orow[t][task_row0 + lane] = lane_swiglu(hg[t], hu[t], a.lim, scale[t]);
       }
     }
   }

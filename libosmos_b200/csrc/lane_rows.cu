@@ -76,9 +76,6 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
   const uint32_t parity = a.ep.step ? (*a.ep.step & 1u) : 0u;
   const int8_t* const in_q = a.q + parity * a.ep.half_q;
   const float* const in_d = (const float*) ((const uint8_t*) a.d + parity * a.ep.half_d);
-  auto out_row_ptr = [&](uint32_t r) -> float* {
-    return a.ep.out_rows ? a.ep.out_rows[r] : a.out + (uint64_t) r * a.out_stride;
-  };
 
   auto live_count = [&](uint32_t m) -> uint32_t {
     const int32_t c = a.cnt[m];
@@ -157,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       }
     }
   };
-  auto do_task = [&](auto live_tag, uint32_t sa, uint32_t row, uint32_t out_row) {
+  auto do_task = [&](auto live_tag, uint32_t sa, uint32_t row, float* const (&orow)[kNT]) {
     constexpr int NTL = decltype(live_tag)::value;
     using A0 = std::integral_constant<int, 0>;
     using A2 = std::integral_constant<int, (SB % 4) ? 2 : 0>;
@@ -171,7 +168,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       for (int o = kBlocks / 2; o > 0; o >>= 1)
 #pragma unroll
         for (int l = 0; l < o; l++) prod[t][l] = __fadd_rn(prod[t][l], prod[t][l + o]);
-      out_row_ptr(out_row + t)[row] = prod[t][0];
+      orow[t][row] = prod[t][0];
     }
   };
 
@@ -186,8 +183,11 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
     const uint32_t r0 = (uint32_t) a.xrow[m] + g * kNT;
     // the task's tokens into the warp's piece of shared memory: 16 bytes a lane a token, then the scales
     __syncwarp();  // (every lane has finished the last task's reads)
+    float* orow[kNT];  // where each token's results go: looked up now, used when the task's rows are done
 #pragma unroll
     for (int t = 0; t < kNT; t++) {
+      const uint32_t ro = r0 + ((uint32_t) t < live ? (uint32_t) t : live - 1);
+      orow[t] = a.ep.out_rows ? a.ep.out_rows[ro] : a.out + (uint64_t) ro * a.out_stride;
       if ((uint32_t) t < live) {
         const uint32_t r = r0 + t;
         const uint64_t xr = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
@@ -202,8 +202,8 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       break;
     }
     const uint32_t sa = smem_addr(ring + slot * a.slot_bytes);
-    if (live == (uint32_t) kNT) do_task(I2{}, sa, row0 + lane, r0);
-    else do_task(I1{}, sa, row0 + lane, r0);
+    if (live == (uint32_t) kNT) do_task(I2{}, sa, row0 + lane, orow);
+    else do_task(I1{}, sa, row0 + lane, orow);
     __syncwarp();  // every lane is done reading the slot: refill it
     if (lane == 0) {
       fence_async_smem();

@@ -18,8 +18,9 @@ from libosmos_b200 import api, ep, runner, workloads
 
 pytestmark = pytest.mark.gpu
 
-SMALL = dict(name="moe_small", type="IQ3_XXS", n_exp=16, k=4, n_tok=24, dim=512, ff=256, sigma=0.005, lim=1.0e30)
-WIDE = dict(name="moe_wide", type="IQ3_XXS", n_exp=32, k=6, n_tok=16, dim=2048, ff=512, sigma=0.005, lim=1.0e30)
+# (the fused step runs on the warp-ring / thread-a-row kernels only: rows of 512 columns or more)
+SMALL = dict(name="moe_small", type="IQ3_XXS", n_exp=16, k=4, n_tok=24, dim=512, ff=512, sigma=0.005, lim=1.0e30)
+WIDE = dict(name="moe_wide", type="IQ1_M", n_exp=32, k=6, n_tok=16, dim=2048, ff=1024, sigma=0.005, lim=7.0)
 
 
 def _bits(t):
