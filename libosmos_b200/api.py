@@ -44,6 +44,29 @@ class LaneScratch(C.Structure):
                 ("tab", LaneTables)]
 
 
+class LaneScratchF32(C.Structure):
+    _fields_ = [("max_tok", U32), ("xg", P), ("wg", P), ("ga", P), ("up", P), ("hh", P), ("ye", P), ("tab", LaneTables)]
+
+
+class SharedExpert(C.Structure):
+    _fields_ = [("type_gu", U32), ("type_down", U32), ("dim", U32), ("ff", U32), ("lim", F32), ("gate", P), ("up", P), ("down", P)]
+
+
+class SharedScratch(C.Structure):
+    _fields_ = [("max_tok", U32), ("g", P), ("u", P), ("h", P), ("x16", P), ("overflow", P)]
+
+
+class Q4xMoeLayer(C.Structure):
+    _fields_ = [("type", U32 * 3), ("dim", U32), ("ff", U32), ("n_exp", U32), ("k", U32), ("base", P * 3), ("bytes", U64 * 3),
+                ("tab", P * 3)]
+
+
+class Q4xMoeScratch(C.Structure):
+    _fields_ = [("max_tok", U32), ("bounds", Q4xExpertBounds), ("ids", P), ("rows", P), ("w", P), ("ptr", P), ("cnt", P),
+                ("gidx", P), ("hidx", P), ("where", P), ("off", P), ("xg", P), ("yg", P), ("xd", P), ("yd", P), ("xe16", P),
+                ("ga", P), ("up", P), ("y", P), ("overflow", P)]
+
+
 class EpSegment(C.Structure):
     _fields_ = [("ids", U64), ("weights", U64), ("q", U64), ("d", U64), ("bytes", U64)]
 
@@ -140,6 +163,16 @@ SIGNATURES = {
     "lane_scratch_bytes": (U64, [C.POINTER(LaneLayer), U32]),
     "lane_scratch_bind": (B, [C.POINTER(LaneLayer), U32, P, U64, C.POINTER(LaneScratch)]),
     "lane_ffn": (B, [C.POINTER(LaneLayer), C.POINTER(LaneScratch), P, P, P, U32, P, P, P]),
+    # ffn.h
+    "lane_f32_scratch_bytes": (U64, [C.POINTER(LaneLayer), U32]),
+    "lane_f32_scratch_bind": (B, [C.POINTER(LaneLayer), U32, P, U64, C.POINTER(LaneScratchF32)]),
+    "lane_ffn_f32": (B, [C.POINTER(LaneLayer), C.POINTER(LaneScratchF32), P, P, P, U32, P, P, P]),
+    "shared_scratch_bytes": (U64, [C.POINTER(SharedExpert), U32]),
+    "shared_scratch_bind": (B, [C.POINTER(SharedExpert), U32, P, U64, C.POINTER(SharedScratch)]),
+    "shared_ffn": (B, [C.POINTER(SharedExpert), C.POINTER(SharedScratch), P, U32, P, P]),
+    "q4x_moe_scratch_bytes": (U64, [C.POINTER(Q4xMoeLayer), U32]),
+    "q4x_moe_scratch_bind": (B, [C.POINTER(Q4xMoeLayer), U32, P, U64, C.POINTER(Q4xMoeScratch)]),
+    "q4x_moe": (B, [C.POINTER(Q4xMoeLayer), C.POINTER(Q4xMoeScratch), P, P, P, P, U32, P, P]),
     # ep.h
     "ep_segment": (None, [U32, U32, U32, C.POINTER(EpSegment)]),
     "ep_unpack": (B, [P, U32, U32, U32, U32, P, P, P, P, P]),

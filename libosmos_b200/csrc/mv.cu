@@ -138,6 +138,11 @@ template <uint32_t T>
 bool group(const void* const* w, uint32_t n, uint32_t rows, uint32_t cols, const float* x, uint32_t x_mat,
            uint32_t x_div, float* y, cudaStream_t s) {
   if (!shape_ok<T>(cols) || x_mat % kChunk || !x_div) return false;
+  if (g_use_staged) {  // the staged kernel when it takes the shape: the same bits
+    mvs::Request r{nullptr, x, y, rows, cols, cols, rows, 1};
+    r.wt = w, r.n_entries = n, r.x_mat = x_mat, r.x_div = x_div;
+    if (const int st = mvs::try_launch(T, r, s)) return st > 0;
+  }
   MvArgs a{};
   a.wt = (const uint8_t* const*) w, a.x = x, a.y = y, a.rows = rows, a.cols = cols, a.xs = cols, a.ys = rows;
   a.n_tok = 1, a.x_mat = x_mat, a.x_div = x_div;
@@ -148,6 +153,11 @@ template <uint32_t T>
 bool group_tok(const void* const* w, const int32_t* cnt, const int32_t* xrow, uint32_t n, uint32_t max_cnt,
                uint32_t rows, uint32_t cols, const float* x, uint32_t xs, float* y, uint32_t ys, cudaStream_t s) {
   if (!shape_ok<T>(cols) || xs < cols || xs % kChunk) return false;
+  if (g_use_staged) {  // the staged kernel when it takes the shape: the same bits
+    mvs::Request r{nullptr, x, y, rows, cols, xs, ys, max_cnt};
+    r.wt = w, r.n_entries = n, r.cnt = cnt, r.xrow = xrow;
+    if (const int st = mvs::try_launch(T, r, s)) return st > 0;
+  }
   MvArgs a{};
   a.wt = (const uint8_t* const*) w, a.cnt = cnt, a.xrow = xrow, a.x = x, a.y = y;
   a.rows = rows, a.cols = cols, a.xs = xs, a.ys = ys, a.n_tok = max_cnt;

@@ -38,7 +38,33 @@ struct Args {
   uint32_t rows, cols, xs, ys, n_tok;
   uint32_t slots, slot_bytes, ring_off, units;
   uint32_t* status;
+  // grouped forms: blockIdx.y is the entry
+  const uint8_t* const* wt;
+  const int32_t *cnt, *xrow;
+  uint32_t x_mat, x_div, cnt_lo, cnt_hi;  // an entry of this launch has cnt_lo .. cnt_hi tokens (the others belong to another
+                                          // launch); of more than NT, the first NT are served
 };
+
+// A grouped launch's block finds its entry: false when the entry is not this launch's (nothing read or written).
+// Called after pdl_wait: the tables may be the output of the kernel ahead.
+template <int NT>
+__device__ __forceinline__ bool entry_of_block(const Args& a, const uint8_t*& w, const float*& x, float*& y, uint32_t& n_tok) {
+  const uint32_t m = blockIdx.y;
+  if (a.cnt) {
+    const int32_t c = a.cnt[m];
+    if (c < (int32_t) a.cnt_lo || c > (int32_t) a.cnt_hi) return false;
+    const uint64_t r0 = (uint64_t) a.xrow[m];
+    x = a.x + r0 * a.xs, y = a.y + r0 * a.ys, n_tok = (uint32_t) c < (uint32_t) NT ? (uint32_t) c : (uint32_t) NT;
+  } else {
+    x = a.x + (uint64_t) (m / a.x_div) * a.x_mat, y = a.y + (uint64_t) m * a.rows, n_tok = 1;
+  }
+  w = a.wt[m];
+  if ((uintptr_t) w & 15u) {  // such a matrix cannot be copied in bulk: reported, its rows left alone
+    if (threadIdx.x == 0) atomicOr(a.status, 2u);
+    return false;
+  }
+  return true;
+}
 
 // Small integers reach F32 without a conversion instruction: byte j of `bytes` (a value n < 256) placed in bits 8 .. 15
 // of 0x47000000 is the F32 32768 + n, one byte-permute.
@@ -177,7 +203,7 @@ template <> struct LanePlan<QTYPE_MXFP4> {
   }
 };
 
-template <uint32_t T, int NT, int RW>
+template <uint32_t T, int NT, int RW, bool GROUP>
 __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
@@ -190,6 +216,15 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
   const uint32_t row_bytes = a.cols / Fmt<T>::values * Fmt<T>::bytes;
   const uint32_t S = a.slots;
   uint8_t* ring = smem + a.ring_off + warp * S * a.slot_bytes;
+  const uint8_t* mat = a.w;
+  const float* xin = a.x;
+  float* yout = a.y;
+  uint32_t n_tok = a.n_tok;
+  if constexpr (GROUP) {
+    pdl_wait();  // (a dependent launch: the tables and x may be the output of the kernel ahead)
+    pdl_launch_next();
+    if (!entry_of_block<NT>(a, mat, xin, yout, n_tok)) return;  // (the whole block)
+  }
 
   // this block's units (RW rows each), dealt to its warps round-robin
   const uint32_t u_lo = (uint32_t) ((uint64_t) blockIdx.x * a.units / gridDim.x);
@@ -200,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
     const uint32_t r0 = u * RW, nrows = a.rows - r0 < (uint32_t) RW ? a.rows - r0 : (uint32_t) RW;
     const uint32_t slot = i % S, bytes = nrows * row_bytes;
     bar_expect(&full[warp][slot], bytes);
-    bulk_load(ring + slot * a.slot_bytes, a.w + (uint64_t) r0 * row_bytes, bytes, &full[warp][slot]);
+    bulk_load(ring + slot * a.slot_bytes, mat + (uint64_t) r0 * row_bytes, bytes, &full[warp][slot]);
   };
   if (lane == 0) {
     for (uint32_t s = 0; s < S; s++) bar_init(&full[warp][s], 1);
@@ -208,17 +243,19 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
     for (uint32_t i = 0; i < S; i++) issue(i);
   }
 
-  pdl_wait();  // (a dependent launch: x may be the output of the kernel ahead; the weight copies above are not)
-  pdl_launch_next();
+  if constexpr (!GROUP) {
+    pdl_wait();  // (a dependent launch: x may be the output of the kernel ahead; the weight copies above are not)
+    pdl_launch_next();
+  }
   // the tokens' x (the live ones) and the codebooks, while the first copies fly
-  const uint32_t live = a.n_tok < (uint32_t) NT ? a.n_tok : (uint32_t) NT;
+  const uint32_t live = n_tok < (uint32_t) NT ? n_tok : (uint32_t) NT;
   {
     const uint32_t per = a.cols / 4;
     // a token's chunks as two planes - every chunk's first four values, then every chunk's last four - so that a
     // warp's 16-byte reads of one plane are contiguous (chunk after chunk 32 bytes apart, they would pair up on banks)
     for (uint32_t i = tid; i < live * per; i += kThreads) {
       const uint32_t t = i / per, j = i - t * per;
-      ((float4*) smem)[t * per + (j & 1u) * (per / 2) + (j >> 1)] = __ldg((const float4*) (a.x + (uint64_t) t * a.xs) + j);
+      ((float4*) smem)[t * per + (j & 1u) * (per / 2) + (j >> 1)] = __ldg((const float4*) (xin + (uint64_t) t * a.xs) + j);
     }
   }
   const Grids g = stage_grids<T>(tables);
@@ -277,14 +314,14 @@ __global__ void __launch_bounds__(kThreads, 1) mv_staged_kernel(const Args a) {
 #pragma unroll
       for (int t = 0; t < NT; t++) {
         const float s = xor_tree<kWarp>(acc[q][t]);
-        if (lane == 0 && r0 + q < a.rows && (uint32_t) t < live) a.y[(uint64_t) t * a.ys + r0 + q] = s;
+        if (lane == 0 && r0 + q < a.rows && (uint32_t) t < live) yout[(uint64_t) t * a.ys + r0 + q] = s;
       }
   }
 }
 
 constexpr int kRegIters = 8;  // 256-value stretches of a row whose x a lane can keep in registers (cols <= 2048)
 
-template <uint32_t T, int RW>
+template <uint32_t T, int RW, bool GROUP>
 __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
@@ -297,6 +334,15 @@ __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
   const uint32_t row_bytes = a.cols / Fmt<T>::values * Fmt<T>::bytes;
   const uint32_t S = a.slots, ni = a.cols / 256;
   uint8_t* ring = smem + warp * S * a.slot_bytes;
+  const uint8_t* mat = a.w;
+  const float* xin = a.x;
+  float* yout = a.y;
+  if constexpr (GROUP) {
+    pdl_wait();  // (a dependent launch: the tables and x may be the output of the kernel ahead)
+    pdl_launch_next();
+    uint32_t n_tok;
+    if (!entry_of_block<1>(a, mat, xin, yout, n_tok)) return;  // (the whole block)
+  }
 
   const uint32_t u_lo = (uint32_t) ((uint64_t) blockIdx.x * a.units / gridDim.x);
   const uint32_t u_hi = (uint32_t) ((uint64_t) (blockIdx.x + 1) * a.units / gridDim.x);
@@ -306,22 +352,24 @@ __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
     const uint32_t r0 = u * RW, nrows = a.rows - r0 < (uint32_t) RW ? a.rows - r0 : (uint32_t) RW;
     const uint32_t slot = i % S, bytes = nrows * row_bytes;
     bar_expect(&full[warp][slot], bytes);
-    bulk_load(ring + slot * a.slot_bytes, a.w + (uint64_t) r0 * row_bytes, bytes, &full[warp][slot]);
+    bulk_load(ring + slot * a.slot_bytes, mat + (uint64_t) r0 * row_bytes, bytes, &full[warp][slot]);
   };
   if (lane == 0) {
     for (uint32_t s = 0; s < S; s++) bar_init(&full[warp][s], 1);
     bar_init_fence();
     for (uint32_t i = 0; i < S; i++) issue(i);
   }
-  pdl_wait();  // (a dependent launch: x may be the output of the kernel ahead; the weight copies above are not)
-  pdl_launch_next();
+  if constexpr (!GROUP) {
+    pdl_wait();  // (a dependent launch: x may be the output of the kernel ahead; the weight copies above are not)
+    pdl_launch_next();
+  }
   // the lane's x: chunk lane + 32 it of every stretch
   float xr[kRegIters][kChunk];
 #pragma unroll
   for (int it = 0; it < kRegIters; it++) {
     float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
     if ((uint32_t) it < ni) {
-      const float4* xp = (const float4*) (a.x + (lane + 32u * it) * kChunk);
+      const float4* xp = (const float4*) (xin + (lane + 32u * it) * kChunk);
       lo = __ldg(xp), hi = __ldg(xp + 1);
     }
     xr[it][0] = lo.x, xr[it][1] = lo.y, xr[it][2] = lo.z, xr[it][3] = lo.w;
@@ -391,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) mv_regx_kernel(const Args a) {
 #pragma unroll
     for (int q = 0; q < RW; q++) {
       const float s = xor_tree<kWarp>(acc[q]);
-      if (lane == 0 && r0 + q < a.rows) a.y[r0 + q] = s;
+      if (lane == 0 && r0 + q < a.rows) yout[r0 + q] = s;
     }
   }
 }
@@ -415,24 +463,39 @@ const Device* device_info() {
   return &devs[d];
 }
 
-template <uint32_t T, int NT, int RW, bool REGX>
-int launch(const Request& r, const Device* dev, uint32_t slots, cudaStream_t s) {
+template <uint32_t T, int NT, int RW, bool REGX, bool GROUP>
+int launch(const Request& r, const Device* dev, uint32_t slots, uint32_t cnt_lo, cudaStream_t s, uint32_t cnt_hi = (uint32_t) NT) {
   const uint32_t row_bytes = r.cols / Fmt<T>::values * Fmt<T>::bytes;
   Args a{};
   a.w = (const uint8_t*) r.w, a.x = r.x, a.y = r.y, a.rows = r.rows, a.cols = r.cols, a.xs = r.xs, a.ys = r.ys;
-  a.n_tok = r.n_tok, a.slots = slots, a.slot_bytes = RW * row_bytes;
-  a.ring_off = REGX ? 0u : (r.n_tok * r.cols * 4u + 127u) & ~127u;
+  a.n_tok = GROUP ? (uint32_t) NT : r.n_tok, a.slots = slots, a.slot_bytes = RW * row_bytes;
+  a.ring_off = REGX ? 0u : (a.n_tok * r.cols * 4u + 127u) & ~127u;
   a.units = (r.rows + RW - 1) / RW;
   a.status = dev->status;
+  a.wt = (const uint8_t* const*) r.wt, a.cnt = r.cnt, a.xrow = r.xrow, a.x_mat = r.x_mat, a.x_div = r.x_div, a.cnt_lo = cnt_lo, a.cnt_hi = cnt_hi;
   const uint32_t total = a.ring_off + kWarps * slots * a.slot_bytes + 16u;  // + the window's read past a last block
   static bool sized[64] = {};  // (one record a template instance, one flag a device)
   void (*kernel)(const Args);
-  if constexpr (REGX) kernel = mv_regx_kernel<T, RW>;
-  else kernel = mv_staged_kernel<T, NT, RW>;
+  if constexpr (REGX) kernel = mv_regx_kernel<T, RW, GROUP>;
+  else kernel = mv_staged_kernel<T, NT, RW, GROUP>;
   if (!allow_dynamic_smem(kernel, (int) kSmemLimit<T>, sized)) return 0;
-  uint32_t grid = (uint32_t) dev->sms;
-  if (a.units < grid) grid = a.units;
-  return launch_dependent(kernel, dim3(grid), dim3(kThreads), total, s, a) == cudaSuccess ? 1 : -1;
+  dim3 grid((uint32_t) dev->sms);
+  if (a.units < grid.x) grid.x = a.units;
+  if constexpr (GROUP) {  // an entry's rows over a few blocks: about four units a warp each, at most eight blocks
+    const uint32_t per = a.units / (4u * kWarps);
+    grid.x = per < 1u ? 1u : per > 8u ? 8u : per, grid.y = r.n_entries;
+  }
+  return launch_dependent(kernel, grid, dim3(kThreads), total, s, a) == cudaSuccess ? 1 : -1;
+}
+
+// as deep a ring as fits beside n_tok tokens' x (0 tokens: x in registers)
+template <uint32_t T>
+uint32_t slots_for(uint32_t rw, uint32_t x_tokens, uint32_t cols) {
+  const uint32_t row_bytes = cols / Fmt<T>::values * Fmt<T>::bytes, budget = kSmemLimit<T> - 16u;
+  const uint32_t x_bytes = (x_tokens * cols * 4u + 127u) & ~127u;
+  if (x_bytes >= budget) return 0;
+  const uint32_t n = (budget - x_bytes) / (kWarps * rw * row_bytes);
+  return n > (uint32_t) kMaxSlots ? (uint32_t) kMaxSlots : n;
 }
 
 template <uint32_t T>
@@ -443,30 +506,54 @@ int by_shape(const Request& r, cudaStream_t s) {
   if (r.cols % 256 || row_bytes % 16u) return 0;  // whole 256-value stretches; a row's bytes are a bulk copy's
   if (r.n_tok > 8) return 0;
   const bool regx = r.n_tok == 1 && r.cols <= 256u * kRegIters;
-  const uint32_t budget = kSmemLimit<T> - 16u;
-  const uint32_t x_bytes = regx ? 0u : (r.n_tok * r.cols * 4u + 127u) & ~127u;
-  if (x_bytes >= budget) return 0;
-  auto slots_for = [&](uint32_t rw) -> uint32_t {  // as deep a ring as fits
-    const uint32_t n = (budget - x_bytes) / (kWarps * rw * row_bytes);
-    return n > (uint32_t) kMaxSlots ? (uint32_t) kMaxSlots : n;
-  };
   // two rows a unit (the decode of one overlaps the other's chain; with x in shared memory they share its loads)
   // when the matrix has rows to spare and the ring still has three slots
-  const bool pair = (uint64_t) r.rows >= 8ull * kWarps * dev->sms && slots_for(2) >= 3;
-  const uint32_t slots = slots_for(pair ? 2 : 1);
+  const uint32_t xt = regx ? 0u : r.n_tok;
+  const bool pair = (uint64_t) r.rows >= 8ull * kWarps * dev->sms && slots_for<T>(2, xt, r.cols) >= 3;
+  const uint32_t slots = slots_for<T>(pair ? 2 : 1, xt, r.cols);
   if (slots < 2) return 0;
-  if (regx) return pair ? launch<T, 1, 2, true>(r, dev, slots, s) : launch<T, 1, 1, true>(r, dev, slots, s);
-  if (r.n_tok <= 1) return pair ? launch<T, 1, 2, false>(r, dev, slots, s) : launch<T, 1, 1, false>(r, dev, slots, s);
-  if (r.n_tok <= 2) return pair ? launch<T, 2, 2, false>(r, dev, slots, s) : launch<T, 2, 1, false>(r, dev, slots, s);
+  if (regx) return pair ? launch<T, 1, 2, true, false>(r, dev, slots, 0, s) : launch<T, 1, 1, true, false>(r, dev, slots, 0, s);
+  if (r.n_tok <= 1) return pair ? launch<T, 1, 2, false, false>(r, dev, slots, 0, s) : launch<T, 1, 1, false, false>(r, dev, slots, 0, s);
+  if (r.n_tok <= 2) return pair ? launch<T, 2, 2, false, false>(r, dev, slots, 0, s) : launch<T, 2, 1, false, false>(r, dev, slots, 0, s);
   // 3 .. 8 tokens: a chunk is decoded once and meets every token's values (four or eight chains a row)
-  if (r.n_tok <= 4) return pair ? launch<T, 4, 2, false>(r, dev, slots, s) : launch<T, 4, 1, false>(r, dev, slots, s);
-  return pair ? launch<T, 8, 2, false>(r, dev, slots, s) : launch<T, 8, 1, false>(r, dev, slots, s);
+  if (r.n_tok <= 4) return pair ? launch<T, 4, 2, false, false>(r, dev, slots, 0, s) : launch<T, 4, 1, false, false>(r, dev, slots, 0, s);
+  return pair ? launch<T, 8, 2, false, false>(r, dev, slots, 0, s) : launch<T, 8, 1, false, false>(r, dev, slots, 0, s);
+}
+
+// The grouped forms: a block an (entry, part of its rows). By token, the entries are served in classes of their token
+// count - 1, 2, 3 .. 4, 5 .. 8 - a launch a class up to the call's max_cnt, each over all entries: a block whose entry
+// belongs to another class leaves at once, so an entry of one token never pays for eight chains.
+template <uint32_t T>
+int grouped(const Request& r, cudaStream_t s) {
+  const Device* dev = device_info();
+  if (!dev) return 0;
+  const uint32_t row_bytes = r.cols / Fmt<T>::values * Fmt<T>::bytes;
+  if (r.cols % 256 || row_bytes % 16u || !r.n_entries || r.n_entries > 65535u) return 0;
+  const uint32_t most = r.cnt ? r.n_tok : 1u;
+  // every class this call needs must fit, or none is taken (the generic kernel then serves the whole call)
+  const bool regx = r.cols <= 256u * kRegIters;
+  const uint32_t top = most <= 1 ? 1u : most <= 2 ? 2u : most <= 4 ? 4u : 8u;
+  if (slots_for<T>(1, top == 1 && regx ? 0u : top, r.cols) < 2) return 0;
+  // (the last class also takes the entries whose count is past the call's max_cnt: their first max_cnt tokens)
+  constexpr uint32_t kAny = 0x7FFFFFFFu;
+  int st = regx ? launch<T, 1, 1, true, true>(r, dev, slots_for<T>(1, 0, r.cols), 1, s, top == 1 ? kAny : 1u)
+                : launch<T, 1, 1, false, true>(r, dev, slots_for<T>(1, 1, r.cols), 1, s, top == 1 ? kAny : 1u);
+  if (st > 0 && top >= 2) st = launch<T, 2, 1, false, true>(r, dev, slots_for<T>(1, 2, r.cols), 2, s, top == 2 ? kAny : 2u);
+  if (st > 0 && top >= 4) st = launch<T, 4, 1, false, true>(r, dev, slots_for<T>(1, 4, r.cols), 3, s, top == 4 ? kAny : 4u);
+  if (st > 0 && top >= 8) st = launch<T, 8, 1, false, true>(r, dev, slots_for<T>(1, 8, r.cols), 5, s, kAny);
+  return st;
 }
 
 }  // namespace
 
 int try_launch(uint32_t type, const Request& r, void* stream) {
   if (!r.rows || !r.n_tok || r.n_tok > 8 || r.cols % 8) return 0;
+  if (r.wt) {  // grouped: every entry's x row starts on 16 bytes when the first does and the strides are whole words of 16
+    if (((uintptr_t) r.x & 15u) || r.xs % 4 || r.x_mat % 4) return 0;
+#define CASE(T) return grouped<T>(r, (cudaStream_t) stream);
+    OSMOS_SWITCH_QUANT(type, CASE, return 0)
+#undef CASE
+  }
   if (((uintptr_t) r.w | (uintptr_t) r.x) & 15u) return 0;
   if (r.n_tok > 1 && r.xs % 4) return 0;
 #define CASE(T) return by_shape<T>(r, (cudaStream_t) stream);

@@ -175,3 +175,57 @@ def test_mv_group_and_group_tok(lib, dev, oracle, name):
             r = xrow[m] + t
             want[r, :rows] = oracle.mv_rows(tid, mats[m], rows, cols, np.ascontiguousarray(xx[r:r + 1, :cols]))[0]
     assert same_bits(got, want)
+
+
+@pytest.mark.parametrize("name,rows,cols", [("MXFP4", 96, 4096), ("MXFP4", 64, 1536), ("Q4_K", 80, 2048), ("IQ1_M", 48, 7168),
+                                             ("Q8_0", 40, 1024), ("IQ3_XXS", 32, 2048), ("Q4_0", 33, 2048)])
+def test_mv_grouped_on_the_staged_kernel(lib, dev, oracle, name, rows, cols):
+    """mv_group_tok / mv_group where the staged kernel takes the shape (whole 256-value stretches, rows of whole 16 bytes):
+    entries of every count 0 .. 8 in their count classes, the generic kernel's bits and the oracle's"""
+    tid = TYPES[name]
+    rng = synth.rng_for(15, tid, rows)
+    cnt = np.array([1, 3, 0, 8, 2, 1, 5, 4, 7, 1, 6, 2], dtype=np.int32)
+    n_mat = cnt.size
+    mats = [synth.random_tensor(tid, rows, cols, rng) for _ in range(n_mat)]
+    nbytes = mats[0].size
+    assert nbytes % 16 == 0
+    pool = to_dev(np.concatenate(mats), dev)
+    table = pointer_table(pool, [m * nbytes for m in range(n_mat)], dev)
+    xrow = np.concatenate([[0], np.cumsum(cnt)[:-1]]).astype(np.int32)
+    total, xs, ys = int(cnt.sum()), cols + 8, rows + 4
+    xx = rng.standard_normal((total, xs)).astype(np.float32)
+    xd, cd, rd = to_dev(xx, dev), to_dev(cnt, dev), to_dev(xrow, dev)
+    outs = []
+    for staged in (1, 0):
+        lib.mv_set_staged(staged)
+        yy = torch.full((total, ys), -5.0, dtype=torch.float32, device=dev)
+        assert lib.mv_group_tok(tid, ptr(table), ptr(cd), ptr(rd), n_mat, 8, rows, cols, ptr(xd), xs, ptr(yy), ys, None)
+        sync()
+        outs.append(yy.cpu().numpy())
+    lib.mv_set_staged(1)
+    assert lib.mv_status() == 0
+    assert same_bits(outs[0], outs[1])
+    want = np.full_like(outs[0], -5.0)
+    for m in range(n_mat):
+        if cnt[m]:
+            r0 = xrow[m]
+            want[r0:r0 + cnt[m], :rows] = oracle.mv_rows(tid, mats[m], rows, cols, np.ascontiguousarray(xx[r0:r0 + cnt[m], :cols]))
+    assert same_bits(outs[0], want)
+    # a call whose max_cnt is below an entry's count serves the entry's first max_cnt tokens, as the generic kernel does
+    for staged in (1, 0):
+        lib.mv_set_staged(staged)
+        yy = torch.full((total, ys), -5.0, dtype=torch.float32, device=dev)
+        assert lib.mv_group_tok(tid, ptr(table), ptr(cd), ptr(rd), n_mat, 2, rows, cols, ptr(xd), xs, ptr(yy), ys, None)
+        sync()
+        outs.append(yy.cpu().numpy())
+    lib.mv_set_staged(1)
+    assert same_bits(outs[2], outs[3])
+    # mv_group: matrix m on vector m / 3
+    x = rng.standard_normal((4, cols)).astype(np.float32)
+    y = torch.empty((n_mat, rows), dtype=torch.float32, device=dev)
+    assert lib.mv_group(tid, ptr(table), n_mat, rows, cols, ptr(to_dev(x, dev)), cols, 3, ptr(y), None)
+    sync()
+    got = y.cpu().numpy()
+    for m in range(n_mat):
+        assert same_bits(got[m], oracle.mv_rows(tid, mats[m], rows, cols, x[m // 3:m // 3 + 1])[0])
+    assert lib.mv_status() == 0
