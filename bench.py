@@ -105,8 +105,16 @@ def dist_env():
 
 def workload_config(cfg):
     """the workload's description: the same keys in both arms"""
-    return {"workload": cfg["name"], "tokens": cfg["n_tok"], "experts": cfg["n_exp"], "top_k": cfg["k"],
-            "hidden": cfg["dim"], "expert_ff": cfg["ff"], "format": cfg["type"]}
+    c = {"workload": cfg["name"], "tokens": cfg["n_tok"], "experts": cfg["n_exp"], "top_k": cfg["k"],
+         "hidden": cfg["dim"], "expert_ff": cfg["ff"], "format": cfg["type"]}
+    if cfg.get("router"):
+        c["router"] = cfg["router"]
+    if cfg.get("shared"):
+        c["shared_expert"] = "%s, ff %d" % (cfg["shared"]["type"], cfg["shared"]["ff"])
+    if cfg.get("path"):
+        c["path"] = {"f32_lane": "F32 activations, an expert read once for its tokens (mv_group_tok)",
+                     "f16_group": "f16 activations, grouped tensor-core product (mm_group)"}[cfg["path"]]
+    return c
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -131,7 +139,7 @@ def lane_rows_of(cfg, x, ids, wts):
 def cpu_step_inputs(cfg, step):
     from libosmos_b200 import workloads
     x, logits = workloads.moe_inputs_host(cfg, step)
-    ids, wts = workloads.softmax_topk(logits, cfg["k"])
+    ids, wts = workloads.route_host(cfg, logits)
     return lane_rows_of(cfg, x, ids, wts)
 
 
@@ -197,6 +205,36 @@ class CpuArm:
             out[tok[r]] = (out[tok[r]] + y[r]).astype(np.float32)
         return out
 
+    def shared_seconds(self):
+        """a step's shared expert on this CPU: the scalar restatement's F32 matvec (not reference code: the reference has
+        no CPU path for the shared expert's type), its rows split over as many threads as the lane uses, timed on one
+        token and scaled to the step's tokens"""
+        cfg = self.cfg
+        if not cfg.get("shared"):
+            return 0.0
+        from concurrent.futures import ThreadPoolExecutor
+
+        from libosmos_b200 import synth, workloads
+        from oracle.oracle import Oracle
+        sh, orc = cfg["shared"], Oracle()
+        tid = synth.TYPE_ID[sh["type"]]
+        w = workloads.shared_expert_host(cfg)
+        x = np.ones((1, cfg["dim"]), np.float32)
+
+        def product(mat, rows, cols, v, pool):
+            rb = mat.size // rows
+            cuts = np.linspace(0, rows, self.threads + 1).astype(int)
+            parts = pool.map(lambda i: orc.mv_rows(tid, mat[cuts[i] * rb:cuts[i + 1] * rb], int(cuts[i + 1] - cuts[i]), cols, v),
+                             [i for i in range(self.threads) if cuts[i + 1] > cuts[i]])
+            return np.concatenate(list(parts), axis=1)
+
+        with ThreadPoolExecutor(self.threads) as pool:
+            t0 = time.perf_counter()
+            g = product(w[0], sh["ff"], cfg["dim"], x, pool)
+            product(w[1], sh["ff"], cfg["dim"], x, pool)
+            product(w[2], cfg["dim"], sh["ff"], g, pool)
+            return (time.perf_counter() - t0) * cfg["n_tok"]
+
     def timed(self, steps, warmup, first_step=0):
         """tokens/s over `steps` steps after `warmup`; each step's job is built outside its clock"""
         cfg, limit = self.cfg, (None if self.kind == "reference" else 24)
@@ -208,7 +246,27 @@ class CpuArm:
                 times.append(dt), (rows := rows + done)
         sample = ("%d full steps of %d tokens (%d expert rows each) after %d warm-up" % (steps, cfg["n_tok"], cfg["n_tok"] * cfg["k"], warmup)
                   if limit is None else "the first %d expert rows of %d steps, scaled to tokens" % (limit, steps))
-        return rows / cfg["k"] / sum(times), 1e3 * sum(times) / len(times), sample
+        shared = self.shared_seconds()
+        if shared:
+            sample += "; + the shared expert by the scalar restatement on the same threads (one token timed, scaled to the step: %.1f ms a step)" % (1e3 * shared)
+        per_step = sum(times) / len(times) * (cfg["n_tok"] * cfg["k"] / (rows / len(times))) + shared
+        return cfg["n_tok"] / per_step, 1e3 * per_step, sample
+
+
+def port_tokens_per_s(cfg, host, per):
+    """the CPU figure of a workload the reference has no CPU path for (its experts' type is not a CPU lane type): this
+    repository's scalar restatement of the F32 matvec on ONE pick's three matrices, scaled to the step's picks"""
+    from libosmos_b200 import synth
+    from oracle.oracle import Oracle
+    orc, tid = Oracle(), synth.TYPE_ID[cfg["type"]]
+    x = np.ones((1, cfg["dim"]), np.float32)
+    p = [host[m][:per[m]] for m in range(3)]
+    t0 = time.perf_counter()
+    g = orc.mv_rows(tid, p[0], cfg["ff"], cfg["dim"], x)
+    orc.mv_rows(tid, p[1], cfg["ff"], cfg["dim"], x)
+    orc.mv_rows(tid, p[2], cfg["dim"], cfg["ff"], g)
+    dt = (time.perf_counter() - t0) * cfg["n_tok"] * cfg["k"]
+    return cfg["n_tok"] / dt, 1e3 * dt, "one pick's gate, up and down by the scalar restatement (1 thread), scaled to the step's %d picks" % (cfg["n_tok"] * cfg["k"])
 
 
 def run_reference(args):
@@ -217,6 +275,16 @@ def run_reference(args):
     if rank != 0:
         return
     cfg = workloads.BY_NAME[args.workload]
+    if cfg.get("path"):
+        per = workloads.moe_expert_bytes(cfg)
+        tok_s, ms, sample = port_tokens_per_s(cfg, workloads.moe_layer_host(cfg, expert_range=(0, 1)), per)
+        line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic", "config": workload_config(cfg),
+                "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample},
+                "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
     host = workloads.moe_layer_host(cfg)
     arm = CpuArm(cfg, host)
     tok_s, ms, sample = arm.timed(args.steps, args.warmup)
@@ -252,10 +320,15 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     lib = libosmos_b200.load()
     cfg = workloads.BY_NAME[args.workload]
+    if cfg.get("path"):  # the experts over F32 activations, or through the grouped f16 product: one GPU
+        return run_f32_or_f16(args, cfg, lib, dev)
     n_tok, dim, k = cfg["n_tok"], cfg["dim"], cfg["k"]
+    if n_tok % world:
+        raise SystemExit("bench: %d tokens do not split over %d ranks" % (n_tok, world))
     host = workloads.moe_layer_host(cfg)
     per = workloads.moe_expert_bytes(cfg)
-    copies = 4
+    # cold weights every step: copies of the layer cycled (a large layer's step touches far more than L2 by itself)
+    copies = 4 if sum(per) * cfg["n_exp"] // world < (3 << 30) // 2 else 2
     transport = os.environ.get("OSMOS_EP_TRANSPORT", "peer")
     try:
         layer = ep.EpMoeLane(lib, cfg, dev, rank, world, copies=copies, host_tensors=host, transport=transport, dist=dist)
@@ -285,19 +358,39 @@ def run_ours(args):
 
     # parity first: EVERY home token of step 0 against the CPU checker's bits (the reference's own CPU lane where it
     # runs, else the scalar restatement), with the picks the GPU made (checked equal to a double-precision softmax)
-    layer.step(dx[0], dl[0], out, 0, stream)
+    layer.step(dx[0], dl[0], out, 0, stream, shared=False)
     torch.cuda.synchronize()
     got_ids, got_wts = layer.last_picks()
-    want_ids, want_wts = workloads.softmax_topk(hl[0][t0:t1], k)
+    want_ids, want_wts = workloads.route_host(cfg, hl[0][t0:t1])
     arm = CpuArm(cfg, host)
     ok = np.array_equal(got_ids, want_ids) and np.allclose(got_wts, want_wts, rtol=1e-5, atol=0)
     want = arm.layer(hx[0][t0:t1], got_ids, got_wts)
-    ok = ok and np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
-    if not all_ok(ok):
-        raise SystemExit("bench: the GPU layer's output differs from the CPU checker's bits on some rank - not timing a wrong result")
-    parity = "all %d home tokens of step 0 on every rank, bit-equal to the %s" % (
+    routed = out.cpu().numpy().copy()
+    ok = ok and np.array_equal(routed.view(np.uint32), want.view(np.uint32))
+    parity = "all %d home tokens of step 0 on every rank, the routed experts' sum bit-equal to the %s" % (
         T, "reference's cpu_lane_submit" if arm.kind == "reference" else "scalar restatement of the reference's CPU lane")
-    distinct = [np.unique(workloads.softmax_topk(l, k)[0]) for l in hl]
+    if ok and cfg.get("shared"):
+        # the shared expert runs on the f16 tensor cores: its sums are held to the reference test's bound of a float64 sum
+        # over the f16-rounded operands, on this rank's first tokens
+        from libosmos_b200 import synth
+        from oracle.oracle import Oracle
+        layer.step(dx[0], dl[0], out, 0, stream)
+        torch.cuda.synchronize()
+        sh, orc, ns = cfg["shared"], Oracle(), min(T, 2)
+        tid = synth.TYPE_ID[sh["type"]]
+        wf = [orc.dequant(tid, a, r * c).reshape(r, c).astype(np.float16).astype(np.float64) for a, (r, c) in
+              zip(workloads.shared_expert_host(cfg), ((sh["ff"], dim), (sh["ff"], dim), (dim, sh["ff"])))]
+        x16 = hx[0][t0:t0 + ns].astype(np.float16).astype(np.float64)
+        g, u = np.minimum(x16 @ wf[0].T, sh["lim"]), np.clip(x16 @ wf[1].T, -sh["lim"], sh["lim"])
+        h16 = (g / (1 + np.exp(-g)) * u).astype(np.float16).astype(np.float64)
+        ref = h16 @ wf[2].T
+        mag = np.abs(h16) @ np.abs(wf[2]).T
+        diff = out.cpu().numpy()[:ns].astype(np.float64) - routed[:ns]
+        ok = bool((np.abs(diff - ref) <= 2.0 ** -9 * mag + 1e-6 * np.abs(routed[:ns])).all())
+        parity += "; the shared expert's output within 2^-9 sum |h w| of a float64 model over f16-rounded operands (%d tokens)" % ns
+    if not all_ok(ok):
+        raise SystemExit("bench: the GPU layer's output differs from the CPU checker on some rank - not timing a wrong result")
+    distinct = [np.unique(workloads.route_host(cfg, l)[0]) for l in hl]
 
     def barrier():
         if world > 1:
@@ -449,7 +542,7 @@ def run_ours(args):
                          "achieved": achieved, "frac": achieved / peak,
                          "traffic": 296433152 if (world == 1 and cfg["name"] == workloads.MOE_IQ3["name"]) else None,
                          "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, profiles/lane_ring_rows_iq3xxs_moe.md"
-                         if world == 1 else None,
+                         if (world == 1 and cfg["name"] == workloads.MOE_IQ3["name"]) else None,
                          "algorithmic_bytes_per_launch": float(np.mean(alg)), "us_per_launch": float(np.mean(k_ms) * 1e3)})
         cpu = None
         try:
@@ -492,6 +585,183 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_f32_or_f16(args, cfg, lib, dev):
+    """The MXFP4 experts (128 of them, top-4) on one GPU: 32 tokens through the F32 lane (q4x_route + lane_ffn_f32: an
+    expert read once for its tokens by mv_group_tok - the reference's decode path for a type without an int8 form), or
+    2048 tokens through the grouped f16 tensor-core product (q4x_moe). Same contract as the default workload's line."""
+    import torch
+
+    from libosmos_b200 import api, synth, workloads
+    from oracle.oracle import Oracle
+    if dist_env()[1] > 1:
+        raise SystemExit("bench: workload %s runs on one GPU" % cfg["name"])
+    tid, n_tok, dim, ff, k, n_exp = synth.TYPE_ID[cfg["type"]], cfg["n_tok"], cfg["dim"], cfg["ff"], cfg["k"], cfg["n_exp"]
+    picks = n_tok * k
+    host = workloads.moe_layer_host(cfg)
+    per = workloads.moe_expert_bytes(cfg)
+    copies = 2
+    first = [torch.from_numpy(h).to(dev) for h in host]
+    weights = [first] + [[t.clone() for t in first] for _ in range(copies - 1)]
+    f32 = cfg["path"] == "f32_lane"
+    layers = []
+    for w in weights:
+        if f32:
+            L = api.LaneLayer(tid, tid, dim, ff, n_exp, k, cfg["lim"], api.LaneExperts())
+            for j in range(3):
+                L.experts.base[j], L.experts.bytes[j] = w[j].data_ptr(), per[j]
+        else:
+            L = api.Q4xMoeLayer()
+            L.dim, L.ff, L.n_exp, L.k = dim, ff, n_exp, k
+            for j in range(3):
+                L.type[j], L.base[j], L.bytes[j] = tid, w[j].data_ptr(), per[j]
+        layers.append(L)
+    if f32:
+        nbytes, scratch = lib.lane_f32_scratch_bytes(layers[0], n_tok), api.LaneScratchF32()
+        bind = lib.lane_f32_scratch_bind
+    else:
+        nbytes, scratch = lib.q4x_moe_scratch_bytes(layers[0], n_tok), api.Q4xMoeScratch()
+        bind = lib.q4x_moe_scratch_bind
+    assert nbytes, "the driver refused the layer"
+    mem = torch.zeros(nbytes + 256, dtype=torch.uint8, device=dev)
+    assert bind(layers[0], n_tok, (mem.data_ptr() + 255) // 256 * 256, nbytes, scratch)
+    ids = torch.zeros(picks, dtype=torch.int32, device=dev)
+    wts = torch.zeros(picks, dtype=torch.float32, device=dev)
+    rows = torch.zeros(picks, dtype=torch.int32, device=dev)
+    zeros = torch.zeros((n_tok, dim), dtype=torch.float32, device=dev)  # q4x_moe's shared-expert term: none here
+    zlog = torch.zeros(n_tok, dtype=torch.float32, device=dev)
+    n_inputs = 8 if f32 else 4
+    hx, hl = zip(*[workloads.moe_inputs_host(cfg, s) for s in range(n_inputs)])
+    dx = [torch.from_numpy(a).to(dev) for a in hx]
+    dl = [torch.from_numpy(a).to(dev) for a in hl]
+    px = [torch.from_numpy(a).pin_memory() for a in hx]
+    pl = [torch.from_numpy(a).pin_memory() for a in hl]
+    out = torch.empty((n_tok, dim), dtype=torch.float32, device=dev)
+    pout = torch.empty((n_tok, dim), dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step(x, logits, o, copy, st):
+        L = layers[copy % copies]
+        if f32:
+            ok = lib.q4x_route(logits.data_ptr(), n_tok, n_exp, k, ids.data_ptr(), wts.data_ptr(), rows.data_ptr(), st) and \
+                lib.lane_ffn_f32(L, scratch, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), n_tok, None, o.data_ptr(), st)
+        else:
+            ok = lib.q4x_moe(L, scratch, x.data_ptr(), logits.data_ptr(), zeros.data_ptr(), zlog.data_ptr(), n_tok, o.data_ptr(), st)
+        if not ok:
+            raise RuntimeError("libosmos_b200 refused a call of the step")
+
+    # parity first, on the step's first tokens
+    orc = Oracle()
+    step(dx[0], dl[0], out, 0, stream)
+    torch.cuda.synchronize()
+    want_ids, want_w = workloads.softmax_topk(hl[0], k)
+    ns = 8 if f32 else 4
+    got = out.cpu().numpy()[:ns]
+    if f32:
+        gi, gw = ids.cpu().numpy().reshape(n_tok, k), wts.cpu().numpy().reshape(n_tok, k)
+        ok = np.array_equal(gi, want_ids) and np.allclose(gw, want_w, rtol=1e-5, atol=0)
+        want = np.zeros((ns, dim), np.float32)
+        for t in range(ns):
+            acc = np.zeros(dim, np.float32)
+            for j in np.argsort(gi[t], kind="stable"):
+                e = int(gi[t, j])
+                p = [host[m][e * per[m]:(e + 1) * per[m]] for m in range(3)]
+                g = orc.mv_rows(tid, p[0], ff, dim, hx[0][t:t + 1])
+                u = orc.mv_rows(tid, p[1], ff, dim, hx[0][t:t + 1])
+                acc = (acc + orc.mv_rows(tid, p[2], dim, ff, orc.swiglu_lane(g, u, cfg["lim"], gw[t, j:j + 1]))[0]).astype(np.float32)
+            want[t] = acc
+        ok = ok and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        parity = "the first %d tokens of step 0 bit-equal to the CPU checker (the F32 matvec's order, the lane's activation)" % ns
+    else:
+        ref = np.zeros((ns, dim))
+        for t in range(ns):
+            x16 = hx[0][t].astype(np.float16).astype(np.float64)
+            for j in range(k):
+                e = int(want_ids[t, j])
+                wf = [orc.dequant(tid, host[m][e * per[m]:(e + 1) * per[m]], r * c).reshape(r, c).astype(np.float64)
+                      for m, (r, c) in enumerate(((ff, dim), (ff, dim), (dim, ff)))]
+                g, u = wf[0] @ x16, wf[1] @ x16
+                h16 = (g / (1 + np.exp(-g)) * u).astype(np.float16).astype(np.float64)
+                ref[t] += float(want_w[t, j]) * (wf[2] @ h16)
+        err = np.abs(got - ref).max() / np.abs(ref).max()
+        ok = bool(err < 1e-3)
+        parity = "the first %d tokens of step 0 within 1e-3 (of the largest value) of a float64 model over f16-rounded activations: %.2e" % (ns, err)
+    if not ok:
+        raise SystemExit("bench: the GPU layer's output fails its check against the CPU checker - not timing a wrong result")
+    distinct = [len(np.unique(workloads.softmax_topk(l, k)[0])) for l in hl]
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(steps):
+            fn(s)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3
+
+    def resident(s):
+        step(dx[s % n_inputs], dl[s % n_inputs], out, s, stream)
+
+    bx, bl = torch.empty_like(dx[0]), torch.empty_like(dl[0])
+
+    def end_to_end(s):  # host buffers in, host buffer out, every step
+        bx.copy_(px[s % n_inputs], non_blocking=True)
+        bl.copy_(pl[s % n_inputs], non_blocking=True)
+        step(bx, bl, out, s, stream)
+        pout.copy_(out, non_blocking=True)
+
+    for s in range(args.warmup):
+        resident(s), end_to_end(s)
+    torch.cuda.synchronize()
+    graphs, side = [], torch.cuda.Stream()
+    for s in range(n_inputs):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            step(dx[s], dl[s], out, s, side.cuda_stream)
+        graphs.append(g)
+
+    def resident_graph(s):
+        graphs[s % n_inputs].replay()
+
+    with ClockSampler(dev.index) as clocks:
+        n_warm = int(min(20000, max(args.steps, 1.0 / (timed(resident_graph, args.steps) / args.steps))))
+        for s in range(n_warm):
+            resident_graph(s)
+        torch.cuda.synchronize()
+        t_regions = [timed(resident_graph, args.steps) for _ in range(REGIONS)]
+        t_stream = [timed(resident, args.steps) for _ in range(REGIONS)]
+        t_e2e = [timed(end_to_end, args.steps) for _ in range(REGIONS)]
+    t_res, t_str, t_ee = float(np.median(t_regions)), float(np.median(t_stream)), float(np.median(t_e2e))
+    if lib.mv_status() or lib.mm_status():
+        raise SystemExit("bench: a bounded wait ran out")
+    peak, peak_kind = measured_peaks()
+    alg = float(np.mean(distinct)) * sum(per)
+    achieved = alg / (t_res / args.steps) / 1e9
+    roof = {"bound": "hbm", "kernel": "the whole step (its three expert products: %s)" % ("mv_group_tok x 3" if f32 else "mm_group x 3"),
+            "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+            "algorithmic_bytes_per_launch": alg, "us_per_launch": 1e6 * t_res / args.steps}
+    if not f32:
+        tf, kind = measured_tflops()
+        flops = 2.0 * 3 * ff * dim * picks
+        roof["tensor"] = {"tflops": flops / (t_res / args.steps) / 1e12, "peak_tflops": tf, "peak_kind": kind + " bf16 burst",
+                          "frac": flops / (t_res / args.steps) / 1e12 / tf}
+    cpu_tok_s, _, sample = port_tokens_per_s(cfg, host, per)
+    line = {"metric": METRIC, "value": n_tok * args.steps / t_res, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32" if f32 else "f16xf16->f32", "data": "synthetic", "config": workload_config(cfg),
+            "run": {"parallelism": "1 gpu", "launch": "value: CUDA graph replay; the same steps launched on the stream take %.4f ms" % (1e3 * t_str / args.steps),
+                    "cold_cache": "%d copies of the layer's %d MB of expert weights cycled; a step touches ~%d MB" % (copies, sum(per) * n_exp // 1000000, int(alg) // 1000000),
+                    "timing": "median of %d regions of exactly %d steps, CUDA events" % (REGIONS, args.steps),
+                    "regions_ms_per_step": [1e3 * t / args.steps for t in t_regions], "parity": parity,
+                    "inputs": "activations are bf16 values held as F32 (the conversion is exact)"},
+            "e2e": {"value": n_tok * args.steps / t_ee, "unit": UNIT, "h2d_bytes_per_step": int((px[0].numel() + pl[0].numel()) * 4),
+                    "d2h_bytes_per_step": int(pout.numel() * 4)},
+            "gpu_launches": (10 if f32 else 13) * args.steps, "roofline": roof,
+            "cpu_baseline": {"value": cpu_tok_s, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample},
+            "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
 
 
 def graph_time(fn, n=64, reps=5):

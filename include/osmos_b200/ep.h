@@ -113,7 +113,13 @@ typedef struct EpPlan /* host memory; made once, read by every step */
   float **rows;             /* device scratch [n_tok * k]: where each of this rank's rows goes */
   LaneLayer layer;          /* the layer (its experts' addresses as this rank holds them) */
   LaneScratch scratch;      /* lane_scratch_bind's, for n_tok tokens */
+  uint32_t router;          /* EP_ROUTER_*: q4x_route's softmax, or ops_router's scores */
+  const float *route_bias;  /* device [n_exp]: the scored routers' bias */
+  float route_scale;        /* the scored routers' weight scale */
 } EpPlan;
+#define EP_ROUTER_SOFTMAX 0      /* q4x_route */
+#define EP_ROUTER_SQRT_SOFTPLUS 1 /* ops_router (DeepSeek's); at most 16 picks a token */
+#define EP_ROUTER_SIGMOID 2      /* ops_router_scored with sigmoid scores */
 
 /* x, logits, add (or NULL), out: this rank's home tokens ([n_tok / n_ranks][dim], [..][n_exp], [..][dim]).
    false = refused, nothing queued (a plan, type or shape the fused kernels do not take: use the unfused entries). */

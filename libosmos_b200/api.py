@@ -78,7 +78,8 @@ class EpLayout(C.Structure):
 
 class EpPlan(C.Structure):
     _fields_ = [("rank", U32), ("n_ranks", U32), ("n_tok", U32), ("expert0", U32), ("expert1", U32), ("lay", EpLayout),
-                ("peer", P * 16), ("sync", P), ("rows", P), ("layer", LaneLayer), ("scratch", LaneScratch)]
+                ("peer", P * 16), ("sync", P), ("rows", P), ("layer", LaneLayer), ("scratch", LaneScratch), ("router", U32),
+                ("route_bias", P), ("route_scale", F32)]
 
 
 class QTypeInfo(C.Structure):

@@ -184,12 +184,14 @@ struct StepArgs {
   EpLayout lay;
   uint32_t rank, n_ranks, tokens, k, dim, n_exp;
   uint32_t* sync;  // [0] step, [1] [2] publish counters
+  const float* bias;  // the scored routers'
+  float rscale;
 };
 
 // A block a home token. Its first warp routes it (route.cuh) while all eight round its row to int8 (q8_round.cuh);
 // every result goes straight to its token-major place in every rank's buffer. The last block to finish releases this
 // rank's dispatch flag everywhere and advances the step counter.
-template <int R>
+template <int R, int ROUTER>
 __global__ void __launch_bounds__(256) route_round_push_kernel(const StepArgs a, const float* __restrict__ x,
                                                                const float* __restrict__ logits) {
   pdl_wait();  // (a dependent launch: the step before may still be reading what this one writes)
@@ -197,7 +199,11 @@ __global__ void __launch_bounds__(256) route_round_push_kernel(const StepArgs a,
   const uint32_t step = a.sync[0] + 1u, half = step & 1u;
   const uint32_t tl = blockIdx.x, t = a.rank * a.tokens + tl, lane = threadIdx.x % kWarp;
   if (threadIdx.x < kWarp) {
-    const route::Pick p = route::softmax_topk<R>(logits + (uint64_t) tl * a.n_exp, a.n_exp, a.k, lane);
+    route::Pick p;
+    if constexpr (ROUTER == EP_ROUTER_SOFTMAX) p = route::softmax_topk<R>(logits + (uint64_t) tl * a.n_exp, a.n_exp, a.k, lane);
+    else if constexpr (ROUTER == EP_ROUTER_SIGMOID)
+      p = route::scored_topk<R, route::kSigmoid>(logits + (uint64_t) tl * a.n_exp, a.bias, a.n_exp, a.k, a.rscale, lane);
+    else p = route::scored_topk<R, route::kSqrtSoftplus>(logits + (uint64_t) tl * a.n_exp, a.bias, a.n_exp, a.k, a.rscale, lane);
     if (lane < a.k)
       for (uint32_t r = 0; r < a.n_ranks; r++) {
         ((int32_t*) (a.peers.base[r] + a.lay.ids[half]))[t * a.k + lane] = (int32_t) p.id;
@@ -259,7 +265,7 @@ StepArgs step_args(const EpPlan* p) {
   StepArgs a{};
   for (uint32_t r = 0; r < p->n_ranks; r++) a.peers.base[r] = (uint8_t*) p->peer[r];
   a.lay = p->lay, a.rank = p->rank, a.n_ranks = p->n_ranks, a.tokens = p->n_tok / p->n_ranks, a.k = p->layer.k;
-  a.dim = p->layer.dim, a.n_exp = p->layer.n_exp, a.sync = p->sync;
+  a.dim = p->layer.dim, a.n_exp = p->layer.n_exp, a.sync = p->sync, a.bias = p->route_bias, a.rscale = p->route_scale;
   return a;
 }
 
@@ -307,7 +313,8 @@ extern "C" bool ep_plan_ok(const EpPlan* p) {
   EpLayout want;
   if (!l.dim || l.dim % 256 || !l.ff || l.ff % 256 || !l.k || l.k > 32 || !l.n_exp || l.n_exp > 1024 || l.k > l.n_exp ||
       (uint64_t) p->n_tok * l.k > 1024 || !ep_layout(p->n_ranks, p->n_tok, l.k, l.dim, &want) ||
-      memcmp(&want, &p->lay, sizeof want) != 0 || p->scratch.max_tok < p->n_tok)
+      memcmp(&want, &p->lay, sizeof want) != 0 || p->scratch.max_tok < p->n_tok || p->router > EP_ROUTER_SIGMOID ||
+      (p->router != EP_ROUTER_SOFTMAX && (!p->route_bias || l.k > 16)))
     return false;
   for (uint32_t r = 0; r < p->n_ranks; r++)
     if (!p->peer[r] || ((uintptr_t) p->peer[r] & 255u)) return false;
@@ -323,12 +330,19 @@ extern "C" bool ep_route_round_push(const EpPlan* p, const float* x, const float
   const StepArgs a = step_args(p);
   const dim3 grid(a.tokens), block(256);
   const cudaStream_t s = stream_of(stream);
-  switch (route::regs_for(a.n_exp)) {
-    case 4: return launch_dependent(route_round_push_kernel<4>, grid, block, 0, s, a, x, logits) == cudaSuccess;
-    case 8: return launch_dependent(route_round_push_kernel<8>, grid, block, 0, s, a, x, logits) == cudaSuccess;
-    case 16: return launch_dependent(route_round_push_kernel<16>, grid, block, 0, s, a, x, logits) == cudaSuccess;
-    default: return launch_dependent(route_round_push_kernel<32>, grid, block, 0, s, a, x, logits) == cudaSuccess;
+#define ROUTE(R, KIND) launch_dependent(route_round_push_kernel<R, KIND>, grid, block, 0, s, a, x, logits) == cudaSuccess
+#define BY_REGS(KIND)                     \
+  switch (route::regs_for(a.n_exp)) {     \
+    case 4: return ROUTE(4, KIND);        \
+    case 8: return ROUTE(8, KIND);        \
+    case 16: return ROUTE(16, KIND);      \
+    default: return ROUTE(32, KIND);      \
   }
+  if (p->router == EP_ROUTER_SOFTMAX) BY_REGS(EP_ROUTER_SOFTMAX)
+  if (p->router == EP_ROUTER_SIGMOID) BY_REGS(EP_ROUTER_SIGMOID)
+  BY_REGS(EP_ROUTER_SQRT_SOFTPLUS)
+#undef BY_REGS
+#undef ROUTE
 }
 
 extern "C" bool ep_lane_tables(const EpPlan* p, void* stream) {

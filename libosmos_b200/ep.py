@@ -18,7 +18,9 @@ import ctypes as C
 
 import torch
 
-from . import api, runner
+from . import api, runner, synth, workloads
+
+ROUTERS = {"softmax": 0, "sqrt_softplus": 1, "sigmoid": 2}
 
 
 def expert_range(rank, world, n_exp):
@@ -118,6 +120,19 @@ class EpMoeLane:
                                     expert_range=(self.e0, self.e1))
         self.transport, self.peer = transport, None
         picks = self.n_tok * self.k
+        self.shared = None
+        if cfg.get("shared"):  # a dense expert on every home token, its output added after the routed experts' sum
+            sh = cfg["shared"]
+            self.shared_w = [torch.from_numpy(a).to(dev) for a in workloads.shared_expert_host(cfg)]
+            tid = synth.TYPE_ID[sh["type"]]
+            self.shared = api.SharedExpert(tid, tid, self.dim, sh["ff"], sh["lim"], *[t.data_ptr() for t in self.shared_w])
+            nbytes = lib.shared_scratch_bytes(self.shared, self.T)
+            assert nbytes, "shared_scratch_bytes refused the shared expert"
+            self.shared_mem = torch.zeros(nbytes + 256, dtype=torch.uint8, device=dev)
+            self.shared_scratch = api.SharedScratch()
+            assert lib.shared_scratch_bind(self.shared, self.T, (self.shared_mem.data_ptr() + 255) // 256 * 256, nbytes,
+                                           self.shared_scratch)
+            self.sye = torch.zeros((self.T, self.dim), dtype=torch.float32, device=dev)
         if transport == "peer":
             lay = api.EpLayout()
             assert lib.ep_layout(world, self.n_tok, self.k, self.dim, lay), "ep_layout refused the shape"
@@ -132,11 +147,17 @@ class EpMoeLane:
                 for r in range(world):
                     p.peer[r] = self.peer.base[r]
                 p.sync, p.rows, p.layer, p.scratch = self.sync.data_ptr(), self.rows.data_ptr(), layer, self.local.scratch
+                p.router = ROUTERS[cfg.get("router", "softmax")]
+                if p.router:
+                    self.route_bias = torch.from_numpy(workloads.route_bias_host(cfg)).to(dev)
+                    p.route_bias, p.route_scale = self.route_bias.data_ptr(), cfg["route_scale"]
                 if not lib.ep_plan_ok(p):
                     self.peer.close()
                     raise RuntimeError("the fused step does not take this layer")
                 self.plans.append(p)
-            self.kernels_per_step = 6  # route+round+push, wait+tables, gate_up, round, down+push, wait+combine
+            # route+round+push, wait+tables, gate_up, round, down+push, wait+combine (+ the shared expert's x16,
+            # gate | up, activation, x16, down)
+            self.kernels_per_step = 6 + (5 if self.shared is not None else 0)
             torch.cuda.synchronize()
             return
         # ---- nccl transport: the unfused kernels ----
@@ -172,8 +193,14 @@ class EpMoeLane:
         wts = self.segment[s.weights:s.weights + 4 * self.T * self.k].view(torch.float32).cpu().numpy().reshape(self.T, self.k)
         return ids, wts
 
-    def step(self, x_home, logits_home, out_home, copy=0, stream=0, add=None):
-        """x_home [T, dim], logits_home [T, n_exp], out_home [T, dim]: this rank's tokens; all on this GPU."""
+    def step(self, x_home, logits_home, out_home, copy=0, stream=0, add=None, shared=True):
+        """x_home [T, dim], logits_home [T, n_exp], out_home [T, dim]: this rank's tokens; all on this GPU. A layer with
+        a shared expert runs it first on the home tokens (shared False: the routed experts alone)."""
+        if self.shared is not None and shared:
+            assert add is None
+            if not self.lib.shared_ffn(self.shared, self.shared_scratch, x_home.data_ptr(), self.T, self.sye.data_ptr(), stream):
+                raise RuntimeError("libosmos_b200 refused shared_ffn")
+            add = self.sye
         if self.transport == "peer":
             if not self.lib.ep_layer_step(self.plans[copy % len(self.plans)], x_home.data_ptr(), logits_home.data_ptr(),
                                           add.data_ptr() if add is not None else None, out_home.data_ptr(), stream):
@@ -187,6 +214,11 @@ class EpMoeLane:
         lib, p = self.lib, self.plans[copy % len(self.plans)]
         L, s = p.layer, p.scratch
         picks = self.n_tok * self.k
+        add = None
+        if self.shared is not None:  # (before the first event: the stages are the routed experts')
+            if not lib.shared_ffn(self.shared, self.shared_scratch, x_home.data_ptr(), self.T, self.sye.data_ptr(), stream):
+                raise RuntimeError("libosmos_b200 refused shared_ffn")
+            add = self.sye.data_ptr()
         events[0].record()
         ok = lib.ep_route_round_push(p, x_home.data_ptr(), logits_home.data_ptr(), stream)
         events[1].record()
@@ -198,7 +230,7 @@ class EpMoeLane:
         events[4].record()
         ok = ok and lib.ep_down_push(p, stream)
         events[5].record()
-        ok = ok and lib.ep_combine_wait(p, None, out_home.data_ptr(), stream)
+        ok = ok and lib.ep_combine_wait(p, add, out_home.data_ptr(), stream)
         events[6].record()
         if not ok:
             raise RuntimeError("libosmos_b200 refused a stage of the fused step")

@@ -27,9 +27,14 @@ class MoeLane:
         self.max_tok = max_tok or cfg["n_tok"]
         self.e0, self.e1 = expert_range or (0, self.n_exp)
         self.per = workloads.moe_expert_bytes(cfg)
-        host = host_tensors or workloads.moe_layer_host(cfg)
+        # host_tensors: the whole layer's, or (a workload whose experts have their own random streams) this range's only
+        ranged = bool(cfg.get("per_expert_rng"))
+        host = host_tensors or workloads.moe_layer_host(cfg, expert_range=(self.e0, self.e1) if ranged else None)
         self.host = host
-        first = [_dev_bytes(h[self.e0 * b:self.e1 * b], dev) for h, b in zip(host, self.per)]
+        if ranged and host[0].size == (self.e1 - self.e0) * self.per[0]:
+            first = [_dev_bytes(h, dev) for h in host]
+        else:
+            first = [_dev_bytes(h[self.e0 * b:self.e1 * b], dev) for h, b in zip(host, self.per)]
         self.weights = [first] + [[t.clone() for t in first] for _ in range(copies - 1)]
         self.layers = []
         for w in self.weights:
