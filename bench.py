@@ -361,12 +361,17 @@ def run_ours(args):
     layer.step(dx[0], dl[0], out, 0, stream, shared=False)
     torch.cuda.synchronize()
     got_ids, got_wts = layer.last_picks()
-    want_ids, want_wts = workloads.route_host(cfg, hl[0][t0:t1])
     arm = CpuArm(cfg, host)
-    ok = np.array_equal(got_ids, want_ids) and np.allclose(got_wts, want_wts, rtol=1e-5, atol=0)
+    ok = workloads.router_check(cfg, hl[0][t0:t1], got_ids, got_wts)
+    if not ok:
+        sys.stderr.write("bench: rank %d: the router's picks or weights differ from the double-precision router\n" % rank)
     want = arm.layer(hx[0][t0:t1], got_ids, got_wts)
     routed = out.cpu().numpy().copy()
-    ok = ok and np.array_equal(routed.view(np.uint32), want.view(np.uint32))
+    if not np.array_equal(routed.view(np.uint32), want.view(np.uint32)):
+        bad = np.argwhere(routed.view(np.uint32) != want.view(np.uint32))
+        sys.stderr.write("bench: rank %d: %d of %d values of the routed experts' sum differ from the CPU checker's bits (first at token %d "
+                         "column %d: %r against %r)\n" % (rank, len(bad), routed.size, bad[0][0], bad[0][1], routed[tuple(bad[0])], want[tuple(bad[0])]))
+        ok = False
     parity = "all %d home tokens of step 0 on every rank, the routed experts' sum bit-equal to the %s" % (
         T, "reference's cpu_lane_submit" if arm.kind == "reference" else "scalar restatement of the reference's CPU lane")
     if ok and cfg.get("shared"):
@@ -387,6 +392,9 @@ def run_ours(args):
         mag = np.abs(h16) @ np.abs(wf[2]).T
         diff = out.cpu().numpy()[:ns].astype(np.float64) - routed[:ns]
         ok = bool((np.abs(diff - ref) <= 2.0 ** -9 * mag + 1e-6 * np.abs(routed[:ns])).all())
+        if not ok:
+            sys.stderr.write("bench: rank %d: the shared expert's output is outside its bound (worst %.3e of its magnitude sum)\n"
+                             % (rank, float((np.abs(diff - ref) / (mag + 1e-30)).max())))
         parity += "; the shared expert's output within 2^-9 sum |h w| of a float64 model over f16-rounded operands (%d tokens)" % ns
     if not all_ok(ok):
         raise SystemExit("bench: the GPU layer's output differs from the CPU checker on some rank - not timing a wrong result")

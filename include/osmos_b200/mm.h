@@ -116,13 +116,30 @@ bool mm_group(uint32_t type, const void *const *w, const int32_t *cnt, uint32_t 
    exact in f16 and go through the f16 tensor-core product (every product exact, F32 sums): within the reference's own
    bound (1e-5 relative to float64 sums, tests/gpu/test_mm_fp4_gpu.hip:150), not its bits. Shapes as mm_fits takes
    them (rows in 16s, cols in 128s; the reference: 8s and 64s). The step's f16 activations live in a stream-ordered
-   allocation made and freed by the call. */
+   allocation made and freed by the call.
+   On whole 128-row tiles and 256-value steps of K the product runs on the block-scaled FP4 tensor-core instruction
+   (tcgen05.mma kind::mxf4nvf4: E2M1 x E2M1 under a UE4M3 factor every 16 values on each side, F32 sums), the counterpart
+   of the reference's mma.sync kind::mxf4nvf4 kernel (kernels/mm_fp4.hip:149-259); other shapes take the f16 route.
+   mm_fp4_set_tensor(0) keeps every shape on the f16 route (the tests compare the two routes). */
 bool mm_fp4_ok(void);
 bool mm_fp4_act(const float *x, uint32_t xs, uint32_t n, uint32_t cols, float gs, void *q, void *sc, void *stream);
 bool mm_fp4_quant(const void *x, uint32_t bf16, uint32_t xs, uint32_t n, uint32_t cols, float gs, const float *gs_dev,
                   uint32_t sr_seed, void *q, void *sc, void *stream);
 bool mm_fp4(const void *w, uint32_t rows, uint32_t cols, const void *q, const void *sc, uint32_t n, float scale,
             float *y, uint32_t ys, void *stream);
+void mm_fp4_set_tensor(int on);
+/* Not in the reference (it never feeds quantized activations to an MXFP4 product: kernels/mm.hip:426 decodes the weights
+   to f16): MXFP4 weights (QTYPE_MXFP4) times MXFP4 activations, W4A4, on tcgen05.mma kind::mxf4 (E2M1 x E2M1 under a UE8M0
+   factor every 32 values on each side, F32 sums). `packed` is what ops_fp4_round(x, n * cols, 32, false, packed, cols)
+   writes: a token's cols / 2 code bytes (the even value in the low nibble), then its cols / 32 scale bytes.
+   y[t * ys + r] = scale * sum_c W[r, c] xq[t, c]. false without the device, for rows not whole 128s, cols not whole 512s,
+   n 0, ys shorter than a row with more than one token, or packed / w not 16- / 4-byte aligned. */
+bool mm_mxfp4(const void *w, uint32_t rows, uint32_t cols, const void *packed, uint32_t n, float scale, float *y,
+              uint32_t ys, void *stream);
+/* the block-scaled MMA's 32-bit instruction descriptor as the kernel builds it (M 128, N n, E2M1 operands; mx: UE8M0
+   factors every 32, else UE4M3 every 16; sf_id: the first factor's byte in its word) - for the host test against
+   CUTLASS's encoder */
+uint32_t mm_fp4_desc(uint32_t mx, uint32_t n, uint32_t sf_id);
 /* Not in the reference: the products' kernel never waits without a bound; reads and clears the current device's
    record (synchronizes): bit 0 a wait ran out, the launch's outputs are not valid */
 uint32_t mm_status(void);

@@ -118,6 +118,9 @@ SIGNATURES = {
     "mm_fp4_act": (B, [P, U32, U32, U32, C.c_float, P, P, P]),
     "mm_fp4_quant": (B, [P, U32, U32, U32, U32, C.c_float, P, U32, P, P, P]),
     "mm_fp4": (B, [P, U32, U32, P, P, U32, C.c_float, P, U32, P]),
+    "mm_fp4_set_tensor": (None, [C.c_int]),
+    "mm_mxfp4": (B, [P, U32, U32, P, U32, C.c_float, P, U32, P]),
+    "mm_fp4_desc": (U32, [U32, U32, U32]),
     # q8.h
     "q8_round": (B, [P, U32, U32, U32, P, P, P]),
     "q8_0_round": (B, [P, U32, U32, U32, P, P, P]),

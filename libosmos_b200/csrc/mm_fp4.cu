@@ -13,6 +13,7 @@
 // operands (tests/gpu/test_mm_fp4_gpu.hip:129-153).
 #include "common.cuh"
 #include "decode.cuh"
+#include "fp4_tc_api.h"
 #include "mm_tc_api.h"
 #include "osmos_b200/mm.h"
 
@@ -186,10 +187,24 @@ extern "C" bool mm_fp4_act(const float* x, uint32_t xs, uint32_t n, uint32_t col
   return mm_fp4_quant(x, 0, xs, n, cols, gs, nullptr, 0, q, sc, stream);
 }
 
+static int g_fp4_tensor = 1;  // mm_fp4_set_tensor: 0 keeps the product on the f16 tensor-core route (the tests compare the two)
+
+extern "C" void mm_fp4_set_tensor(int on) { g_fp4_tensor = on; }
+extern "C" uint32_t mm_fp4_desc(uint32_t mx, uint32_t n, uint32_t sf_id) { return fp4_tc::instr_desc(mx != 0, n, sf_id); }
+
+extern "C" bool mm_mxfp4(const void* w, uint32_t rows, uint32_t cols, const void* packed, uint32_t n, float scale, float* y,
+                         uint32_t ys, void* stream) {
+  if (!mm_fp4_ok() || !w || !packed || !y || !n || !rows || !cols || cols % 512 || rows % 128 || (n > 1 && ys < rows)) return false;
+  const uint32_t stride = cols / 2 + cols / 32;  // a token's codes, then its scale bytes
+  return fp4_tc::try_launch(true, w, rows, cols, packed, stride, (const uint8_t*) packed + cols / 2, stride, n, scale, y, ys, stream) > 0;
+}
+
 extern "C" bool mm_fp4(const void* w, uint32_t rows, uint32_t cols, const void* q, const void* sc, uint32_t n, float scale,
                        float* y, uint32_t ys, void* stream) {
   if (!mm_fp4_ok() || !w || !q || !sc || !y || !n || !mm_tc::shape_ok(QTYPE_NVFP4, rows, cols) || (n > 1 && ys < rows) || ((uintptr_t) q & 7u))
     return false;
+  if (g_fp4_tensor)  // the block-scaled FP4 MMA when it takes the shape (whole 128-row tiles, 256-value steps)
+    if (const int st = fp4_tc::try_launch(false, w, rows, cols, q, cols / 2, sc, cols / 16, n, scale, y, ys, stream)) return st > 0;
   const cudaStream_t s = stream_of(stream);
   const uint32_t most = n < MM_MAX_TOKENS ? n : MM_MAX_TOKENS, most16 = (most + MM_TILE - 1) / MM_TILE * MM_TILE;
   void* x16 = nullptr;  // the step's f16 activations: allocated and freed in stream order

@@ -29,6 +29,7 @@
 
 #include "decode.cuh"
 #include "dispatch.cuh"
+#include "fp4_tc_api.h"
 #include "mm_tc_api.h"
 #include "osmos_b200/mm.h"
 #include "tma.cuh"
@@ -509,7 +510,7 @@ extern "C" uint32_t mm_status(void) {
   uint32_t v = 0, zero = 0;
   if (cudaMemcpy(&v, at, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return 0x80000000u;
   cudaMemcpy(at, &zero, sizeof zero, cudaMemcpyHostToDevice);
-  return v;
+  return v | fp4_tc::read_status();  // (the block-scaled FP4 product's record beside the f16 product's)
 }
 
 extern "C" bool mm_run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n, float* y,

@@ -108,3 +108,27 @@ def softmax_topk(logits, k):
     ids = np.argsort(-p, axis=1, kind="stable")[:, :k]
     pk = np.take_along_axis(p, ids, 1)
     return ids.astype(np.int32), (pk / np.maximum(pk.sum(1, keepdims=True), 2.0 ** -14)).astype(np.float32)
+
+
+def router_check(cfg, logits, got_ids, got_wts, tol=2e-6):
+    """whether a device's picks and weights are the workload's router's, in double precision: every picked key reaches the
+    k-th greatest key (keys within `tol` of each other may be picked either way: the device's F32 scores round), the
+    picks are distinct, in non-increasing key order (to `tol`), and the weights are the picked scores' normalisation"""
+    l = logits.astype(np.float64)
+    k = cfg["k"]
+    if cfg.get("router", "softmax") == "softmax":
+        p = np.exp(l - l.max(1, keepdims=True))
+        key = score = p / p.sum(1, keepdims=True)
+        norm = lambda pk: pk / np.maximum(pk.sum(1, keepdims=True), 2.0 ** -14)
+    else:
+        score = 1 / (1 + np.exp(-l)) if cfg["router"] == "sigmoid" else np.sqrt(np.where(l > 20, l, np.log1p(np.exp(np.minimum(l, 20)))))
+        key = score + route_bias_host(cfg)[None, :].astype(np.float64)
+        norm = lambda pk: pk / (pk.sum(1, keepdims=True) + 1e-20) * cfg["route_scale"]
+    kth = -np.sort(-key, axis=1)[:, k - 1:k]
+    gk = np.take_along_axis(key, got_ids.astype(np.int64), 1)
+    scale = np.abs(key).max()
+    distinct = all(len(set(r)) == k for r in got_ids.tolist())
+    ordered = bool((gk[:, :-1] >= gk[:, 1:] - tol * scale).all()) if k > 1 else True
+    reach = bool((gk >= kth - tol * scale).all())
+    want_w = norm(np.take_along_axis(score, got_ids.astype(np.int64), 1))
+    return distinct and ordered and reach and bool(np.allclose(got_wts, want_w, rtol=1e-5, atol=1e-12))

@@ -154,3 +154,28 @@ def test_plan_refusals(lib, dev):
     lay = api.EpLayout()
     assert not lib.ep_layout(3, 64, 10, 2048, lay) and not lib.ep_layout(17, 68, 10, 2048, lay) and not lib.ep_layout(2, 64, 33, 2048, lay)
     layer.close()
+
+
+@pytest.mark.parametrize("n_tok,k", [(1, 8), (2, 3), (1, 1)])
+def test_one_rank_step_of_very_few_tokens(lib, dev, n_tok, k):
+    """a decode step of one or two tokens: fewer picks than experts, entries of one token, a single block in the
+    per-token kernels"""
+    cfg = dict(name="moe_tiny", type="IQ1_M", n_exp=32, k=k, n_tok=n_tok, dim=4096, ff=1024, sigma=0.01, lim=10.0,
+               router="sqrt_softplus", route_scale=2.5)
+    host = workloads.moe_layer_host(cfg)
+    layer = ep.EpMoeLane(lib, cfg, dev, 0, 1, host_tensors=host)
+    stream = torch.cuda.current_stream().cuda_stream
+    got = torch.empty((n_tok, cfg["dim"]), dtype=torch.float32, device=dev)
+    from oracle.oracle import Oracle
+    orc = Oracle()
+    for step in range(2):
+        x, logits = workloads.moe_inputs_host(cfg, 20 + step)
+        layer.step(torch.from_numpy(x).to(dev), torch.from_numpy(logits).to(dev), got, 0, stream)
+        torch.cuda.synchronize()
+        ids, wts = layer.last_picks()
+        want_ids, want_w = workloads.route_host(cfg, logits)
+        assert np.array_equal(ids, want_ids) and np.allclose(wts, want_w, rtol=1e-5, atol=0)
+        want = runner.moe_oracle(orc, cfg, host, x, ids, wts)
+        assert np.array_equal(_bits(got), want.view(np.uint32))
+    assert lib.ep_wait_status() == 0 and lib.q8_status() == 0
+    layer.close()

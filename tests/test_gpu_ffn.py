@@ -149,10 +149,13 @@ def test_q4x_moe(lib, dev, oracle, name, n_tok):
         slack = 2.0 ** -10 * (np.abs(h.astype(np.float64))[None] @ np.abs(wf[2][e].astype(np.float64)).T)
         assert (np.abs(y[r] - ref[0]) <= bound[0] + slack[0]).all()
     gate = 1 / (1 + np.exp(-slog.astype(np.float64)))
-    want = np.zeros((n_tok, dim))
+    want, mag = np.zeros((n_tok, dim)), np.zeros((n_tok, dim))
     for i in range(picks):
         want[i // k] += y[where[i]].astype(np.float64) * ids_w[i]
+        mag[i // k] += np.abs(y[where[i]].astype(np.float64) * ids_w[i])
     want += shared * gate[:, None]
-    assert np.allclose(out.cpu().numpy(), want, rtol=2e-6, atol=2e-6)
+    mag += np.abs(shared * gate[:, None])
+    # (F32 products and sums in pick order: a few roundings of the terms' magnitudes, whatever cancels)
+    assert (np.abs(out.cpu().numpy() - want) <= 1e-6 * mag + 1e-30).all()
     assert lib.mm_status() == 0 and np.frombuffer(fetch(s.overflow, 1, 1).tobytes(), np.int32)[0] == 0
     assert not lib.q4x_moe(L, s, ptr(out), ptr(out), ptr(out), ptr(out), n_tok + 1, ptr(out), None)

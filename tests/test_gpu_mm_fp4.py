@@ -149,3 +149,65 @@ def test_mm_fp4_refusals(lib, dev):
     assert not lib.mm_fp4_act(ptr(y), 96, 1, 96, 1.0, ptr(a), ptr(a), None)              # cols not in 64s
     assert not lib.mm_fp4_act(ptr(y), 64, 1, 64, 0.0, ptr(a), ptr(a), None)              # a scale not above 0
     assert not lib.mm_fp4_act(ptr(y), 32, 2, 64, 1.0, ptr(a), ptr(a), None)              # xs shorter than a row
+
+
+# ---- the block-scaled FP4 tensor-core route ------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols,n", [(128, 256, 1), (128, 256, 16), (128, 512, 129), (256, 1024, 256), (384, 2048, 700)])
+def test_mm_fp4_tensor_route(lib, dev, oracle, rows, cols, n):
+    """mm_fp4 on tcgen05.mma kind::mxf4nvf4 (whole 128-row tiles, 256-value steps) against float64 sums over the quantized
+    operands, and against the f16 route; scale bytes with a sign bit and the byte 0x7F (ggml: ignored, zero) among them"""
+    rng = synth.rng_for(75, rows, cols, n)
+    gs, wscale = 0.05, 0.7
+    w = synth.random_tensor(NVFP4, rows, cols, rng).reshape(-1, 36)
+    w[3::17, 1] |= 0x80   # a sign bit on a scale: read without it
+    w[5::23, 2] = 0x7F    # the byte ggml reads as zero
+    w = w.reshape(-1)
+    x = (rng.standard_normal((n, cols)) * gs * 6.0).astype(np.float32)
+    q, sc = oracle.fp4_act(x, cols, gs)
+    want, mag = oracle.fp4_mm(w, rows, cols, q, sc, scale=wscale * gs)
+    wd, qd, sd = to_dev(w, dev), to_dev(q, dev), to_dev(sc, dev)
+    outs = []
+    for tensor in (1, 0):
+        lib.mm_fp4_set_tensor(tensor)
+        y = torch.full((n, rows), float("nan"), dtype=torch.float32, device=dev)
+        assert lib.mm_fp4(ptr(wd), rows, cols, ptr(qd), ptr(sd), n, wscale * gs, ptr(y), rows, None)
+        sync()
+        outs.append(y.cpu().numpy().astype(np.float64))
+    lib.mm_fp4_set_tensor(1)
+    assert lib.mm_status() == 0
+    for got in outs:
+        assert (np.abs(got - want) <= (cols / 16 + 20) * 2.0 ** -24 * mag + 1e-30).all()
+        assert np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()) < 1e-5
+    # a token's sums do not depend on the tokens beside it
+    for t in sorted({0, n // 2, n - 1}):
+        y1 = torch.zeros((1, rows), dtype=torch.float32, device=dev)
+        assert lib.mm_fp4(ptr(wd), rows, cols, ptr(qd[t:t + 1].contiguous()), ptr(sd[t:t + 1].contiguous()), 1, wscale * gs, ptr(y1), rows, None)
+        sync()
+        assert np.array_equal(y1.cpu().numpy()[0].astype(np.float64), outs[0][t])
+
+
+@pytest.mark.parametrize("rows,cols,n", [(128, 512, 1), (128, 512, 40), (256, 1536, 300), (384, 4096, 64)])
+def test_mm_mxfp4(lib, dev, oracle, rows, cols, n):
+    """MXFP4 weights x MXFP4 activations on tcgen05.mma kind::mxf4: the activations rounded by ops_fp4_round (its packed
+    rows feed the product as they are), against float64 sums over the quantized operands"""
+    tid = TYPES["MXFP4"]
+    rng = synth.rng_for(76, rows, cols, n)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    x = (rng.standard_normal((n, cols)) * 3.0).astype(np.float32)
+    xr, packed = oracle.fp4_round(x, 32, False, cols)  # the rounded values and the packed codes + scales
+    xd = to_dev(x.reshape(-1), dev)
+    pk = torch.zeros(n * (cols // 2 + cols // 32), dtype=torch.uint8, device=dev)
+    assert lib.ops_fp4_round(ptr(xd), n * cols, 32, False, ptr(pk), cols, None)
+    sync()
+    assert np.array_equal(pk.cpu().numpy(), packed)
+    wf = oracle.dequant(tid, w, rows * cols).reshape(rows, cols).astype(np.float64)
+    xq = xr.reshape(n, cols).astype(np.float64)
+    want, mag = 0.5 * (xq @ wf.T), 0.5 * (np.abs(xq) @ np.abs(wf).T)
+    y = torch.full((n, rows), float("nan"), dtype=torch.float32, device=dev)
+    assert lib.mm_mxfp4(ptr(to_dev(w, dev)), rows, cols, ptr(pk), n, 0.5, ptr(y), rows, None)
+    sync()
+    assert lib.mm_status() == 0
+    got = y.cpu().numpy().astype(np.float64)
+    assert (np.abs(got - want) <= (cols / 16 + 20) * 2.0 ** -24 * mag + 1e-30).all()
+    assert not lib.mm_mxfp4(ptr(pk), 128, 256, ptr(pk), 1, 1.0, ptr(y), 128, None)  # cols not whole 512s
+    assert not lib.mm_mxfp4(ptr(pk), 64, 512, ptr(pk), 1, 1.0, ptr(y), 64, None)    # rows not whole 128s
