@@ -936,6 +936,8 @@ def run_kernel(args):
        python bench.py --kernel q8_run Q4_0 49152 2048 --plain 4    four plain launches, nothing timed (for a profiler)
        python bench.py --kernel mm_run Q4_K 4096 4096 --tokens 512  the f16 prefill product (x16 made once)
        python bench.py --kernel mm_fp4 NVFP4 17408 5120 --tokens 2048   W4A4: quantization + product a launch
+       python bench.py --kernel mm_fp4_only NVFP4 17408 5120 --tokens 2048   the product alone (--generic: the f16 route)
+       python bench.py --kernel mm_mxfp4 MXFP4 16384 4096 --tokens 2048  W4A4 on MXFP4: rounding + product a launch
        python bench.py --kernel mmq_group Q4_K 4096 4096 --tokens 512   the int8 prefill product (x8 made once)
     64 launches on successive cold copies of the matrix (more than 1 GiB cycled) in one CUDA graph, replayed 5 times."""
     import torch
@@ -966,6 +968,22 @@ def run_kernel(args):
         fn = lambda i, st: (lib.mm_fp4_act(x.data_ptr(), cols, tokens, cols, 0.5, xq.data_ptr(), xsc.data_ptr(), st)
                             and lib.mm_fp4(pool.data_ptr() + (i % copies) * nb, rows, cols, xq.data_ptr(),
                                            xsc.data_ptr(), tokens, 1.0, y.data_ptr(), rows, st))
+    elif op == "mm_mxfp4":  # W4A4 on MXFP4 (TYPE must be MXFP4): the activations' rounding and the product a launch
+        flops = 2.0 * rows * cols * tokens
+        pk = torch.zeros(tokens * (cols // 2 + cols // 32), dtype=torch.uint8, device=dev)
+        xr = x.clone()
+        fn = lambda i, st: (lib.ops_fp4_round(xr.data_ptr(), tokens * cols, 32, False, pk.data_ptr(), cols, st)
+                            and lib.mm_mxfp4(pool.data_ptr() + (i % copies) * nb, rows, cols, pk.data_ptr(), tokens, 1.0,
+                                             y.data_ptr(), rows, st))
+    elif op == "mm_fp4_only":  # the W4A4 product alone (TYPE NVFP4): the activations quantized once, outside
+        flops = 2.0 * rows * cols * tokens
+        xq = torch.zeros(tokens, cols // 2, dtype=torch.uint8, device=dev)
+        xsc = torch.zeros(tokens, cols // 16, dtype=torch.uint8, device=dev)
+        assert lib.mm_fp4_act(x.data_ptr(), cols, tokens, cols, 0.5, xq.data_ptr(), xsc.data_ptr(), None)
+        if args.generic:
+            lib.mm_fp4_set_tensor(0)
+        fn = lambda i, st: lib.mm_fp4(pool.data_ptr() + (i % copies) * nb, rows, cols, xq.data_ptr(), xsc.data_ptr(), tokens,
+                                      1.0, y.data_ptr(), rows, st)
     elif op in ("mm_run", "mmq_group"):
         n16 = (tokens + 15) // 16 * 16
         flops = 2.0 * rows * cols * tokens

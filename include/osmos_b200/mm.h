@@ -128,6 +128,8 @@ bool mm_fp4_quant(const void *x, uint32_t bf16, uint32_t xs, uint32_t n, uint32_
 bool mm_fp4(const void *w, uint32_t rows, uint32_t cols, const void *q, const void *sc, uint32_t n, float scale,
             float *y, uint32_t ys, void *stream);
 void mm_fp4_set_tensor(int on);
+/* which route mm_fp4's last call took: 1 the block-scaled FP4 MMA, 0 the f16 product, -1 no call yet (for the tests) */
+int mm_fp4_last_route(void);
 /* Not in the reference (it never feeds quantized activations to an MXFP4 product: kernels/mm.hip:426 decodes the weights
    to f16): MXFP4 weights (QTYPE_MXFP4) times MXFP4 activations, W4A4, on tcgen05.mma kind::mxf4 (E2M1 x E2M1 under a UE8M0
    factor every 32 values on each side, F32 sums). `packed` is what ops_fp4_round(x, n * cols, 32, false, packed, cols)

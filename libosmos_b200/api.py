@@ -119,6 +119,7 @@ SIGNATURES = {
     "mm_fp4_quant": (B, [P, U32, U32, U32, U32, C.c_float, P, U32, P, P, P]),
     "mm_fp4": (B, [P, U32, U32, P, P, U32, C.c_float, P, U32, P]),
     "mm_fp4_set_tensor": (None, [C.c_int]),
+    "mm_fp4_last_route": (C.c_int, []),
     "mm_mxfp4": (B, [P, U32, U32, P, U32, C.c_float, P, U32, P]),
     "mm_fp4_desc": (U32, [U32, U32, U32]),
     # q8.h

@@ -9,8 +9,13 @@
 //   producers (8 warps)  the rows' blocks as the GGUF holds them -> the tensor core's operand layout: the nibbles
 //                        reordered from ggml's "low nibbles first, then high" to K order (two values a byte, the lower K
 //                        in the low nibble) into K-major core matrices of 8 rows x 16 bytes, and the block scales into
-//                        the scale-factor chunk layout (128 rows x 4 factors: byte (r % 32) * 16 + (r / 32) * 4 + f);
-//                        the tokens' codes and scales are already in K order and go to the same layouts by cp.async.
+//                        the scale-factor chunk layout (128 rows x 4 factors: byte (r % 32) * 16 + (r / 32) * 4 + f).
+//                        The raw bytes reach shared memory by the loader's tensor-map copies (a ring of its own, three
+//                        stages ahead), so a producer only ever waits on shared memory. The tokens' scale bytes go to
+//                        the chunk layout by 4-byte cp.async that nobody waits for (the stage's barrier counts them).
+//   loaders (2 warps)    one the rows' raw bytes (a box of 128 rows x 144 bytes a stage), one the tokens' codes, already in
+//                        K order: one tensor-map copy a stage, a box of 256 tokens x 128 bytes written with the 128-byte
+//                        swizzle, which the MMA's B descriptor names (an MMA's 32 bytes of K 32 bytes along the row).
 //   issuer (1 warp)      per 64 values of K: tcgen05.cp of the scale-factor chunks into tensor memory (32 lanes x 16
 //                        bytes, broadcast to the four lane quarters), then one tcgen05.mma M128 N(16 .. 256) K64 with
 //                        the chunks' addresses; tcgen05.commit onto the stage's "empty" barrier after a stage's four,
@@ -24,6 +29,10 @@
 // to the common exit and tensor memory is released.
 #include "fp4_tc_api.h"
 
+#include <cuda.h>
+
+#include <cstring>
+
 #include "common.cuh"
 
 namespace osmos {
@@ -32,17 +41,26 @@ namespace {
 
 constexpr int kM = 128, kNMax = 256;
 constexpr int kEpiWarps = 4, kProdWarps = 8;
-constexpr int kIssuerWarp = kEpiWarps;
-constexpr int kFirstProdWarp = kEpiWarps + 1;
+constexpr int kIssuerWarp = kEpiWarps;      // warp 4
+constexpr int kLoaderWarp = kEpiWarps + 1;  // warp 5: the tokens' codes by tensor-map copies
+constexpr int kRawWarp = kEpiWarps + 2;     // warp 6: the rows' raw bytes by tensor-map copies
+constexpr int kFirstProdWarp = kEpiWarps + 3;
 constexpr int kProdThreads = kProdWarps * kWarp;
-constexpr int kThreads = (kEpiWarps + 1 + kProdWarps) * kWarp;
-constexpr int kStages = 4;
+constexpr int kTasks = kM * 4 / kProdThreads;  // (row, MMA) tasks a producer thread takes a stage: 2
+constexpr int kThreads = (kEpiWarps + 3 + kProdWarps) * kWarp;
+constexpr int kStages = 3, kRawStages = 3;
 constexpr int kStepValues = 256, kMmaK = 64, kMmas = kStepValues / kMmaK;  // a stage: 256 values of K, four MMAs
-constexpr int kABytes = kM * kStepValues / 2;                              // 16 KB: 4 MMA tiles of 128 rows x 32 bytes
+constexpr int kATile = kM * 32 + 32;   // an MMA's A tile (128 rows x 32 bytes) and 32 bytes, so that the four tiles of a
+                                       // stage start 8 banks apart: a producer warp's stores (8 rows x 4 tiles) then
+                                       // fall on 32 different banks
+constexpr int kABytes = 17 * 1024;                                         // the 4 tiles, rounded up to B's 1024-byte alignment
 constexpr int kBBytes = kNMax * kStepValues / 2;                           // 32 KB
 constexpr int kChunk = 512;                                                // a scale-factor chunk: 128 rows x 4 factors
 constexpr int kSfaBytes = 4 * kChunk, kSfbBytes = 2 * 4 * kChunk;          // at most 4 chunks of K a stage; B: two row halves
-constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;     // 54 KB
+constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;     // 55 KB
+static_assert(4 * kATile <= kABytes && kABytes % 1024 == 0 && kStageBytes % 1024 == 0, "the tokens' tile starts on 1024 bytes");
+constexpr int kRawRow = 144;                // a row's raw bytes of one stage: 4 x 36 (NVFP4), or 8 x 17 = 136 and the 8 a
+constexpr int kRawBytes = kM * kRawRow;     // 16-byte window may start before them (MXFP4)
 constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
 // tensor memory: the accumulator's 256 columns, then the scale factors of one stage (a column = 4 factors of 32 rows)
 constexpr uint32_t kSfaCol = 256, kSfbCol = kSfaCol + 16, kTmemCols = 512;
@@ -76,12 +94,6 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
     else if (global_ns() - t0 > kWaitLimitNs) return false;
   }
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
 
 // shared-memory matrix descriptor: K-major, no swizzle, core matrices of 8 rows x 16 bytes; lbo: to the next 16 bytes of
 // K, sbo: to the next 8 rows (cute/arch/mma_sm100_desc.hpp: start >> 4, leading >> 4 at bit 16, stride >> 4 at bit 32,
@@ -89,6 +101,12 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ uint64_t tile_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) (lbo_bytes >> 4) << 16 | (uint64_t) (sbo_bytes >> 4) << 32 |
          (uint64_t) 1 << 46;
+}
+
+// the same for the tokens' tile as the tensor-map copy writes it with the 128-byte swizzle: rows of 128 bytes (a stage's K of
+// a token), 8 rows 1024 bytes on; an MMA's 32 bytes of K start 32 bytes further into the row (layout type 2 at bit 61)
+__device__ __forceinline__ uint64_t tile_desc_sw128(uint32_t addr) {
+  return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) 1 << 16 | (uint64_t) (1024u >> 4) << 32 | (uint64_t) 1 << 46 | (uint64_t) 2 << 61;
 }
 
 // where row r's 16 bytes `half` (0, 1) of an MMA's 32 bytes of K lie in an operand tile
@@ -116,7 +134,7 @@ struct Args {
 };
 
 struct Shared {
-  uint64_t full[kStages], empty[kStages], acc_full;
+  uint64_t full[kStages], empty[kStages], raw_full[kRawStages], raw_empty[kRawStages], acc_full;
   uint32_t tmem_base;
   int fail;
 };
@@ -124,7 +142,8 @@ struct Shared {
 // MX false: NVFP4 (a 36-byte block of 64 values: 4 UE4M3 bytes, then 8 bytes a 16); MX true: MXFP4 (a 17-byte block of
 // 32 values: the E8M0 byte, then 16 bytes)
 template <bool MX>
-__global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a) {
+__global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a, const __grid_constant__ CUtensorMap tmap,
+                                                             const __grid_constant__ CUtensorMap wmap) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ Shared sh;
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
@@ -136,7 +155,10 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a) {
   const uint64_t row_bytes = MX ? (uint64_t) (a.cols / 32) * 17 : (uint64_t) (a.cols / 64) * 36;
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdThreads), bar_init(&sh.empty[i], 1);
+    // a stage is full when every producer has stored its part of A (an arrival each), every producer's scale-byte copies
+    // have landed (an arrival each, made by the copy engine) and the loader's tensor-map copy has delivered its bytes
+    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdThreads + 1), bar_init(&sh.empty[i], 1);
+    for (int i = 0; i < kRawStages; i++) bar_init(&sh.raw_full[i], 1), bar_init(&sh.raw_empty[i], kProdThreads);
     bar_init(&sh.acc_full, 1);
     sh.fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -153,6 +175,23 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a) {
   if (warp >= (uint32_t) kFirstProdWarp) {
     // ================= producers =================
     const uint32_t pt = tid - kFirstProdWarp * kWarp;
+    const uint32_t raw0 = smem_addr(smem + kStages * kStageBytes);
+    // this thread's token of the block: a warp takes tokens 8 b .. 8 b + 7 of each of a half's four 32-token groups,
+    // whose words lie side by side in a chunk (32 lanes on 32 banks). A stage's scale bytes of a token are 16 (8)
+    // bytes in a row: one load.
+    const uint32_t sf_j = pt & 127u, sf_t128 = ((sf_j >> 3) & 3u) * 32u + (sf_j >> 5) * 8u + (sf_j & 7u);
+    const uint32_t sf_t = (pt >> 7) * 128u + sf_t128, sf_at = chunk_at(sf_t128);
+    const uint8_t* sf_row = a.as + (uint64_t) (c0 + (sf_t < n_valid ? sf_t : n_valid - 1)) * a.as_stride;
+    uint32_t sfw[kSfChunks];
+    auto read_sf = [&](uint32_t it) {
+      if constexpr (MX)
+        asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(sfw[0]), "=r"(sfw[1]) : "l"(sf_row + (uint64_t) it * 8u));
+      else
+        asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(sfw[0]), "=r"(sfw[1]), "=r"(sfw[2]), "=r"(sfw[3])
+                     : "l"(sf_row + (uint64_t) it * 16u));
+    };
+    if (sf_t < n_mma) read_sf(0);
     for (uint32_t it = 0; it < steps; it++) {
       const uint32_t stage = it % kStages, use = it / kStages;
       if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
@@ -160,33 +199,37 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a) {
         break;
       }
       const uint32_t st = smem_addr(smem + stage * kStageBytes);
-      const uint32_t sa = st, sb = st + kABytes, sfa = sb + kBBytes, sfb = sfa + kSfaBytes;
-      // B: a token's 128 bytes of codes as 8 pieces of 16 (MMA m's halves 0, 1), its scale bytes a chunk's word at a time
-      for (uint32_t i = pt; i < n_mma * 8u; i += kProdThreads) {
-        const uint32_t t = i >> 3, piece = i & 7u, tok = c0 + (t < n_valid ? t : n_valid - 1);
-        cp_async16(sb + (piece >> 1) * (kNMax * 32u) + tile_at(t, piece & 1u),
-                   a.aq + (uint64_t) tok * a.aq_stride + (uint64_t) it * 128u + piece * 16u);
+      const uint32_t sa = st, sfa = st + kABytes + kBBytes, sfb = sfa + kSfaBytes;
+      // the tokens' scale bytes of the stage (read a stage ahead), a word into each chunk
+      if (sf_t < n_mma) {
+#pragma unroll
+        for (uint32_t ch = 0; ch < kSfChunks; ch++)
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(sfb + (ch * 2u + (sf_t >> 7)) * kChunk + sf_at), "r"(sfw[ch]) : "memory");
+        if (it + 1 < steps) read_sf(it + 1);
       }
-      for (uint32_t i = pt; i < n_mma * kSfChunks; i += kProdThreads) {
-        const uint32_t t = i / kSfChunks, ch = i % kSfChunks, tok = c0 + (t < n_valid ? t : n_valid - 1);
-        cp_async4(sfb + (ch * 2u + (t >> 7)) * kChunk + chunk_at(t & 127u),
-                  a.as + (uint64_t) tok * a.as_stride + (uint64_t) it * (kSfChunks * 4u) + ch * 4u);
+      // the stage's raw rows have landed (the loader's tensor-map copy): a task = (row, 64 values of K = one MMA's 32
+      // bytes of the row), its raw bytes nine aligned words of the row's 144-byte window
+      const uint32_t rs = it % kRawStages;
+      if (!bar_wait(&sh.raw_full[rs], (it / kRawStages) & 1u)) {
+        sh.fail = 1;
+        break;
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      // A: a task = (row, 64 values of K = one MMA's 32 bytes of the row)
-      for (uint32_t task = pt; task < (uint32_t) (kM * kMmas); task += kProdThreads) {
-        const uint32_t row = task >> 2, mm = task & 3u;
+      const uint32_t lead = MX ? 8u * (it & 1u) : 0u;  // (MXFP4: the window starts 8 bytes before an odd stage's bytes)
+#pragma unroll
+      for (int u = 0; u < kTasks; u++) {
+        const uint32_t task = pt + (uint32_t) u * kProdThreads, row = task >> 2, mm = task & 3u;
+        const uint32_t off = row * kRawRow + lead + mm * (MX ? 34u : 36u), sh_bits = (off & 3u) * 8u;
+        uint32_t r[9];
+#pragma unroll
+        for (int i = 0; i < 9; i++)
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r[i]) : "r"(raw0 + rs * kRawBytes + (off & ~3u) + 4u * i));
         uint32_t q[8];  // the 64 values' nibbles in K order: 32 bytes
         if constexpr (!MX) {
-          const uint32_t* blk = (const uint32_t*) (a.w + (uint64_t) (row0 + row) * row_bytes + ((uint64_t) it * 4u + mm) * 36u);
-          uint32_t r[9];
-#pragma unroll
-          for (int i = 0; i < 9; i++) r[i] = __ldg(blk + i);
           // the four scale bytes: ggml reads a byte without its sign bit and 0x7F as zero
           uint32_t s = r[0] & 0x7F7F7F7Fu;
-          const uint32_t z = s ^ 0x7F7F7F7Fu;                                  // a zero byte where the scale was 0x7F
-          const uint32_t hit = ((z - 0x01010101u) & ~z & 0x80808080u) >> 7;    // 1 in such a byte (no borrow can reach a
-          s &= ~(hit * 0xFFu);                                                 // byte above a non-zero one falsely: z < 0x80)
+          const uint32_t z = s ^ 0x7F7F7F7Fu;                                // a zero byte where the scale was 0x7F
+          const uint32_t hit = ((z - 0x01010101u) & ~z & 0x80808080u) >> 7;  // 1 in such a byte (z's bytes are below 0x80:
+          s &= ~(hit * 0xFFu);                                               // a borrow only leaves a byte that is zero)
           asm volatile("st.shared.u32 [%0], %1;" ::"r"(sfa + mm * kChunk + chunk_at(row)), "r"(s) : "memory");
 #pragma unroll
           for (int sub = 0; sub < 4; sub++) {
@@ -194,17 +237,10 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a) {
             q[2 * sub] = k.x, q[2 * sub + 1] = k.y;
           }
         } else {
-          // two 17-byte blocks (34 bytes) that start 2 mod 4 bytes into a word for every other pair
-          const uint64_t off = (uint64_t) (row0 + row) * row_bytes + ((uint64_t) it * 4u + mm) * 34u;
-          const uint32_t* al = (const uint32_t*) (a.w + (off & ~(uint64_t) 3));
-          const uint32_t shb = (uint32_t) (off & 3u) * 8u;
-          uint32_t r[10];
-#pragma unroll
-          for (int i = 0; i < 9; i++) r[i] = __ldg(al + i);
-          r[9] = 0;
           uint32_t v[9];
 #pragma unroll
-          for (int i = 0; i < 9; i++) v[i] = __funnelshift_r(r[i], r[i + 1], shb);
+          for (int i = 0; i < 8; i++) v[i] = __funnelshift_r(r[i], r[i + 1], sh_bits);
+          v[8] = r[8] >> sh_bits;
           const uint32_t e0 = v[0] & 0xFFu, e1 = (v[4] >> 8) & 0xFFu;
           asm volatile("st.shared.u16 [%0], %1;" ::"r"(sfa + (mm >> 1) * kChunk + chunk_at(row) + 2u * (mm & 1u)),
                        "h"((uint16_t) (e0 | e1 << 8))
@@ -218,13 +254,52 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a) {
             q[4 * b] = k0.x, q[4 * b + 1] = k1.x, q[4 * b + 2] = k0.y, q[4 * b + 3] = k1.y;
           }
         }
-        const uint32_t at = sa + mm * (kM * 32u);
+        const uint32_t at = sa + mm * (uint32_t) kATile;
         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at + tile_at(row, 0)), "r"(q[0]), "r"(q[1]), "r"(q[2]), "r"(q[3]) : "memory");
         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at + tile_at(row, 1)), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
       }
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes before the tensor core's reads
       bar_arrive(&sh.full[stage]);
+      bar_arrive(&sh.raw_empty[rs]);  // (this thread has read its part of the raw rows)
+    }
+  } else if (warp == (uint32_t) kRawWarp) {
+    // ================= the rows' raw bytes =================
+    if (lane == 0) {
+      // the rows' raw bytes, a stage's 144-byte window of each of the block's 128 rows a copy, as far ahead as the raw
+      // ring is deep (the window of an odd MXFP4 stage starts 8 bytes early, on the 16 bytes a copy must start on)
+      const uint32_t raw0 = smem_addr(smem + kStages * kStageBytes);
+      for (uint32_t it = 0; it < steps; it++) {
+        const uint32_t rs = it % kRawStages, use = it / kRawStages;
+        if (use > 0 && !bar_wait(&sh.raw_empty[rs], (use - 1) & 1u)) {
+          sh.fail = 1;
+          break;
+        }
+        const uint32_t bar = smem_addr(&sh.raw_full[rs]);
+        const uint32_t x = MX ? (it * 136u) & ~15u : it * 144u;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t) kRawBytes) : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                         raw0 + rs * kRawBytes),
+                     "l"(&wmap), "r"(x), "r"(row0), "r"(bar)
+                     : "memory");
+      }
+    }
+  } else if (warp == (uint32_t) kLoaderWarp) {
+    // ================= the tokens' codes =================
+    if (lane == 0) {
+      for (uint32_t it = 0; it < steps; it++) {
+        const uint32_t stage = it % kStages, use = it / kStages;
+        if (use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) {
+          sh.fail = 1;
+          break;
+        }
+        const uint32_t bar = smem_addr(&sh.full[stage]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t) kBBytes) : "memory");
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                smem_addr(smem + stage * kStageBytes + kABytes)),
+            "l"(&tmap), "r"(it * 128u), "r"(c0), "r"(bar)
+            : "memory");
+      }
     }
   } else if (warp == (uint32_t) kIssuerWarp) {
     // ================= issuer =================
@@ -254,7 +329,9 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a) {
                          : "memory");
         }
         for (uint32_t mm = 0; mm < (uint32_t) kMmas; mm++) {
-          const uint64_t da = tile_desc(sa + mm * (kM * 32u), 128, 256), db = tile_desc(sb + mm * (kNMax * 32u), 128, 256);
+          // A: an MMA's two 16-byte pieces of K 128 bytes apart, 8 rows 256; B as the tensor-map copy laid it: a token a
+          // 128-byte row under the 128-byte swizzle, the MMA's 32 bytes of K at 32 mm
+          const uint64_t da = tile_desc(sa + mm * (uint32_t) kATile, 128, 256), db = tile_desc_sw128(sb + mm * 32u);
           const uint32_t accumulate = (it | mm) ? 1u : 0u;
           if constexpr (!MX) {  // a chunk a MMA: its four factors are the MMA's four 16s
             asm volatile(
@@ -327,13 +404,55 @@ uint32_t* status_word() {
   return at[d];
 }
 
+// the driver's tensor-map encoder, looked up once (no link against the driver library)
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled) p;
+  }
+  return fn;
+}
+
+// the tokens' codes as [token][byte] (n rows of cols / 2 bytes, a row `stride` bytes on): a box of 256 tokens x 128 bytes (a
+// stage's K), written with the 128-byte swizzle the MMA's B descriptor names; tokens past the last are filled with zeros
+bool codes_map(const void* aq, uint32_t n, uint32_t cols, uint32_t stride, CUtensorMap* tm) {
+  const EncodeTiled enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {cols / 2, n};
+  const cuuint64_t strides[1] = {stride};
+  const cuuint32_t box[2] = {128, (cuuint32_t) kNMax}, unit[2] = {1, 1};
+  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(aq), dims, strides, box, unit, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// the weight matrix as [row][byte]: a box of 128 rows x 144 bytes (a stage's raw bytes of each row)
+bool rows_map(const void* w, uint32_t rows, uint64_t row_bytes, CUtensorMap* tm) {
+  const EncodeTiled enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t) kRawRow, (cuuint32_t) kM}, unit[2] = {1, 1};
+  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides, box, unit, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <bool MX>
 int launch(const Args& a, cudaStream_t s) {
+  alignas(64) CUtensorMap tmap, wmap;
+  memset(&tmap, 0, sizeof tmap), memset(&wmap, 0, sizeof wmap);
+  const uint64_t row_bytes = MX ? (uint64_t) (a.cols / 32) * 17 : (uint64_t) (a.cols / 64) * 36;
+  if (!codes_map(a.aq, a.n, a.cols, a.aq_stride, &tmap) || !rows_map(a.w, a.rows, row_bytes, &wmap)) return 0;
   static bool sized[64] = {};  // (one record a template instance, one flag a device)
-  const int smem_bytes = kStages * kStageBytes;
+  const int smem_bytes = kStages * kStageBytes + kRawStages * kRawBytes;
   if (!allow_dynamic_smem(fp4_tc_kernel<MX>, smem_bytes, sized)) return 0;
   const dim3 grid(a.rows / kM, (a.n + kNMax - 1) / kNMax);
-  fp4_tc_kernel<MX><<<grid, kThreads, smem_bytes, s>>>(a);
+  fp4_tc_kernel<MX><<<grid, kThreads, smem_bytes, s>>>(a, tmap, wmap);
   return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
@@ -345,10 +464,12 @@ uint32_t instr_desc(bool mx, uint32_t n, uint32_t sf_id) {
 
 int try_launch(bool mx, const void* w, uint32_t rows, uint32_t cols, const void* aq, uint32_t aq_stride, const void* as,
                uint32_t as_stride, uint32_t n, float scale, float* y, uint32_t ys, void* stream) {
-  // whole 128-row tiles and 256-value steps; the tokens' rows copied 16 bytes (codes) and 4 bytes (scales) at a time
+  // whole 128-row tiles and 256-value steps; the tokens' codes copied 16 bytes at a time, a stage's scale bytes of a token read by one load
   if (!rows || rows % kM || !cols || cols % kStepValues || !n) return 0;
-  if (((uintptr_t) aq & 15u) || aq_stride % 16u || ((uintptr_t) as & 3u) || as_stride % 4u) return 0;
-  if (mx ? ((uintptr_t) w & 3u) != 0 || (cols / 32 * 17) % 4u != 0 : ((uintptr_t) w & 3u) != 0) return 0;
+  if (((uintptr_t) aq & 15u) || aq_stride % 16u || ((uintptr_t) as & (mx ? 7u : 15u)) || as_stride % (mx ? 8u : 16u)) return 0;
+  // the rows' raw bytes come by tensor-map copies: the matrix and its rows start on 16 bytes (a row of whole 256-value
+  // steps is 144 or 136 bytes a step: cols in 512s gives MXFP4 rows of whole 16s)
+  if (((uintptr_t) w & 15u) || (mx ? (uint64_t) (cols / 32) * 17 : (uint64_t) (cols / 64) * 36) % 16u) return 0;
   uint32_t* status = status_word();
   if (!status) return 0;
   const Args a{(const uint8_t*) w, (const uint8_t*) aq, (const uint8_t*) as, y, rows, cols, n, ys, aq_stride, as_stride, scale, status};

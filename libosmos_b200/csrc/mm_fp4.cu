@@ -188,6 +188,9 @@ extern "C" bool mm_fp4_act(const float* x, uint32_t xs, uint32_t n, uint32_t col
 }
 
 static int g_fp4_tensor = 1;  // mm_fp4_set_tensor: 0 keeps the product on the f16 tensor-core route (the tests compare the two)
+static int g_fp4_route = -1;  // the route mm_fp4's last call took: 1 the block-scaled FP4 MMA, 0 the f16 product
+
+extern "C" int mm_fp4_last_route(void) { return g_fp4_route; }
 
 extern "C" void mm_fp4_set_tensor(int on) { g_fp4_tensor = on; }
 extern "C" uint32_t mm_fp4_desc(uint32_t mx, uint32_t n, uint32_t sf_id) { return fp4_tc::instr_desc(mx != 0, n, sf_id); }
@@ -204,7 +207,11 @@ extern "C" bool mm_fp4(const void* w, uint32_t rows, uint32_t cols, const void* 
   if (!mm_fp4_ok() || !w || !q || !sc || !y || !n || !mm_tc::shape_ok(QTYPE_NVFP4, rows, cols) || (n > 1 && ys < rows) || ((uintptr_t) q & 7u))
     return false;
   if (g_fp4_tensor)  // the block-scaled FP4 MMA when it takes the shape (whole 128-row tiles, 256-value steps)
-    if (const int st = fp4_tc::try_launch(false, w, rows, cols, q, cols / 2, sc, cols / 16, n, scale, y, ys, stream)) return st > 0;
+    if (const int st = fp4_tc::try_launch(false, w, rows, cols, q, cols / 2, sc, cols / 16, n, scale, y, ys, stream)) {
+      g_fp4_route = 1;
+      return st > 0;
+    }
+  g_fp4_route = 0;
   const cudaStream_t s = stream_of(stream);
   const uint32_t most = n < MM_MAX_TOKENS ? n : MM_MAX_TOKENS, most16 = (most + MM_TILE - 1) / MM_TILE * MM_TILE;
   void* x16 = nullptr;  // the step's f16 activations: allocated and freed in stream order

@@ -171,6 +171,7 @@ def test_mm_fp4_tensor_route(lib, dev, oracle, rows, cols, n):
         lib.mm_fp4_set_tensor(tensor)
         y = torch.full((n, rows), float("nan"), dtype=torch.float32, device=dev)
         assert lib.mm_fp4(ptr(wd), rows, cols, ptr(qd), ptr(sd), n, wscale * gs, ptr(y), rows, None)
+        assert lib.mm_fp4_last_route() == tensor
         sync()
         outs.append(y.cpu().numpy().astype(np.float64))
     lib.mm_fp4_set_tensor(1)
