@@ -110,7 +110,8 @@ typedef struct EpPlan /* host memory; made once, read by every step */
   EpLayout lay;
   void *peer[EP_MAX_RANKS]; /* every rank's exchange buffer (lay.bytes, zeroed, 256-byte aligned) as mapped here */
   uint32_t *sync;           /* device, this rank's: 4 zeroed words ([0] the step counter, [1] [2] publish counters) */
-  float **rows;             /* device scratch [n_tok * k]: where each of this rank's rows goes */
+  float **rows;             /* device scratch, 2 * n_tok * k words of 8 bytes: where each of this rank's rows goes, and
+                               after those n_tok * k addresses the rows' routed weights (F32) */
   LaneLayer layer;          /* the layer (its experts' addresses as this rank holds them) */
   LaneScratch scratch;      /* lane_scratch_bind's, for n_tok tokens */
   uint32_t router;          /* EP_ROUTER_*: q4x_route's softmax, or ops_router's scores */

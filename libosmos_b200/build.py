@@ -9,6 +9,7 @@ nvcc cross-compiles without a GPU. The codebook tables are generated from the in
 import os
 import subprocess
 import sys
+import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
@@ -61,12 +62,16 @@ def build(force=False, verbose=False, jobs=8):
             cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
         else:
             cmd = ["gcc"] + CC_FLAGS + ["-c", src, "-o", obj]
-        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-        while len([p for _, p in procs if p.poll() is None]) >= jobs:
-            [p.wait() for _, p in procs if p.poll() is None][:1]
+        log = tempfile.TemporaryFile(mode="w+")  # (a file, not a pipe: a compiler that prints much never blocks on us)
+        procs.append((src, subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT, text=True), log))
+        while len([p for _, p, _ in procs if p.poll() is None]) >= jobs:
+            [p.wait() for _, p, _ in procs if p.poll() is None][:1]
     failed = False
-    for src, p in procs:
-        out, _ = p.communicate()
+    for src, p, log in procs:
+        p.wait()
+        log.seek(0)
+        out = log.read()
+        log.close()
         if p.returncode != 0 or verbose:
             sys.stderr.write("== %s\n%s\n" % (src, out))
         failed |= p.returncode != 0

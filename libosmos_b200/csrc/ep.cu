@@ -188,17 +188,18 @@ struct StepArgs {
   float rscale;
 };
 
-// A block a home token. Its first warp routes it (route.cuh) while all eight round its row to int8 (q8_round.cuh);
-// every result goes straight to its token-major place in every rank's buffer. The last block to finish releases this
-// rank's dispatch flag everywhere and advances the step counter.
+// A block a home token. Its last warp routes it (route.cuh) while the eight before it round its row to int8
+// (q8_round.cuh); every result goes straight to its token-major place in every rank's buffer. The last block to finish
+// releases this rank's dispatch flag everywhere and advances the step counter.
+constexpr int kRoundWarps = 8, kStepThreads = (kRoundWarps + 1) * kWarp;
 template <int R, int ROUTER>
-__global__ void __launch_bounds__(256) route_round_push_kernel(const StepArgs a, const float* __restrict__ x,
-                                                               const float* __restrict__ logits) {
+__global__ void __launch_bounds__(kStepThreads) route_round_push_kernel(const StepArgs a, const float* __restrict__ x,
+                                                                        const float* __restrict__ logits) {
   pdl_wait();  // (a dependent launch: the step before may still be reading what this one writes)
   pdl_launch_next();
   const uint32_t step = a.sync[0] + 1u, half = step & 1u;
   const uint32_t tl = blockIdx.x, t = a.rank * a.tokens + tl, lane = threadIdx.x % kWarp;
-  if (threadIdx.x < kWarp) {
+  if (threadIdx.x >= kRoundWarps * kWarp) {
     route::Pick p;
     if constexpr (ROUTER == EP_ROUTER_SOFTMAX) p = route::softmax_topk<R>(logits + (uint64_t) tl * a.n_exp, a.n_exp, a.k, lane);
     else if constexpr (ROUTER == EP_ROUTER_SIGMOID)
@@ -209,18 +210,19 @@ __global__ void __launch_bounds__(256) route_round_push_kernel(const StepArgs a,
         ((int32_t*) (a.peers.base[r] + a.lay.ids[half]))[t * a.k + lane] = (int32_t) p.id;
         ((float*) (a.peers.base[r] + a.lay.weights[half]))[t * a.k + lane] = p.w;
       }
-  }
-  const uint32_t per = a.dim / 8;
-  for (uint32_t c0 = 0; c0 < per; c0 += blockDim.x) {  // (whole warps: per is a multiple of 4, the bound is the block's)
-    const uint32_t c = c0 + threadIdx.x;
-    const bool live = c < per;
-    float v[8], scale;
-    load8(x + (uint64_t) tl * a.dim + (uint64_t) (live ? c : 0) * 8, v);
-    const uint2 codes = round_block8<false>(v, &scale);
-    if (!live) continue;
-    for (uint32_t r = 0; r < a.n_ranks; r++) {
-      *(uint2*) (a.peers.base[r] + a.lay.q[half] + (uint64_t) t * a.dim + (uint64_t) c * 8) = codes;
-      if (c % 4 == 0) ((float*) (a.peers.base[r] + a.lay.d[half]))[(uint64_t) t * (a.dim / 32) + c / 4] = scale;
+  } else {
+    const uint32_t per = a.dim / 8;
+    for (uint32_t c0 = 0; c0 < per; c0 += kRoundWarps * kWarp) {  // (whole warps: per is a multiple of 4)
+      const uint32_t c = c0 + threadIdx.x;
+      const bool live = c < per;
+      float v[8], scale;
+      load8(x + (uint64_t) tl * a.dim + (uint64_t) (live ? c : 0) * 8, v);
+      const uint2 codes = round_block8<false>(v, &scale);
+      if (!live) continue;
+      for (uint32_t r = 0; r < a.n_ranks; r++) {
+        *(uint2*) (a.peers.base[r] + a.lay.q[half] + (uint64_t) t * a.dim + (uint64_t) c * 8) = codes;
+        if (c % 4 == 0) ((float*) (a.peers.base[r] + a.lay.d[half]))[(uint64_t) t * (a.dim / 32) + c / 4] = scale;
+      }
     }
   }
   publish_step(a.peers, a.lay.flags_dispatch, a.rank, a.n_ranks, step, a.sync + 1, a.sync);
@@ -274,7 +276,7 @@ LaneEp lane_ep(const EpPlan* p, bool gathered_inputs, bool push) {
   LaneEp e{};
   e.step = p->sync;
   if (gathered_inputs)
-    e.half_q = p->lay.q[1] - p->lay.q[0], e.half_d = p->lay.d[1] - p->lay.d[0], e.half_scale = p->lay.weights[1] - p->lay.weights[0];
+    e.half_q = p->lay.q[1] - p->lay.q[0], e.half_d = p->lay.d[1] - p->lay.d[0];  // (the rows' scales: a table of the step's)
   if (push) {
     e.out_rows = p->rows, e.publish = true, e.flags_off = p->lay.flags_combine, e.rank = p->rank, e.n_ranks = p->n_ranks;
     e.counter = p->sync + 2;
@@ -328,7 +330,7 @@ extern "C" bool ep_plan_ok(const EpPlan* p) {
 extern "C" bool ep_route_round_push(const EpPlan* p, const float* x, const float* logits, void* stream) {
   if (!p || !x || !logits) return false;
   const StepArgs a = step_args(p);
-  const dim3 grid(a.tokens), block(256);
+  const dim3 grid(a.tokens), block(kStepThreads);
   const cudaStream_t s = stream_of(stream);
 #define ROUTE(R, KIND) launch_dependent(route_round_push_kernel<R, KIND>, grid, block, 0, s, a, x, logits) == cudaSuccess
 #define BY_REGS(KIND)                     \
@@ -351,11 +353,12 @@ extern "C" bool ep_lane_tables(const EpPlan* p, void* stream) {
   LaneTablesSync sy;
   sy.flags = (const uint32_t*) (mine + p->lay.flags_dispatch), sy.step = p->sync, sy.n_ranks = p->n_ranks;
   sy.half_bytes = p->lay.ids[1] - p->lay.ids[0];
+  sy.weights = (const float*) (mine + p->lay.weights[0]), sy.weights_half = p->lay.weights[1] - p->lay.weights[0];
   void* status = nullptr;
   if (cudaGetSymbolAddress(&status, g_peer_wait_status) != cudaSuccess) return false;
   sy.status = (uint32_t*) status;
   LaneRowHomes homes;
-  homes.rows = p->rows, homes.recv[0] = p->lay.recv[0], homes.recv[1] = p->lay.recv[1];
+  homes.rows = p->rows, homes.scale = (float*) (p->rows + (uint64_t) p->n_tok * p->layer.k), homes.recv[0] = p->lay.recv[0], homes.recv[1] = p->lay.recv[1];
   homes.tokens = p->n_tok / p->n_ranks, homes.dim = p->layer.dim;
   for (uint32_t r = 0; r < p->n_ranks; r++) homes.base[r] = (uint8_t*) p->peer[r];
   return lane_tables_launch((const int32_t*) (mine + p->lay.ids[0]), p->n_tok * p->layer.k, p->layer.k, p->layer.n_exp,
@@ -367,10 +370,11 @@ extern "C" bool ep_gate_up(const EpPlan* p, void* stream) {
   const LaneLayer& l = p->layer;
   const LaneTables& t = p->scratch.tab;
   const uint8_t* mine = (const uint8_t*) p->peer[p->rank];
-  return q8_gate_up_ep(l.type_gu, t.w[0], t.w[1], t.cnt, t.xrow, t.tok, t.pair, t.max_entries, LANE_MAX_TOKENS, l.ff, l.dim,
+  // (a row's scale is its routed weight, laid out by row by the tables' kernel: no index between a row and its scale)
+  return q8_gate_up_ep(l.type_gu, t.w[0], t.w[1], t.cnt, t.xrow, t.tok, nullptr, t.max_entries, LANE_MAX_TOKENS, l.ff, l.dim,
                        (const int8_t*) (mine + p->lay.q[0]), (const float*) (mine + p->lay.d[0]),
-                       (const float*) (mine + p->lay.weights[0]), l.lim, p->scratch.hh, l.ff, lane_ep(p, true, false), false,
-                       stream_of(stream));
+                       (const float*) (p->rows + (uint64_t) p->n_tok * l.k), l.lim, p->scratch.hh, l.ff,
+                       lane_ep(p, true, false), false, stream_of(stream));
 }
 
 extern "C" bool ep_down_push(const EpPlan* p, void* stream) {

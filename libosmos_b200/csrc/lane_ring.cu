@@ -10,8 +10,8 @@
 //   - the weights come by bulk copies into a ring of slots that belongs to the warp: it waits on its own mbarriers,
 //     and refills a slot the moment its lanes have read it. After the start-up (codebooks, the list of live entries,
 //     their matrix pointers) the block never meets again.
-// Tasks are dealt round-robin to all warps of the grid in (entry, rows) order, so a block's warps stream neighbouring
-// rows of the same matrices.
+// Tasks are dealt round-robin to all warps of the grid in (entry, rows) order, block by block (task i to block
+// i % blocks), so the blocks' shares differ by one task at most.
 #include "lane_ring_api.h"
 
 #include "dispatch.cuh"
@@ -140,9 +140,10 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
   const uint32_t sub = lane % L, grp = lane / L;
   const uint32_t nblk = a.cols / 32, row_bytes = (a.cols / 256) * SB, nbl = nblk / L;
-  const uint32_t S = a.slots, RC = a.slot_rows, TS = a.task_slots;
+  const uint32_t S = a.slots, RC = a.slot_rows;
   uint16_t* list = (uint16_t*) (smem + a.list_off);
   const uint8_t** wptr = (const uint8_t**) (smem + a.ptr_off);
+  int2* meta = (int2*) (wptr + a.n_entries * (FUSED ? 2 : 1));  // an entry's (live tokens, first row): no trip to the tables a task
   uint8_t* ring = smem + a.ring_off + warp * S * a.slot_bytes;
 
   if (lane == 0) {
@@ -173,7 +174,9 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
       const uint32_t m = base + tid;
       uint32_t mine = 0;
       if (m < a.n_entries) {
-        mine = (live_count(m) + NT - 1) / NT;
+        const uint32_t c = live_count(m);
+        meta[m] = make_int2((int) c, a.xrow[m]);
+        mine = (c + NT - 1) / NT;
         const uint8_t* g = a.wg[m];
         wptr[m * M] = g;
         if (mine && ((uintptr_t) g & 15u)) aligned = false;
@@ -209,9 +212,15 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
     if (tid == 0) atomicOr(a.status, 2u);
     return;
   }
+  // a task: at most a.task_slots slots, halved while the launch has fewer than four tasks a warp (few entries, as a
+  // rank of many has: finer tasks fill the last round of warps better than they cost in activation loads)
+  const uint32_t stride = gridDim.x * kWarps;
+  uint32_t TS = a.task_slots;
+  while (TS > 1 && (uint32_t) s_pairs * (a.rows / (RC * TS)) < 4u * stride) TS >>= 1;
   const uint32_t tpp = a.rows / (RC * TS);  // tasks an (entry, token group)
   const uint32_t tasks = (uint32_t) s_pairs * tpp;
-  const uint32_t gw = blockIdx.x * kWarps + warp, stride = gridDim.x * kWarps;
+  // this warp's place in the deal: neighbouring tasks go to different blocks, so every block gets the same share
+  const uint32_t gw = warp * gridDim.x + blockIdx.x;
 
   // slot q of this warp's sequence: slot q % TS of its task q / TS
   auto issue = [&](uint32_t q) {  // one lane
@@ -317,8 +326,9 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
     if (tk >= tasks) break;
     const uint32_t pair = tk / tpp, task_row0 = (tk - pair * tpp) * RC * TS;
     const uint32_t v = list[pair], m = v & 0x3FFu, g = v >> 10;
-    const uint32_t cnt = live_count(m), live = cnt - g * NT < (uint32_t) NT ? cnt - g * NT : (uint32_t) NT;
-    const uint32_t r0 = (uint32_t) a.xrow[m] + g * NT;
+    const int2 me = meta[m];
+    const uint32_t cnt = (uint32_t) me.x, live = cnt - g * NT < (uint32_t) NT ? cnt - g * NT : (uint32_t) NT;
+    const uint32_t r0 = (uint32_t) me.y + g * NT;
     // the task's tokens: the lane's blocks of their int8 rows, their scales, the routed weights
     int xq[NT][NB][8];
     float xd[NT][NB], scale[NT];
@@ -410,7 +420,7 @@ int launch(const Request& r, cudaStream_t s) {
   Args a{};
   a.list_off = (uint32_t) ((Rep<T>::bytes + 127) & ~127);
   a.ptr_off = a.list_off + kMaxEntries * (8 / NT) * 2;
-  a.ring_off = (a.ptr_off + r.n_entries * M * 8 + 127u) & ~127u;
+  a.ring_off = (a.ptr_off + r.n_entries * (M * 8 + 8) + 127u) & ~127u;  // (pointers, then (count, first row))
   if (a.ring_off + 16u >= kSmemLimit) return 0;
   // a slot: the fewest rows (a multiple of the rows a pass takes) whose bytes are a multiple of 16 and reach about 3 KB
   uint32_t rc = RU;

@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
   uint16_t* list = (uint16_t*) (smem + a.list_off);
   const uint8_t** wptr = (const uint8_t**) (smem + a.ptr_off);
+  int2* meta = (int2*) (wptr + a.n_entries);  // an entry's (live tokens, first row): no trip to the tables a task
   uint8_t* xs = smem + a.x_off + warp * kXBytes;
   uint8_t* ring = smem + a.ring_off + warp * kSlots * a.slot_bytes;
 
@@ -88,7 +89,9 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       const uint32_t m = base + tid;
       uint32_t mine = 0;
       if (m < a.n_entries) {
-        mine = (live_count(m) + kNT - 1) / kNT;
+        const uint32_t c = live_count(m);
+        meta[m] = make_int2((int) c, a.xrow[m]);
+        mine = (c + kNT - 1) / kNT;
         const uint8_t* g = a.w[m];
         wptr[m] = g;
         if (mine && ((uintptr_t) g & 15u)) aligned = false;
@@ -120,6 +123,7 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
   }
   const uint32_t tpp = a.rows / kWarp;  // tasks an (entry, token group): 32 rows each
   const uint32_t tasks = (uint32_t) s_pairs * tpp;
+  // (a block's warps take neighbouring tasks: mostly the same entry and tokens, whose activations then come from L1)
   const uint32_t gw = blockIdx.x * kWarps + warp, stride = gridDim.x * kWarps;
 
   auto issue = [&](uint32_t n) {  // one lane: the warp's n-th task into slot n % kSlots
@@ -174,13 +178,36 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
 
   using I1 = std::integral_constant<int, 1>;
   using I2 = std::integral_constant<int, kNT>;
+  // a task's tokens: this lane's 16 bytes of each int8 row and, on the first sixteen lanes, a block scale - read a task
+  // ahead into registers, so that the trip to L2 runs under the task before
+  auto fetch = [&](uint32_t n, int4 (&xq)[kNT], float (&xd)[kNT]) {
+    const uint32_t tk = gw + n * stride;
+    if (tk >= tasks) return;
+    const uint32_t v = list[tk / tpp], g = v >> 10;
+    const int2 me = meta[v & 0x3FFu];
+    const uint32_t left = (uint32_t) me.x - g * kNT, r0 = (uint32_t) me.y + g * kNT;
+#pragma unroll
+    for (int t = 0; t < kNT; t++)
+      if ((uint32_t) t < left) {
+        const uint32_t r = r0 + t;
+        const uint64_t xr = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
+        xq[t] = __ldg((const int4*) (in_q + xr * kCols) + lane);
+        if (lane < (uint32_t) kBlocks) xd[t] = __ldg(in_d + xr * kBlocks + lane);
+      }
+  };
+  int4 xq[kNT];
+  float xd[kNT];
+#pragma unroll
+  for (int t = 0; t < kNT; t++) xq[t] = make_int4(0, 0, 0, 0), xd[t] = 0.0f;
+  fetch(0, xq, xd);
   for (uint32_t n = 0;; n++) {
     const uint32_t tk = gw + n * stride;
     if (tk >= tasks) break;
     const uint32_t pair = tk / tpp, row0 = (tk - pair * tpp) * kWarp;
     const uint32_t v = list[pair], m = v & 0x3FFu, g = v >> 10;
-    const uint32_t cnt = live_count(m), live = cnt - g * kNT < (uint32_t) kNT ? cnt - g * kNT : (uint32_t) kNT;
-    const uint32_t r0 = (uint32_t) a.xrow[m] + g * kNT;
+    const int2 me = meta[m];
+    const uint32_t cnt = (uint32_t) me.x, live = cnt - g * kNT < (uint32_t) kNT ? cnt - g * kNT : (uint32_t) kNT;
+    const uint32_t r0 = (uint32_t) me.y + g * kNT;
     // the task's tokens into the warp's piece of shared memory: 16 bytes a lane a token, then the scales
     __syncwarp();  // (every lane has finished the last task's reads)
     float* orow[kNT];  // where each token's results go: looked up now, used when the task's rows are done
@@ -189,13 +216,12 @@ __global__ void __launch_bounds__(kThreads, 1) lane_rows_kernel(const Args a) {
       const uint32_t ro = r0 + ((uint32_t) t < live ? (uint32_t) t : live - 1);
       orow[t] = a.ep.out_rows ? a.ep.out_rows[ro] : a.out + (uint64_t) ro * a.out_stride;
       if ((uint32_t) t < live) {
-        const uint32_t r = r0 + t;
-        const uint64_t xr = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
-        ((int4*) (xs + t * kCols))[lane] = __ldg((const int4*) (in_q + xr * kCols) + lane);
-        if (lane < (uint32_t) kBlocks) ((float*) (xs + kNT * kCols))[t * kBlocks + lane] = __ldg(in_d + xr * kBlocks + lane);
+        ((int4*) (xs + t * kCols))[lane] = xq[t];
+        if (lane < (uint32_t) kBlocks) ((float*) (xs + kNT * kCols))[t * kBlocks + lane] = xd[t];
       }
     }
     __syncwarp();
+    fetch(n + 1, xq, xd);
     const uint32_t slot = n % kSlots;
     if (!bar_wait(&full[warp][slot], (n / kSlots) & 1u)) {  // a copy never landed: report it and leave
       if (lane == 0) atomicOr(a.status, 1u);
@@ -240,7 +266,7 @@ int launch(const Request& r, cudaStream_t s) {
   Args a{};
   a.list_off = (uint32_t) ((Rep<T>::bytes + 127) & ~127);
   a.ptr_off = a.list_off + kMaxEntries * (8 / kNT) * 2;
-  a.x_off = (a.ptr_off + r.n_entries * 8 + 127u) & ~127u;
+  a.x_off = (a.ptr_off + r.n_entries * 16 + 127u) & ~127u;  // (pointers, then (count, first row))
   a.ring_off = (a.x_off + kWarps * kXBytes + 127u) & ~127u;
   a.slot_bytes = kWarp * kNSB * Super<T>::bytes;
   const uint32_t total = a.ring_off + kWarps * kSlots * a.slot_bytes + 16u;

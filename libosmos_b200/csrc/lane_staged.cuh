@@ -82,20 +82,43 @@ template <uint32_t T> struct RepLuts {
   }
 };
 
-template <uint32_t T> __device__ inline RepLuts<T> build_luts(uint8_t* smem, int threads = kThreads) {
+// every word of a codebook read once, a thread's loads issued together (a first touch of the table costs a trip to
+// L2: one trip, not one a copy), each written COPIES times side by side
+template <int COPIES, class W>
+__device__ __forceinline__ void replicate(W* dst, const W* src, int words, int threads) {
+  constexpr int U = 4;
+  for (int i0 = threadIdx.x; i0 < words; i0 += threads * U) {
+    W v[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) v[u] = i0 + u * threads < words ? src[i0 + u * threads] : W(0);
+#pragma unroll
+    for (int u = 0; u < U; u++)
+      if (i0 + u * threads < words) {
+#pragma unroll
+        for (int c = 0; c < COPIES; c++) dst[(i0 + u * threads) * COPIES + c] = v[u];
+      }
+  }
+}
+
+// the grids; returns where the sign masks' table starts
+template <uint32_t T> __device__ inline uint8_t* build_grids(uint8_t* smem, int threads, RepLuts<T>& l) {
   const uint32_t lane = threadIdx.x % kWarp;
-  RepLuts<T> l{0, 0, 0};
+  l.g64 = l.g32 = l.mask = 0;
   if constexpr (Rep<T>::g64 > 0) {
-    uint64_t* d = (uint64_t*) smem;
-    const uint64_t* s = global_grid64<T>();
-    for (int i = threadIdx.x; i < GridOf<T>::words64 * Rep<T>::g64; i += threads) d[i] = s[i / Rep<T>::g64];
-    l.g64 = smem_addr(d) + (lane & (Rep<T>::g64 - 1)) * 8, smem += GridOf<T>::words64 * Rep<T>::g64 * 8;
+    replicate<Rep<T>::g64>((uint64_t*) smem, global_grid64<T>(), GridOf<T>::words64, threads);
+    l.g64 = smem_addr(smem) + (lane & (Rep<T>::g64 - 1)) * 8, smem += GridOf<T>::words64 * Rep<T>::g64 * 8;
   }
   if constexpr (Rep<T>::g32 > 0) {
-    uint32_t* d = (uint32_t*) smem;
-    for (int i = threadIdx.x; i < GridOf<T>::words32 * 32; i += threads) d[i] = osmos_grid_iq3xxs[i / 32];
-    l.g32 = smem_addr(d) + lane * 4, smem += GridOf<T>::words32 * 32 * 4;
+    replicate<32>((uint32_t*) smem, osmos_grid_iq3xxs, GridOf<T>::words32, threads);
+    l.g32 = smem_addr(smem) + lane * 4, smem += GridOf<T>::words32 * 32 * 4;
   }
+  return smem;
+}
+
+template <uint32_t T> __device__ inline RepLuts<T> build_luts(uint8_t* smem, int threads = kThreads) {
+  const uint32_t lane = threadIdx.x % kWarp;
+  RepLuts<T> l;
+  smem = build_grids<T>(smem, threads, l);
   if constexpr (Rep<T>::mask > 0) {
     uint4* d = (uint4*) smem;
     for (int i = threadIdx.x; i < 128 * 8; i += threads) {
@@ -110,8 +133,8 @@ template <uint32_t T> __device__ inline RepLuts<T> build_luts(uint8_t* smem, int
 
 // The same tables with the sign masks as 8-byte (m0, m1) entries in 16 copies (a half-warp's lanes each their own
 // banks; an 8-byte read is half the shared-memory passes of the 16-byte one, the two "+ 1" words then cost an AND
-// each): for the kernels whose every lane looks masks up at once. Built over build_luts' 16 KB mask table; every
-// thread of the block calls it (two barriers).
+// each): for the kernels whose every lane looks masks up at once. In the place of build_luts' 16 KB mask table; every
+// thread of the block calls it (it ends on a barrier: the tables are complete when it returns).
 template <uint32_t T> struct RepLuts2 : RepLuts<T> {
   uint32_t mask2;
   __device__ __forceinline__ uint2 sign_masks2(uint32_t s7) const { return lds64(mask2 + s7 * 128u); }
@@ -122,18 +145,21 @@ template <uint32_t T> struct RepLuts2 : RepLuts<T> {
 };
 template <uint32_t T> __device__ inline RepLuts2<T> build_luts2(uint8_t* smem, int threads) {
   RepLuts2<T> l;
-  (RepLuts<T>&) l = build_luts<T>(smem, threads);
+  smem = build_grids<T>(smem, threads, l);
   l.mask2 = 0;
   if constexpr (Rep<T>::mask > 0) {
-    const uint32_t lane = threadIdx.x % kWarp, base = l.mask - (lane & 7u) * 16u;
-    __syncthreads();  // the table's first form is complete and nobody reads it
-    for (uint32_t i = threadIdx.x; i < 128u * 16u; i += (uint32_t) threads) {
-      const uint32_t sg = osmos_ksigns[i / 16u];
-      asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(base + i * 8u), "r"(byte_mask4(sg)), "r"(byte_mask4(sg >> 4)) : "memory");
+    const uint32_t lane = threadIdx.x % kWarp, base = smem_addr(smem);
+    l.mask = base + (lane & 7u) * 16u;
+    // a thread a quarter of an entry's copies: one byte read, four stores
+    for (uint32_t i = threadIdx.x; i < 128u * 4u; i += (uint32_t) threads) {
+      const uint32_t sg = osmos_ksigns[i / 4u], m0 = byte_mask4(sg), m1 = byte_mask4(sg >> 4);
+#pragma unroll
+      for (uint32_t c = 0; c < 4u; c++)
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(base + (i * 4u + c) * 8u), "r"(m0), "r"(m1) : "memory");
     }
-    __syncthreads();
     l.mask2 = base + (lane & 15u) * 8u;
   }
+  __syncthreads();
   return l;
 }
 

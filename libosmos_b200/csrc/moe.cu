@@ -278,11 +278,20 @@ __global__ void __launch_bounds__(kTableThreads) lane_tables_kernel(const int32_
     if (r < 0) continue;
     t.tok[r] = (int32_t) (i / k), t.pair[r] = (int32_t) i;
     if (homes.rows) homes.rows[r] = home_row(homes, step & 1u, i, k);
+    if (homes.scale) homes.scale[r] = ((const float*) ((const uint8_t*) sy.weights + (step & 1u) * sy.weights_half))[i];
   }
-  // each token's rows in order, in the same launch
+  // each token's rows in order, in the same launch, a thread a pick: its place among its token's picks is the number
+  // of them with a smaller row (the picks without a row, -1, compare as the largest; equal ones keep their order)
   __syncthreads();
-  for (uint32_t tk = threadIdx.x; tk < n / k; tk += kTableThreads)
-    order_token([&](uint32_t i) { return srow[i]; }, tk, k, t.order);
+  for (uint32_t i = threadIdx.x; i < n; i += kTableThreads) {
+    const uint32_t first = i / k * k, mine = (uint32_t) srow[i];
+    uint32_t place = 0;
+    for (uint32_t j = first; j < first + k; j++) {
+      const uint32_t other = (uint32_t) srow[j];
+      place += other < mine || (other == mine && j < i);
+    }
+    t.order[first + place] = (int32_t) mine;
+  }
 }
 
 __global__ void __launch_bounds__(kThreads) lane_place_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_t k,

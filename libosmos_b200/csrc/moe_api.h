@@ -15,11 +15,15 @@ struct LaneTablesSync {
   const uint32_t* step = nullptr;   // the step counter (device): the value the flags must have reached
   uint32_t n_ranks = 0;
   uint64_t half_bytes = 0;          // an odd step's ids lie this many bytes after the even steps'
+  const float* weights = nullptr;   // the picks' routed weights (an even step's; an odd step's weights_half bytes on)
+  uint64_t weights_half = 0;
   uint32_t* status = nullptr;       // bit 0 set when a wait ran out
 };
 
 struct LaneRowHomes {
   float** rows = nullptr;  // out [picks]: where row r's result goes (NULL: not wanted)
+  float* scale = nullptr;  // out [picks]: row r's routed weight (NULL: not wanted) - a row's gate / up scale without the
+                           // trip through its pick index
   uint8_t* base[16] = {};  // every rank's exchange buffer as mapped here
   uint64_t recv[2] = {};   // the receive block's offset in a buffer, by step parity
   uint32_t tokens = 0;     // home tokens a rank

@@ -139,7 +139,7 @@ class EpMoeLane:
             self.lay = lay
             self.peer = PeerBuffers(lib, dist, dev, rank, world, lay.bytes)
             self.sync = torch.zeros(4, dtype=torch.int32, device=dev)
-            self.rows = torch.zeros(picks, dtype=torch.int64, device=dev)
+            self.rows = torch.zeros(2 * picks, dtype=torch.int64, device=dev)  # (the rows' homes, then their weights)
             self.plans = []
             for layer in self.local.layers:
                 p = api.EpPlan()

@@ -94,7 +94,7 @@ def test_emulated_ranks_have_the_single_gpu_bits(lib, dev, world):
         e0, e1 = ep.expert_range(r, world, cfg["n_exp"])
         local = runner.MoeLane(lib, cfg, dev, max_tok=n_tok, host_tensors=host, expert_range=(e0, e1))
         sync = torch.zeros(4, dtype=torch.int32, device=dev)
-        rows = torch.zeros(n_tok * k, dtype=torch.int64, device=dev)
+        rows = torch.zeros(2 * n_tok * k, dtype=torch.int64, device=dev)
         p = api.EpPlan()
         p.rank, p.n_ranks, p.n_tok, p.expert0, p.expert1, p.lay = r, world, n_tok, e0, e1, lay
         for q in range(world):
