@@ -33,6 +33,19 @@ def test_library_exports_every_declared_function(lib):
     assert not unbound, "no ctypes signature for: %s" % unbound
 
 
+def test_library_leaves_none_of_its_own_symbols_undefined(lib):
+    """a source file dropped from the build while another still calls into it links (a shared library may have
+    undefined symbols) and only fails when the call is made: every undefined symbol must be somebody else's"""
+    import shutil
+    import subprocess
+    if not shutil.which("nm"):
+        import pytest
+        pytest.skip("no nm")
+    out = subprocess.run(["nm", "-D", "--undefined-only", lib.path], capture_output=True, text=True, check=True).stdout
+    ours = [line for line in out.splitlines() if "osmos" in line]
+    assert not ours, ours
+
+
 def test_missing_library_fails_loudly(tmp_path):
     try:
         api.Lib(str(tmp_path / "nope.so"))
