@@ -1,11 +1,12 @@
 // Q4_K x int8 on the 5th-generation tensor cores (include/osmos_b200/mmq.h): tcgen05.mma kind::i8 with the int32
 // group dots in tensor memory, drained group by group into the contract's F32 epilogue.
 //
-// A block computes 128 weight rows x 128 tokens of one matrix. Twenty warps, three roles:
-//   producers (3 warps)   per 256-value step: unpack the rows' Q4_K nibbles of that superblock into int8 operand
+// A block computes 128 weight rows x 128 tokens of one matrix. Twenty warps, four roles:
+//   loader (1 warp)       per 256-value step: the rows' raw 144-byte blocks by bulk copies into a ring of three
+//   producers (2 warps)   per 256-value step: unpack the rows' Q4_K nibbles of that superblock into int8 operand
 //                         tiles (one 128 x 32 tile a 32-value group, K-major core matrices of 8 rows x 16 bytes),
 //                         copy the tokens' int8 codes into the same layout (cp.async), and their dx / sx beside them; then a
-//                         proxy fence and an arrive on the stage's "full" mbarrier. Three stages deep.
+//                         proxy fence and an arrive on the stage's "full" mbarrier. Two stages deep.
 //   issuer (1 warp)       per group one tcgen05.mma M128 N128 K32 that OVERWRITES one of four 128-column accumulators
 //                         in tensor memory, then tcgen05.commit onto that accumulator's "full" mbarrier; after a
 //                         step's eight groups a commit onto the stage's "empty" mbarrier (which also counts the sixteen
@@ -30,16 +31,19 @@ namespace mmq_tc {
 namespace {
 
 constexpr int kM = 128, kN = 128;              // rows and tokens a block
-constexpr int kEpiWarps = 16, kProdWarps = 3;
+constexpr int kEpiWarps = 16, kProdWarps = 2;
 constexpr int kCols = kN / (kEpiWarps / 4);    // tokens an epilogue thread: 32
 constexpr int kIssuerWarp = kEpiWarps;         // warp 16
-constexpr int kFirstProdWarp = kEpiWarps + 1;  // warps 17 .. 19
+constexpr int kLoaderWarp = kEpiWarps + 1;     // warp 17: the rows' raw blocks, by bulk copies
+constexpr int kFirstProdWarp = kEpiWarps + 2;  // warps 18, 19
 constexpr int kProdThreads = kProdWarps * kWarp;
-constexpr int kThreads = (kEpiWarps + 1 + kProdWarps) * kWarp;
-constexpr int kStages = 3, kAccs = 4;
+constexpr int kThreads = (kEpiWarps + 2 + kProdWarps) * kWarp;
+constexpr int kStages = 2, kRawStages = 3, kAccs = 4;
 constexpr int kGroups = 8, kBlockBytes = 144, kBlockValues = 256;
 constexpr int kTileBytes = kM * MMQ_GROUP;     // one operand tile: 128 rows x 32 int8 = 4 KB
-constexpr int kStageBytes = 2 * kGroups * kTileBytes + 2 * kGroups * kN * 4;  // A, B, dx, sx: 72 KB
+constexpr int kHeadOff = 2 * kGroups * kTileBytes + 2 * kGroups * kN * 4;  // after A, B, dx, sx: the rows' 16-byte block heads
+constexpr int kStageBytes = kHeadOff + kM * 16;                            // 74 KB
+constexpr int kRawBytes = kM * kBlockBytes;    // a step's raw blocks, a row's after another: 18 KB
 constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
 
 __device__ uint32_t g_status;
@@ -72,6 +76,29 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// packed F32 pairs: one instruction, two IEEE operations
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // 16 bytes global -> shared, asynchronously (both 16-byte aligned)
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
@@ -98,7 +125,7 @@ struct Args {
 };
 
 struct Shared {
-  uint64_t full[kStages], empty[kStages], acc_full[kAccs], acc_empty[kAccs];
+  uint64_t full[kStages], empty[kStages], acc_full[kAccs], acc_empty[kAccs], raw_full[kRawStages], raw_empty[kRawStages];
   uint32_t tmem_base;
   int fail;
 };
@@ -109,6 +136,10 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
   const uint32_t m = blockIdx.y, n_tok = (uint32_t) a.cnt[m], row0 = blockIdx.x * kM, c0 = blockIdx.z * kN;
   if (c0 >= n_tok) return;  // the whole block, before anything is allocated
+  if ((uintptr_t) a.wt[m] & 15u) {  // the rows' blocks come by 16-byte-aligned bulk copies: the block stands down
+    if (tid == 0) atomicOr(a.status, 2u);
+    return;
+  }
   const uint32_t n_valid = n_tok - c0 < (uint32_t) kN ? n_tok - c0 : (uint32_t) kN;
   const uint32_t n_valid16 = (n_valid + 15u) & ~15u;
   const uint32_t nb = a.cols / kBlockValues, groups = a.cols / MMQ_GROUP;
@@ -117,8 +148,9 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
   const uint32_t s0 = a.soff[m] + c0;  // the block's first slot: a multiple of 16
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdWarps * kWarp), bar_init(&sh.empty[i], 1 + kEpiWarps);
+    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdThreads), bar_init(&sh.empty[i], 1 + kEpiWarps);
     for (int i = 0; i < kAccs; i++) bar_init(&sh.acc_full[i], 1), bar_init(&sh.acc_empty[i], kEpiWarps);
+    for (int i = 0; i < kRawStages; i++) bar_init(&sh.raw_full[i], 1), bar_init(&sh.raw_empty[i], kProdThreads);
     sh.fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -146,7 +178,31 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
     return 0;
   };
 
-  if (warp >= (uint32_t) kFirstProdWarp) {
+  uint8_t* const raw = smem + kStages * kStageBytes;  // the raw ring
+  if (warp == (uint32_t) kLoaderWarp) {
+    // ================= the rows' raw blocks =================
+    // a step's 144-byte block of each of the tile's 128 rows, a bulk copy a row, as far ahead as the raw ring is deep:
+    // the trip to memory is over when the producers want the bytes
+    for (uint32_t it = 0; it < nb; it++) {
+      const uint32_t rs = it % kRawStages, use = it / kRawStages;
+      if (use > 0 && !bar_wait(&sh.raw_empty[rs], (use - 1) & 1u)) {
+        sh.fail = 1;
+        break;
+      }
+      uint32_t p;
+      bool last;
+      const uint32_t b = block_of(it, p, last);
+      const uint32_t bar = smem_addr(&sh.raw_full[rs]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // (the producers' reads before these writes)
+      if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t) kRawBytes) : "memory");
+      __syncwarp();
+      for (uint32_t r = lane; r < (uint32_t) kM; r += kWarp)
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         smem_addr(raw + rs * kRawBytes + r * kBlockBytes)),
+                     "l"(w + r * row_bytes + (uint64_t) b * kBlockBytes), "r"((uint32_t) kBlockBytes), "r"(bar)
+                     : "memory");
+    }
+  } else if (warp >= (uint32_t) kFirstProdWarp) {
     // ================= producers =================
     const uint32_t pt = tid - kFirstProdWarp * kWarp;  // 0 .. kProdThreads - 1
     for (uint32_t it = 0; it < nb; it++) {
@@ -180,33 +236,31 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
       }
-      // A: a task = (row, pair of groups): 32 bytes of nibbles -> the low nibbles' group and the high nibbles' group;
-      // three tasks' loads go out before their stores
-      for (uint32_t base = 0; base < 4u * kM; base += 3u * kProdThreads) {
-        uint4 r0[3], r1[3];
-#pragma unroll
-        for (int u = 0; u < 3; u++) {
-          const uint32_t task = base + pt + kProdThreads * u, row = task >> 2, gp = task & 3u;
-          if (task < 4u * kM) {
-            const uint4* src = (const uint4*) (w + row * row_bytes + (uint64_t) b * kBlockBytes + 16 + gp * 32);
-            r0[u] = __ldg(src), r1[u] = __ldg(src + 1);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 3; u++) {
-          const uint32_t task = base + pt + kProdThreads * u, row = task >> 2, gp = task & 3u;
-          if (task < 4u * kM) {
-            const uint32_t at = (row >> 3) * 256 + (row & 7u) * 16;
-            uint8_t* lo = sa + (2 * gp) * kTileBytes + at;
-            uint8_t* hi = sa + (2 * gp + 1) * kTileBytes + at;
-            const uint32_t k = 0x0F0F0F0Fu;
-            *(uint4*) lo = make_uint4(r0[u].x & k, r0[u].y & k, r0[u].z & k, r0[u].w & k);
-            *(uint4*) (lo + 128) = make_uint4(r1[u].x & k, r1[u].y & k, r1[u].z & k, r1[u].w & k);
-            *(uint4*) hi = make_uint4((r0[u].x >> 4) & k, (r0[u].y >> 4) & k, (r0[u].z >> 4) & k, (r0[u].w >> 4) & k);
-            *(uint4*) (hi + 128) = make_uint4((r1[u].x >> 4) & k, (r1[u].y >> 4) & k, (r1[u].z >> 4) & k, (r1[u].w >> 4) & k);
-          }
-        }
+      // A: the step's raw blocks have landed; a task = (row, pair of groups): 32 bytes of nibbles -> the low nibbles'
+      // group and the high nibbles' group
+      const uint32_t rs = it % kRawStages;
+      if (!bar_wait(&sh.raw_full[rs], (it / kRawStages) & 1u)) {
+        sh.fail = 1;
+        break;
       }
+      const uint8_t* rawb = raw + rs * kRawBytes;
+#pragma unroll 2
+      for (uint32_t task = pt; task < 4u * kM; task += kProdThreads) {
+        const uint32_t row = task >> 2, gp = task & 3u;
+        const uint4* src = (const uint4*) (rawb + row * kBlockBytes + 16 + gp * 32);
+        const uint4 r0 = src[0], r1 = src[1];
+        const uint32_t at = (row >> 3) * 256 + (row & 7u) * 16;
+        uint8_t* lo = sa + (2 * gp) * kTileBytes + at;
+        uint8_t* hi = sa + (2 * gp + 1) * kTileBytes + at;
+        const uint32_t k = 0x0F0F0F0Fu;
+        *(uint4*) lo = make_uint4(r0.x & k, r0.y & k, r0.z & k, r0.w & k);
+        *(uint4*) (lo + 128) = make_uint4(r1.x & k, r1.y & k, r1.z & k, r1.w & k);
+        *(uint4*) hi = make_uint4((r0.x >> 4) & k, (r0.y >> 4) & k, (r0.z >> 4) & k, (r0.w >> 4) & k);
+        *(uint4*) (hi + 128) = make_uint4((r1.x >> 4) & k, (r1.y >> 4) & k, (r1.z >> 4) & k, (r1.w >> 4) & k);
+      }
+      for (uint32_t r = pt; r < (uint32_t) kM; r += kProdThreads)  // the rows' d, dmin and packed scales, for the epilogue
+        *(uint4*) (st + kHeadOff + r * 16) = *(const uint4*) (rawb + r * kBlockBytes);
+      bar_arrive(&sh.raw_empty[rs]);  // (this thread has read its part of the raw blocks)
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes before the tensor core's reads
       bar_arrive(&sh.full[stage]);
@@ -254,31 +308,54 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
     const uint32_t row = 32u * (warp & 3u) + lane;  // this thread's weight row of the tile = its TMEM lane
     const uint32_t col0 = (uint32_t) kCols * (warp >> 2);  // its 32 tokens
     const uint32_t lane_base = tmem + ((32u * (warp & 3u)) << 16);
-    const uint8_t* wrow = w + row * row_bytes;
     float* y = a.y + a.yoff[m] + (uint64_t) c0 * a.ys + row0 + row;
-    float acc[kCols];
+    uint64_t acc[kCols / 2];  // the thread's 32 sums, two neighbouring tokens a register pair
 #pragma unroll
-    for (int i = 0; i < kCols; i++) acc[i] = 0.0f;
+    for (int i = 0; i < kCols / 2; i++) acc[i] = 0ull;
     uint32_t acc_it = 0;
     bool dead = false;
-    uint4 hd_next;
-    {
-      uint32_t p0;
-      bool l0;
-      hd_next = __ldg((const uint4*) (wrow + (uint64_t) block_of(0, p0, l0) * kBlockBytes));
-    }
+    // sixteen tokens' int32 dots of this thread's row out of tensor memory (asynchronous: tcgen05.wait::ld before use;
+    // the kernel must build without register spills, a spilled destination would be saved before its value lands)
+    auto load16 = [](uint32_t (&r)[16], uint32_t at) {
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+            "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+          : "r"(at)
+          : "memory");
+    };
+    // those sixteen into the sums, two tokens an instruction (packed F32: each half is the scalar operation, same rounding)
+    auto half_sums = [](const uint32_t (&r)[16], uint64_t dsc2, uint64_t ndm2, const float* dx, const float* ns, uint64_t* acc8) {
+      const ulonglong2* dx4 = (const ulonglong2*) dx;
+      const ulonglong2* ns4 = (const ulonglong2*) ns;
+      const uint64_t bias2 = pack2(-12582912.0f, -12582912.0f);
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const ulonglong2 dv = dx4[q], nv = ns4[q];
+        const uint64_t dxs[2] = {dv.x, dv.y}, nss[2] = {nv.x, nv.y};
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          // (float) I without the conversion pipe: |I| <= 32 * 15 * 127 < 2^22, so 1.5 * 2^23 + I is exact
+          const uint64_t f = add2(pack2(__int_as_float((int) r[4 * q + 2 * e] + 0x4B400000),
+                                        __int_as_float((int) r[4 * q + 2 * e + 1] + 0x4B400000)),
+                                  bias2);
+          const uint64_t v = mul2(dsc2, dxs[e]);
+          acc8[2 * q + e] = fma2(ndm2, nss[e], fma2(v, f, acc8[2 * q + e]));
+        }
+      }
+    };
     for (uint32_t it = 0; it < nb && !dead; it++) {
       const uint32_t stage = it % kStages;
       uint32_t p;
       bool last;
       block_of(it, p, last);
-      // the row's scales of this block: d sc and dmin m for its 8 groups (the next block's header is already on its way)
-      const uint4 hd = hd_next;
-      if (it + 1 < nb) {
-        uint32_t p1;
-        bool l1;
-        hd_next = __ldg((const uint4*) (wrow + (uint64_t) block_of(it + 1, p1, l1) * kBlockBytes));
+      // the row's scales of this block: d sc and dmin m for its 8 groups, from the head the producers kept in the stage
+      // (read once the stage is full: this thread may be a whole step ahead of the producers)
+      if (!bar_wait(&sh.full[stage], (it / kStages) & 1u)) {
+        sh.fail = 1;
+        break;
       }
+      const uint4 hd = *(const uint4*) (smem + stage * kStageBytes + kHeadOff + row * 16);
       const float d = half_value(hd.x & 0xFFFFu), dmin = half_value(hd.x >> 16);
       const uint32_t sw[3] = {hd.y, hd.z, hd.w};
       auto sbyte = [&](int i) -> uint32_t { return (sw[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
@@ -291,56 +368,41 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
         else sc = (sbyte(g + 4) & 0x0F) | ((sbyte(g - 4) >> 6) << 4), mn = (sbyte(g + 4) >> 4) | ((sbyte(g) >> 6) << 4);
         const float dsc = mul_rn(d, (float) sc), ndm = -mul_rn(dmin, (float) mn);  // (dmin m) (-sx) = (-(dmin m)) sx
         const uint32_t ab = acc_it % kAccs, ause = acc_it / kAccs;
+        const uint64_t dsc2 = pack2(dsc, dsc), ndm2 = pack2(ndm, ndm);
         if (!bar_wait(&sh.acc_full[ab], ause & 1u)) {
           sh.fail = 1, dead = true;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t r[32];
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-            : "r"(lane_base + ab * kN + col0)
-            : "memory");
+        uint32_t ra[16], rb[16];
+        load16(ra, lane_base + ab * kN + col0);
+        load16(rb, lane_base + ab * kN + col0 + 16);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        // the accumulator is read: hand it back before the arithmetic
+        // the accumulator is read: hand it back before the arithmetic (the tensor core runs four groups ahead at most,
+        // and the slowest of the sixteen warps sets when it may reuse this one)
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) bar_arrive(&sh.acc_empty[ab]);
-        const float4* dx4 = (const float4*) (sdx + g * kN + col0);
-        const float4* ns4 = (const float4*) (ssx + g * kN + col0);
-#pragma unroll
-        for (int q = 0; q < kCols / 4; q++) {
-          const float4 dv = dx4[q], nv = ns4[q];
-          const float dxs[4] = {dv.x, dv.y, dv.z, dv.w}, nss[4] = {nv.x, nv.y, nv.z, nv.w};
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            // (float) I without the conversion pipe: |I| <= 32 * 15 * 127 < 2^22, so 1.5 * 2^23 + I is exact
-            const float f = __fsub_rn(__int_as_float((int) r[4 * q + e] + 0x4B400000), 12582912.0f);
-            const float v = mul_rn(dsc, dxs[e]);
-            float s2 = acc[4 * q + e];
-            s2 = __fmaf_rn(v, f, s2);
-            s2 = __fmaf_rn(ndm, nss[e], s2);
-            acc[4 * q + e] = s2;
-          }
-        }
+        half_sums(ra, dsc2, ndm2, sdx + g * kN + col0, ssx + g * kN + col0, &acc[0]);
+        half_sums(rb, dsc2, ndm2, sdx + g * kN + col0 + 16, ssx + g * kN + col0 + 16, &acc[8]);
       }
       if (dead) break;
       __syncwarp();
       if (lane == 0) bar_arrive(&sh.empty[stage]);  // done with the stage's dx / -sx
       if (last) {  // partition p is complete: y = its sum (p = 0) or y + its sum
 #pragma unroll
-        for (int i = 0; i < kCols; i++) {
-          const uint32_t t = col0 + i;
-          if (t < n_valid) {
-            float* at = y + (uint64_t) t * a.ys;
-            *at = p == 0 ? acc[i] : __fadd_rn(*at, acc[i]);
+        for (int i = 0; i < kCols / 2; i++) {
+          float pair[2];
+          unpack2(acc[i], pair[0], pair[1]);
+#pragma unroll
+          for (int h = 0; h < 2; h++) {
+            const uint32_t t = col0 + 2 * i + h;
+            if (t < n_valid) {
+              float* at = y + (uint64_t) t * a.ys;
+              *at = p == 0 ? pair[h] : __fadd_rn(*at, pair[h]);
+            }
           }
-          acc[i] = 0.0f;
+          acc[i] = 0ull;
         }
       }
     }
@@ -386,7 +448,7 @@ int try_launch(const void* const* w, const int32_t* cnt, uint32_t n_mat, uint32_
   uint32_t* status = status_word();
   if (!status) return 0;
   static bool sized[64] = {};  // (one flag a device)
-  const int smem_bytes = kStages * kStageBytes;
+  const int smem_bytes = kStages * kStageBytes + kRawStages * kRawBytes;
   if (!allow_dynamic_smem(q4k_tc_kernel, smem_bytes, sized)) return 0;
   Args a{(const uint8_t* const*) w, cnt, x8, dx, sx, soff, yoff, y, cols, ys, status};
   const dim3 grid(rows / kM, n_mat, (max_cnt + kN - 1) / kN);
