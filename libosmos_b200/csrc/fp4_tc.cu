@@ -50,15 +50,12 @@ constexpr int kTasks = kM * 4 / kProdThreads;  // (row, MMA) tasks a producer th
 constexpr int kThreads = (kEpiWarps + 3 + kProdWarps) * kWarp;
 constexpr int kStages = 3, kRawStages = 3;
 constexpr int kStepValues = 256, kMmaK = 64, kMmas = kStepValues / kMmaK;  // a stage: 256 values of K, four MMAs
-constexpr int kATile = kM * 32 + 32;   // an MMA's A tile (128 rows x 32 bytes) and 32 bytes, so that the four tiles of a
-                                       // stage start 8 banks apart: a producer warp's stores (8 rows x 4 tiles) then
-                                       // fall on 32 different banks
-constexpr int kABytes = 17 * 1024;                                         // the 4 tiles, rounded up to B's 1024-byte alignment
+constexpr int kABytes = kM * kStepValues / 2;                              // 16 KB: 128 rows of 128 bytes, the tokens' layout
 constexpr int kBBytes = kNMax * kStepValues / 2;                           // 32 KB
 constexpr int kChunk = 512;                                                // a scale-factor chunk: 128 rows x 4 factors
 constexpr int kSfaBytes = 4 * kChunk, kSfbBytes = 2 * 4 * kChunk;          // at most 4 chunks of K a stage; B: two row halves
-constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;     // 55 KB
-static_assert(4 * kATile <= kABytes && kABytes % 1024 == 0 && kStageBytes % 1024 == 0, "the tokens' tile starts on 1024 bytes");
+constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;     // 54 KB
+static_assert(kABytes % 1024 == 0 && kStageBytes % 1024 == 0, "both tiles start on 1024 bytes: the swizzle's period");
 constexpr int kRawRow = 144;                // a row's raw bytes of one stage: 4 x 36 (NVFP4), or 8 x 17 = 136 and the 8 a
 constexpr int kRawBytes = kM * kRawRow;     // 16-byte window may start before them (MXFP4)
 constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
@@ -109,8 +106,9 @@ __device__ __forceinline__ uint64_t tile_desc_sw128(uint32_t addr) {
   return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) 1 << 16 | (uint64_t) (1024u >> 4) << 32 | (uint64_t) 1 << 46 | (uint64_t) 2 << 61;
 }
 
-// where row r's 16 bytes `half` (0, 1) of an MMA's 32 bytes of K lie in an operand tile
-__device__ __forceinline__ uint32_t tile_at(uint32_t r, uint32_t half) { return (r >> 3) * 256u + half * 128u + (r & 7u) * 16u; }
+// where the 16 bytes j (0 .. 7) of row r's 128 bytes of K lie in a tile under the 128-byte swizzle: rows of 128 bytes, a
+// row's 16-byte pieces permuted by its place among its eight (what a tensor-map copy with that swizzle writes)
+__device__ __forceinline__ uint32_t tile_at(uint32_t r, uint32_t j) { return r * 128u + ((j ^ (r & 7u)) << 4); }
 // where row r's four factors lie in a scale-factor chunk (r < 128)
 __device__ __forceinline__ uint32_t chunk_at(uint32_t r) { return (r & 31u) * 16u + (r >> 5) * 4u; }
 
@@ -157,8 +155,10 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a, const
   if (tid == 0) {
     // a stage is full when every producer has stored its part of A (an arrival each), every producer's scale-byte copies
     // have landed (an arrival each, made by the copy engine) and the loader's tensor-map copy has delivered its bytes
-    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdThreads + 1), bar_init(&sh.empty[i], 1);
-    for (int i = 0; i < kRawStages; i++) bar_init(&sh.raw_full[i], 1), bar_init(&sh.raw_empty[i], kProdThreads);
+    // (the producers arrive a warp at a time: an arrival is an atomic on shared memory, and hundreds a stage would be the
+    // slowest thing in the kernel)
+    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdWarps + 1), bar_init(&sh.empty[i], 1);
+    for (int i = 0; i < kRawStages; i++) bar_init(&sh.raw_full[i], 1), bar_init(&sh.raw_empty[i], kProdWarps);
     bar_init(&sh.acc_full, 1);
     sh.fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -254,13 +254,16 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a, const
             q[4 * b] = k0.x, q[4 * b + 1] = k1.x, q[4 * b + 2] = k0.y, q[4 * b + 3] = k1.y;
           }
         }
-        const uint32_t at = sa + mm * (uint32_t) kATile;
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at + tile_at(row, 0)), "r"(q[0]), "r"(q[1]), "r"(q[2]), "r"(q[3]) : "memory");
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at + tile_at(row, 1)), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
+        // (a warp's stores: 8 rows x an MMA's two pieces of each - the swizzle spreads them over all the banks)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sa + tile_at(row, 2u * mm)), "r"(q[0]), "r"(q[1]), "r"(q[2]), "r"(q[3]) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sa + tile_at(row, 2u * mm + 1u)), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes before the tensor core's reads
-      bar_arrive(&sh.full[stage]);
-      bar_arrive(&sh.raw_empty[rs]);  // (this thread has read its part of the raw rows)
+      __syncwarp();
+      if (lane == 0) {
+        bar_arrive(&sh.full[stage]);
+        bar_arrive(&sh.raw_empty[rs]);  // (the warp has read its part of the raw rows)
+      }
     }
   } else if (warp == (uint32_t) kRawWarp) {
     // ================= the rows' raw bytes =================
@@ -329,9 +332,9 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a, const
                          : "memory");
         }
         for (uint32_t mm = 0; mm < (uint32_t) kMmas; mm++) {
-          // A: an MMA's two 16-byte pieces of K 128 bytes apart, 8 rows 256; B as the tensor-map copy laid it: a token a
-          // 128-byte row under the 128-byte swizzle, the MMA's 32 bytes of K at 32 mm
-          const uint64_t da = tile_desc(sa + mm * (uint32_t) kATile, 128, 256), db = tile_desc_sw128(sb + mm * 32u);
+          // both tiles as a tensor-map copy lays the tokens': a row (a token) 128 bytes of K under the 128-byte swizzle, the
+          // MMA's 32 bytes of K at 32 mm
+          const uint64_t da = tile_desc_sw128(sa + mm * 32u), db = tile_desc_sw128(sb + mm * 32u);
           const uint32_t accumulate = (it | mm) ? 1u : 0u;
           if constexpr (!MX) {  // a chunk a MMA: its four factors are the MMA's four 16s
             asm volatile(
