@@ -17,7 +17,23 @@
     case QTYPE_IQ1_M: CASE(QTYPE_IQ1_M)            \
     case QTYPE_MXFP4: CASE(QTYPE_MXFP4)            \
     case QTYPE_NVFP4: CASE(QTYPE_NVFP4)            \
+    case QTYPE_Q5_1: CASE(QTYPE_Q5_1)              \
+    case QTYPE_Q3_K: CASE(QTYPE_Q3_K)              \
+    case QTYPE_Q5_K: CASE(QTYPE_Q5_K)              \
+    case QTYPE_Q6_K: CASE(QTYPE_Q6_K)              \
+    case QTYPE_IQ4_NL: CASE(QTYPE_IQ4_NL)          \
+    case QTYPE_IQ4_XS: CASE(QTYPE_IQ4_XS)          \
+    case QTYPE_Q2_0: CASE(QTYPE_Q2_0)              \
+    case QTYPE_MXFP8: CASE(QTYPE_MXFP8)            \
     default: OTHERWISE;                            \
+  }
+
+// those and the unquantized weights a matvec may meet (a router's F32 matrix, BF16)
+#define OSMOS_SWITCH_WEIGHTS(type, CASE, OTHERWISE)                     \
+  switch (type) {                                                       \
+    case QTYPE_F32: CASE(QTYPE_F32)                                     \
+    case QTYPE_BF16: CASE(QTYPE_BF16)                                   \
+    default: OSMOS_SWITCH_QUANT(type, CASE, OTHERWISE)                  \
   }
 
 // the reference's int8 lane types (q8_group_tok, q8_gate_up)

@@ -55,6 +55,12 @@ def render():
     _emit(out, "osmos_ksigns", "uint8_t", [int(v) for v in Q.IQ2_XXS.ksigns], "0x%02x", 16)
     _emit(out, "osmos_iq4nl_values", "int8_t", [int(v) for v in Q.IQ4_NL.kvalues], "%d", 16)
     _emit(out, "osmos_e2m1_doubled", "int8_t", [int(v) for v in Q.MXFP4.kvalues], "%d", 16)
+    # the two 16-entry code tables once more as four words each (entry i the byte i % 4 of word i / 4): constants a
+    # byte permute can index
+    for name, vals in (("OSMOS_IQ4NL_WORDS", Q.IQ4_NL.kvalues), ("OSMOS_E2M1_WORDS", Q.MXFP4.kvalues)):
+        b = bytes(int(v) & 0xFF for v in vals)
+        out.append("#define %s %s" % (name, ", ".join("0x%08xu" % int.from_bytes(b[i:i + 4], "little") for i in range(0, 16, 4))))
+    out.append("")
     assert Q.IQ1_M.grid_hex == Q.IQ1_S.grid_hex and float(Q.IQ1_S.delta) == 0.125
     out.append("#endif")
     return "\n".join(out) + "\n"

@@ -41,7 +41,7 @@ __device__ __forceinline__ void sub_codes(uint32_t sb, const LaneAt& at, LaneCod
     for (int k = 0; k < 4; k++) {
       const uint32_t i0 = __byte_perm(w[k >> 1], 0, 0x4440 + 2 * (k & 1)), i1 = __byte_perm(w[k >> 1], 0, 0x4441 + 2 * (k & 1));
       const uint2 mm = lut.sign_masks2((aux >> (7 * k)) & 0x7F);
-      apply_masks(((uint64_t) lut.grid32(i1) << 32) | lut.grid32(i0), mm.x, mm.y, c.w[2 * k], c.w[2 * k + 1]);
+      c.w[2 * k] = negated4(lut.grid32(i0), mm.x, mm.x & kOnes), c.w[2 * k + 1] = negated4(lut.grid32(i1), mm.y, mm.y & kOnes);
     }
     c.s21[0] = c.s21[1] = 2 * (2 * (int) (aux >> 28) + 1);
     c.d = half_value(lds16(sb));

@@ -173,7 +173,7 @@ extern "C" bool mv_strided(uint32_t type, const void* w, uint32_t rows, uint32_t
                            uint32_t n_tok, float* y, uint32_t ys, void* stream) {
   if (!w || !x || !y) return false;
 #define CASE(T) return strided<T>(w, rows, cols, x, xs, n_tok, y, ys, stream_of(stream));
-  OSMOS_SWITCH_QUANT(type, CASE, return false)
+  OSMOS_SWITCH_WEIGHTS(type, CASE, return false)
 #undef CASE
 }
 
@@ -190,7 +190,7 @@ extern "C" bool mv_group(uint32_t type, const void* const* w, uint32_t n, uint32
                          uint32_t x_mat, uint32_t x_div, float* y, void* stream) {
   if (!w || !x || !y || !n || n > MV_MAX_GROUP || !rows) return false;
 #define CASE(T) return group<T>(w, n, rows, cols, x, x_mat, x_div, y, stream_of(stream));
-  OSMOS_SWITCH_QUANT(type, CASE, return false)
+  OSMOS_SWITCH_WEIGHTS(type, CASE, return false)
 #undef CASE
 }
 

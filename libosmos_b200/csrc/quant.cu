@@ -57,13 +57,13 @@ extern "C" bool quant_known(uint32_t type) {
 extern "C" bool quant_dequant(uint32_t type, const void* src, uint64_t values, float* dst, void* stream) {
   if (!src || !dst) return false;
 #define CASE(T) return osmos::dequant<T, false>(src, values, dst, osmos::stream_of(stream));
-  OSMOS_SWITCH_QUANT(type, CASE, return false)
+  OSMOS_SWITCH_WEIGHTS(type, CASE, return false)
 #undef CASE
 }
 
 extern "C" bool quant_dequant_f16(uint32_t type, const void* src, uint64_t values, void* dst, void* stream) {
   if (!src || !dst) return false;
 #define CASE(T) return osmos::dequant<T, true>(src, values, dst, osmos::stream_of(stream));
-  OSMOS_SWITCH_QUANT(type, CASE, return false)
+  OSMOS_SWITCH_WEIGHTS(type, CASE, return false)
 #undef CASE
 }

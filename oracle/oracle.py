@@ -17,9 +17,12 @@ ORACLE_SO = os.path.join(HERE, "_build", "libosmos_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libosmos_ref.so")
 
 TYPES = {"Q4_0": 2, "Q8_0": 8, "Q2_K": 10, "Q4_K": 12, "IQ2_XXS": 16, "IQ2_XS": 17, "IQ3_XXS": 18, "IQ1_S": 19,
-         "IQ2_S": 22, "IQ1_M": 29, "MXFP4": 39, "NVFP4": 40}
+         "IQ2_S": 22, "IQ1_M": 29, "MXFP4": 39, "NVFP4": 40, "Q5_1": 7, "Q3_K": 11, "Q5_K": 13, "Q6_K": 14,
+         "IQ4_NL": 20, "IQ4_XS": 23, "Q2_0": 42, "MXFP8": 43, "F32": 0, "BF16": 30}
 BLOCK = {2: (32, 18), 8: (32, 34), 10: (256, 84), 12: (256, 144), 16: (256, 66), 17: (256, 74), 18: (256, 98),
-         19: (256, 50), 22: (256, 82), 29: (256, 56), 39: (32, 17), 40: (64, 36)}
+         19: (256, 50), 22: (256, 82), 29: (256, 56), 39: (32, 17), 40: (64, 36),
+         7: (32, 24), 11: (256, 110), 13: (256, 176), 14: (256, 210), 20: (32, 18), 23: (256, 136), 42: (64, 18),
+         43: (32, 33), 0: (1, 4), 30: (1, 2)}
 LANE_TYPES = ("IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ1_S", "IQ2_S", "IQ1_M", "Q2_K")
 
 

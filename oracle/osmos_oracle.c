@@ -260,6 +260,103 @@ static void decode_block(uint32_t type, const uint8_t *b, float *out)
     }
     break;
   }
+  case QTYPE_Q5_1: /* kernels/quant.h:108-116: d q + m, q a nibble and a fifth bit (value i: bit i of the word at 4) */
+  {
+    const float d = half_value(rd16(b)), m = half_value(rd16(b + 2));
+    const uint32_t qh = (uint32_t)rd16(b + 4) | (uint32_t)rd16(b + 6) << 16;
+    for (int i = 0; i < 32; i++)
+    {
+      const int nib = i < 16 ? b[8 + i] & 0x0F : b[8 + i - 16] >> 4;
+      out[i] = d * (float)(nib | (int)((qh >> i) & 1) << 4) + m;
+    }
+    break;
+  }
+  case QTYPE_Q5_K: /* kernels/quant.h:75-90: Q4_K's scales; q a nibble of the 128 bytes at 48 and bit g of byte i % 32 at 16 */
+  {
+    const float d = half_value(rd16(b)), dmin = half_value(rd16(b + 2));
+    for (int i = 0; i < 256; i++)
+    {
+      const int g = i / 32, l = i % 32;
+      int sc, mn;
+      q4k_scale_min(b + 4, g, &sc, &mn);
+      const int q = ((b[48 + (g / 2) * 32 + l] >> (4 * (g % 2))) & 0x0F) | ((b[16 + l] >> g) & 1) << 4;
+      out[i] = (d * (float)sc) * (float)q - dmin * (float)mn;
+    }
+    break;
+  }
+  case QTYPE_Q6_K: /* kernels/quant.h:170-183: (d sc) (q - 32), sixteen int8 scales at 192, d at 208 */
+  {
+    const float d = half_value(rd16(b + 208));
+    for (int i = 0; i < 256; i++)
+    {
+      const int h = i / 128, r = (i % 128) / 32, l = i % 32;
+      const int lo = (b[h * 64 + (r % 2) * 32 + l] >> (4 * (r / 2))) & 0x0F, hi = (b[128 + h * 32 + l] >> (2 * r)) & 0x03;
+      out[i] = (d * (float)(int8_t)b[192 + i / 16]) * (float)((lo | hi << 4) - 32);
+    }
+    break;
+  }
+  case QTYPE_Q3_K: /* kernels/quant.h:270-287: (d (sc - 32)) (q - (high bit ? 0 : 4)) */
+  {
+    const float d = half_value(rd16(b + 108));
+    for (int i = 0; i < 256; i++)
+    {
+      const int n = i / 128, j = (i % 128) / 32, l = i % 32, g = i / 16;
+      const int low = g < 8 ? b[96 + g] & 0x0F : b[96 + g - 8] >> 4;
+      const int sc = (low | ((b[104 + g % 4] >> (2 * (g / 4))) & 0x03) << 4) - 32;
+      const int q = ((b[32 + 32 * n + l] >> (2 * j)) & 0x03) - ((b[l] >> (4 * n + j)) & 1 ? 0 : 4);
+      out[i] = (d * (float)sc) * (float)q;
+    }
+    break;
+  }
+  case QTYPE_IQ4_NL: /* kernels/quant.h:214-219: d times the table's value, Q4_0's nibble order */
+  {
+    const float d = half_value(rd16(b));
+    for (int i = 0; i < 32; i++)
+      out[i] = d * (float)osmos_iq4nl_values[i < 16 ? b[2 + i] & 0x0F : b[2 + i - 16] >> 4];
+    break;
+  }
+  case QTYPE_IQ4_XS: /* kernels/quant.h:233-241: (d (ls - 32)) times the table's value, a 6-bit ls a 32 values */
+  {
+    const float d = half_value(rd16(b));
+    const uint32_t top = rd16(b + 2);
+    for (int i = 0; i < 256; i++)
+    {
+      const int g = i / 32, l = i % 32;
+      const int ls = ((b[4 + g / 2] >> (4 * (g % 2))) & 0x0F) | (int)((top >> (2 * g)) & 0x03) << 4;
+      const int nib = l < 16 ? b[8 + 16 * g + l] & 0x0F : b[8 + 16 * g + l - 16] >> 4;
+      out[i] = (d * (float)(ls - 32)) * (float)osmos_iq4nl_values[nib];
+    }
+    break;
+  }
+  case QTYPE_Q2_0: /* kernels/quant.h:252-256: d (code - 1), value i bits 2 (i % 4) of byte 2 + i / 4 */
+  {
+    const float d = half_value(rd16(b));
+    for (int i = 0; i < 64; i++)
+      out[i] = d * (float)(((b[2 + i / 4] >> (2 * (i % 4))) & 0x03) - 1);
+    break;
+  }
+  case QTYPE_MXFP8: /* kernels/quant.h:308-311: 2^(e - 127) times an E4M3 value (0x7F / 0xFF are NaN) */
+  {
+    const float d = ldexpf(1.0f, (int)b[0] - 127);
+    for (int i = 0; i < 32; i++)
+    {
+      const uint32_t c = b[1 + i], mag = c & 0x7F;
+      float v = (mag >> 3) ? ldexpf(1.0f + (float)(mag & 7) * 0.125f, (int)(mag >> 3) - 7) : (float)mag * 0.001953125f;
+      if (mag == 0x7F)
+        v = NAN;
+      out[i] = d * (c & 0x80 ? -v : v);
+    }
+    break;
+  }
+  case QTYPE_F32: /* kernels/quant.h:357-359 */
+    memcpy(out, b, 4);
+    break;
+  case QTYPE_BF16: /* kernels/quant.h:352-354: the top half of an F32 */
+  {
+    const uint32_t bits = (uint32_t)rd16(b) << 16;
+    memcpy(out, &bits, 4);
+    break;
+  }
   default:
     break;
   }
@@ -269,7 +366,7 @@ static void decode_block(uint32_t type, const uint8_t *b, float *out)
 ORC_API int orc_dequant(uint32_t type, const void *src, uint64_t values, float *dst)
 {
   const OsmosQTypeInfo *t = type_row(type);
-  if (!t || !(t->paths & QTYPE_PATH_DECODE) || !values || values % t->values)
+  if (!t || !(t->paths & (QTYPE_PATH_DECODE | QTYPE_PATH_MV)) || !values || values % t->values)
     return 0;
   const uint64_t nb = values / t->values;
   for (uint64_t i = 0; i < nb; i++)
@@ -297,7 +394,7 @@ ORC_API int orc_mv_rows(uint32_t type, const void *w, uint32_t cols, uint32_t r0
                         uint32_t xs, uint32_t n_tok, float *y, uint32_t ys)
 {
   const OsmosQTypeInfo *t = type_row(type);
-  if (!t || !(t->paths & QTYPE_PATH_MV) || type == QTYPE_F32 || r1 < r0 || !cols || cols % t->values || cols % 8 ||
+  if (!t || !(t->paths & QTYPE_PATH_MV) || r1 < r0 || !cols || cols % t->values || cols % 8 ||
       !n_tok || xs < cols)
     return 0;
   const uint64_t row_bytes = (uint64_t)(cols / t->values) * t->bytes;

@@ -27,19 +27,29 @@ from oracle import oracle as orc  # noqa: E402
 
 GG = gguf.GGMLQuantizationType
 GG_TYPE = {2: GG.Q4_0, 8: GG.Q8_0, 10: GG.Q2_K, 12: GG.Q4_K, 16: GG.IQ2_XXS, 17: GG.IQ2_XS, 18: GG.IQ3_XXS,
-           19: GG.IQ1_S, 22: GG.IQ2_S, 29: GG.IQ1_M, 39: GG.MXFP4, 40: GG.NVFP4}
+           19: GG.IQ1_S, 22: GG.IQ2_S, 29: GG.IQ1_M, 39: GG.MXFP4, 40: GG.NVFP4, 7: GG.Q5_1, 11: GG.Q3_K, 13: GG.Q5_K,
+           14: GG.Q6_K, 20: GG.IQ4_NL, 23: GG.IQ4_XS, 0: GG.F32, 30: GG.BF16}
+# (Q2_0 and MXFP8 are the reference's own ids 42 and 43: gguf-py has no decoder for them, so they have no third-party
+# golden - the oracle's restatement of kernels/quant.h:252-256, 308-311 stands alone for those two)
 
 
 def dequant_golden():
     out = {}
     for name, tid in orc.TYPES.items():
+        if tid not in GG_TYPE:
+            continue
         rng = synth.rng_for(101, tid)
         raw = synth.random_blocks(tid, 48, rng)
         if tid == 39:
             raw[:, 0] = rng.integers(0, 256, size=48)
         if tid == 40:
             raw[:, 0:4] = rng.integers(0, 256, size=(48, 4))
-        vals = Q.dequantize(raw, GG_TYPE[tid]).astype(np.float32).reshape(-1)
+        if tid == 0:  # (the unquantized types: what the bytes are, no decoder to speak of)
+            vals = raw.reshape(-1).view(np.float32)
+        elif tid == 30:
+            vals = (raw.reshape(-1).view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+        else:
+            vals = Q.dequantize(raw, GG_TYPE[tid]).astype(np.float32).reshape(-1)
         out[name + "_raw"] = raw
         out[name + "_values"] = vals
     np.savez_compressed(os.path.join(HERE, "dequant.npz"), gguf_version=gguf.__version__ if hasattr(gguf, "__version__") else "?", **out)

@@ -11,7 +11,7 @@ from libosmos_b200 import synth
 from oracle.oracle import TYPES
 
 pytestmark = pytest.mark.gpu
-ALL = sorted(TYPES)
+ALL = sorted(set(TYPES) - {"F32", "BF16"})  # (the block types: an unquantized matrix has no f16 product here)
 
 
 def _x16(lib, dev, x, cols):

@@ -15,7 +15,7 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 ALL = sorted(TYPES)
 
 
-@pytest.mark.parametrize("name", ALL)
+@pytest.mark.parametrize("name", sorted(set(TYPES) - {"Q2_0", "MXFP8"}))  # (those two: no gguf-py decoder, the oracle below)
 def test_dequant_golden(lib, dev, name):
     g = np.load(os.path.join(GOLD, "dequant.npz"))
     raw, want = g[name + "_raw"], g[name + "_values"]
@@ -35,6 +35,8 @@ def test_dequant_golden(lib, dev, name):
 def test_dequant_large_vs_oracle(lib, dev, oracle, name):
     tid = TYPES[name]
     values = BLOCK[tid][0] * 3000 + (0 if BLOCK[tid][0] == 256 else BLOCK[tid][0] * 5)
+    if BLOCK[tid][0] == 1:
+        values = 8 * 3001  # the unquantized types go 8 values at a time
     raw = synth.random_blocks(tid, values // BLOCK[tid][0], synth.rng_for(11, tid))
     want = oracle.dequant(tid, raw, values)
     dst = torch.full((values + 8,), -7.0, dtype=torch.float32, device=dev)
