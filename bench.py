@@ -364,7 +364,8 @@ def run_ours(args):
     arm = CpuArm(cfg, host)
     ok = workloads.router_check(cfg, hl[0][t0:t1], got_ids, got_wts)
     if not ok:
-        sys.stderr.write("bench: rank %d: the router's picks or weights differ from the double-precision router\n" % rank)
+        sys.stderr.write("bench: rank %d: the router's picks or weights differ from the double-precision router (first token: picks %r weights %r)\n"
+                         % (rank, got_ids[0].tolist(), got_wts[0].tolist()))
     want = arm.layer(hx[0][t0:t1], got_ids, got_wts)
     routed = out.cpu().numpy().copy()
     if not np.array_equal(routed.view(np.uint32), want.view(np.uint32)):

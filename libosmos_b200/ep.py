@@ -141,15 +141,17 @@ class EpMoeLane:
             self.sync = torch.zeros(4, dtype=torch.int32, device=dev)
             self.rows = torch.zeros(2 * picks, dtype=torch.int64, device=dev)  # (the rows' homes, then their weights)
             self.plans = []
+            router = ROUTERS[cfg.get("router", "softmax")]
+            if router:  # (one tensor for all the plans, alive as long as they are)
+                self.route_bias = torch.from_numpy(workloads.route_bias_host(cfg)).to(dev)
             for layer in self.local.layers:
                 p = api.EpPlan()
                 p.rank, p.n_ranks, p.n_tok, p.expert0, p.expert1, p.lay = rank, world, self.n_tok, self.e0, self.e1, lay
                 for r in range(world):
                     p.peer[r] = self.peer.base[r]
                 p.sync, p.rows, p.layer, p.scratch = self.sync.data_ptr(), self.rows.data_ptr(), layer, self.local.scratch
-                p.router = ROUTERS[cfg.get("router", "softmax")]
-                if p.router:
-                    self.route_bias = torch.from_numpy(workloads.route_bias_host(cfg)).to(dev)
+                p.router = router
+                if router:
                     p.route_bias, p.route_scale = self.route_bias.data_ptr(), cfg["route_scale"]
                 if not lib.ep_plan_ok(p):
                     self.peer.close()
