@@ -82,11 +82,37 @@ class EpPlan(C.Structure):
                 ("route_bias", P), ("route_scale", F32)]
 
 
+class GgufValue(C.Union):
+    _fields_ = [("u", U64), ("i", C.c_int64), ("f", C.c_double), ("s", C.c_char_p), ("items", P)]
+
+
+class GgufKv(C.Structure):
+    _fields_ = [("key", C.c_char_p), ("type", C.c_int), ("item", C.c_int), ("n", U64), ("v", GgufValue)]
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("type", U32), ("n_dims", U32), ("dims", U64 * 4), ("file", C.c_int), ("offset", U64),
+                ("bytes", U64)]
+
+
+class Gguf(C.Structure):
+    _fields_ = [("n_files", C.c_int), ("paths", C.POINTER(C.c_char_p)), ("sizes", C.POINTER(U64)), ("kv", C.POINTER(GgufKv)),
+                ("n_kv", C.c_size_t), ("tensors", C.POINTER(GgufTensor)), ("n_tensors", C.c_size_t)]
+
+
 class QTypeInfo(C.Structure):
     _fields_ = [("id", U32), ("values", U32), ("bytes", U32), ("paths", U32), ("name", C.c_char_p)]
 
 
 SIGNATURES = {
+    # gguf.h
+    "gguf_create": (C.POINTER(Gguf), [C.c_char_p, C.c_char_p]),
+    "gguf_header": (C.POINTER(Gguf), [C.c_char_p, C.c_char_p]),
+    "gguf_destroy": (None, [C.POINTER(Gguf)]),
+    "gguf_tensor": (C.POINTER(GgufTensor), [C.POINTER(Gguf), C.c_char_p]),
+    "gguf_kv": (C.POINTER(GgufKv), [C.POINTER(Gguf), C.c_char_p]),
+    "gguf_bytes": (U64, [U32, U64]),
+    "gguf_int": (B, [C.POINTER(GgufKv), C.c_size_t, C.POINTER(C.c_int64)]),
     # quant.h / qtype.h
     "qtype_info": (C.POINTER(QTypeInfo), [U32]),
     "qtype_tensor_bytes": (U64, [U32, U64, U64]),

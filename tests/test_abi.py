@@ -17,7 +17,7 @@ def declared_functions():
         text = open(os.path.join(INC, f)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         text = re.sub(r"static inline[^{;]*\{.*?\n\}", "", text, flags=re.S)  # inline helpers are not exports
-        for m in re.finditer(r"^\s*(?:const\s+)?(?:bool|void|int|uint32_t|uint64_t|OsmosQTypeInfo\s*\*)\s*\*?\s*(\w+)\s*\(",
+        for m in re.finditer(r"^\s*(?:const\s+)?(?:bool|void|int|uint32_t|uint64_t|OsmosQTypeInfo\s*\*|Gguf\w*\s*\*)\s*\*?\s*(\w+)\s*\(",
                              text, flags=re.M):
             names.add(m.group(1))
     return names
