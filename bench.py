@@ -275,6 +275,29 @@ def run_reference(args):
     if rank != 0:
         return
     cfg = workloads.BY_NAME[args.workload]
+    if cfg.get("path") == "dense_rows":  # the product's scalar restatement on a sample of rows, scaled to the matrix
+        from libosmos_b200 import synth
+        from oracle.oracle import Oracle
+        orc = Oracle()
+        tid, rows, cols, n_tok = synth.TYPE_ID[cfg["type"]], cfg["rows"], cfg["cols"], cfg["tokens"]
+        w = synth.random_tensor(tid, rows, cols, synth.rng_for(2, tid, rows), cfg["sigma"])
+        x = synth.rng_for(8, n_tok, 0).standard_normal((n_tok, cols)).astype(np.float32)
+        sample_rows, times = 8, []
+        for _ in range(max(1, min(args.steps, 5))):
+            t0 = time.perf_counter()
+            hx8, hdx, hsx = orc.mmq_x8_rows(x, np.arange(n_tok, dtype=np.int32), cols)
+            orc.mmq_rows(np.ascontiguousarray(w.reshape(rows, -1)[:sample_rows]).reshape(-1), sample_rows, cols, hx8, hdx, hsx, 0, n_tok)
+            times.append(time.perf_counter() - t0)
+        sec = float(np.median(times)) * rows / sample_rows
+        sample = "%d rows x all tokens through the scalar restatement, scaled to %d rows" % (sample_rows, rows)
+        line = {"impl": "reference", "metric": "prefill_tokens_per_s", "value": n_tok / sec, "unit": "tokens/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sec, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
+                "config": {"workload": cfg["name"], "format": cfg["type"], "rows": rows, "cols": cols, "tokens": n_tok},
+                "cpu_baseline": {"value": n_tok / sec, "unit": "tokens/s", "cores": 1, "kind": "port", "sample": sample},
+                "e2e": {"value": n_tok / sec, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
     if cfg.get("path"):
         per = workloads.moe_expert_bytes(cfg)
         tok_s, ms, sample = port_tokens_per_s(cfg, workloads.moe_layer_host(cfg, expert_range=(0, 1)), per)
@@ -320,6 +343,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     lib = libosmos_b200.load()
     cfg = workloads.BY_NAME[args.workload]
+    if cfg.get("path") == "dense_rows":  # the prefill product, rows split among the ranks
+        return run_dense_rows(args, cfg, lib, dev, rank, world, dist)
     if cfg.get("path"):  # the experts over F32 activations, or through the grouped f16 product: one GPU
         return run_f32_or_f16(args, cfg, lib, dev)
     n_tok, dim, k = cfg["n_tok"], cfg["dim"], cfg["k"]
@@ -594,6 +619,135 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_dense_rows(args, cfg, lib, dev, rank, world, dist):
+    """The prefill product of a dense projection with its output rows split among the GPUs: Q4_K W[rows x cols] over the
+    tokens, every rank rounding all the tokens to int8 (the activations are not split) and multiplying its slice of
+    whole 128-row tiles - no collective on the data path, a rank's columns of y stay with it. Before timing every rank
+    compares its slice's sampled rows x all tokens with the CPU checker's bits. A step = mmq_x8_rows + mmq_group on a
+    cold copy of the slice; value = tokens through the whole matrix a second (max over ranks); strong scaling."""
+    import torch
+
+    from libosmos_b200 import shard, synth
+    from oracle.oracle import Oracle
+    orc = Oracle()
+    tid, rows, cols, n_tok = synth.TYPE_ID[cfg["type"]], cfg["rows"], cfg["cols"], cfg["tokens"]
+    w = synth.random_tensor(tid, rows, cols, synth.rng_for(2, tid, rows), cfg["sigma"])
+    nb_all = int(w.size)
+    r0, r1 = shard.row_range(rank, world, rows)
+    mine = r1 - r0
+    copies = max(2, int((160 << 20) // max(1, nb_all * mine // rows)) + 1)  # more than the 126 MB L2 cycled
+    copies = min(copies, 256)
+    layer = shard.DenseRows(lib, dev, tid, rows, cols, w, rank, world, copies=copies, max_tok=n_tok)
+    n_inputs = 4
+    hx = [synth.rng_for(8, n_tok, s).standard_normal((n_tok, cols)).astype(np.float32) for s in range(n_inputs)]
+    dx = [torch.from_numpy(a).to(dev) for a in hx]
+    px = [torch.from_numpy(a).pin_memory() for a in hx]
+    y = torch.zeros((n_tok, max(mine, 1)), dtype=torch.float32, device=dev)
+    pout = torch.empty((n_tok, max(mine, 1)), dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def all_ok(ok):
+        if world == 1:
+            return ok
+        flag = torch.tensor([0 if ok else 1], device=dev)
+        dist.all_reduce(flag)
+        return int(flag.item()) == 0
+
+    layer.step(dx[0], n_tok, y, 0, stream)
+    torch.cuda.synchronize()
+    ok = True
+    if mine:
+        pick = np.sort(synth.rng_for(7, rank).choice(mine, min(mine, 64), replace=False))
+        rb = nb_all // rows
+        wsel = np.ascontiguousarray(w.reshape(rows, rb)[r0 + pick]).reshape(-1)
+        hx8, hdx, hsx = orc.mmq_x8_rows(hx[0], np.arange(n_tok, dtype=np.int32), cols)
+        want = orc.mmq_rows(wsel, len(pick), cols, hx8, hdx, hsx, 0, n_tok)
+        ok = bool(np.array_equal(y.cpu().numpy()[:, pick].view(np.uint32), want.view(np.uint32)))
+        if not ok:
+            sys.stderr.write("bench: rank %d: its slice's rows differ from the CPU checker's bits\n" % rank)
+    if not all_ok(ok):
+        raise SystemExit("bench: a slice of the product differs from the CPU checker - not timing a wrong result")
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(steps):
+            fn(s)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 1e3], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def resident(s):
+        layer.step(dx[s % n_inputs], n_tok, y, s, stream)
+
+    bx = torch.empty_like(dx[0])
+
+    def end_to_end(s):  # the tokens from pinned host memory in, this rank's columns out, every step
+        bx.copy_(px[s % n_inputs], non_blocking=True)
+        layer.step(bx, n_tok, y, s, stream)
+        pout.copy_(y, non_blocking=True)
+
+    for s in range(max(args.warmup, 3)):
+        resident(s), end_to_end(s)
+    with ClockSampler(dev.index) as clocks:
+        n_warm = int(min(5000, max(args.steps, 0.5 / (timed(resident, args.steps) / args.steps))))
+        for s in range(n_warm):
+            resident(s)
+        t_regions = [timed(resident, args.steps) for _ in range(REGIONS)]
+        t_e2e = [timed(end_to_end, args.steps) for _ in range(REGIONS)]
+        # the product alone, by events around each launch of the slice's kernel (the roofline's kernel)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(32)]
+        for s, (a, b) in enumerate(ev):
+            lib.mmq_x8_rows(dx[0].data_ptr(), cols, layer.idx.data_ptr(), n_tok, cols, layer.x8.data_ptr(), layer.dx.data_ptr(),
+                            layer.sx.data_ptr(), stream)
+            a.record()
+            if mine:
+                lib.mmq_group(tid, layer.tabs[s % copies].data_ptr(), layer.cnt.data_ptr(), 1, n_tok, mine, cols, layer.x8.data_ptr(),
+                              layer.dx.data_ptr(), layer.sx.data_ptr(), layer.zero.data_ptr(), y.data_ptr(), layer.zero.data_ptr(), mine, stream)
+            b.record()
+        torch.cuda.synchronize()
+        us_kernel = float(np.median([a.elapsed_time(b) for a, b in ev[4:]])) * 1e3
+    t_res, t_ee = float(np.median(t_regions)), float(np.median(t_e2e))
+    if lib.mmq_status():
+        raise SystemExit("bench: a bounded wait ran out")
+    if rank != 0:
+        return
+    tf_peak, kind = measured_tflops()
+    ops = 2.0 * mine * cols * n_tok
+    # the CPU arm: the scalar restatement of the product on a sample of rows, scaled to the matrix
+    t0 = time.perf_counter()
+    sample_rows = 8
+    hx8, hdx, hsx = orc.mmq_x8_rows(hx[0], np.arange(n_tok, dtype=np.int32), cols)
+    orc.mmq_rows(np.ascontiguousarray(w.reshape(rows, nb_all // rows)[:sample_rows]).reshape(-1), sample_rows, cols, hx8, hdx, hsx, 0, n_tok)
+    cpu_s = (time.perf_counter() - t0) * rows / sample_rows
+    line = {"metric": "prefill_tokens_per_s", "value": n_tok * args.steps / t_res, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * t_res / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8xint8->f32", "data": "synthetic",
+            "config": {"workload": cfg["name"], "format": cfg["type"], "rows": rows, "cols": cols, "tokens": n_tok},
+            "run": {"parallelism": "rows%d: a rank a slice of whole 128-row tiles (rank 0: rows %d-%d), every rank rounds all the tokens; no collective" % (world, r0, r1),
+                    "cold_cache": "%d copies of the slice's %.1f MB cycled" % (copies, nb_all * mine / rows / 1e6),
+                    "timing": "median of %d regions of exactly %d steps, CUDA events, max over ranks; launched on the stream" % (REGIONS, args.steps),
+                    "regions_ms_per_step": [1e3 * t / args.steps for t in t_regions],
+                    "parity": "every rank: 64 sampled rows of its slice x all tokens bit-equal to the CPU checker (mmq_rows)"},
+            "e2e": {"value": n_tok * args.steps / t_ee, "unit": "tokens/s", "h2d_bytes_per_step": int(px[0].numel() * 4),
+                    "d2h_bytes_per_step": int(pout.numel() * 4)},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "mmq_group (q4k_tc_kernel) on rank 0's slice", "achieved": ops / us_kernel / 1e6,
+                         "peak": 2 * tf_peak, "unit": "TOP/s", "frac": ops / us_kernel / 1e6 / (2 * tf_peak),
+                         "peak_kind": "nominal: twice the %s bf16 burst (no int8 peak measured)" % kind, "traffic": None,
+                         "us_per_launch": us_kernel, "algorithmic_ops_per_launch": ops},
+            "cpu_baseline": {"value": n_tok / cpu_s, "unit": "tokens/s", "cores": 1, "kind": "port",
+                             "sample": "%d rows x all tokens through the scalar restatement, scaled to %d rows" % (sample_rows, rows)},
+            "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
 
 
 def run_f32_or_f16(args, cfg, lib, dev):

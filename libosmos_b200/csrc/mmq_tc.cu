@@ -2,7 +2,7 @@
 // group dots in tensor memory, drained group by group into the contract's F32 epilogue.
 //
 // A block computes 128 weight rows x 128 tokens of one matrix. Twenty warps, four roles:
-//   loader (1 warp)       per 256-value step: the rows' raw 144-byte blocks by bulk copies into a ring of three
+//   loader (1 warp)       per 256-value step: the rows' raw 144-byte blocks by 16-byte cp.async into a ring of three
 //   producers (2 warps)   per 256-value step: unpack the rows' Q4_K nibbles of that superblock into int8 operand
 //                         tiles (one 128 x 32 tile a 32-value group, K-major core matrices of 8 rows x 16 bytes),
 //                         copy the tokens' int8 codes into the same layout (cp.async), and their dx / sx beside them; then a
@@ -30,9 +30,8 @@ namespace osmos {
 namespace mmq_tc {
 namespace {
 
-constexpr int kM = 128, kN = 128;              // rows and tokens a block
+constexpr int kM = 128, kNMax = 128;           // rows a block, and the most tokens (a block takes 128, 64 or 32: kN)
 constexpr int kEpiWarps = 16, kProdWarps = 2;
-constexpr int kCols = kN / (kEpiWarps / 4);    // tokens an epilogue thread: 32
 constexpr int kIssuerWarp = kEpiWarps;         // warp 16
 constexpr int kLoaderWarp = kEpiWarps + 1;     // warp 17: the rows' raw blocks, by bulk copies
 constexpr int kFirstProdWarp = kEpiWarps + 2;  // warps 18, 19
@@ -41,7 +40,7 @@ constexpr int kThreads = (kEpiWarps + 2 + kProdWarps) * kWarp;
 constexpr int kStages = 2, kRawStages = 3, kAccs = 4;
 constexpr int kGroups = 8, kBlockBytes = 144, kBlockValues = 256;
 constexpr int kTileBytes = kM * MMQ_GROUP;     // one operand tile: 128 rows x 32 int8 = 4 KB
-constexpr int kHeadOff = 2 * kGroups * kTileBytes + 2 * kGroups * kN * 4;  // after A, B, dx, sx: the rows' 16-byte block heads
+constexpr int kHeadOff = 2 * kGroups * kTileBytes + 2 * kGroups * kNMax * 4;  // after A, B, dx, sx: the rows' 16-byte block heads
 constexpr int kStageBytes = kHeadOff + kM * 16;                            // 74 KB
 constexpr int kRawBytes = kM * kBlockBytes;    // a step's raw blocks, a row's after another: 18 KB
 constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
@@ -111,7 +110,7 @@ __device__ __forceinline__ uint64_t tile_desc(uint32_t addr, uint32_t lbo_bytes,
          (uint64_t) 1 << 46;
 }
 // instruction descriptor: D int32, A unsigned 8-bit (the nibbles), B signed 8-bit, both K-major, N = 128, M = 128
-constexpr uint32_t kIdesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t) (kN >> 3) << 17) | ((uint32_t) (kM >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_for(int n) { return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (kM >> 4) << 24); }
 
 struct Args {
   const uint8_t* const* wt;
@@ -130,7 +129,12 @@ struct Shared {
   int fail;
 };
 
+// kN: tokens a block (its accumulators' width): narrower blocks when the launch has few, so the grid still fills the GPU -
+// an element's sums do not depend on it
+template <int kN>
 __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
+  constexpr int kCols = kN / (kEpiWarps / 4);  // tokens an epilogue thread: 32, 16 or 8
+  constexpr uint32_t kIdesc = idesc_for(kN);
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ Shared sh;
   const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
@@ -148,14 +152,14 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
   const uint32_t s0 = a.soff[m] + c0;  // the block's first slot: a multiple of 16
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], kProdThreads), bar_init(&sh.empty[i], 1 + kEpiWarps);
+    for (int i = 0; i < kStages; i++) bar_init(&sh.full[i], 2 * kProdThreads), bar_init(&sh.empty[i], 1 + kEpiWarps);
     for (int i = 0; i < kAccs; i++) bar_init(&sh.acc_full[i], 1), bar_init(&sh.acc_empty[i], kEpiWarps);
-    for (int i = 0; i < kRawStages; i++) bar_init(&sh.raw_full[i], 1), bar_init(&sh.raw_empty[i], kProdThreads);
+    for (int i = 0; i < kRawStages; i++) bar_init(&sh.raw_full[i], kWarp), bar_init(&sh.raw_empty[i], kProdThreads);
     sh.fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == (uint32_t) kIssuerWarp) {  // all of tensor memory: four accumulators of 128 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sh.tmem_base)), "r"(512));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sh.tmem_base)), "r"(kAccs * kN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -181,7 +185,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
   uint8_t* const raw = smem + kStages * kStageBytes;  // the raw ring
   if (warp == (uint32_t) kLoaderWarp) {
     // ================= the rows' raw blocks =================
-    // a step's 144-byte block of each of the tile's 128 rows, a bulk copy a row, as far ahead as the raw ring is deep:
+    // a step's 144-byte block of each of the tile's 128 rows, as far ahead as the raw ring is deep:
     // the trip to memory is over when the producers want the bytes
     for (uint32_t it = 0; it < nb; it++) {
       const uint32_t rs = it % kRawStages, use = it / kRawStages;
@@ -192,15 +196,17 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
       uint32_t p;
       bool last;
       const uint32_t b = block_of(it, p, last);
-      const uint32_t bar = smem_addr(&sh.raw_full[rs]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // (the producers' reads before these writes)
-      if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t) kRawBytes) : "memory");
-      __syncwarp();
-      for (uint32_t r = lane; r < (uint32_t) kM; r += kWarp)
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                         smem_addr(raw + rs * kRawBytes + r * kBlockBytes)),
-                     "l"(w + r * row_bytes + (uint64_t) b * kBlockBytes), "r"((uint32_t) kBlockBytes), "r"(bar)
-                     : "memory");
+      // 16-byte asynchronous copies, nine a row (a bulk copy a row was the slowest thing in the kernel: 128 small requests
+      // a step took the copy engine 4.4 us); nobody waits for them: the ring's barrier hears of their landing, an
+      // arrival a lane
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      uint8_t* dst = raw + rs * kRawBytes;
+      const uint8_t* src = w + (uint64_t) b * kBlockBytes;
+      for (uint32_t i = lane; i < (uint32_t) (kM * (kBlockBytes / 16)); i += kWarp) {
+        const uint32_t r = i / (kBlockBytes / 16), piece = i % (kBlockBytes / 16);
+        cp_async16(dst + r * kBlockBytes + piece * 16, src + r * row_bytes + piece * 16);
+      }
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&sh.raw_full[rs])) : "memory");
     }
   } else if (warp >= (uint32_t) kFirstProdWarp) {
     // ================= producers =================
@@ -234,7 +240,9 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
           const uint64_t at = mmq_dx_at(s0 + tile * 16 + qt * 4, b * kGroups + g, groups);
           cp_async16((which ? ssx : sdx) + g * kN + tile * 16 + qt * 4, (which ? a.sx : a.dx) + at);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        // nobody waits for these copies: the stage's barrier hears of their landing (an arrival a thread, not counted
+        // as one of the expected ones until it happens)
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&sh.full[stage])) : "memory");
       }
       // A: the step's raw blocks have landed; a task = (row, pair of groups): 32 bytes of nibbles -> the low nibbles'
       // group and the high nibbles' group
@@ -261,7 +269,6 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
       for (uint32_t r = pt; r < (uint32_t) kM; r += kProdThreads)  // the rows' d, dmin and packed scales, for the epilogue
         *(uint4*) (st + kHeadOff + r * 16) = *(const uint4*) (rawb + r * kBlockBytes);
       bar_arrive(&sh.raw_empty[rs]);  // (this thread has read its part of the raw blocks)
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes before the tensor core's reads
       bar_arrive(&sh.full[stage]);
     }
@@ -275,6 +282,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // (the tokens' codes came by cp.async)
       const uint32_t sa = smem_addr(smem + stage * kStageBytes), sb = sa + kGroups * kTileBytes;
       for (uint32_t g = 0; g < (uint32_t) kGroups; g++, acc_it++) {
         const uint32_t acc = acc_it % kAccs, ause = acc_it / kAccs;
@@ -324,13 +332,21 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
           : "r"(at)
           : "memory");
     };
-    // those sixteen into the sums, two tokens an instruction (packed F32: each half is the scalar operation, same rounding)
-    auto half_sums = [](const uint32_t (&r)[16], uint64_t dsc2, uint64_t ndm2, const float* dx, const float* ns, uint64_t* acc8) {
+    auto load8 = [](uint32_t (&r)[16], uint32_t at) {
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                   : "r"(at)
+                   : "memory");
+    };
+    // NV of them (16 or 8) into the sums, two tokens an instruction (packed F32: each half is the scalar operation, same
+    // rounding)
+    auto sums = [](auto nv_tag, const uint32_t (&r)[16], uint64_t dsc2, uint64_t ndm2, const float* dx, const float* ns, uint64_t* acc8) {
+      constexpr int NV = decltype(nv_tag)::value;
       const ulonglong2* dx4 = (const ulonglong2*) dx;
       const ulonglong2* ns4 = (const ulonglong2*) ns;
       const uint64_t bias2 = pack2(-12582912.0f, -12582912.0f);
 #pragma unroll
-      for (int q = 0; q < 4; q++) {
+      for (int q = 0; q < NV / 4; q++) {
         const ulonglong2 dv = dx4[q], nv = ns4[q];
         const uint64_t dxs[2] = {dv.x, dv.y}, nss[2] = {nv.x, nv.y};
 #pragma unroll
@@ -375,16 +391,20 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         uint32_t ra[16], rb[16];
-        load16(ra, lane_base + ab * kN + col0);
-        load16(rb, lane_base + ab * kN + col0 + 16);
+        if constexpr (kCols == 8) {
+          load8(ra, lane_base + ab * kN + col0);
+        } else {
+          load16(ra, lane_base + ab * kN + col0);
+          if constexpr (kCols == 32) load16(rb, lane_base + ab * kN + col0 + 16);
+        }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         // the accumulator is read: hand it back before the arithmetic (the tensor core runs four groups ahead at most,
         // and the slowest of the sixteen warps sets when it may reuse this one)
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) bar_arrive(&sh.acc_empty[ab]);
-        half_sums(ra, dsc2, ndm2, sdx + g * kN + col0, ssx + g * kN + col0, &acc[0]);
-        half_sums(rb, dsc2, ndm2, sdx + g * kN + col0 + 16, ssx + g * kN + col0 + 16, &acc[8]);
+        sums(std::integral_constant<int, (kCols < 16 ? kCols : 16)>{}, ra, dsc2, ndm2, sdx + g * kN + col0, ssx + g * kN + col0, &acc[0]);
+        if constexpr (kCols == 32) sums(std::integral_constant<int, 16>{}, rb, dsc2, ndm2, sdx + g * kN + col0 + 16, ssx + g * kN + col0 + 16, &acc[8]);
       }
       if (dead) break;
       __syncwarp();
@@ -422,7 +442,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_tc_kernel(const Args a) {
   __syncthreads();
   if (warp == (uint32_t) kIssuerWarp) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kAccs * kN));
   }
   if (tid == 0 && sh.fail) atomicOr(a.status, 1u);
 }
@@ -447,13 +467,22 @@ int try_launch(const void* const* w, const int32_t* cnt, uint32_t n_mat, uint32_
   if (rows % kM || cols % kBlockValues || (((uintptr_t) x8 | (uintptr_t) dx | (uintptr_t) sx) & 15u)) return 0;
   uint32_t* status = status_word();
   if (!status) return 0;
-  static bool sized[64] = {};  // (one flag a device)
   const int smem_bytes = kStages * kStageBytes + kRawStages * kRawBytes;
-  if (!allow_dynamic_smem(q4k_tc_kernel, smem_bytes, sized)) return 0;
   Args a{(const uint8_t* const*) w, cnt, x8, dx, sx, soff, yoff, y, cols, ys, status};
-  const dim3 grid(rows / kM, n_mat, (max_cnt + kN - 1) / kN);
-  q4k_tc_kernel<<<grid, kThreads, smem_bytes, (cudaStream_t) stream>>>(a);
-  return cudaGetLastError() == cudaSuccess ? 1 : -1;
+  // the widest blocks that still make a grid of about a hundred (148 SMs, a block each): a slice of a matrix's rows, or
+  // a few tokens, then takes narrower and therefore more and shorter blocks
+  auto blocks = [&](uint32_t n) { return (uint64_t) (rows / kM) * n_mat * ((max_cnt + n - 1) / n); };
+  auto go = [&](auto n_tag, bool (&sized)[64]) -> int {
+    constexpr int N = decltype(n_tag)::value;
+    if (!allow_dynamic_smem(q4k_tc_kernel<N>, smem_bytes, sized)) return 0;
+    const dim3 grid(rows / kM, n_mat, (max_cnt + N - 1) / N);
+    q4k_tc_kernel<N><<<grid, kThreads, smem_bytes, (cudaStream_t) stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+  };
+  static bool sized128[64] = {}, sized64[64] = {}, sized32[64] = {};  // (one flag a device and an instance)
+  if (blocks(128) >= 100) return go(std::integral_constant<int, 128>{}, sized128);
+  if (blocks(64) >= 100) return go(std::integral_constant<int, 64>{}, sized64);
+  return go(std::integral_constant<int, 32>{}, sized32);
 }
 
 uint32_t read_status() {

@@ -26,7 +26,10 @@ MOE_MX = dict(name="moe_mxfp4_128e_top4_b32", type="MXFP4", n_exp=128, k=4, n_to
               lim=7.0, per_expert_rng=True, bf16_inputs=True, path="f32_lane")
 MOE_MX_PREFILL = dict(MOE_MX, name="moe_mxfp4_128e_top4_b2048", n_tok=2048, path="f16_group", lim=1.0e30)
 
-BY_NAME = {c["name"]: c for c in (MOE_IQ3, MOE_DS, MOE_DS_B1, MOE_MX, MOE_MX_PREFILL)}
+# the prefill product with its rows split among the GPUs (a rank a slice of whole 128-row tiles, no collective)
+DENSE_Q4_K = dict(MM_Q4_K, name="prefill_q4k_4096x4096_b512_rows", path="dense_rows")
+
+BY_NAME = {c["name"]: c for c in (MOE_IQ3, MOE_DS, MOE_DS_B1, MOE_MX, MOE_MX_PREFILL, DENSE_Q4_K)}
 
 
 def moe_layer_host(cfg, layer=0, expert_range=None):

@@ -126,3 +126,18 @@ def test_exchange_buffer_layout_regions_do_not_overlap():
         assert spans[-1][0] + spans[-1][1] <= lay.bytes and all(a % 256 == 0 for a, _ in spans)
         # the halves are the same distance apart for every array the lane kernels read by parity
         assert lay.q[1] - lay.q[0] == lay.d[1] - lay.d[0] == lay.ids[1] - lay.ids[0] == lay.weights[1] - lay.weights[0]
+
+
+def test_row_ranges_cover_a_matrix_in_whole_tiles():
+    """dense projections across GPUs: every row in exactly one rank's slice, slices in whole 128-row tiles"""
+    from libosmos_b200 import shard
+    for rows in (128, 512, 4096, 17408):
+        for world in (1, 2, 3, 4, 8):
+            got = [shard.row_range(r, world, rows) for r in range(world)]
+            assert got[0][0] == 0 and got[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(got, got[1:]))
+            assert all(r0 % 128 == 0 and r1 % 128 == 0 and r1 >= r0 for r0, r1 in got)
+            sizes = [r1 - r0 for r0, r1 in got]
+            assert max(sizes) - min(sizes) <= 128
+    with pytest.raises(ValueError):
+        shard.row_range(0, 2, 100)

@@ -99,3 +99,24 @@ def test_config3_moe_layer_all_tokens(lib, dev):
     assert same_bits(out.cpu().numpy(), arm.layer(x, ids, wts))
     assert lib.ep_wait_status() == 0 and lib.q8_status() == 0
     layer.close()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_config2_rows_split_among_ranks_have_the_whole_products_bits(lib, dev, world):
+    """the prefill product with its rows split among `world` ranks (each emulated here in turn): the slices side by side
+    are the whole product bit for bit, whatever block width a slice's smaller grid makes the kernel choose"""
+    from libosmos_b200 import shard
+    cfg = workloads.MM_Q4_K
+    tid, rows, cols, tokens = synth.TYPE_ID[cfg["type"]], cfg["rows"], cfg["cols"], cfg["tokens"]
+    w = synth.random_tensor(tid, rows, cols, synth.rng_for(402), cfg["sigma"])
+    x = torch.from_numpy(synth.rng_for(403).standard_normal((tokens, cols)).astype(np.float32)).to(dev)
+    whole = shard.DenseRows(lib, dev, tid, rows, cols, w, 0, 1, max_tok=tokens)
+    want = torch.zeros((tokens, rows), dtype=torch.float32, device=dev)
+    whole.step(x, tokens, want, 0, None)
+    for rank in range(world):
+        part = shard.DenseRows(lib, dev, tid, rows, cols, w, rank, world, max_tok=tokens)
+        y = torch.full((tokens, part.rows), -3.0, dtype=torch.float32, device=dev)
+        part.step(x, tokens, y, 0, None)
+        sync()
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), want[:, part.r0:part.r1].cpu().numpy().view(np.uint32)), rank
+    assert lib.mmq_status() == 0
