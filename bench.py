@@ -1130,6 +1130,12 @@ def run_kernel(args):
         fn = lambda i, st: (lib.ops_fp4_round(xr.data_ptr(), tokens * cols, 32, False, pk.data_ptr(), cols, st)
                             and lib.mm_mxfp4(pool.data_ptr() + (i % copies) * nb, rows, cols, pk.data_ptr(), tokens, 1.0,
                                              y.data_ptr(), rows, st))
+    elif op == "mm_mxfp4_only":  # the MXFP4 W4A4 product alone: the activations rounded once, outside
+        flops = 2.0 * rows * cols * tokens
+        pk = torch.zeros(tokens * (cols // 2 + cols // 32), dtype=torch.uint8, device=dev)
+        assert lib.ops_fp4_round(x.clone().data_ptr(), tokens * cols, 32, False, pk.data_ptr(), cols, None)
+        fn = lambda i, st: lib.mm_mxfp4(pool.data_ptr() + (i % copies) * nb, rows, cols, pk.data_ptr(), tokens, 1.0,
+                                        y.data_ptr(), rows, st)
     elif op == "mm_fp4_only":  # the W4A4 product alone (TYPE NVFP4): the activations quantized once, outside
         flops = 2.0 * rows * cols * tokens
         xq = torch.zeros(tokens, cols // 2, dtype=torch.uint8, device=dev)

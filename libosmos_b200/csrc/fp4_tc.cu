@@ -41,13 +41,25 @@ namespace {
 
 constexpr int kM = 128, kNMax = 256;
 constexpr int kEpiWarps = 4, kProdWarps = 8;
-constexpr int kIssuerWarp = kEpiWarps;      // warp 4
-constexpr int kLoaderWarp = kEpiWarps + 1;  // warp 5: the tokens' codes by tensor-map copies
-constexpr int kRawWarp = kEpiWarps + 2;     // warp 6: the rows' raw bytes by tensor-map copies
-constexpr int kFirstProdWarp = kEpiWarps + 3;
+// Who does what goes by the warp scheduler a warp lives on (its index mod 4). Scheduler 0 has the issuer and the two
+// loaders, which issue little and wait much, and an epilogue warp that sleeps until the end - so the issuer, whose
+// chain of tcgen05 instructions a stage is the kernel's critical path (35 cycles a scale-factor copy, 75 an MMA, measured
+// by leaving them out), never waits for an issue slot behind a producer. The eight producers share schedulers 1, 2 and 3
+// with the other three epilogue warps. (A second issuing warp for the scale factors' copies, a stage ahead with two sets
+// of tensor-memory columns, was slower: what the hand-over costs exceeds what the copies' issue saved.)
+constexpr int kIssuerWarp = 4;   // scheduler 0
+constexpr int kRawWarp = 8;      // scheduler 0: the rows' raw bytes by tensor-map copies
+constexpr int kLoaderWarp = 12;  // scheduler 0: the tokens' codes by tensor-map copies
+// producer p's warp: 5, 6, 7, 9, 10, 11, 13, 14
+__host__ __device__ constexpr int producer_of(int warp) {  // 0 .. 7, or -1
+  return (warp < 5 || warp > 14 || warp % 4 == 0) ? -1 : (warp / 4 - 1) * 3 + warp % 4 - 1;
+}
+static_assert(producer_of(5) == 0 && producer_of(7) == 2 && producer_of(9) == 3 && producer_of(11) == 5 && producer_of(13) == 6 &&
+                  producer_of(14) == 7 && producer_of(8) == -1 && producer_of(12) == -1 && producer_of(4) == -1,
+              "eight producers on schedulers 1 to 3");
 constexpr int kProdThreads = kProdWarps * kWarp;
 constexpr int kTasks = kM * 4 / kProdThreads;  // (row, MMA) tasks a producer thread takes a stage: 2
-constexpr int kThreads = (kEpiWarps + 3 + kProdWarps) * kWarp;
+constexpr int kThreads = 15 * kWarp;
 constexpr int kStages = 3, kRawStages = 3;
 constexpr int kStepValues = 256, kMmaK = 64, kMmas = kStepValues / kMmaK;  // a stage: 256 values of K, four MMAs
 constexpr int kABytes = kM * kStepValues / 2;                              // 16 KB: 128 rows of 128 bytes, the tokens' layout
@@ -172,9 +184,9 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a, const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sh.tmem_base;
 
-  if (warp >= (uint32_t) kFirstProdWarp) {
+  if (producer_of((int) warp) >= 0) {
     // ================= producers =================
-    const uint32_t pt = tid - kFirstProdWarp * kWarp;
+    const uint32_t pt = (uint32_t) producer_of((int) warp) * kWarp + lane;
     const uint32_t raw0 = smem_addr(smem + kStages * kStageBytes);
     // this thread's token of the block: a warp takes tokens 8 b .. 8 b + 7 of each of a half's four 32-token groups,
     // whose words lie side by side in a chunk (32 lanes on 32 banks). A stage's scale bytes of a token are 16 (8)
@@ -308,41 +320,48 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a, const
     // ================= issuer =================
     // instruction descriptor (block scaled): A and B E2M1 (format 1), both K-major, N, the scale format, M = 128
     const uint32_t idesc = (1u << 7) | (1u << 10) | ((n_mma >> 3) << 17) | ((MX ? 1u : 0u) << 23) | ((uint32_t) (kM >> 4) << 24);
-    for (uint32_t it = 0; it < steps && !sh.fail; it++) {
+    // (one lane runs the whole loop: nothing here is the warp's, and the other lanes' polling and the meeting after
+    // every stage only stood in its way)
+    for (uint32_t it = 0; lane == 0 && it < steps && !sh.fail; it++) {
       const uint32_t stage = it % kStages, use = it / kStages;
       if (!bar_wait(&sh.full[stage], use & 1u)) {
         sh.fail = 1;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (lane == 0) {
+      {
         const uint32_t st = smem_addr(smem + stage * kStageBytes);
-        const uint32_t sa = st, sb = st + kABytes, sfa = sb + kBBytes, sfb = sfa + kSfaBytes;
-        // the stage's scale factors into tensor memory: a chunk = 32 lanes x 16 bytes = 4 columns
-        for (uint32_t ch = 0; ch < kSfChunks; ch++) {
-          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfaCol + 4u * ch),
-                       "l"(tile_desc(sfa + ch * kChunk, 16, 128))
-                       : "memory");
-          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 8u * ch),
-                       "l"(tile_desc(sfb + (ch * 2u) * kChunk, 16, 128))
-                       : "memory");
+        // descriptors: everything but the address is the same all along (every address here is below 2^18, so the
+        // 14-bit field of address / 16 takes an offset by plain addition)
+        constexpr uint64_t kSfDesc = (uint64_t) (16u >> 4) << 16 | (uint64_t) (128u >> 4) << 32 | (uint64_t) 1 << 46;
+        constexpr uint64_t kTileDesc = (uint64_t) 1 << 16 | (uint64_t) (1024u >> 4) << 32 | (uint64_t) 1 << 46 | (uint64_t) 2 << 61;
+        const uint64_t da0 = kTileDesc | (st >> 4), db0 = kTileDesc | ((st + kABytes) >> 4);
+        const uint64_t sfa0 = kSfDesc | ((st + kABytes + kBBytes) >> 4), sfb0 = kSfDesc | ((st + kABytes + kBBytes + kSfaBytes) >> 4);
+        // a chunk of scale factors (32 lanes x 16 bytes = 4 columns of tensor memory) for the rows and two for the tokens,
+        // then the MMAs that read them: the first MMA of a stage starts after three copies, not twelve
+        auto copy_chunk = [&](uint32_t ch) {
+          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfaCol + 4u * ch), "l"(sfa0 + ch * (kChunk >> 4)) : "memory");
+          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 8u * ch), "l"(sfb0 + 2u * ch * (kChunk >> 4)) : "memory");
           if (n_mma > 128u)
             asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 8u * ch + 4u),
-                         "l"(tile_desc(sfb + (ch * 2u + 1u) * kChunk, 16, 128))
+                         "l"(sfb0 + (2u * ch + 1u) * (kChunk >> 4))
                          : "memory");
-        }
+        };
+#pragma unroll
         for (uint32_t mm = 0; mm < (uint32_t) kMmas; mm++) {
           // both tiles as a tensor-map copy lays the tokens': a row (a token) 128 bytes of K under the 128-byte swizzle, the
           // MMA's 32 bytes of K at 32 mm
-          const uint64_t da = tile_desc_sw128(sa + mm * 32u), db = tile_desc_sw128(sb + mm * 32u);
+          const uint64_t da = da0 + 2u * mm, db = db0 + 2u * mm;
           const uint32_t accumulate = (it | mm) ? 1u : 0u;
           if constexpr (!MX) {  // a chunk a MMA: its four factors are the MMA's four 16s
+            copy_chunk(mm);
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                 " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::"r"(tmem),
                 "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(tmem + kSfaCol + 4u * mm), "r"(tmem + kSfbCol + 8u * mm)
                 : "memory");
           } else {  // a chunk two MMAs: factors 0, 1 then 2, 3 (the factor id in the descriptor is the first's byte)
+            if ((mm & 1u) == 0) copy_chunk(mm >> 1);
             const uint32_t id = 2u * (mm & 1u), idesc_mm = idesc | (id << 4) | (id << 29);
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
@@ -356,8 +375,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_tc_kernel(const Args a, const
         if (it + 1 == steps)
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&sh.acc_full)) : "memory");
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ================= epilogue =================
     const uint32_t row = 32u * warp + lane;  // this thread's weight row of the tile = its TMEM lane

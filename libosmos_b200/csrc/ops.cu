@@ -214,6 +214,39 @@ __global__ void __launch_bounds__(kThreads) fp4_kernel(float* x, uint64_t blocks
     row[dim / 2 + j / block] = (uint8_t) (e4m3_scale ? (s > 448.0f ? 0x7Fu : e4m3_code(s)) : (uint32_t) (ilogbf(s) + 127));
 }
 
+// MXFP4 rows for the W4A4 product (32-value blocks, E8M0 scales, packed output): eight lanes a block, four values a
+// lane - one 16-byte load, two shuffles for the block's largest magnitude, the rounded values back as one 16-byte
+// store and the lane's four codes as one 2-byte store. The same operations a value as fp4_kernel (a power-of-two scale
+// divides exactly, so the quotient is a product with its reciprocal), hence the same bits.
+__global__ void __launch_bounds__(kThreads) mxfp4_rows_kernel(float* x, uint64_t blocks, uint8_t* packed, uint32_t dim) {
+  const uint64_t t = (uint64_t) blockIdx.x * kThreads + threadIdx.x;
+  const uint64_t b = t / 8;
+  const uint32_t part = (uint32_t) (t % 8);
+  const bool live = b < blocks;  // (eight lanes are live or not together; the shuffles want every lane)
+  float4* at = (float4*) (x + (live ? b : 0) * 32) + part;
+  const float4 v = live ? *at : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o, kWarp));
+  const float s = exp2f(ceilf(log2f(__fdiv_rn(fmaxf(amax, 6.0f * 1.1754943508222875e-38f), 6.0f))));
+  const float r = __fdiv_rn(1.0f, s);
+  const float in[4] = {v.x, v.y, v.z, v.w};
+  float q[4];
+  uint32_t codes = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    q[i] = e2m1_round(fminf(fmaxf(mul_rn(in[i], r), -6.0f), 6.0f));
+    codes |= e2m1_code(q[i]) << (4 * i);
+  }
+  if (!live) return;
+  *at = make_float4(mul_rn(q[0], s), mul_rn(q[1], s), mul_rn(q[2], s), mul_rn(q[3], s));
+  const uint64_t row = b * 32 / dim;
+  const uint32_t j = (uint32_t) (b * 32 - row * dim);  // the block's first column
+  uint8_t* out = packed + row * (dim / 2 + dim / 32);
+  *(uint16_t*) (out + j / 2 + 2 * part) = (uint16_t) codes;
+  if (part == 0) out[dim / 2 + j / 32] = (uint8_t) (ilogbf(s) + 127);
+}
+
 __global__ void __launch_bounds__(kThreads) fp8_kernel(float* x, uint64_t blocks, uint8_t* packed, uint32_t dim) {
   const uint64_t b = (uint64_t) blockIdx.x * (kThreads / kWarp) + threadIdx.x / kWarp;
   if (b >= blocks) return;
@@ -367,6 +400,11 @@ extern "C" bool ops_fp4_round(float* x, uint64_t n, uint32_t block, bool e4m3_sc
                               void* stream) {
   if (!x || !n || !block || n % block || block > 32) return false;
   if (packed && (!dim || dim % block || dim % 4 || n % dim || block != (e4m3_scale ? 16u : 32u))) return false;
+  if (packed && !e4m3_scale && ((uintptr_t) x & 15u) == 0 && ((uintptr_t) packed & 1u) == 0 && dim % 64 == 0) {
+    // (whole rows of an even number of blocks: every block's codes start on 2 bytes)
+    mxfp4_rows_kernel<<<blocks_for(n / 32 * 8, kThreads), kThreads, 0, stream_of(stream)>>>(x, n / 32, (uint8_t*) packed, dim);
+    return launched();
+  }
   fp4_kernel<<<blocks_for(n / block, kThreads / kWarp), kThreads, 0, stream_of(stream)>>>(x, n / block, block, e4m3_scale,
                                                                                        (uint8_t*) packed, dim);
   return launched();
