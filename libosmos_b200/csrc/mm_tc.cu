@@ -44,7 +44,17 @@ constexpr int kM = 128, kN = 128;  // rows a block; tokens an accumulator
 constexpr int kMaxAcc = 4;         // accumulators a block: 512 tokens
 constexpr int kEpiWarps = 4, kProdWarps = 16;
 constexpr int kLoaderWarps = 4;
-constexpr int kIssuerWarp = kEpiWarps, kFirstLoaderWarp = kEpiWarps + 1, kFirstProdWarp = kFirstLoaderWarp + kLoaderWarps;
+// Roles go by the warp scheduler a warp lives on (its index mod 4): scheduler 0 has the issuer - whose chain of tcgen05
+// instructions a step is the critical path, and must not queue for issue slots behind the decoders - the four loaders
+// and one producer; the other fifteen producers share schedulers 1 to 3 with the epilogue warps.
+constexpr int kIssuerWarp = 4;
+__host__ __device__ constexpr int loader_of(int warp) { return (warp >= 8 && warp <= 20 && warp % 4 == 0) ? (warp - 8) / 4 : -1; }
+__host__ __device__ constexpr int producer_of(int warp) {
+  return warp == 24 ? 15 : (warp >= 5 && warp <= 23 && warp % 4 != 0) ? ((warp - 5) / 4) * 3 + warp % 4 - 1 : -1;
+}
+static_assert(producer_of(5) == 0 && producer_of(7) == 2 && producer_of(9) == 3 && producer_of(23) == 14 && producer_of(24) == 15 &&
+                  producer_of(8) == -1 && producer_of(4) == -1 && loader_of(8) == 0 && loader_of(20) == 3 && loader_of(24) == -1,
+              "sixteen producers, four loaders");
 constexpr int kProdThreads = kProdWarps * kWarp, kLoaderThreads = kLoaderWarps * kWarp;
 constexpr int kThreads = (kEpiWarps + 1 + kLoaderWarps + kProdWarps) * kWarp;
 constexpr int kStep = 64;                        // values of K a stage
@@ -192,12 +202,12 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
   const uint32_t tmem = sh.tmem_base;
   const uint32_t S = a.stages;
 
-  if (warp >= (uint32_t) kFirstProdWarp) {
+  if (producer_of((int) warp) >= 0) {
     // ================= producers =================
     // The rows' bytes come through shared memory kRawK values of K at a time: 16-byte cp.async pieces of the aligned
     // span around each row's bytes (a block may start anywhere in a 16-byte piece), two buffers, the next block's values
     // on their way while these are decoded - so the decoders' many narrow reads are shared-memory reads.
-    const uint32_t pt = tid - kFirstProdWarp * kWarp;
+    const uint32_t pt = (uint32_t) producer_of((int) warp) * kWarp + lane;
     constexpr uint32_t kKb = kRawK<T>, kKbBytes = kRawBytes<T>, kSlot = kRawSlot<T>;
     constexpr uint32_t kPieces = (kKbBytes + 30u + 15u) / 16u;  // (the slot may be one piece longer: an odd count)
     uint8_t* raw = smem + a.raw_off;
@@ -268,12 +278,12 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
       if (lane == 0) bar_arrive(&sh.full_a[stage]);  // (one arrival a warp: 512 would queue on the one word)
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-  } else if (warp >= (uint32_t) kFirstLoaderWarp) {
+  } else if (loader_of((int) warp) >= 0) {
     // ================= the activations' loader =================
     // token n's 8-value piece kc of step `it`, 16 bytes, to sub-tile (n / 128, kc / 2) of the step's stage; the warp
     // never waits for its own copies: each thread's arrival on the stage's barrier is made by the hardware when that
     // thread's copies have landed, so the loads run as far ahead of the tensor core as the ring is deep
-    const uint32_t lt = tid - kFirstLoaderWarp * kWarp;
+    const uint32_t lt = (uint32_t) loader_of((int) warp) * kWarp + lane;
     if (a.use_tma) {
       // One warp, a tensor-map copy a (128 tokens, 16 values of K) sub-tile: the tiled x16 seen as [token tile][K
       // fragment][token in tile][value in fragment], a box of 8 tiles x 1 fragment written with the 32-byte swizzle the
