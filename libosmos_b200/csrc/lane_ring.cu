@@ -35,6 +35,7 @@ using lanes::sub_codes;
 
 constexpr int kWarps = 16, kThreads = kWarps * kWarp;
 constexpr int kMaxSlots = 4;
+constexpr uint32_t kTaskRows = 32;  // rows a fused task has at most, a lane each (its tokens' loads are shared by them)
 constexpr uint32_t kMaxEntries = 1024;  // entries a launch takes (their pointers and live list sit in shared memory)
 constexpr uint32_t kSmemLimit = 226u * 1024u;
 
@@ -214,9 +215,9 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
         row_chain(live_tag, sa + grp * half_bytes + p * row_bytes, xq, xd, acc);
 #pragma unroll
         for (int t = 0; t < NTL; t++) {
-          const float v = tree(acc[t]);
-          const float up = __shfl_sync(0xFFFFFFFFu, v, 16, kWarp);
-          if (lane == place0 + p) hg[t] = v, hu[t] = up;
+          const float v = tree(acc[t]);  // (lanes 0 .. 15: the gate row's sum, 16 .. 31: the up row's)
+          const float gate = __shfl_sync(0xFFFFFFFFu, v, 0, kWarp), up = __shfl_sync(0xFFFFFFFFu, v, 16, kWarp);
+          if (lane == place0 + p) hg[t] = gate, hu[t] = up;
         }
       }
     } else if constexpr (FUSED) {
@@ -356,15 +357,15 @@ int launch(const Request& r, cudaStream_t s) {
   while ((rc * row_bytes) % 16u) rc += RU;
   while (M * rc * row_bytes < 3072u && r.rows % (2 * rc) == 0) rc *= 2;
   if (r.rows % rc) return 0;
-  if (FUSED && rc > 16) return 0;  // (a fused task's rows each have a lane of the first sixteen)
+  if (FUSED && rc > 32) return 0;  // (a fused task's rows each have a lane)
   const uint32_t slot_bytes = M * rc * row_bytes;
   uint32_t slots = (kSmemLimit - a.ring_off - 16u) / (kWarps * slot_bytes);
   if (slots > (uint32_t) kMaxSlots) slots = kMaxSlots;
   if (slots < 2) return 0;
   // a task: slots of one entry that share the activation registers - about 8 rows of work a token's loads
   uint32_t ts = 1;
-  while (ts * rc < 8 && r.rows % (2 * ts * rc) == 0) ts *= 2;
-  if (FUSED && ts * rc > 16) return 0;
+  while (ts * rc < (FUSED ? kTaskRows : 8u) && r.rows % (2 * ts * rc) == 0) ts *= 2;
+  if (FUSED && ts * rc > 32) return 0;
   a.wg = (const uint8_t* const*) r.wg, a.wu = (const uint8_t* const*) r.wu, a.cnt = r.cnt, a.xrow = r.xrow, a.xin = r.xin;
   a.win = r.win, a.q = r.q, a.d = r.d, a.scale = r.scale, a.lim = r.lim, a.out = r.out, a.rows = r.rows, a.cols = r.cols;
   a.out_stride = r.out_stride, a.n_entries = r.n_entries, a.max_cnt = r.max_cnt;
