@@ -2,7 +2,7 @@
  *
  * Drop-in for the reference's include/osmos/gpu/mm.h: the activation side mm_x16 (:13), mm_x16_rows (:35),
  * mm_x16_heads (:37) with the layout function of kernels/mm.h:41-51, and the products mm_known, mm_fits, mm_run,
- * mm_run2, mm_tokens[_scaled], mm_group (:10-38) - same names, argument meaning, limits and refusals. The products
+ * mm_run_silu, mm_run_gated_mean, mm_run2, mm_tokens[_scaled], mm_group (:10-38) - same names, argument meaning, limits and refusals. The products
  * compute what the reference's do - the weights' exact values rounded to f16, times the f16 activations,
  * accumulated in F32 - on the tensor cores, with the tensor core's order of additions along K instead of the
  * reference's wave partitions: results agree with the reference's within its own test bound
@@ -84,6 +84,25 @@ uint32_t mm_col_tiles(uint32_t type, uint32_t n);
    with more than one token ys shorter than a row, or x16 not 16-byte aligned. */
 bool mm_run(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const void *x16, uint32_t n, float *y,
             uint32_t ys, void *stream);
+/* mm_run with y = silu(y scale) as its epilogue - silu(v) = v / (1 + expf(-v)), every operation rounded by itself -
+   written to y and, as f16, into x16_out (tiled as mm_x16 lays it, rows values wide, the overflow flag set past
+   f16's range): the next product's activations in the same launch (reference: mm.h:27-29, kernels/mm.hip:493-501,
+   the mixers' down). x16_out must not be x16. false - nothing queued, the caller's mm_run and its own silu pass
+   then - past MM_SILU_MAX_TOKENS tokens, for a shape mm_run refuses, x16_out NULL / x16 / not 16-byte aligned, or no
+   overflow word. Every type mm_run takes (the reference: Q8_0 alone). */
+#define MM_SILU_MAX_TOKENS 64
+bool mm_run_silu(uint32_t type, const void *w, uint32_t rows, uint32_t cols, const void *x16, uint32_t n, float *y,
+                 uint32_t ys, float scale, void *x16_out, int32_t *overflow, void *stream);
+/* the hyper-connection mixer's up (hc dim rows: hc streams of dim) with the gated mean as its epilogue:
+   out[t][d] = (sum over s in order, from zero, of xn[t][s][d] sigmoid(up_t[s dim + d])) / hc, sigmoid(v) =
+   1 / (1 + expf(-v)), every operation rounded by itself; and its f16 into out16 (dim wide, token t at row row0 + t;
+   NULL: none). The up's own F32 output is never stored (reference: mm.h:30-33, kernels/mm.h:668-704). out16 must not
+   be x16. false - nothing queued - for more than MM_GATED_MEAN_MAX_HC streams, dim not a multiple of MM_TILE, a
+   shape mm_run refuses for hc dim rows, out16 without an overflow word. Every type mm_run takes. */
+#define MM_GATED_MEAN_MAX_HC 8
+bool mm_run_gated_mean(uint32_t type, const void *w, uint32_t hc, uint32_t dim, uint32_t cols, const void *x16,
+                       uint32_t n, const float *xn, float *out, void *out16, uint32_t row0, int32_t *overflow,
+                       void *stream);
 /* two matrices of one type and cols on the same x16, each the bits mm_run gives it alone (reference: mm.h:23);
    refused as a whole when either would be */
 bool mm_run2(uint32_t type, const void *w0, uint32_t rows0, float *y0, uint32_t ys0, const void *w1, uint32_t rows1,

@@ -135,6 +135,8 @@ SIGNATURES = {
     "mm_fits": (B, [U32, U32, U32]),
     "mm_col_tiles": (U32, [U32, U32]),
     "mm_run": (B, [U32, P, U32, U32, P, U32, P, U32, P]),
+    "mm_run_silu": (B, [U32, P, U32, U32, P, U32, P, U32, C.c_float, P, P, P]),
+    "mm_run_gated_mean": (B, [U32, P, U32, U32, U32, P, U32, P, P, P, U32, P, P]),
     "mm_run2": (B, [U32, P, U32, P, U32, P, U32, P, U32, U32, P, U32, P]),
     "mm_tokens": (B, [U32, P, U32, P, U32, P, U32, P, U32, U32, P, U32, U32, P, P, C.c_bool, P]),
     "mm_tokens_scaled": (B, [U32, P, U32, P, U32, C.c_float, P, U32, P, U32, C.c_float, U32, P, U32, U32, P, P, C.c_bool, P]),

@@ -20,13 +20,18 @@
 //   issuer (1 warp)      per step and accumulator four tcgen05.mma M128 N128 K16 (the first of the whole K loop
 //                        overwrites, the rest accumulate), then tcgen05.commit onto the stage's "empty" mbarrier; after
 //                        the last step a commit onto "done".
-//   epilogue (4 warps)   thread = one weight row (its TMEM lane): tcgen05.ld the sums, scale, store y[t][row].
+//   epilogue (4 warps)   thread = one weight row (its TMEM lane): tcgen05.ld the sums, scale, store y[t][row] - or, for
+//                        mm_run_silu, silu(scale sum) to y and as f16 into the next product's tiled activations; for
+//                        mm_run_gated_mean the block's rows are hc streams' rows of the same dim values (row map
+//                        below), each thread gates its sum, and the streams are added in order through shared memory
+//                        (the operand ring, idle by then).
 // Every mbarrier wait is bounded (%globaltimer); a wait that runs out raises the status word, every role falls through
 // to the common exit and tensor memory is released.
 #include <cuda.h>
 
 #include <cstring>
 
+#include "act.cuh"
 #include "decode.cuh"
 #include "dispatch.cuh"
 #include "fp4_tc_api.h"
@@ -159,7 +164,17 @@ struct Args {
   uint32_t stages, stage_bytes, raw_off;  // the operand ring's depth, a stage's bytes; where the raw weight buffers start
   float scale;
   uint32_t* status;
+  // the epilogue: kStore y = scale sum; kSilu y = silu(scale sum), and its f16 into x16_out (rows wide, tiled);
+  // kGatedMean: the matrix is hc streams of dim rows, out[t][d] = (sum over s in order of xn[t][s][d]
+  // sigmoid(sum_t[s dim + d])) / hc, and its f16 into x16_out (dim wide, token t at row out_row0 + t; NULL: none)
+  uint32_t epi;
+  __half* x16_out;
+  int32_t* overflow;
+  const float* xn;
+  float* out;
+  uint32_t hc, dim, per, out_row0;  // per: the dim values a block takes (hc per <= 128 rows of its tile are used)
 };
+enum : uint32_t { kStore = 0, kSilu = 1, kGatedMean = 2 };
 
 struct Shared {
   uint64_t full_a[kMaxStages], full_b[kMaxStages], empty[kMaxStages], done;
@@ -182,6 +197,15 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
   const uint32_t steps = a.cols / kStep;
   const uint64_t row_bytes = (uint64_t) (a.cols / Fmt<T>::values) * Fmt<T>::bytes;
   const uint8_t* w = a.wt ? a.wt[m] : a.w;
+  // the weight row behind row r of the block's tile: the matrix's next 128 rows - or, for the gated mean, stream
+  // r / per's row of value d0 + r % per, so the hc sums of one output value lie in one block (a row past the matrix,
+  // or past the streams, repeats a valid one and is never stored)
+  const uint32_t d0 = blockIdx.x * a.per;
+  auto wrow = [&](uint32_t r) -> uint32_t {
+    if (a.epi != kGatedMean) return row0 + r < a.rows ? row0 + r : a.rows - 1;
+    const uint32_t st = r / a.per, d = d0 + (r - st * a.per);
+    return (st < a.hc ? st : a.hc - 1) * a.dim + (d < a.dim ? d : a.dim - 1);
+  };
   const __half* x16 = a.x16 + (a.wt ? a.xoff[m] : 0u);
   float* y = a.y + (a.wt ? a.yoff[m] : 0u);
 
@@ -217,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
       uint8_t* buf = raw + (kb & 1u) * (kM * kSlot);
       for (uint32_t i = pt; i < (uint32_t) kM * kPieces; i += kProdThreads) {
         const uint32_t r = i / kPieces, piece = i - r * kPieces;
-        const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
+        const uint32_t row = wrow(r);
         const uint8_t* src = (const uint8_t*) ((uintptr_t) (w + row * row_bytes + (uint64_t) kb * kKbBytes) & ~(uintptr_t) 15) + piece * 16u;
         const uint32_t have = src >= w_end ? 0u : (w_end - src < 16 ? (uint32_t) (w_end - src) : 16u);  // (zero fill past the tensor)
         asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(buf + r * kSlot + piece * 16u)), "l"(src), "r"(have)
@@ -235,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
 #pragma unroll
     for (int u = 0; u < kMine; u++) {
       const uint32_t task = pt + (uint32_t) u * kProdThreads, r = (task >> 6) * 8u + (task & 7u);
-      const uint32_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;  // (a row past the matrix repeats the last one)
+      const uint32_t row = wrow(r);  // (a row past the matrix repeats the last one)
       slot_at[u] = r * kSlot, dst_at[u] = (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16;
       base15[u] = (uint32_t) ((uintptr_t) (w + row * row_bytes) & 15u);
     }
@@ -370,6 +394,9 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
       for (uint32_t tries = 0; tries < 25u && !sh.fail && !landed; tries++) landed = bar_wait(&sh.done, 0);
       if (!landed) sh.fail = 1;
     }
+    // (nobody else writes the word once the last product has landed or been given up: after this barrier every
+    // epilogue thread reads the same value, so all of them or none take the barriers below)
+    asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * kWarp) : "memory");
     if (!sh.fail) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       for (uint32_t acc = 0; acc < n_acc; acc++) {
@@ -387,13 +414,46 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
               : "r"(lane_base + acc * kN + c32)
               : "memory");
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (row0 + row < a.rows) {
+          if (a.epi == kGatedMean) {
+            // each thread gates its row's sums into the idle operand ring ([token of the 32][tile row]); then thread e
+            // adds value e % per's streams in order for the tokens e / per, e / per + 128 / per, ...
+            float* ex = (float*) smem;
+            const uint32_t st = row / a.per, d = d0 + (row - st * a.per);
+            const bool mine = st < a.hc && d < a.dim;
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+              const uint32_t t = acc * kN + c32 + i;
+              float p = 0.0f;
+              if (mine && t < n_valid)
+                p = mul_rn(a.xn[((uint64_t) (c0 + t) * a.hc + st) * a.dim + d], sigmoidf(__uint_as_float(r[i])));
+              ex[i * kM + row] = p;
+            }
+            asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * kWarp) : "memory");
+            const uint32_t j = row % a.per, tg = row / a.per, groups = (uint32_t) kM / a.per;
+            if (tg < groups && d0 + j < a.dim) {
+              for (uint32_t i = tg; i < 32u; i += groups) {
+                const uint32_t t = acc * kN + c32 + i;
+                if (t >= n_valid) break;
+                float sum = 0.0f;
+                for (uint32_t q = 0; q < a.hc; q++) sum = __fadd_rn(sum, ex[i * kM + q * a.per + j]);
+                const float v = __fdiv_rn(sum, (float) a.hc);
+                a.out[(uint64_t) (c0 + t) * a.dim + d0 + j] = v;
+                if (a.x16_out) x16_store(a.x16_out, a.overflow, a.out_row0 + c0 + t, d0 + j, a.dim, v);
+              }
+            }
+            asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * kWarp) : "memory");  // (the next 32 tokens reuse ex)
+          } else if (row0 + row < a.rows) {
 #pragma unroll
             for (int i = 0; i < 32; i++) {
               const uint32_t t = acc * kN + c32 + i;
               if (t < n_valid) {
-                const float v = __uint_as_float(r[i]);
-                y[(uint64_t) (c0 + t) * a.ys + row0 + row] = a.scale == 1.0f ? v : mul_rn(v, a.scale);
+                float v = __uint_as_float(r[i]);
+                if (a.scale != 1.0f) v = mul_rn(v, a.scale);
+                if (a.epi == kSilu) {
+                  v = siluf(v);
+                  x16_store(a.x16_out, a.overflow, c0 + t, row0 + row, a.rows, v);
+                }
+                y[(uint64_t) (c0 + t) * a.ys + row0 + row] = v;
               }
             }
           }
@@ -461,7 +521,7 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return false;
   constexpr uint32_t kSlot = kRawSlot<T>, kLimit = 224u * 1024u - (uint32_t) ((grid_smem_bytes<T>() + 1023) / 1024 * 1024);
-  const uint32_t row_tiles = (a.rows + kM - 1) / kM;
+  const uint32_t row_tiles = a.epi == kGatedMean ? (a.dim + a.per - 1) / a.per : (a.rows + kM - 1) / kM;
   auto stages_for = [&](uint32_t k) { return k >= 4 ? 2u : k == 2 ? 3u : 4u; };  // a deeper ring where a stage is small
   auto smem_for = [&](uint32_t k) { return stages_for(k) * (kStageA + k * kSubs * kSubTile) + 2u * kM * kSlot; };
   // tokens a block: the accumulator count (1, 2 or 4 of 128 tokens; a weight is decoded once a block) with the least
@@ -491,6 +551,14 @@ bool shape_ok(uint32_t type, uint32_t rows, uint32_t cols) {
   return t && rows && rows % MM_TILE == 0 && cols && cols % 128 == 0 && cols % t->values == 0;
 }
 
+namespace {
+bool run_with(uint32_t type, const Args& a, void* stream) {
+#define CASE(T) return launch<T>(a, 1, a.n, stream_of(stream));
+  OSMOS_SWITCH_QUANT(type, CASE, return false)
+#undef CASE
+}
+}  // namespace
+
 bool run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n, float* y, uint32_t ys,
          float scale, void* stream) {
   if (!w || !x16 || !y || !n || n > MM_MAX_TOKENS || !shape_ok(type, rows, cols) || (n > 1 && ys < rows)) return false;
@@ -498,9 +566,32 @@ bool run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void*
   Args a{};
   a.w = (const uint8_t*) w, a.x16 = (const __half*) x16, a.y = y, a.rows = rows, a.cols = cols, a.n = n, a.xts = cols;
   a.ys = ys, a.scale = scale;
-#define CASE(T) return launch<T>(a, 1, n, stream_of(stream));
-  OSMOS_SWITCH_QUANT(type, CASE, return false)
-#undef CASE
+  return run_with(type, a, stream);
+}
+
+bool run_silu(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n, float* y, uint32_t ys,
+              float scale, void* x16_out, int32_t* overflow, void* stream) {
+  if (!w || !x16 || !y || !x16_out || x16_out == x16 || !overflow || !n || n > MM_SILU_MAX_TOKENS ||
+      !shape_ok(type, rows, cols) || (n > 1 && ys < rows) || (((uintptr_t) x16 | (uintptr_t) x16_out) & 15u))
+    return false;
+  Args a{};
+  a.w = (const uint8_t*) w, a.x16 = (const __half*) x16, a.y = y, a.rows = rows, a.cols = cols, a.n = n, a.xts = cols;
+  a.ys = ys, a.scale = scale, a.epi = kSilu, a.x16_out = (__half*) x16_out, a.overflow = overflow;
+  return run_with(type, a, stream);
+}
+
+bool run_gated_mean(uint32_t type, const void* w, uint32_t hc, uint32_t dim, uint32_t cols, const void* x16, uint32_t n,
+                    const float* xn, float* out, void* out16, uint32_t row0, int32_t* overflow, void* stream) {
+  if (!w || !x16 || !xn || !out || out16 == x16 || (out16 && !overflow) || !n || n > MM_MAX_TOKENS || !hc ||
+      hc > MM_GATED_MEAN_MAX_HC || !dim || dim % MM_TILE || (uint64_t) hc * dim > 0xFFFFFFFFull ||
+      !shape_ok(type, hc * dim, cols) || ((uintptr_t) x16 & 15u))
+    return false;
+  Args a{};
+  a.w = (const uint8_t*) w, a.x16 = (const __half*) x16, a.rows = hc * dim, a.cols = cols, a.n = n, a.xts = cols;
+  a.scale = 1.0f, a.epi = kGatedMean, a.x16_out = (__half*) out16, a.overflow = overflow, a.xn = xn, a.out = out;
+  a.hc = hc, a.dim = dim, a.out_row0 = row0;
+  a.per = ((uint32_t) kM / hc) & ~(uint32_t) (MM_TILE - 1);  // whole tiles of 16 values: 128, 64, 32, 32, 16, ... for 1 - 8 streams
+  return run_with(type, a, stream);
 }
 
 }  // namespace mm_tc
@@ -526,6 +617,17 @@ extern "C" uint32_t mm_status(void) {
 extern "C" bool mm_run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n, float* y,
                        uint32_t ys, void* stream) {
   return mm_tc::run(type, w, rows, cols, x16, n, y, ys, 1.0f, stream);
+}
+
+extern "C" bool mm_run_silu(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n,
+                            float* y, uint32_t ys, float scale, void* x16_out, int32_t* overflow, void* stream) {
+  return mm_tc::run_silu(type, w, rows, cols, x16, n, y, ys, scale, x16_out, overflow, stream);
+}
+
+extern "C" bool mm_run_gated_mean(uint32_t type, const void* w, uint32_t hc, uint32_t dim, uint32_t cols, const void* x16,
+                                  uint32_t n, const float* xn, float* out, void* out16, uint32_t row0, int32_t* overflow,
+                                  void* stream) {
+  return mm_tc::run_gated_mean(type, w, hc, dim, cols, x16, n, xn, out, out16, row0, overflow, stream);
 }
 
 extern "C" bool mm_run2(uint32_t type, const void* w0, uint32_t rows0, float* y0, uint32_t ys0, const void* w1,

@@ -9,6 +9,7 @@
 // stable sort by expert without a thread ever scanning the picks before its own.
 #include "moe_api.h"
 
+#include "act.cuh"
 #include "decode.cuh"
 #include "osmos_b200/moe.h"
 #include "route.cuh"
@@ -319,15 +320,6 @@ __global__ void lane_order_kernel(const int32_t* __restrict__ row_of, uint32_t n
 }
 
 // ---- activation and combine ------------------------------------------------------------------------------------
-__device__ __forceinline__ float sigmoidf(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
-__device__ __forceinline__ float siluf(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
-
-// value (token t, column c) of a cols-wide activation into the 16 x 16 tiled f16 layout, a value past f16 flagged
-__device__ __forceinline__ void x16_store(__half* x16, int32_t* overflow, uint32_t t, uint32_t c, uint32_t cols, float v) {
-  if (!(fabsf(v) <= 65504.0f)) atomicOr(overflow, 1);
-  x16[(uint64_t) (t / 16) * 16 * cols + (c / 16) * 256 + (t % 16) * 16 + c % 16] = __float2half_rn(v);
-}
-
 // four neighbouring values a thread where the addresses allow it (VEC 4), else one
 template <int VEC>
 __global__ void __launch_bounds__(kThreads) swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u, uint64_t n,

@@ -157,3 +157,102 @@ def test_mm_group_entries(lib, dev, oracle):
         assert (got[at + cnt[m]:at + tiles[m] * 16] == -3.0).all()
         at += tiles[m] * 16
     assert lib.mm_status() == 0
+
+
+def _tiled16(buf, n, cols):
+    """the tiled f16 activations (16 x 16 tiles, mm_x16_at) back as rows: [n][cols] float16"""
+    t16 = (n + 15) // 16
+    a = buf.cpu().numpy()[: t16 * 16 * cols].reshape(t16, cols // 16, 16, 16)  # [token tile][col tile][token][col]
+    return a.transpose(0, 2, 1, 3).reshape(t16 * 16, cols)[:n]
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_K", "IQ4_NL"])
+def test_mm_run_silu(lib, dev, oracle, name):
+    """mm_run_silu = mm_run, then y = silu(y scale) and its f16 for the next product, in one launch (the reference's
+    test: tests/gpu/test_mm_gpu.hip:252-283 - 1, 16 and 64 tokens, and its refusals)"""
+    tid = TYPES[name]
+    rows, cols, scale = 320, 512, 0.25
+    rng = synth.rng_for(57, tid)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    wd = to_dev(w, dev)
+    for n in (1, 16, 37, 64):
+        x = rng.standard_normal((n, cols)).astype(np.float32) * 4.0
+        if n == 37:
+            x[5] *= 3.0e4  # one token past f16's range after the silu: the flag must be raised
+        xb = _x16(lib, dev, np.clip(x, -6.0e4, 6.0e4), cols)
+        y0 = torch.empty((n, rows), dtype=torch.float32, device=dev)
+        assert lib.mm_run(tid, ptr(wd), rows, cols, ptr(xb), n, ptr(y0), rows, None)
+        y = torch.full((n, rows + 3), -7.0, dtype=torch.float32, device=dev)
+        out16 = torch.full((((n + 15) // 16) * 16 * rows,), 9.0, dtype=torch.float16, device=dev)
+        flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        lib.mm_status()
+        assert lib.mm_run_silu(tid, ptr(wd), rows, cols, ptr(xb), n, ptr(y), rows + 3, scale, ptr(out16), ptr(flag), None)
+        sync()
+        assert lib.mm_status() == 0
+        got = y.cpu().numpy()
+        u = y0.cpu().numpy() * np.float32(scale)  # (one F32 product, as the kernel rounds it)
+        with np.errstate(over="ignore"):
+            want = u.astype(np.float64) / (1.0 + np.exp(-u.astype(np.float64)))
+        assert (got[:, rows:] == -7.0).all()
+        # (where expf(-u) passes F32's range the expression gives -0: an absolute 1e-35 covers that band of u near -89)
+        assert np.all(np.abs(got[:, :rows] - want) <= 3e-6 * np.abs(want) + 1e-35)
+        with np.errstate(over="ignore"):
+            assert same_bits(_tiled16(out16, n, rows), got[:, :rows].astype(np.float16))  # the f16 of the same F32 values
+        assert int(flag.item()) == int(bool((np.abs(got[:, :rows]) > 65504.0).any()))
+        if n == 37:
+            assert int(flag.item()) == 1
+    assert not lib.mm_run_silu(tid, ptr(wd), rows, cols, ptr(xb), 65, ptr(y), rows, scale, ptr(out16), ptr(flag), None)
+    assert not lib.mm_run_silu(tid, ptr(wd), rows, cols, ptr(xb), 1, ptr(y), rows, scale, ptr(xb), ptr(flag), None)  # its own x16
+    assert not lib.mm_run_silu(tid, ptr(wd), rows, cols, ptr(xb), 1, ptr(y), rows, scale, None, ptr(flag), None)
+    assert not lib.mm_run_silu(tid, ptr(wd), rows, cols, ptr(xb), 1, ptr(y), rows, scale, ptr(out16), None, None)
+    assert not lib.mm_run_silu(tid, ptr(wd), rows, cols + 64, ptr(xb), 1, ptr(y), rows, scale, ptr(out16), ptr(flag), None)
+
+
+@pytest.mark.parametrize("hc,dim,cols,counts", [(4, 2560, 384, (1, 5, 16, 17, 37, 64, 100, 2048)), (2, 64, 128, (3, 33)),
+                                                 (3, 48, 128, (40,)), (8, 80, 256, (130,)), (1, 144, 128, (7,))])
+def test_mm_run_gated_mean(lib, dev, oracle, hc, dim, cols, counts):
+    """mm_run_gated_mean = mm_run of the hc dim rows, then out[t][d] = (sum over s in order of xn[t][s][d]
+    sigmoid(up[t][s dim + d])) / hc and its f16, the up never stored (the reference's test:
+    tests/gpu/test_gated_mean_gpu.hip - its stream counts, token counts, overflow case and refusals)"""
+    tid = TYPES["Q8_0"]
+    rows = hc * dim
+    rng = synth.rng_for(58, hc * 1000 + dim)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    wd = to_dev(w, dev)
+    for n in counts:
+        x = rng.standard_normal((n, cols)).astype(np.float32)
+        xn = rng.standard_normal((n, hc, dim)).astype(np.float32)
+        if n > 3:
+            xn[2, 0, 5] = 1.0e30  # one token's mean past f16's range: the flag set
+        xb, xnd = _x16(lib, dev, x, cols), to_dev(xn, dev)
+        up = torch.empty((n, rows), dtype=torch.float32, device=dev)
+        assert lib.mm_run(tid, ptr(wd), rows, cols, ptr(xb), n, ptr(up), rows, None)
+        out = torch.full((n, dim), -7.0, dtype=torch.float32, device=dev)
+        row0 = 16
+        out16 = torch.full(((row0 + n + 15) // 16 * 16 * dim,), 9.0, dtype=torch.float16, device=dev)
+        flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        lib.mm_status()
+        assert lib.mm_run_gated_mean(tid, ptr(wd), hc, dim, cols, ptr(xb), n, ptr(xnd), ptr(out), ptr(out16), row0, ptr(flag), None)
+        sync()
+        assert lib.mm_status() == 0
+        got = out.cpu().numpy()
+        g = up.cpu().numpy().reshape(n, hc, dim).astype(np.float64)
+        terms = xn.astype(np.float64) / (1.0 + np.exp(-g))
+        want, mag = terms.sum(axis=1) / hc, np.abs(terms).sum(axis=1) / hc
+        assert np.all(np.abs(got - want) <= 3e-6 * mag + 1e-37)
+        rows16 = _tiled16(out16, row0 + n, dim)
+        with np.errstate(over="ignore"):
+            assert same_bits(rows16[row0:], got.astype(np.float16))
+        assert (rows16[:row0] == np.float16(9.0)).all()  # (the rows before row0 are someone else's)
+        assert int(flag.item()) == (1 if n > 3 else 0)
+        # without the f16 copy: the same F32 bits
+        out2 = torch.empty_like(out)
+        assert lib.mm_run_gated_mean(tid, ptr(wd), hc, dim, cols, ptr(xb), n, ptr(xnd), ptr(out2), None, 0, None, None)
+        sync()
+        assert same_bits(out2.cpu().numpy(), got)
+    f = ptr(out)
+    assert not lib.mm_run_gated_mean(tid, ptr(wd), hc, dim, cols, ptr(xb), 8, ptr(xnd), f, ptr(xb), 0, ptr(flag), None)  # out16 = x16
+    assert not lib.mm_run_gated_mean(tid, ptr(wd), hc, dim, cols, ptr(xb), 8, ptr(xnd), f, ptr(out16), 0, None, None)  # no flag
+    assert not lib.mm_run_gated_mean(tid, ptr(wd), 9, dim, cols, ptr(xb), 8, ptr(xnd), f, None, 0, None, None)
+    assert not lib.mm_run_gated_mean(tid, ptr(wd), hc, dim + 8, cols, ptr(xb), 8, ptr(xnd), f, None, 0, None, None)  # dim not 16s
+    assert not lib.mm_run_gated_mean(tid, ptr(wd), hc, dim, cols, ptr(xb), 2049, ptr(xnd), f, None, 0, None, None)
