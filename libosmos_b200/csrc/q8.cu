@@ -1,9 +1,12 @@
 // The int8 lane (include/osmos_b200/q8.h): activation rounding and the grouped expert matvecs over int8 inputs,
 // with the gate + up + activation fusion. One kernel template serves q8_group_tok, q8_gate_up and q8_run.
 //
-// Thread mapping of this generic kernel: a lane of the contract is a thread; a warp holds 32 / L rows. It takes any
-// shape the entry points accept. The order of every floating-point operation is fixed by the contract, so any other
-// kernel for the same entry points must (and is tested to) give the same bits.
+// This generic kernel takes any shape the entry points accept. A block owns one entry (or one group of a dense call's
+// tokens) and a run of its rows: the entry's tokens - their int8 rows and block scales - are brought into shared
+// memory once, NT at a time, and every row of the run reads them from there; a thread is a lane of the contract, a
+// warp holds 32 / L rows at a time and walks the run. The order of every floating-point operation is fixed by the
+// contract (a lane's blocks in ascending order, the xor tree, the activation), so any other kernel for the same
+// entry points must (and is tested to) give the same bits.
 #include "decode.cuh"
 #include "dispatch.cuh"
 #include "lane_plain_api.h"
@@ -20,6 +23,7 @@ namespace {
 
 constexpr int kWarps = 8, kThreads = kWarps * kWarp;
 constexpr uint32_t kLongCols = 4096;  // rows this long or longer split over 32 lanes, shorter over 16
+constexpr uint32_t kTokenSmem = 160u * 1024u;  // the most shared memory a block's tokens may take
 
 struct LaneArgs {
   const uint8_t* w_dense;       // q8_run: the matrix (tables NULL)
@@ -32,87 +36,117 @@ struct LaneArgs {
   float lim;
   float* out;
   uint32_t rows, cols, out_stride, n_tok;
+  uint32_t max_cnt;   // the grouped forms: the most tokens an entry has
+  uint32_t run_rows;  // rows a block walks (a multiple of the rows its warps hold at once)
 };
 
 template <uint32_t T, int NT, bool FUSED, bool DENSE>
 __global__ void __launch_bounds__(kThreads) lane_kernel(const LaneArgs a) {
+  extern __shared__ __align__(16) uint8_t tokens[];  // NT int8 rows, then their NT rows of block scales
   __shared__ __align__(16) uint8_t tables[grid_smem_bytes<T>() > 0 ? grid_smem_bytes<T>() : 16];
+  __shared__ uint32_t s_src[NT];  // where each staged token's row lies in q / d
   const Grids g = stage_grids<T>(tables);
-  const int lane = threadIdx.x % kWarp;
-  const int L = a.cols >= kLongCols ? 32 : 16, ll = lane % L;
-  const uint32_t row = (blockIdx.x * kWarps + threadIdx.x / kWarp) * (uint32_t) (kWarp / L) + (uint32_t) (lane / L);
-  const uint32_t nblk = a.cols / 32;
+  const uint32_t tid = threadIdx.x, lane = tid % kWarp, warp = tid / kWarp;
+  const uint32_t L = a.cols >= kLongCols ? 32u : 16u, sub = lane % L, at_once = kWarp / L;
+  const uint32_t nblk = a.cols / 32, pieces = a.cols / 16;
+  const int4* const xq = (const int4*) tokens;
+  const float* const xd = (const float*) (tokens + (size_t) NT * a.cols);
 
+  // whose tokens: `count` rows of the inputs from `first`, and the matrices they meet
+  uint32_t first, count;
   const uint8_t *wg, *wu = nullptr;
-  uint32_t r0, live;
   if constexpr (DENSE) {
-    r0 = blockIdx.y * NT;
-    live = a.n_tok - r0 < (uint32_t) NT ? a.n_tok - r0 : (uint32_t) NT;
+    first = blockIdx.y * NT, count = a.n_tok - first < (uint32_t) NT ? a.n_tok - first : (uint32_t) NT;
     wg = a.w_dense;
   } else {
     const uint32_t m = blockIdx.y;
     const int32_t c = a.cnt[m];
     if (c <= 0) return;
-    r0 = (uint32_t) a.xrow[m], live = (uint32_t) c < (uint32_t) NT ? (uint32_t) c : (uint32_t) NT;
+    first = (uint32_t) a.xrow[m], count = (uint32_t) c < a.max_cnt ? (uint32_t) c : a.max_cnt;
     wg = a.wg[m];
     if constexpr (FUSED) wu = a.wu[m];
   }
-  const uint64_t off = (uint64_t) (row < a.rows ? row : 0) * (uint64_t) (a.cols / Fmt<T>::values) * Fmt<T>::bytes;
-  wg += off;
-  if constexpr (FUSED) wu += off;
-
-  // the input row of each token slot (a slot past the live ones is skipped: nothing of it is read)
-  uint64_t xr[NT];
-#pragma unroll
-  for (int t = 0; t < NT; t++) {
-    const uint32_t r = r0 + ((uint32_t) t < live ? (uint32_t) t : live - 1);
-    xr[t] = a.xin ? (uint64_t) (uint32_t) a.xin[r] : r;
-  }
-  float ag[NT], au[NT];
-#pragma unroll
-  for (int t = 0; t < NT; t++) ag[t] = au[t] = 0.0f;
-
+  const uint64_t row_bytes = (uint64_t) (a.cols / Fmt<T>::values) * Fmt<T>::bytes;
+  const uint32_t run0 = blockIdx.x * a.run_rows, run1 = run0 + a.run_rows < a.rows ? run0 + a.run_rows : a.rows;
   constexpr int kSubs = Fmt<T>::subs;
-  for (uint32_t s = ll; s < nblk; s += L) {
-    LaneCodes cg, cu;
-    const uint64_t at = (uint64_t) (s / kSubs) * Fmt<T>::bytes;
-    lane_codes<T>(wg + at, (int) (s % kSubs), cg, g);
-    if constexpr (FUSED) lane_codes<T>(wu + at, (int) (s % kSubs), cu, g);
-#pragma unroll
-    for (int t = 0; t < NT; t++) {
-      if ((uint32_t) t < live) {
-        const int4* xp = (const int4*) (a.q + xr[t] * a.cols + (uint64_t) s * 32);
-        const int4 lo = __ldg(xp), hi = __ldg(xp + 1);
-        const int x[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        const float dx = __ldg(a.d + xr[t] * nblk + s);
-        ag[t] = __fmaf_rn(dx, lane_block_sum<T>(cg, x), ag[t]);
-        if constexpr (FUSED) au[t] = __fmaf_rn(dx, lane_block_sum<T>(cu, x), au[t]);
-      }
+
+  for (uint32_t t0 = 0; t0 < count; t0 += NT) {
+    const uint32_t live = count - t0 < (uint32_t) NT ? count - t0 : (uint32_t) NT;
+    // ---- the group's tokens into shared memory
+    if (t0) __syncthreads();  // (the rows of the group before are done with it)
+    if (tid < live) s_src[tid] = a.xin ? (uint32_t) a.xin[first + t0 + tid] : first + t0 + tid;
+    __syncthreads();
+    for (uint32_t i = tid; i < live * pieces; i += kThreads) {
+      const uint32_t t = i / pieces, c = i - t * pieces;
+      ((int4*) tokens)[t * pieces + c] = __ldg((const int4*) (a.q + (uint64_t) s_src[t] * a.cols) + c);
     }
-  }
+    for (uint32_t i = tid; i < live * nblk; i += kThreads) {
+      const uint32_t t = i / nblk, c = i - t * nblk;
+      ((float*) (tokens + (size_t) NT * a.cols))[t * nblk + c] = __ldg(a.d + (uint64_t) s_src[t] * nblk + c);
+    }
+    __syncthreads();
+    // ---- the run's rows, 32 / L a warp at a time
+    for (uint32_t base = run0 + warp * at_once; base < run1; base += kWarps * at_once) {
+      const uint32_t row = base + lane / L;  // (a row past the matrix is computed from row 0 and dropped)
+      const uint64_t off = (uint64_t) (row < a.rows ? row : 0) * row_bytes;
+      float ag[NT], au[NT];
 #pragma unroll
-  for (int t = 0; t < NT; t++) {
-    float vg = ag[t], vu = au[t];
+      for (int t = 0; t < NT; t++) ag[t] = au[t] = 0.0f;
+      for (uint32_t s = sub; s < nblk; s += L) {
+        LaneCodes cg, cu;
+        const uint64_t at = off + (uint64_t) (s / kSubs) * Fmt<T>::bytes;
+        lane_codes<T>(wg + at, (int) (s % kSubs), cg, g);
+        if constexpr (FUSED) lane_codes<T>(wu + at, (int) (s % kSubs), cu, g);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-      if (o < L) {
-        vg = __fadd_rn(vg, __shfl_xor_sync(0xFFFFFFFFu, vg, o, kWarp));
-        if constexpr (FUSED) vu = __fadd_rn(vu, __shfl_xor_sync(0xFFFFFFFFu, vu, o, kWarp));
+        for (int t = 0; t < NT; t++) {
+          if ((uint32_t) t < live) {
+            const int4 lo = xq[(uint32_t) t * pieces + 2 * s], hi = xq[(uint32_t) t * pieces + 2 * s + 1];
+            const int x[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            const float dx = xd[(uint32_t) t * nblk + s];
+            ag[t] = __fmaf_rn(dx, lane_block_sum<T>(cg, x), ag[t]);
+            if constexpr (FUSED) au[t] = __fmaf_rn(dx, lane_block_sum<T>(cu, x), au[t]);
+          }
+        }
       }
-    if (ll == 0 && row < a.rows && (uint32_t) t < live) {
-      const uint64_t r = r0 + (uint32_t) t;
-      if constexpr (FUSED)
-        a.out[r * a.out_stride + row] = lane_swiglu(vg, vu, a.lim, a.scale[a.win ? a.win[r] : r]);
-      else
-        a.out[r * a.out_stride + row] = vg;
+#pragma unroll
+      for (int t = 0; t < NT; t++) {
+        float vg = ag[t], vu = au[t];
+        for (uint32_t o = L / 2; o > 0; o >>= 1) {
+          vg = __fadd_rn(vg, __shfl_xor_sync(0xFFFFFFFFu, vg, o, kWarp));
+          if constexpr (FUSED) vu = __fadd_rn(vu, __shfl_xor_sync(0xFFFFFFFFu, vu, o, kWarp));
+        }
+        if (sub == 0 && row < a.rows && (uint32_t) t < live) {
+          const uint64_t r = first + t0 + (uint32_t) t;
+          if constexpr (FUSED)
+            a.out[r * a.out_stride + row] = lane_swiglu(vg, vu, a.lim, a.scale[a.win ? a.win[r] : r]);
+          else
+            a.out[r * a.out_stride + row] = vg;
+        }
+      }
     }
   }
 }
 
+// tokens a block stages at once: the fewest of 1, 2, 4, 8 that cover n, fewer where their rows would not fit
 template <uint32_t T, int NT, bool FUSED, bool DENSE>
-bool launch(const LaneArgs& a, uint32_t grid_y, cudaStream_t s) {
-  const uint32_t per_block = kWarps * (kWarp / (a.cols >= kLongCols ? 32 : 16));
-  lane_kernel<T, NT, FUSED, DENSE><<<dim3(blocks_for(a.rows, per_block), grid_y), kThreads, 0, s>>>(a);
+bool launch(LaneArgs a, uint32_t grid_y, cudaStream_t s) {
+  const uint32_t bytes = (uint32_t) NT * (a.cols + a.cols / 32 * 4);
+  if (bytes > kTokenSmem) {
+    if constexpr (NT > 1) return launch<T, NT / 2, FUSED, DENSE>(a, DENSE ? (a.n_tok + NT / 2 - 1) / (NT / 2) : grid_y, s);
+    return false;
+  }
+  // rows a block walks: as many as leave every SM about two blocks, at most eight passes of its warps
+  const uint32_t at_once = kWarps * (kWarp / (a.cols >= kLongCols ? 32u : 16u));
+  int sms = 0, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return false;
+  uint32_t passes = 8;
+  while (passes > 1 && (uint64_t) blocks_for(a.rows, at_once * passes) * grid_y < 2u * (uint32_t) sms) passes >>= 1;
+  a.run_rows = at_once * passes;
+  static bool sized[64] = {};  // (one record a template instance, one flag a device)
+  auto kernel = lane_kernel<T, NT, FUSED, DENSE>;
+  if (!allow_dynamic_smem(kernel, (int) kTokenSmem, sized)) return false;
+  kernel<<<dim3(blocks_for(a.rows, a.run_rows), grid_y), kThreads, bytes, s>>>(a);
   return launched();
 }
 
@@ -235,7 +269,7 @@ extern "C" bool q8_group_tok(uint32_t type, const void* const* w, const int32_t*
     return false;
   LaneArgs a{};
   a.wg = (const uint8_t* const*) w, a.cnt = cnt, a.xrow = xrow, a.xin = xin, a.q = q, a.d = d, a.out = y;
-  a.rows = rows, a.cols = cols, a.out_stride = ys;
+  a.rows = rows, a.cols = cols, a.out_stride = ys, a.max_cnt = max_cnt;
   if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8)) {
     if (g_use_staged == 1) {  // 512-column matrices: a thread a row
       const rows::Request r{w, cnt, xrow, xin, q, d, y, rows, cols, ys, n, max_cnt, LaneEp{}, false};
@@ -259,6 +293,7 @@ extern "C" bool q8_gate_up(uint32_t type, const void* const* wg, const void* con
   LaneArgs a{};
   a.wg = (const uint8_t* const*) wg, a.wu = (const uint8_t* const*) wu, a.cnt = cnt, a.xrow = xrow, a.xin = xin;
   a.win = win, a.q = q, a.d = d, a.scale = scale, a.lim = lim, a.out = h, a.rows = rows, a.cols = cols, a.out_stride = hs;
+  a.max_cnt = max_cnt;
   if (qtype_row(type) && (qtype_row(type)->paths & QTYPE_PATH_Q8)) {
     if (const int st = ring_first(type, a, true, n, max_cnt, stream)) return st > 0;
     if (const int st = staged_first(type, a, true, false, n, max_cnt, stream)) return st > 0;

@@ -162,10 +162,11 @@ ALL_LANE = list(LANE_TYPES)
 
 @pytest.mark.parametrize("name", ALL_LANE)
 @pytest.mark.parametrize("cols,rows", [(512, 136), (512, 160), (512, 128), (1024, 32), (1024, 256), (2048, 64), (2048, 512),
-                                       (4096, 24), (7168, 16), (8192, 8)])
+                                       (4096, 24), (7168, 16), (8192, 8), (24576, 8)])
 def test_staged_kernel_matches_generic_and_oracle(lib, dev, oracle, name, cols, rows):
     """shapes the staged (bulk-copy) kernel takes: its bits are the generic kernel's and the oracle's, for every count
-    1..8, with token and weight indirection, a skipped entry, and rows that leave the last tile partial"""
+    1..8, with token and weight indirection, a skipped entry, and rows that leave the last tile partial (at 24576
+    columns eight tokens' rows pass the generic kernel's shared memory: it takes an entry's tokens four at a time)"""
     tid = TYPES[name]
     n_mat = 6
     rng = synth.rng_for(24, tid, cols)
