@@ -164,10 +164,9 @@ struct Args {
   uint32_t stages, stage_bytes, raw_off;  // the operand ring's depth, a stage's bytes; where the raw weight buffers start
   float scale;
   uint32_t* status;
-  // the epilogue: kStore y = scale sum; kSilu y = silu(scale sum), and its f16 into x16_out (rows wide, tiled);
+  // the epilogue (the kernel's EPI): kStore y = scale sum; kSilu y = silu(scale sum), and its f16 into x16_out (rows wide, tiled);
   // kGatedMean: the matrix is hc streams of dim rows, out[t][d] = (sum over s in order of xn[t][s][d]
   // sigmoid(sum_t[s dim + d])) / hc, and its f16 into x16_out (dim wide, token t at row out_row0 + t; NULL: none)
-  uint32_t epi;
   __half* x16_out;
   int32_t* overflow;
   const float* xn;
@@ -182,7 +181,9 @@ struct Shared {
   int fail;
 };
 
-template <uint32_t T>
+// EPI: the epilogue (kStore / kSilu / kGatedMean), a compile-time choice so that the plain product carries none of
+// the others' code
+template <uint32_t T, uint32_t EPI>
 __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ Shared sh;
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
   // or past the streams, repeats a valid one and is never stored)
   const uint32_t d0 = blockIdx.x * a.per;
   auto wrow = [&](uint32_t r) -> uint32_t {
-    if (a.epi != kGatedMean) return row0 + r < a.rows ? row0 + r : a.rows - 1;
+    if constexpr (EPI != kGatedMean) return row0 + r < a.rows ? row0 + r : a.rows - 1;
     const uint32_t st = r / a.per, d = d0 + (r - st * a.per);
     return (st < a.hc ? st : a.hc - 1) * a.dim + (d < a.dim ? d : a.dim - 1);
   };
@@ -414,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
               : "r"(lane_base + acc * kN + c32)
               : "memory");
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (a.epi == kGatedMean) {
+          if constexpr (EPI == kGatedMean) {
             // each thread gates its row's sums into the idle operand ring ([token of the 32][tile row]); then thread e
             // adds value e % per's streams in order for the tokens e / per, e / per + 128 / per, ...
             float* ex = (float*) smem;
@@ -449,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
               if (t < n_valid) {
                 float v = __uint_as_float(r[i]);
                 if (a.scale != 1.0f) v = mul_rn(v, a.scale);
-                if (a.epi == kSilu) {
+                if constexpr (EPI == kSilu) {
                   v = siluf(v);
                   x16_store(a.x16_out, a.overflow, c0 + t, row0 + row, a.rows, v);
                 }
@@ -509,7 +510,7 @@ bool x16_map(const void* x16, uint32_t n, uint32_t xts, CUtensorMap* tm) {
              CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <uint32_t T>
+template <uint32_t T, uint32_t EPI = kStore>
 bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   alignas(64) CUtensorMap tmap;
   memset(&tmap, 0, sizeof tmap);
@@ -521,7 +522,7 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return false;
   constexpr uint32_t kSlot = kRawSlot<T>, kLimit = 224u * 1024u - (uint32_t) ((grid_smem_bytes<T>() + 1023) / 1024 * 1024);
-  const uint32_t row_tiles = a.epi == kGatedMean ? (a.dim + a.per - 1) / a.per : (a.rows + kM - 1) / kM;
+  const uint32_t row_tiles = EPI == kGatedMean ? (a.dim + a.per - 1) / a.per : (a.rows + kM - 1) / kM;
   auto stages_for = [&](uint32_t k) { return k >= 4 ? 2u : k == 2 ? 3u : 4u; };  // a deeper ring where a stage is small
   auto smem_for = [&](uint32_t k) { return stages_for(k) * (kStageA + k * kSubs * kSubTile) + 2u * kM * kSlot; };
   // tokens a block: the accumulator count (1, 2 or 4 of 128 tokens; a weight is decoded once a block) with the least
@@ -538,9 +539,9 @@ bool launch(Args a, uint32_t n_mat, uint32_t max_cnt, cudaStream_t s) {
   a.stages = stages_for(a.accs), a.stage_bytes = kStageA + a.accs * kSubs * kSubTile, a.raw_off = a.stages * a.stage_bytes;
   const int smem_bytes = (int) smem_for(a.accs);
   static bool sized[64] = {};  // (one record a template instance, one flag a device)
-  if (!allow_dynamic_smem(mm_tc_kernel<T>, (int) kLimit, sized)) return false;
+  if (!allow_dynamic_smem(mm_tc_kernel<T, EPI>, (int) kLimit, sized)) return false;
   const dim3 grid(row_tiles, n_mat, (max_cnt + a.accs * kN - 1) / (a.accs * kN));
-  mm_tc_kernel<T><<<grid, kThreads, smem_bytes, s>>>(a, tmap);
+  mm_tc_kernel<T, EPI><<<grid, kThreads, smem_bytes, s>>>(a, tmap);
   return launched();
 }
 
@@ -552,8 +553,9 @@ bool shape_ok(uint32_t type, uint32_t rows, uint32_t cols) {
 }
 
 namespace {
+template <uint32_t EPI>
 bool run_with(uint32_t type, const Args& a, void* stream) {
-#define CASE(T) return launch<T>(a, 1, a.n, stream_of(stream));
+#define CASE(T) return launch<T, EPI>(a, 1, a.n, stream_of(stream));
   OSMOS_SWITCH_QUANT(type, CASE, return false)
 #undef CASE
 }
@@ -566,7 +568,7 @@ bool run(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void*
   Args a{};
   a.w = (const uint8_t*) w, a.x16 = (const __half*) x16, a.y = y, a.rows = rows, a.cols = cols, a.n = n, a.xts = cols;
   a.ys = ys, a.scale = scale;
-  return run_with(type, a, stream);
+  return run_with<kStore>(type, a, stream);
 }
 
 bool run_silu(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const void* x16, uint32_t n, float* y, uint32_t ys,
@@ -576,8 +578,8 @@ bool run_silu(uint32_t type, const void* w, uint32_t rows, uint32_t cols, const 
     return false;
   Args a{};
   a.w = (const uint8_t*) w, a.x16 = (const __half*) x16, a.y = y, a.rows = rows, a.cols = cols, a.n = n, a.xts = cols;
-  a.ys = ys, a.scale = scale, a.epi = kSilu, a.x16_out = (__half*) x16_out, a.overflow = overflow;
-  return run_with(type, a, stream);
+  a.ys = ys, a.scale = scale, a.x16_out = (__half*) x16_out, a.overflow = overflow;
+  return run_with<kSilu>(type, a, stream);
 }
 
 bool run_gated_mean(uint32_t type, const void* w, uint32_t hc, uint32_t dim, uint32_t cols, const void* x16, uint32_t n,
@@ -588,10 +590,10 @@ bool run_gated_mean(uint32_t type, const void* w, uint32_t hc, uint32_t dim, uin
     return false;
   Args a{};
   a.w = (const uint8_t*) w, a.x16 = (const __half*) x16, a.rows = hc * dim, a.cols = cols, a.n = n, a.xts = cols;
-  a.scale = 1.0f, a.epi = kGatedMean, a.x16_out = (__half*) out16, a.overflow = overflow, a.xn = xn, a.out = out;
+  a.scale = 1.0f, a.x16_out = (__half*) out16, a.overflow = overflow, a.xn = xn, a.out = out;
   a.hc = hc, a.dim = dim, a.out_row0 = row0;
   a.per = ((uint32_t) kM / hc) & ~(uint32_t) (MM_TILE - 1);  // whole tiles of 16 values: 128, 64, 32, 32, 16, ... for 1 - 8 streams
-  return run_with(type, a, stream);
+  return run_with<kGatedMean>(type, a, stream);
 }
 
 }  // namespace mm_tc
