@@ -385,10 +385,16 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
     if (ok && !sh.fail && lane == 0)
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&sh.done)) : "memory");
     __syncwarp();
-  } else {
-    // ================= epilogue =================
-    const uint32_t row = 32u * warp + lane;  // this thread's weight row of the tile = its TMEM lane
-    const uint32_t lane_base = tmem + ((32u * warp) << 16);
+  }
+  // ================= epilogue =================
+  // Every warp, once its own role is done: a warp reads the tensor-memory lanes of its quarter (its index mod 4: the
+  // hardware's rule), so the six or seven warps of a quarter share its rows' 32-token chunks - twenty-five warps
+  // storing instead of four. (The gated mean's exchange through shared memory stays with the first four warps.)
+  if (EPI != kGatedMean || warp < (uint32_t) kEpiWarps) {
+    const uint32_t quarter = warp % 4u, part = EPI == kGatedMean ? 0u : warp / 4u;
+    const uint32_t parts = EPI == kGatedMean ? 1u : ((uint32_t) (kThreads / kWarp) - quarter + 3u) / 4u;  // the quarter's warps
+    const uint32_t row = 32u * quarter + lane;  // this thread's weight row of the tile = its TMEM lane
+    const uint32_t lane_base = tmem + ((32u * quarter) << 16);
     if (!bar_wait(&sh.done, 0)) {
       // (the K loop's own waits are 0.2 s each and can queue up: look again while nobody has given up)
       bool landed = false;
@@ -397,13 +403,14 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
     }
     // (nobody else writes the word once the last product has landed or been given up: after this barrier every
     // epilogue thread reads the same value, so all of them or none take the barriers below)
-    asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * kWarp) : "memory");
+    if constexpr (EPI == kGatedMean) asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * kWarp) : "memory");
     if (!sh.fail) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       for (uint32_t acc = 0; acc < n_acc; acc++) {
 #pragma unroll 1
         for (uint32_t c32 = 0; c32 < (uint32_t) kN; c32 += 32) {
           if (acc * kN + c32 >= n_valid) break;
+          if ((acc * (uint32_t) (kN / 32) + c32 / 32u) % parts != part) continue;  // (a chunk of another warp of the quarter)
           uint32_t r[32];
           asm volatile(
               "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
