@@ -344,7 +344,11 @@ def run_ours(args):
     lib = libosmos_b200.load()
     cfg = workloads.BY_NAME[args.workload]
     if cfg.get("path") == "dense_rows":  # the prefill product, rows split among the ranks
-        return run_dense_rows(args, cfg, lib, dev, rank, world, dist)
+        run_dense_rows(args, cfg, lib, dev, rank, world, dist)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if cfg.get("path"):  # the experts over F32 activations, or through the grouped f16 product: one GPU
         return run_f32_or_f16(args, cfg, lib, dev)
     n_tok, dim, k = cfg["n_tok"], cfg["dim"], cfg["k"]
