@@ -405,8 +405,8 @@ def run_ours(args):
     parity = "all %d home tokens of step 0 on every rank, the routed experts' sum bit-equal to the %s" % (
         T, "reference's cpu_lane_submit" if arm.kind == "reference" else "scalar restatement of the reference's CPU lane")
     if ok and cfg.get("shared"):
-        # the shared expert runs on the f16 tensor cores: its sums are held to the reference test's bound of a float64 sum
-        # over the f16-rounded operands, on this rank's first tokens
+        # the shared expert runs on the f16 tensor cores (more than 8 home tokens) or through the F32 matvec: either way its
+        # sums are held to a bound around a float64 sum over the f16-rounded operands, on this rank's first tokens
         from libosmos_b200 import synth
         from oracle.oracle import Oracle
         layer.step(dx[0], dl[0], out, 0, stream)
@@ -425,7 +425,8 @@ def run_ours(args):
         if not ok:
             sys.stderr.write("bench: rank %d: the shared expert's output is outside its bound (worst %.3e of its magnitude sum)\n"
                              % (rank, float((np.abs(diff - ref) / (mag + 1e-30)).max())))
-        parity += "; the shared expert's output within 2^-9 sum |h w| of a float64 model over f16-rounded operands (%d tokens)" % ns
+        parity += "; the shared expert's output (%s) within 2^-9 sum |h w| of a float64 model over f16-rounded operands (%d tokens)" % (
+            "F32 matvec: a decode step's tokens" if T <= 8 else "f16 tensor-core product", ns)
     if not all_ok(ok):
         raise SystemExit("bench: the GPU layer's output differs from the CPU checker on some rank - not timing a wrong result")
     distinct = [np.unique(workloads.route_host(cfg, l)[0]) for l in hl]
@@ -578,7 +579,7 @@ def run_ours(args):
             achieved = float(np.sum(alg) / (np.sum(k_ms) * 1e-3) / 1e9)
             roof.update({"kernel": "q8_gate_up (lane_ring_kernel, %s, fused gate + up + activation) on rank 0" % cfg["type"],
                          "achieved": achieved, "frac": achieved / peak,
-                         "traffic": 296433152 if (world == 1 and cfg["name"] == workloads.MOE_IQ3["name"]) else None,
+                         "traffic": 296292352 if (world == 1 and cfg["name"] == workloads.MOE_IQ3["name"]) else None,
                          "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, profiles/lane_ring_rows_iq3xxs_moe.md"
                          if (world == 1 and cfg["name"] == workloads.MOE_IQ3["name"]) else None,
                          "algorithmic_bytes_per_launch": float(np.mean(alg)), "us_per_launch": float(np.mean(k_ms) * 1e3)})

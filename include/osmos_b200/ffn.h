@@ -7,6 +7,8 @@
  *                  (src/run/hip_lane.c:71-113 with q8 false, :194-221);
  *   shared_ffn     a dense (shared) expert on every token through the f16 tensor-core product
  *                  (src/run/hip_ffn.c:171-185: mm_tokens on gate and up, the clamped activation, mm_tokens on down);
+ *                  up to MV_MAX_TOKENS tokens (a decode step) through the F32 matvec instead (mv_strided: the
+ *                  reference's product for the types without an f16 kernel, src/run/hip_mat.c:27-35);
  *   q4x_moe        the routed experts through the grouped f16 product, tables built on the GPU
  *                  (src/q4x/hip_layers.c:317-368: q4x_expert_tiles, mm_x16_rows, mm_group x 2, q4x_swiglu_rows,
  *                  mm_group, q4x_moe_sum).
@@ -62,7 +64,9 @@ typedef struct SharedScratch
 } SharedScratch;
 uint64_t shared_scratch_bytes(const SharedExpert *e, uint32_t max_tok);
 bool shared_scratch_bind(const SharedExpert *e, uint32_t max_tok, void *mem, uint64_t bytes, SharedScratch *s);
-/* y[t][:] = down (silu(min(gate x, lim)) * clamp(up x, +-lim)) for n tokens of x ([n][dim], row stride dim) */
+/* y[t][:] = down (silu(min(gate x, lim)) * clamp(up x, +-lim)) for n tokens of x ([n][dim], row stride dim). More than
+   MV_MAX_TOKENS tokens: f16 operands, F32 sums (mm_tokens' bound). Fewer: F32 operands in the matvec's order (mv_run's
+   bits) - a token's bits are those of its step's path, not the same on both. */
 bool shared_ffn(const SharedExpert *e, const SharedScratch *s, const float *x, uint32_t n, float *y, void *stream);
 
 /* ---- the routed experts through the grouped f16 product -------------------------------------------------------------- */

@@ -158,8 +158,8 @@ class EpMoeLane:
                     raise RuntimeError("the fused step does not take this layer")
                 self.plans.append(p)
             # route+round+push, wait+tables, gate_up, round, down+push, wait+combine (+ the shared expert's x16,
-            # gate | up, activation, x16, down)
-            self.kernels_per_step = 6 + (5 if self.shared is not None else 0)
+            # gate, up, activation, x16, down - or, for a decode step's few tokens, its three matvecs and the activation)
+            self.kernels_per_step = 6 + (0 if self.shared is None else 4 if self.T <= 8 else 6)
             torch.cuda.synchronize()
             return
         # ---- nccl transport: the unfused kernels ----

@@ -138,6 +138,14 @@ bool shared_ffn(const SharedExpert *e, const SharedScratch *s, const float *x, u
   if (!shared_ok(e) || !s || !x || !y || !n || n > s->max_tok || !s->g || !s->u || !s->h || !s->x16 || !s->overflow ||
       ((uintptr_t)s->x16 & 15u))
     return false;
+  /* a decode step's few tokens: the F32 matvec, which reads each matrix once at the rate of its bytes (the tensor-core
+     product decodes 128-row tiles a block: a 2048-row matrix would keep 16 of the GPU's blocks busy). Its sums are the
+     reference's mv order, bit for bit; nothing it can refuse is left unchecked above (mm_fits holds the shapes) */
+  if (n <= MV_MAX_TOKENS)
+    return mv_strided(e->type_gu, e->gate, e->ff, e->dim, x, e->dim, n, s->g, e->ff, stream) &&
+           mv_strided(e->type_gu, e->up, e->ff, e->dim, x, e->dim, n, s->u, e->ff, stream) &&
+           ops_swiglu(s->g, s->u, e->ff, e->lim, NULL, n, s->h, stream) &&
+           mv_strided(e->type_down, e->down, e->dim, e->ff, s->h, e->ff, n, y, e->dim, stream);
   /* gate and up in one pass over x's f16 (each the bits it has alone), the clamped activation, then down */
   return mm_tokens(e->type_gu, e->gate, e->ff, s->g, e->ff, e->up, e->ff, s->u, e->ff, e->dim, x, e->dim, n, s->x16, s->overflow,
                    false, stream) &&
