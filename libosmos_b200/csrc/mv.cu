@@ -127,6 +127,23 @@ bool strided(const void* w, uint32_t rows, uint32_t cols, const float* x, uint32
   if (g_use_staged && n_tok <= MV_MAX_TOKENS) {  // the staged kernel when it takes the shape: the same bits
     const mvs::Request r{w, x, y, rows, cols, xs, ys, n_tok};
     if (const int st = mvs::try_launch(T, r, s)) return st > 0;
+    // long rows: as many tokens a pass as the staged kernel holds x for (a token's sums do not depend on its batch),
+    // a pass it still does not take on the generic kernel
+    const uint32_t fit = mvs::max_tokens(T, cols);
+    if (fit && fit < n_tok) {
+      for (uint32_t t = 0; t < n_tok; t += fit) {
+        const uint32_t c = n_tok - t < fit ? n_tok - t : fit;
+        const mvs::Request part{w, x + (uint64_t) t * xs, y + (uint64_t) t * ys, rows, cols, xs, ys, c};
+        const int st = mvs::try_launch(T, part, s);
+        if (st < 0) return false;
+        if (st == 0) {
+          MvArgs a{};
+          a.w = (const uint8_t*) w, a.x = part.x, a.y = part.y, a.rows = rows, a.cols = cols, a.xs = xs, a.ys = ys, a.n_tok = c;
+          if (!by_tokens<T, kDense>(a, c, 1, s)) return false;
+        }
+      }
+      return true;
+    }
   }
   MvArgs a{};
   a.w = (const uint8_t*) w, a.x = x, a.y = y, a.rows = rows, a.cols = cols, a.xs = xs, a.ys = ys, a.n_tok = n_tok;

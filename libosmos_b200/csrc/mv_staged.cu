@@ -561,6 +561,19 @@ int try_launch(uint32_t type, const Request& r, void* stream) {
 #undef CASE
 }
 
+uint32_t max_tokens(uint32_t type, uint32_t cols) {
+  if (!cols || cols % 256) return 0;
+#define CASE(T)                                                                          \
+  {                                                                                      \
+    if ((cols / Fmt<T>::values * Fmt<T>::bytes) % 16u) return 0;                          \
+    uint32_t n = 8;                                                                      \
+    while (n && slots_for<T>(1, n, cols) < 2) n--;                                       \
+    return n;                                                                            \
+  }
+  OSMOS_SWITCH_QUANT(type, CASE, return 0)
+#undef CASE
+}
+
 uint32_t read_status() {
   const Device* dev = device_info();
   if (!dev) return 0x80000000u;

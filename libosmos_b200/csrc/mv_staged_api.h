@@ -21,6 +21,9 @@ struct Request {
 // 1: queued on the stream; 0: not a shape this kernel takes (nothing queued: use the generic kernel); -1: the launch
 // was refused
 int try_launch(uint32_t type, const Request& r, void* stream);
+// the most tokens (0 .. 8) a dense launch takes for rows of `cols` values of `type`: their x must fit in shared memory
+// beside the rows' ring (0: the type or the columns are not this kernel's)
+uint32_t max_tokens(uint32_t type, uint32_t cols);
 // the current device's status word, read and cleared (synchronizes): bit 0 a copy never landed, bit 1 a grouped
 // entry's matrix was not 16-byte aligned (its rows were not written)
 uint32_t read_status();

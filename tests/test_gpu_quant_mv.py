@@ -133,6 +133,29 @@ def test_mv_strided_many_tokens(lib, dev, oracle, name):
     assert same_bits(got[:, :rows], want) and (got[:, rows:] == -3.0).all()
 
 
+@pytest.mark.parametrize("name,cols,ntok", [("Q4_K", 7168, 8), ("Q4_K", 7168, 5), ("Q8_0", 14336, 7), ("IQ1_M", 16384, 4)])
+def test_mv_long_rows_in_passes(lib, dev, oracle, name, cols, ntok):
+    """rows so long that the staged kernel cannot hold every token's x: the tokens go a few a pass, with the bits of the
+    generic kernel and the oracle"""
+    tid = TYPES[name]
+    rows, xs, ys = 150, cols + 8, 152
+    rng = synth.rng_for(14, tid, cols)
+    w = synth.random_tensor(tid, rows, cols, rng)
+    x = rng.standard_normal((ntok, xs)).astype(np.float32)
+    want = oracle.mv_rows(tid, w, rows, cols, np.ascontiguousarray(x[:, :cols]))
+    wd, xd = to_dev(w, dev), to_dev(x, dev)
+    lib.mv_status()
+    for staged in (1, 0):
+        lib.mv_set_staged(staged)
+        y = torch.full((ntok, ys), -3.0, dtype=torch.float32, device=dev)
+        assert lib.mv_strided(tid, ptr(wd), rows, cols, ptr(xd), xs, ntok, ptr(y), ys, None)
+        sync()
+        got = y.cpu().numpy()
+        assert same_bits(got[:, :rows], want) and (got[:, rows:] == -3.0).all(), "staged" if staged else "generic"
+    lib.mv_set_staged(1)
+    assert lib.mv_status() == 0
+
+
 @pytest.mark.parametrize("name", LANE_TYPES)
 def test_mv_matches_reference_cpu_golden(lib, dev, name):
     g = np.load(os.path.join(GOLD, "lane_%s.npz" % name))
