@@ -12,7 +12,7 @@
 // Twenty-five warps, four roles:
 //   loader (4 warps)     cp.async of the tokens' 16-byte pieces of x16 into the B operand's layout, its arrivals on the
 //                        stage's second "full" mbarrier made by the hardware when the copies land
-//   producers (16 warps) per 64-value step of K: decode the rows' 8-value chunks to f16 and store them as the A
+//   producers (16 warps, two teams of 8 on alternate steps) per 64-value step of K: decode the rows' 8-value chunks to f16 and store them as the A
 //                        operand (four K = 16 sub-tiles of 128 rows, K-major core matrices of 8 rows x 16 bytes), and
 //                        cp.async the tokens' 16-byte pieces of x16 into the same layout (B, four sub-tiles a
 //                        128-token accumulator); a proxy fence and an arrive on the stage's "full" mbarrier. Two stages; the rows'
@@ -61,6 +61,10 @@ static_assert(producer_of(5) == 0 && producer_of(7) == 2 && producer_of(9) == 3 
                   producer_of(8) == -1 && producer_of(4) == -1 && loader_of(8) == 0 && loader_of(20) == 3 && loader_of(24) == -1,
               "sixteen producers, four loaders");
 constexpr int kProdThreads = kProdWarps * kWarp, kLoaderThreads = kLoaderWarps * kWarp;
+// The producers work as kGroups teams, team g on the K steps g, g + kGroups, ...: a step's chain (raw bytes out of
+// shared memory, decode, store, proxy fence, arrival) is latency, and two steps' chains run side by side.
+// (A team comes back to a stage after at most as many steps as the ring is deep, so its parity waits never skip a phase.)
+constexpr int kGroups = 2, kTeamThreads = kProdThreads / kGroups;
 constexpr int kThreads = (kEpiWarps + 1 + kLoaderWarps + kProdWarps) * kWarp;
 constexpr int kStep = 64;                        // values of K a stage
 constexpr int kSubTile = kM * 32;                // one K = 16 operand sub-tile: 128 rows x 32 bytes
@@ -211,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
   float* y = a.y + (a.wt ? a.yoff[m] : 0u);
 
   if (tid == 0) {
-    for (int i = 0; i < kMaxStages; i++) bar_init(&sh.full_a[i], kProdWarps), bar_init(&sh.full_b[i], a.use_tma ? 1u : (uint32_t) kLoaderThreads), bar_init(&sh.empty[i], 1);
+    for (int i = 0; i < kMaxStages; i++) bar_init(&sh.full_a[i], kProdWarps / kGroups), bar_init(&sh.full_b[i], a.use_tma ? 1u : (uint32_t) kLoaderThreads), bar_init(&sh.empty[i], 1);
     bar_init(&sh.done, 1);
     sh.fail = 0;
     bar_init_fence();
@@ -253,13 +257,14 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
     // this thread's chunks of a step: chunk kc of rows 64 apart (eight neighbouring threads take one K piece of eight
     // neighbouring rows - eight different 16-byte bank columns of the operand tile, and of the raw buffer, whose row
     // slots are an odd number of 16-byte pieces); what does not change from step to step is worked out here
-    constexpr int kMine = kM * (kStep / 8) / kProdThreads;
-    static_assert(kMine * kProdThreads == kM * (kStep / 8), "every producer thread the same number of chunks");
-    const uint32_t kc = (pt >> 3) & 7u;
+    constexpr int kMine = kM * (kStep / 8) / kTeamThreads;
+    static_assert(kMine * kTeamThreads == kM * (kStep / 8) && kTeamThreads % 64 == 0, "every producer thread the same number of chunks");
+    const uint32_t team = pt / kTeamThreads, tt = pt % kTeamThreads;  // the thread's team and its place in it
+    const uint32_t kc = (tt >> 3) & 7u;
     uint32_t slot_at[kMine], dst_at[kMine], base15[kMine];
 #pragma unroll
     for (int u = 0; u < kMine; u++) {
-      const uint32_t task = pt + (uint32_t) u * kProdThreads, r = (task >> 6) * 8u + (task & 7u);
+      const uint32_t task = tt + (uint32_t) u * kTeamThreads, r = (task >> 6) * 8u + (task & 7u);
       const uint32_t row = wrow(r);  // (a row past the matrix repeats the last one)
       slot_at[u] = r * kSlot, dst_at[u] = (kc >> 1) * kSubTile + (r >> 3) * 256 + (kc & 1u) * 128 + (r & 7u) * 16;
       base15[u] = (uint32_t) ((uintptr_t) (w + row * row_bytes) & 15u);
@@ -267,15 +272,17 @@ __global__ void __launch_bounds__(kThreads, 1) mm_tc_kernel(const Args a, const 
     bool dead = false;  // a wait ran out: no more work, but the producers' own barrier is still kept
     fetch_raw(0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    for (uint32_t it = 0; it < steps; it++) {
+    static_assert((kKb / kStep) % kGroups == 0, "every team has steps in every K block");
+    for (uint32_t it = team; it < steps; it += kGroups) {
       const uint32_t stage = it % S, use = it / S, kb = it / (kKb / kStep), sub = it % (kKb / kStep);
-      if (sub == 0) {  // this thread's pieces of block kb have landed; after the barrier everyone's have, and block
+      const bool first = sub == team;  // the team's first step of K block kb
+      if (first) {  // this thread's pieces of block kb have landed; after the barrier everyone's have, and block
         asm volatile("cp.async.wait_group 0;" ::: "memory");  // kb - 1's buffer is free for kb + 1
         asm volatile("bar.sync 1, %0;" ::"n"(kProdThreads) : "memory");
       }
       if (!dead && use > 0 && !bar_wait(&sh.empty[stage], (use - 1) & 1u)) sh.fail = 1, dead = true;
       if (dead) continue;
-      if (sub == 0 && kb + 1 < kblocks) fetch_raw(kb + 1);
+      if (first && kb + 1 < kblocks) fetch_raw(kb + 1);
       // A: the chunk decoded to 8 halves, 16 bytes, to sub-tile kc / 2 of the stage
       uint8_t* sa = smem + stage * a.stage_bytes;
       const uint8_t* buf = raw + (kb & 1u) * (kM * kSlot);
