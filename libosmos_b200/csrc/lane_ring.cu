@@ -30,6 +30,7 @@ using staged::RepLuts2;
 using staged::build_luts2;
 using staged::Super;
 using lanes::LaneAt;
+using lanes::iq1m_block_sums;
 using lanes::iq3_block_sums;
 using lanes::sub_codes;
 
@@ -180,9 +181,10 @@ __global__ void __launch_bounds__(kThreads, 1) lane_ring_kernel(const Args a) {
 #pragma unroll
     for (int k = 0; k < NB; k++) {
       if (EXACT || (uint32_t) k < nbl) {
-        if constexpr (T == QTYPE_IQ3_XXS) {
+        if constexpr (T == QTYPE_IQ3_XXS || T == QTYPE_IQ1_M) {
           float bs[NTL];
-          iq3_block_sums<NTL, NT, NB>(ra + sboff[k], at, luts, xq, k, bs);
+          if constexpr (T == QTYPE_IQ3_XXS) iq3_block_sums<NTL, NT, NB>(ra + sboff[k], at, luts, xq, k, bs);
+          else iq1m_block_sums<NTL, NT, NB>(ra + sboff[k], at, luts, xq, k, bs);
 #pragma unroll
           for (int t = 0; t < NTL; t++) acc[t] = __fmaf_rn(xd[t][k], bs[t], acc[t]);
         } else {

@@ -84,5 +84,39 @@ __device__ __forceinline__ void iq3_block_sums(uint32_t sb, const LaneAt& at, co
     out[t] = __fadd_rn(lane_part(d, s21, pos[t][0] - 2 * neg[t][0]), lane_part(d, s21, pos[t][1] - 2 * neg[t][1]));
 }
 
+// IQ1_M's block sums from aligned reads: a 56-byte superblock starts on 8 bytes wherever its row starts on 16, so the
+// sub-block's four index bytes are one word, its four (index top, delta sign) nibbles one half-word and the
+// superblock's scale words one 8-byte read - where the field reader goes a byte or a half-word at a time. A chunk's
+// integer sum is the contract's 8 (grid . x) + delta (sum of x) with delta +-1; exact integers, the same products and
+// order as lane_block_sum: the same bits.
+template <int NTL, int NT, int NB>
+__device__ __forceinline__ void iq1m_block_sums(uint32_t sb, const LaneAt& at, const RepLuts2<QTYPE_IQ1_M>& lut,
+                                                const int (&xq)[NT][NB][8], int k, float* out) {
+  const uint32_t j = at.j;
+  const uint32_t qs = lds32(sb + 4u * j), qh = lds16(sb + 32u + 2u * j);
+  const uint2 sc = lds64(sb + 48u);
+  // the superblock's F16 scale lies in the four scale words' top nibbles; this sub-block's two 3-bit scales in word j / 2
+  const float d = half_value(((sc.x >> 12) & 0x000Fu) | ((sc.x >> 24) & 0x00F0u) | ((sc.y >> 4) & 0x0F00u) | ((sc.y >> 16) & 0xF000u));
+  const uint32_t fields = ((j & 4u ? sc.y : sc.x) >> (16u * ((j >> 1) & 1u))) >> (6u * (j & 1u));
+  const int s21[2] = {2 * (int) (fields & 7u) + 1, 2 * (int) ((fields >> 3) & 7u) + 1};
+  int sum[NTL][2];
+#pragma unroll
+  for (int t = 0; t < NTL; t++) sum[t][0] = sum[t][1] = 0;
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    const uint64_t g = lut.grid64(((qs >> (8 * c)) & 0xFFu) | ((qh >> (4 * c)) & 7u) << 8);
+    const int g0 = (int) (uint32_t) g, g1 = (int) (uint32_t) (g >> 32);
+    const int delta = (qh >> (4 * c + 3)) & 1u ? -1 : 1;
+#pragma unroll
+    for (int t = 0; t < NTL; t++) {
+      const int gx = __dp4a(g1, xq[t][k][2 * c + 1], __dp4a(g0, xq[t][k][2 * c], 0));
+      const int cx = __dp4a(0x01010101, xq[t][k][2 * c + 1], __dp4a(0x01010101, xq[t][k][2 * c], 0));
+      sum[t][c >> 1] += 8 * gx + delta * cx;
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < NTL; t++) out[t] = __fadd_rn(lane_part(d, s21[0], sum[t][0]), lane_part(d, s21[1], sum[t][1]));
+}
+
 }  // namespace lanes
 }  // namespace osmos
