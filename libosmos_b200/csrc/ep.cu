@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(kThreads) combine_wait_kernel(const StepArgs a
   pdl_launch_next();
   const uint32_t step = a.sync[0], half = step & 1u;
   uint8_t* mine = a.peers.base[a.rank];
-  if (threadIdx.x < a.n_ranks && !flag_wait((const uint32_t*) (mine + a.lay.flags_combine) + threadIdx.x, step))
+  if (threadIdx.x < a.n_ranks && !flag_wait((const uint32_t*) (mine + a.lay.flags_combine) + threadIdx.x, step, a.n_ranks == 1))
     atomicOr(&g_peer_wait_status, 1u);
   const uint32_t tl = blockIdx.x, k = a.k;
   if (threadIdx.x < kWarp) {  // pick j's place in the sum: how many of the token's picks have a lower expert id

@@ -15,12 +15,14 @@ __device__ __forceinline__ uint64_t flag_clock_ns() {
   return t;
 }
 
-// true once *flag has reached `step` (acquire, system scope); false when the limit ran out first
-__device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t step) {
+// true once *flag has reached `step` (acquire - at system scope, or the device's where the one writer is this GPU:
+// `alone`); false when the limit ran out first
+__device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t step, bool alone) {
   const uint64_t t0 = flag_clock_ns();
   for (;;) {
     uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (alone) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if ((int32_t) (v - step) >= 0) return true;
     if (flag_clock_ns() - t0 > kFlagWaitNs) return false;
     __nanosleep(64);
@@ -41,16 +43,20 @@ __device__ __forceinline__ void publish_step(const EpPeers& peers, uint64_t flag
                                              uint32_t step, uint32_t* counter, uint32_t* bump) {
   __shared__ bool s_last;
   __syncthreads();
+  // (a rank alone stores into its own GPU's memory only: the fences need not reach past the device)
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    if (n_ranks > 1) __threadfence_system();
+    else __threadfence();
     s_last = atomicAdd(counter, 1u) == gridDim.x * gridDim.y - 1;
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence_system();  // (the other blocks' counts were seen: their stores before these flags)
+  if (n_ranks > 1) __threadfence_system();  // (the other blocks' counts were seen: their stores before these flags)
+  else __threadfence();
   if (threadIdx.x < n_ranks) {
     uint32_t* f = (uint32_t*) (peers.base[threadIdx.x] + flags_off) + rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
+    if (n_ranks > 1) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
+    else asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
   }
   if (threadIdx.x == 0) {
     if (bump) *bump = step;

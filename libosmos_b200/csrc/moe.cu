@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(kTableThreads) lane_tables_kernel(const int32_
   uint32_t step = 0;
   if (sy.flags) {  // expert-parallel: the picks are the peers' - every peer's flag must have reached this step
     step = *sy.step;
-    if (threadIdx.x < sy.n_ranks && !flag_wait(sy.flags + threadIdx.x, step)) atomicOr(sy.status, 1u);
+    if (threadIdx.x < sy.n_ranks && !flag_wait(sy.flags + threadIdx.x, step, sy.n_ranks == 1)) atomicOr(sy.status, 1u);
     ids = (const int32_t*) ((const uint8_t*) ids + (step & 1u) * sy.half_bytes);
   }
   __syncthreads();
