@@ -100,6 +100,12 @@ class Gguf(C.Structure):
                 ("n_kv", C.c_size_t), ("tensors", C.POINTER(GgufTensor)), ("n_tensors", C.c_size_t)]
 
 
+class FfnWeights(C.Structure):
+    _fields_ = [(n, C.POINTER(GgufTensor)) for n in ("router", "exp_gate", "exp_up", "exp_down", "ffn_norm", "router_bias", "sh_gate",
+                                                     "sh_up", "sh_down")] + \
+               [("n_embd", U32), ("expert_ff", U32), ("n_experts", U32), ("shared_ff", U32), ("expert_bytes", U64 * 3)]
+
+
 class QTypeInfo(C.Structure):
     _fields_ = [("id", U32), ("values", U32), ("bytes", U32), ("paths", U32), ("name", C.c_char_p)]
 
@@ -113,6 +119,8 @@ SIGNATURES = {
     "gguf_kv": (C.POINTER(GgufKv), [C.POINTER(Gguf), C.c_char_p]),
     "gguf_bytes": (U64, [U32, U64]),
     "gguf_int": (B, [C.POINTER(GgufKv), C.c_size_t, C.POINTER(C.c_int64)]),
+    # weights.h
+    "weights_ffn": (B, [C.POINTER(Gguf), C.c_int, C.POINTER(FfnWeights), C.c_char_p]),
     # quant.h / qtype.h
     "qtype_info": (C.POINTER(QTypeInfo), [U32]),
     "qtype_tensor_bytes": (U64, [U32, U64, U64]),
